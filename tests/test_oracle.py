@@ -1,0 +1,294 @@
+"""CPU tests that pin the oracle.
+
+The reference ships no golden vectors; these re-create its known-answer unit
+tests (cited per test) and check every analytic backward of the oracle against
+central finite differences of an independent float64 statement.
+"""
+import numpy as np
+import pytest
+
+from refmath import fd_grad, rule_forward64
+
+
+# ── known-answer pins re-created from the reference's unit tests ───────────
+def test_rng_deterministic_and_range(orc):
+    # core/src/tensor.rs:493-526 (determinism; fill_uniform(0.1) stays in range)
+    a = orc.rand_buf(1000, 123, 0.1)
+    b = orc.rand_buf(1000, 123, 0.1)
+    assert np.array_equal(a, b)
+    assert a.min() >= -0.1 and a.max() <= 0.1
+    assert np.unique(a).size > 990
+
+
+def test_rng_xorshift_known_values(orc):
+    # xorshift64 (<<13, >>7, <<17) from seed 1 — computed independently in Python.
+    def py_next(s):
+        s ^= (s << 13) & 0xFFFFFFFFFFFFFFFF
+        s ^= s >> 7
+        s ^= (s << 17) & 0xFFFFFFFFFFFFFFFF
+        return s
+    r = orc.SimpleRng(42)
+    s = 42
+    for _ in range(50):
+        s = py_next(s)
+        assert r.next_u64() == s
+    # uniform(): 2*(u as f32) - 1 scaled
+    s = py_next(7)
+    u = np.float32(np.float64(s) / np.float64(18446744073709551615.0))
+    want = (np.float32(2.0) * u - np.float32(1.0)) * np.float32(0.5)
+    assert orc.rand_buf(1, 7, 0.5)[0] == want
+    toks = orc.rng_tokens(7, 256, 4)
+    s = 7
+    for i in range(4):
+        s = py_next(s)
+        assert toks[i] == s % 256
+
+
+def test_sigmoid_softplus_values(orc):
+    # core/src/tensor.rs:528-547
+    assert abs(orc.sigmoid(0.0) - 0.5) < 1e-6
+    assert orc.sigmoid(100.0) == 1.0 and orc.sigmoid(-100.0) == 0.0
+    assert abs(orc.sigmoid(3.0) - 0.9526) < 1e-3
+    assert abs(orc.softplus(0.0) - 0.6931) < 1e-3
+    assert abs(orc.softplus(20.0) - 20.0) < 1e-2
+    assert orc.softplus(-20.0) < 1e-6
+    assert abs(orc.softplus(-4.6) - 0.01) < 2e-3
+    # saturation thresholds are exactly +-15
+    assert orc.sigmoid(15.0) == 1.0 and orc.sigmoid(14.99) < 1.0
+    assert orc.softplus(15.0) == 15.0
+
+
+def test_bf16_round(orc):
+    # core/src/bf16.rs:183-216: powers of two exact, ~2-3 digits otherwise, zero kept.
+    x = np.array([1.0, 2.0, 0.5, -4.0, 0.0, 1.234567, -3.14159], dtype=np.float32)
+    r = orc.bf16_round(x)
+    assert np.array_equal(r[:5], x[:5])
+    assert abs(r[5] - 1.234567) < 0.01 and abs(r[6] + 3.14159) < 0.03
+    # round-to-nearest-even on the tie 1 + 2^-8
+    tie = np.array([1.0 + 2.0 ** -8, 1.0 + 3 * 2.0 ** -8], dtype=np.float32)
+    rt = orc.bf16_round(tie)
+    assert rt[0] == 1.0 and rt[1] == np.float32(1.0 + 2.0 ** -6)
+    import torch
+    z = orc.rand_buf(4096, 5, 3.0)
+    assert np.array_equal(orc.bf16_round(z), torch.from_numpy(z).bfloat16().float().numpy())
+
+
+def test_swa_single_position_copies_v(orc):
+    # core/src/swa.rs:285-299
+    q = np.array([[1, 0, 0, 1]], dtype=np.float32)
+    v = np.array([[0.5, 0.3, 0.1, 0.7]], dtype=np.float32)
+    o = orc.swa_forward(q, q, v, 1, 4, 4)["out"]
+    assert np.allclose(o, v, atol=1e-6)
+
+
+def test_swa_causal_masking(orc):
+    # core/src/swa.rs:301-323
+    q = np.array([[1, 0], [0, 1], [1, 1]], dtype=np.float32)
+    v = np.array([[1, 0], [0, 1], [0.5, 0.5]], dtype=np.float32)
+    r = orc.swa_forward(q, q, v, 1, 2, 3)
+    assert np.allclose(r["out"][0], [1.0, 0.0], atol=1e-5)
+    assert np.isfinite(r["out"]).all()
+
+
+def test_swa_window_limiting(orc):
+    # core/src/swa.rs:325-344: position 3 with window 2 averages V[2], V[3]
+    q = np.tile(np.array([[1.0, 0.0]], dtype=np.float32), (4, 1))
+    v = np.array([[10, 0], [20, 0], [30, 0], [40, 0]], dtype=np.float32)
+    o = orc.swa_forward(q, q, v, 1, 2, 2)["out"]
+    assert abs(o[3, 0] - 35.0) < 1e-4
+
+
+def test_swa_multi_head_weights_sum_to_one(orc):
+    # core/src/swa.rs:346-378
+    q = np.array([[1, 0, 0, 1], [0, 1, 1, 0]], dtype=np.float32)
+    v = np.array([[0.5, 0.3, 0.1, 0.7], [0.2, 0.8, 0.4, 0.6]], dtype=np.float32)
+    r = orc.swa_forward(q, q, v, 2, 2, 2)
+    assert np.isfinite(r["out"]).all()
+    assert np.allclose(r["attn_weights"].sum(-1), 1.0, atol=1e-5)
+
+
+def test_titans_first_step_is_ema_step(orc):
+    # core/src/momentum.rs:510-530: S_1 = eta*S_0 - theta*grad, grad = outer(M0 k - v, k)
+    d = 4
+    k, v, q = (orc.rand_buf(d, s).reshape(1, d) for s in (1, 2, 3))
+    m0, s0 = orc.rand_buf(d * d, 42), orc.rand_buf(d * d, 99)
+    r = orc.titans_forward(k, v, q, [0.05], [0.01], [0.9], m0, s0)
+    grad = np.outer(m0.reshape(d, d) @ k[0] - v[0], k[0]).reshape(-1)
+    want = np.float32(0.9) * s0 - np.float32(0.01) * grad
+    assert np.allclose(r["s_states"][1], want, atol=1e-7)
+    assert np.allclose(r["m_states"][1], np.float32(0.95) * m0 + r["s_states"][1], atol=1e-7)
+
+
+def test_adamw_one_step_closed_form(orc):
+    # core/src/adamw.rs:102-124 on one element, by hand
+    w, m, v = orc.adamw_step([1.0], [0.5], [0.0], [0.0], 1e-3, 0.9, 0.999, 1e-8,
+                             1 / (1 - 0.9), 1 / (1 - 0.999), 0.1)
+    assert abs(m[0] - 0.05) < 1e-7 and abs(v[0] - 0.00025) < 1e-8
+    # m_hat = 0.5, v_hat = 0.25 -> update = lr*(0.5/0.5 + 0.1*1)
+    assert abs(w[0] - (1.0 - 1e-3 * 1.1)) < 1e-6
+
+
+def test_l2_normalize_and_backward(orc):
+    x = orc.rand_buf(6 * 8, 11, 1.0).reshape(6, 8)
+    xn, norms = orc.l2_normalize_rows(x)
+    assert np.allclose(np.linalg.norm(xn, axis=1), 1.0, atol=1e-6)
+    assert np.allclose(norms, np.linalg.norm(x, axis=1), rtol=1e-6)
+    go = orc.rand_buf(6 * 8, 12, 1.0).reshape(6, 8)
+    gi = orc.l2_normalize_rows_backward(go, xn, norms)
+    fd = fd_grad(lambda z: float((z / np.linalg.norm(z, axis=1, keepdims=True) * go).sum()), x)
+    assert np.allclose(gi, fd, atol=1e-4)
+
+
+# ── analytic backward vs float64 finite differences ────────────────────────
+def _problem(orc, rule, s, d, seed, gates="const"):
+    k = orc.rand_buf(s * d, seed, 0.5).reshape(s, d)
+    v = orc.rand_buf(s * d, seed + 1, 0.5).reshape(s, d)
+    q = orc.rand_buf(s * d, seed + 2, 0.5).reshape(s, d)
+    dy = orc.rand_buf(s * d, seed + 3, 1.0).reshape(s, d)
+    m0 = orc.rand_buf(d * d, seed + 4, 0.3)
+    s0 = orc.rand_buf(d * d, seed + 5, 0.3)
+    if gates == "const":
+        alpha = np.full(s, 0.05, np.float32)
+        theta = np.full(s, 0.01, np.float32)
+        eta = np.full(s, 0.9, np.float32)
+    else:
+        alpha = (orc.rand_buf(s, seed + 6, 0.4) + 0.5).astype(np.float32)
+        theta = (orc.rand_buf(s, seed + 7, 0.4) + 0.5).astype(np.float32)
+        eta = (orc.rand_buf(s, seed + 8, 0.4) + 0.5).astype(np.float32)
+    return dict(k=k, v=v, q=q, dy=dy, m0=m0, s0=s0, alpha=alpha, theta=theta, eta=eta)
+
+
+def _oracle_fwd_bwd(orc, rule, p, chunk):
+    if chunk:
+        has_s = rule == "titans"
+        f = orc.chunkwise_forward(has_s, p["k"], p["v"], p["q"], p["alpha"], p["theta"], p["eta"],
+                                  p["m0"], p["s0"], chunk)
+        b = orc.chunkwise_backward(has_s, p["k"], p["v"], p["q"], p["alpha"], p["theta"],
+                                   p["eta"], f["m_chunk_states"], f["s_chunk_states"], p["dy"],
+                                   chunk)
+    elif rule == "titans":
+        f = orc.titans_forward(p["k"], p["v"], p["q"], p["alpha"], p["theta"], p["eta"], p["m0"],
+                               p["s0"])
+        b = orc.titans_backward(p["k"], p["v"], p["q"], p["alpha"], p["theta"], p["eta"],
+                                f["m_states"], f["s_states"], p["dy"])
+    elif rule == "delta":
+        f = orc.delta_forward(p["k"], p["v"], p["q"], p["alpha"], p["theta"], p["m0"])
+        b = orc.delta_backward(p["k"], p["v"], p["q"], p["alpha"], p["theta"], f["m_states"],
+                               p["dy"])
+    else:
+        f = orc.hebbian_forward(p["k"], p["v"], p["q"], p["alpha"], p["m0"])
+        b = orc.hebbian_backward(p["k"], p["v"], p["q"], p["alpha"], f["m_states"], p["dy"])
+    return f, b
+
+
+@pytest.mark.parametrize("rule,chunk", [("titans", 0), ("delta", 0), ("hebbian", 0),
+                                        ("titans", 3), ("delta", 3), ("titans", 4)])
+def test_backward_matches_fd(orc, rule, chunk):
+    s, d = 7, 4
+    p = _problem(orc, rule, s, d, 100, gates="rand")
+    f, b = _oracle_fwd_bwd(orc, rule, p, chunk)
+    s0 = p["s0"] if rule == "titans" else None
+
+    def loss(**over):
+        a = dict(p); a.update(over)
+        y, _, _ = rule_forward64(rule, a["k"], a["v"], a["q"], a["alpha"], a["theta"], a["eta"],
+                                 a["m0"], a["s0"] if rule == "titans" else None, chunk)
+        return float((y * p["dy"].astype(np.float64)).sum())
+
+    y64, _, _ = rule_forward64(rule, p["k"], p["v"], p["q"], p["alpha"], p["theta"], p["eta"],
+                               p["m0"], s0, chunk)
+    assert np.allclose(f["y"], y64, atol=2e-6)
+    checks = [("d_k", "k"), ("d_v", "v"), ("d_q", "q"), ("d_alpha", "alpha"),
+              ("d_m_initial", "m0")]
+    if rule != "hebbian":
+        checks.append(("d_theta", "theta"))
+    if rule == "titans":
+        checks += [("d_eta", "eta"), ("d_s_initial", "s0")]
+    for gname, xname in checks:
+        fd = fd_grad(lambda z: loss(**{xname: z}), p[xname])
+        got = b[gname].reshape(fd.shape)
+        assert np.allclose(got, fd, rtol=2e-4, atol=2e-5), (rule, chunk, gname,
+                                                          np.abs(got - fd).max())
+
+
+def test_chunk1_equals_per_token_and_chunk4_differs(orc):
+    # core/src/gpu_forward.rs:4193-4585: C=1 chunkwise == exact; C=4 differs.
+    for rule in ("titans", "delta"):
+        p = _problem(orc, rule, 12, 8, 300)
+        fe, be = _oracle_fwd_bwd(orc, rule, p, 0)
+        f1, b1 = _oracle_fwd_bwd(orc, rule, p, 1)
+        f4, _ = _oracle_fwd_bwd(orc, rule, p, 4)
+        assert np.allclose(fe["y"], f1["y"], atol=1e-6)
+        assert np.allclose(fe["m_states"], f1["m_chunk_states"], atol=1e-6)
+        for key in ("d_k", "d_v", "d_q", "d_alpha", "d_theta", "d_m_initial"):
+            assert np.allclose(be[key], b1[key], atol=1e-6), key
+        assert np.abs(fe["y"] - f4["y"]).max() > 1e-6
+
+
+def test_error_clip_and_m_norm(orc):
+    p = _problem(orc, "titans", 8, 8, 500)
+    p["v"] = p["v"] * 10
+    f0 = orc.titans_forward(p["k"], p["v"], p["q"], p["alpha"], p["theta"], p["eta"], p["m0"],
+                            p["s0"])
+    f1 = orc.titans_forward(p["k"], p["v"], p["q"], p["alpha"], p["theta"], p["eta"], p["m0"],
+                            p["s0"], error_clip=1.0, m_norm_max=0.5)
+    assert np.abs(f0["y"] - f1["y"]).max() > 1e-5
+    norms = np.linalg.norm(f1["m_states"][1:], axis=1)
+    assert (norms <= 0.5 + 1e-5).all()
+
+
+def test_segment_seed_composition(orc):
+    # backward over [0,S) == backward over [c,S) then [0,c) seeded with the first's d_M/d_S
+    p = _problem(orc, "titans", 10, 4, 700, gates="rand")
+    f = orc.titans_forward(p["k"], p["v"], p["q"], p["alpha"], p["theta"], p["eta"], p["m0"],
+                           p["s0"])
+    full = orc.titans_backward(p["k"], p["v"], p["q"], p["alpha"], p["theta"], p["eta"],
+                               f["m_states"], f["s_states"], p["dy"])
+    c = 6
+    hi = orc.titans_backward(p["k"][c:], p["v"][c:], p["q"][c:], p["alpha"][c:], p["theta"][c:],
+                             p["eta"][c:], f["m_states"][c:], f["s_states"][c:], p["dy"][c:])
+    lo = orc.titans_backward(p["k"][:c], p["v"][:c], p["q"][:c], p["alpha"][:c], p["theta"][:c],
+                             p["eta"][:c], f["m_states"][:c + 1], f["s_states"][:c + 1],
+                             p["dy"][:c], d_m_seed=hi["d_m_initial"], d_s_seed=hi["d_s_initial"])
+    assert np.allclose(np.concatenate([lo["d_k"], hi["d_k"]]), full["d_k"], atol=1e-6)
+    assert np.allclose(lo["d_m_initial"], full["d_m_initial"], atol=1e-6)
+    assert np.allclose(lo["d_s_initial"], full["d_s_initial"], atol=1e-6)
+
+
+def test_swa_backward_matches_fd(orc):
+    s, nh, hd, w = 9, 2, 4, 4
+    for n_p in (0, 2):
+        q, k, v, do = (orc.rand_buf(s * nh * hd, 40 + i, 0.5).reshape(s, nh * hd)
+                       for i in range(4))
+        f = orc.swa_forward(q, k, v, nh, hd, w, n_p)
+        b = orc.swa_backward(q, k, v, f["attn_weights"], do, nh, hd, w, n_p)
+
+        def fwd64(q_, k_, v_):
+            out = np.zeros((s, nh * hd))
+            for h in range(nh):
+                sl = slice(h * hd, (h + 1) * hd)
+                for i in range(s):
+                    keys = [j for j in range(i + 1) if j < n_p or j >= max(n_p, i + 1 - w)]
+                    sc = np.array([q_[i, sl] @ k_[j, sl] for j in keys]) / np.sqrt(hd)
+                    pr = np.exp(sc - sc.max()); pr /= pr.sum()
+                    out[i, sl] = sum(pj * v_[j, sl] for pj, j in zip(pr, keys))
+            return out
+
+        assert np.allclose(f["out"], fwd64(q, k, v), atol=2e-6)
+        for name, idx in (("d_q", 0), ("d_k", 1), ("d_v", 2)):
+            args = [q.astype(np.float64), k.astype(np.float64), v.astype(np.float64)]
+
+            def loss(z, idx=idx):
+                a = list(args); a[idx] = z
+                return float((fwd64(*a) * do).sum())
+            fd = fd_grad(loss, args[idx])
+            assert np.allclose(b[name], fd, rtol=2e-4, atol=2e-5), (n_p, name)
+
+
+def test_grad_norm_clip(orc):
+    g = orc.rand_buf(1000, 9, 1.0)
+    g2, norm, scale = orc.grad_norm_clip(g, 1.0)
+    assert abs(norm - np.linalg.norm(g.astype(np.float64))) < 1e-3
+    assert abs(np.linalg.norm(g2) - 1.0) < 1e-4 and scale < 1.0
+    g3, _, scale3 = orc.grad_norm_clip(g, 0.0)
+    assert scale3 == 1.0 and np.array_equal(g3, g)
