@@ -1,0 +1,532 @@
+#!/usr/bin/env python
+"""Benchmark of the NL_Hecate hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+One JSON line on stdout (rank 0). A "step" is one forward+backward pass of the
+workload over one batch of seeded synthetic input:
+
+  titans_chunkwise  Titans LMM frozen-M0 chunkwise kernel pair alone: batch 16 x 8 heads,
+                    head_dim 64, seq 2048, chunk 64, fp32 (128 independent problems / GPU)
+  titans_exact      same shapes, exact per-token rule (full-trajectory drop-in pair)
+  swa               SWA forward+backward pair: bf16, batch 8 x 16 heads, head_dim 64,
+                    seq 8192, causal window 512
+  adamw             flat-arena clip + AdamW step over 25.2 M fp32 parameters
+
+`value` is device-timed (CUDA events on the launching stream, max over ranks) with
+inputs resident in HBM; `e2e` goes through the host-slice API: pinned host buffers,
+H2D of every input and D2H of every output inside the timed region. `--impl reference`
+times the CPU restatement of the reference's Rust path (oracle/) on all host cores on
+a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+LOG2E = 1.4426950408889634
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(hbm_gbs=p["hbm_gbs"], bf16_tflops=p["bf16_tflops"],
+                    bf16_tflops_sustained=p.get("bf16_tflops_sustained", p["bf16_tflops"]),
+                    source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks / throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms",
+                 "100", "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL,
+                text=True)
+            self.th = threading.Thread(target=self._read, daemon=True)
+            self.th.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names)
+                   if any(len(r) >= 6 and r[2 + i].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": float(np.median(sm)) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
+                "samples": len(sm)}
+
+
+# ─────────────────────────── workload definitions ───────────────────────────
+class TitansPair:
+    """Titans LMM kernel pair alone. chunk > 0: frozen-M0 chunkwise; chunk == 0: exact."""
+    B, H, S, D = 16, 8, 2048, 64
+
+    def __init__(self, chunk: int):
+        self.chunk = chunk
+        self.N = self.B * self.H
+        self.name = "titans_chunkwise" if chunk else "titans_exact"
+        self.tokens_per_step = self.B * self.S
+        self.dtype = "f32"
+
+    def describe(self):
+        return {"workload": f"Titans LMM kernel pair ({'frozen-M0 chunkwise, chunk 64' if self.chunk else 'exact per-token, full trajectory'}): "
+                            f"batch {self.B} x heads {self.H}, head_dim {self.D}, seq {self.S}, fp32",
+                "problems_per_gpu": self.N, "tokens_per_step_per_gpu": self.tokens_per_step,
+                "l2_policy": "inputs+outputs > L2 (>= 0.9 GB touched per step)"}
+
+    def host_inputs(self, n=None, seed=1234):
+        n = self.N if n is None else n
+        g = np.random.Generator(np.random.Philox(seed))
+        nrm = lambda x: (x / np.linalg.norm(x, axis=-1, keepdims=True)).astype(np.float32)
+        sig = lambda x: (1.0 / (1.0 + np.exp(-x))).astype(np.float32)
+        sh = (n, self.S, self.D)
+        return dict(k=nrm(g.standard_normal(sh)), v=nrm(g.standard_normal(sh)),
+                    q=nrm(g.standard_normal(sh)), alpha=sig(g.standard_normal(sh[:2])),
+                    theta=sig(g.standard_normal(sh[:2])), eta=sig(g.standard_normal(sh[:2])),
+                    dy=g.standard_normal(sh).astype(np.float32),
+                    m0=np.zeros((n, self.D * self.D), np.float32),
+                    s0=np.zeros((n, self.D * self.D), np.float32))
+
+    def setup(self, torch, dispatch):
+        self.torch, self.dd = torch, dispatch
+        self.host = {k: torch.from_numpy(v).pin_memory() for k, v in self.host_inputs().items()}
+        self.dev = {k: v.cuda() for k, v in self.host.items()}
+        n, s, d = self.N, self.S, self.D
+        f32 = lambda *sh: torch.empty(*sh, dtype=torch.float32, device="cuda")
+        slots = (s // self.chunk + 1) if self.chunk else (s + 1)
+        self.mstate, self.sstate, self.y = f32(n, slots, d * d), f32(n, slots, d * d), f32(n, s, d)
+        self.out = {k: f32(n, s, d) for k in ("d_k", "d_v", "d_q")}
+        self.out.update({k: f32(n, s) for k in ("d_alpha", "d_theta", "d_eta")})
+        self.out.update({k: f32(d * d) for k in ("d_m0", "d_s0")})
+        self.host_out = {k: torch.empty(v.shape, dtype=v.dtype).pin_memory()
+                         for k, v in list(self.out.items()) + [("y", self.y)]}
+        self.launches_per_step = 2
+        self.h2d = sum(v.numel() * 4 for k, v in self.host.items())
+        self.d2h = sum(v.numel() * 4 for v in self.host_out.values())
+
+    def fwd(self, t):
+        c = self.dd.call
+        if self.chunk:
+            c("titans_chunkwise_forward_f32_cuda", k_mem=t["k"], v_mem=t["v"], q_mem=t["q"],
+              alpha=t["alpha"], theta=t["theta"], eta=t["eta"], m_initial=t["m0"], s_initial=t["s0"],
+              m_chunk_states=self.mstate, s_chunk_states=self.sstate, y=self.y, seq_len=self.S,
+              d=self.D, batch_size=self.N, chunk_size=self.chunk, error_clip=0.0, m_norm_max=0.0)
+        else:
+            c("titans_forward_f32_cuda", k_mem=t["k"], v_mem=t["v"], q_mem=t["q"], alpha=t["alpha"],
+              theta=t["theta"], eta=t["eta"], m_initial=t["m0"], s_initial=t["s0"],
+              m_states=self.mstate, s_states=self.sstate, y=self.y, seq_len=self.S, d=self.D,
+              batch_size=self.N, input_stride=self.S, m_stride=self.D * self.D, error_clip=0.0,
+              m_norm_max=0.0)
+
+    def bwd(self, t):
+        c, o = self.dd.call, self.out
+        o["d_m0"].zero_(); o["d_s0"].zero_()
+        if self.chunk:
+            c("titans_chunkwise_backward_f32_cuda", k_mem=t["k"], v_mem=t["v"], q_mem=t["q"],
+              alpha=t["alpha"], theta=t["theta"], eta=t["eta"], m_chunk_states=self.mstate,
+              s_chunk_states=self.sstate, d_y=t["dy"], d_k_mem=o["d_k"], d_v_mem=o["d_v"],
+              d_q_mem=o["d_q"], d_alpha=o["d_alpha"], d_theta=o["d_theta"], d_eta=o["d_eta"],
+              d_m_initial=o["d_m0"], d_s_initial=o["d_s0"], seq_len=self.S, d=self.D,
+              batch_size=self.N, chunk_size=self.chunk, error_clip=0.0, m_norm_max=0.0)
+        else:
+            c("titans_backward_f32_cuda", k_mem=t["k"], v_mem=t["v"], q_mem=t["q"], alpha=t["alpha"],
+              theta=t["theta"], eta=t["eta"], m_states=self.mstate, s_states=self.sstate,
+              d_y=t["dy"], d_k_mem=o["d_k"], d_v_mem=o["d_v"], d_q_mem=o["d_q"],
+              d_alpha=o["d_alpha"], d_theta=o["d_theta"], d_eta=o["d_eta"], d_m_initial=o["d_m0"],
+              d_s_initial=o["d_s0"], seq_len=self.S, d=self.D, batch_size=self.N, error_clip=0.0)
+
+    def step(self):
+        self.fwd(self.dev); self.bwd(self.dev)
+
+    def step_e2e(self):
+        t = {k: v.cuda(non_blocking=True) for k, v in self.host.items()}
+        self.fwd(t); self.bwd(t)
+        for k, v in self.out.items():
+            self.host_out[k].copy_(v, non_blocking=True)
+        self.host_out["y"].copy_(self.y, non_blocking=True)
+
+    def dominant(self):
+        """(name, callable, algorithmic bytes per launch, bound). Backward kernel."""
+        n, s, d = self.N, self.S, self.D
+        stream4 = 4 * n * s * d * 4            # k,v,q,d_y read
+        out3 = 3 * n * s * d * 4               # d_k,d_v,d_q written
+        gates = 6 * n * s * 4                  # 3 gates read + 3 gate grads written
+        if self.chunk:
+            states = 2 * n * (s // self.chunk + 1) * d * d * 4
+        else:
+            states = 2 * n * (s + 1) * d * d * 4
+        return ("fast_bwd_kernel<64,TITANS," + ("frozen>" if self.chunk else "exact>"),
+                lambda: self.bwd(self.dev), stream4 + out3 + gates + states, "hbm")
+
+    def cpu_sample(self, oracle, threads, budget_s=12.0):
+        import ctypes as C
+        d, s = self.D, self.S
+
+        def run(nprob):
+            p = self.host_inputs(nprob, seed=99)
+            o = lambda *sh: np.empty(sh, np.float32)
+            L = oracle.lib()
+            ptr = oracle._p
+            t0 = time.perf_counter()
+            if self.chunk:
+                nc = s // self.chunk
+                L.orc_chunkwise_fwd_bwd_batched_mt(
+                    C.c_int(1), ptr(p["k"]), ptr(p["v"]), ptr(p["q"]), ptr(p["alpha"]), ptr(p["theta"]),
+                    ptr(p["eta"]), ptr(p["m0"]), ptr(p["s0"]), ptr(p["dy"]),
+                    ptr(o(nprob, nc + 1, d * d)), ptr(o(nprob, nc + 1, d * d)), ptr(o(nprob, s, d)),
+                    ptr(o(nprob, s, d)), ptr(o(nprob, s, d)), ptr(o(nprob, s, d)), ptr(o(nprob, s)),
+                    ptr(o(nprob, s)), ptr(o(nprob, s)), ptr(o(nprob, d * d)), ptr(o(nprob, d * d)),
+                    C.c_int(nprob), C.c_int(s), C.c_int(d), C.c_int(self.chunk), C.c_float(0.0),
+                    C.c_float(0.0), C.c_int(threads))
+            else:
+                L.orc_titans_fwd_bwd_batched_mt(
+                    ptr(p["k"]), ptr(p["v"]), ptr(p["q"]), ptr(p["alpha"]), ptr(p["theta"]),
+                    ptr(p["eta"]), ptr(p["m0"]), ptr(p["s0"]), ptr(p["dy"]),
+                    ptr(o(nprob, s + 1, d * d)), ptr(o(nprob, s + 1, d * d)), ptr(o(nprob, s, d)),
+                    ptr(o(nprob, s, d)), ptr(o(nprob, s, d)), ptr(o(nprob, s, d)), ptr(o(nprob, s)),
+                    ptr(o(nprob, s)), ptr(o(nprob, s)), ptr(o(nprob, d * d)), ptr(o(nprob, d * d)),
+                    C.c_int(nprob), C.c_int(s), C.c_int(d), C.c_float(0.0), C.c_float(0.0),
+                    C.c_int(threads))
+            return time.perf_counter() - t0
+        t1 = run(threads)                              # one problem per thread
+        reps = max(1, min(8, int(budget_s / max(t1, 1e-3)) - 1))
+        nprob = threads * reps
+        dt = run(nprob) if reps > 1 else t1
+        head_tokens = nprob * s
+        # tokens = sequence positions of the [B,S] batch = head-tokens / H
+        return head_tokens / self.H / dt, f"{nprob} of {self.N} (batch x head) problems, seq {s}, {dt:.1f} s"
+
+
+class SwaPair:
+    B, H, S, HD, W = 8, 16, 8192, 64, 512
+
+    def __init__(self):
+        self.name = "swa"
+        self.tokens_per_step = self.B * self.S
+        self.dtype = "bf16"
+
+    def describe(self):
+        return {"workload": f"SWA forward+backward pair: bf16, batch {self.B} x heads {self.H}, "
+                            f"head_dim {self.HD}, seq {self.S}, causal window {self.W}",
+                "tokens_per_step_per_gpu": self.tokens_per_step,
+                "l2_policy": "inputs+outputs > L2 (1.9 GB touched per step)"}
+
+    def host_inputs(self, b=None, seed=31):
+        b = self.B if b is None else b
+        g = np.random.Generator(np.random.Philox(seed))
+        sh = (b, self.S, self.H * self.HD)
+        mk = lambda: (g.standard_normal(sh) / 8.0).astype(np.float32)
+        return dict(q=mk(), k=mk(), v=mk(), do=g.standard_normal(sh).astype(np.float32))
+
+    def setup(self, torch, dispatch):
+        self.torch, self.dd = torch, dispatch
+        h = self.host_inputs()
+        self.host = {k: (torch.from_numpy(v).bfloat16() if k != "do" else torch.from_numpy(v)).pin_memory()
+                     for k, v in h.items()}
+        self.dev = {k: v.cuda() for k, v in self.host.items()}
+        sh = (self.B, self.S, self.H * self.HD)
+        self.o = torch.empty(sh, dtype=torch.bfloat16, device="cuda")
+        self.lse = torch.empty(self.B, self.H, self.S, dtype=torch.float32, device="cuda")
+        self.g = {k: torch.empty(sh, dtype=torch.float32, device="cuda") for k in ("dq", "dk", "dv")}
+        self.host_out = {k: torch.empty(sh, dtype=torch.float32).pin_memory() for k in self.g}
+        self.host_out["out"] = torch.empty(sh, dtype=torch.bfloat16).pin_memory()
+        self.launches_per_step = 4   # fwd, delta, dK/dV, dQ
+        self.h2d = sum(v.numel() * v.element_size() for v in self.host.values())
+        self.d2h = sum(v.numel() * v.element_size() for v in self.host_out.values())
+
+    def fwd(self, t):
+        self.dd.call("nlh_swa_forward", q=t["q"], k=t["k"], v=t["v"], out=self.o, lse=self.lse,
+                     seq_len=self.S, num_heads=self.H, head_dim=self.HD, window_size=self.W,
+                     batch_size=self.B, n_persistent=0)
+
+    def bwd(self, t):
+        self.dd.call("nlh_swa_backward", q=t["q"], k=t["k"], v=t["v"], out=self.o, lse=self.lse,
+                     d_attn_out=t["do"], d_q=self.g["dq"], d_k=self.g["dk"], d_v=self.g["dv"],
+                     seq_len=self.S, num_heads=self.H, head_dim=self.HD, window_size=self.W,
+                     batch_size=self.B, n_persistent=0)
+
+    def step(self):
+        self.fwd(self.dev); self.bwd(self.dev)
+
+    def step_e2e(self):
+        t = {k: v.cuda(non_blocking=True) for k, v in self.host.items()}
+        self.fwd(t); self.bwd(t)
+        for k, v in self.g.items():
+            self.host_out[k].copy_(v, non_blocking=True)
+        self.host_out["out"].copy_(self.o, non_blocking=True)
+
+    def dominant(self):
+        pairs = (self.S * self.W - self.W * (self.W - 1) // 2) * self.B * self.H
+        flops = pairs * (4 + 10) * self.HD      # fwd 4*hd + bwd 10*hd flop per visible (q,k) pair
+        return ("swa fwd+bwd (4 launches)", lambda: self.step(), flops, "tensor")
+
+    def cpu_sample(self, oracle, threads, budget_s=12.0):
+        import ctypes as C
+        # bounded sample: `threads` sequences (one per host thread) of seq 1024 with the same
+        # window and head shape; attention work per token is the same once seq >= window
+        s, nh, hd, w = 1024, self.H, self.HD, self.W
+        g = np.random.Generator(np.random.Philox(5))
+        sh = (threads, s, nh * hd)
+        q, k, v = ((g.standard_normal(sh) / 8).astype(np.float32) for _ in range(3))
+        do = g.standard_normal(sh).astype(np.float32)
+        o = lambda *shape: np.zeros(shape, np.float32)
+        ptr = oracle._p
+        t0 = time.perf_counter()
+        oracle.lib().orc_swa_fwd_bwd_batched_mt(
+            ptr(q), ptr(k), ptr(v), ptr(do), ptr(o(*sh)), ptr(o(threads, nh, s, w)), ptr(o(*sh)),
+            ptr(o(*sh)), ptr(o(*sh)), C.c_int(threads), C.c_int(s), C.c_int(nh), C.c_int(hd),
+            C.c_int(w), C.c_int(0), C.c_int(threads))
+        dt = time.perf_counter() - t0
+        return threads * s / dt, f"{threads} sequences of seq {s} (window {w}, {nh} heads), {dt:.1f} s"
+
+
+class AdamWStep:
+    N_PARAMS = 25_200_000
+
+    def __init__(self):
+        self.name = "adamw"
+        self.tokens_per_step = 64 * 512     # tokens of the cfg3 step this optimizer step serves
+        self.dtype = "f32"
+
+    def describe(self):
+        return {"workload": f"flat-arena global-norm clip + AdamW step, {self.N_PARAMS} fp32 parameters",
+                "tokens_per_step_per_gpu": self.tokens_per_step,
+                "l2_policy": "4 arenas x 101 MB > L2"}
+
+    def setup(self, torch, dispatch):
+        from nl_hecate_b200.optimizer import FlatAdamW
+        self.torch = torch
+        sizes = [4_194_304, 4_194_304] + [262_144] * 16 + [789_507] * 16 + [1024] * 8
+        sizes.append(self.N_PARAMS - sum(sizes))
+        self.opt = FlatAdamW(sizes, device="cuda")
+        g = torch.Generator(device="cuda").manual_seed(7)
+        self.opt.w.normal_(0, 0.02, generator=g)
+        self.opt.g.normal_(0, 0.01, generator=g)
+        self.steps = [1] * len(sizes)
+        self.host_g = torch.empty(self.opt.arena_len, dtype=torch.float32).pin_memory().normal_(0, 0.01)
+        self.host_norm = torch.empty(1, dtype=torch.float32).pin_memory()
+        self.launches_per_step = 3
+        self.h2d = self.opt.arena_len * 4
+        self.d2h = 4
+        self.t = 0
+
+    def step(self):
+        self.t += 1
+        self.opt.step(lr=3e-4, steps=[self.t] * len(self.steps), max_grad_norm=1.0)
+
+    def step_e2e(self):
+        self.opt.g.copy_(self.host_g, non_blocking=True)
+        self.step()
+        self.host_norm.copy_(self.opt.norm, non_blocking=True)
+
+    def dominant(self):
+        return ("adamw_multi_kernel + arena_sumsq_kernel", lambda: self.step(),
+                self.opt.arena_len * 32, "hbm")   # 4 B norm pass + 16 B read + 12 B written
+
+    def cpu_sample(self, oracle, threads, budget_s=12.0):
+        import ctypes as C
+        n = self.N_PARAMS
+        w, g, m, v = (np.full(n, x, np.float32) for x in (0.01, 0.001, 0.0, 0.0))
+        ptr = oracle._p
+        t0 = time.perf_counter()
+        reps = 3
+        for _ in range(reps):
+            oracle.lib().orc_adamw_step_mt(ptr(w), ptr(g), ptr(m), ptr(v), C.c_int64(n),
+                                           C.c_float(3e-4), C.c_float(0.9), C.c_float(0.999),
+                                           C.c_float(1e-8), C.c_float(10.0), C.c_float(1000.0),
+                                           C.c_float(0.1), C.c_int(threads))
+        dt = (time.perf_counter() - t0) / reps
+        return self.tokens_per_step / dt, f"{reps} full steps over {n} parameters, {dt * 1e3:.0f} ms each"
+
+
+def make_workload(name):
+    if name == "titans_chunkwise":
+        return TitansPair(64)
+    if name == "titans_exact":
+        return TitansPair(0)
+    if name == "swa":
+        return SwaPair()
+    if name == "adamw":
+        return AdamWStep()
+    raise SystemExit(f"unknown workload {name}")
+
+
+DEFAULT_WORKLOAD = "titans_chunkwise"
+METRIC = "fwd+bwd tokens/sec"
+UNIT = "tokens/s"
+
+
+def run_reference(args):
+    """CPU arm: the restated Rust reference path on all host threads, bounded sample."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import oracle
+    oracle.build()
+    wl = make_workload(args.workload)
+    threads = oracle.hardware_threads()
+    vals = []
+    sample = ""
+    for i in range(args.warmup + args.steps):
+        v, sample = wl.cpu_sample(oracle, threads, budget_s=max(2.0, 20.0 / max(1, args.steps)))
+        if i >= args.warmup:
+            vals.append(v)
+    value = float(np.mean(vals))
+    cfg = wl.describe()
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * wl.tokens_per_step / value, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
+        "config": cfg,
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 0)
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    import torch.distributed as dist
+    from nl_hecate_b200 import dispatch, ffi
+    ffi.lib()   # raises if the CUDA library is not built
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (the CPU arm is --impl reference)")
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    warmup = max(args.warmup, 3)
+
+    wl = make_workload(args.workload)
+    wl.setup(torch, dispatch)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, k):
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        ev0.record()
+        for _ in range(k):
+            fn()
+        ev1.record()
+        barrier()
+        ms = ev0.elapsed_time(ev1)
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    for _ in range(warmup):
+        wl.step()
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    ms = timed(wl.step, args.steps)
+    clocks = sampler.stop() if sampler else None
+    tokens = wl.tokens_per_step * world * args.steps
+    value = tokens / (ms * 1e-3)
+
+    # end to end through the host-slice API
+    for _ in range(2):
+        wl.step_e2e()
+    ms_e2e = timed(wl.step_e2e, max(1, min(args.steps, 5)))
+    e2e_value = wl.tokens_per_step * world * max(1, min(args.steps, 5)) / (ms_e2e * 1e-3)
+
+    # roofline of the dominant kernel, timed alone with CUDA events on the launching stream
+    peaks = measured_peaks()
+    name, fn, work, bound = wl.dominant()
+    for _ in range(3):
+        fn()
+    reps = max(3, min(args.steps, 10))
+    ms_dom = timed(fn, reps) / reps
+    if bound == "hbm":
+        achieved = work / (ms_dom * 1e-3) / 1e9
+        peak, runit = peaks["hbm_gbs"], "GB/s"
+    else:
+        achieved = work / (ms_dom * 1e-3) / 1e12
+        peak, runit = peaks["bf16_tflops"], "TFLOP/s"
+    roofline = {"kernel": name, "bound": bound, "achieved": achieved, "peak": peak, "unit": runit,
+                "frac": achieved / peak, "traffic": None, "ms_per_launch": ms_dom,
+                "algorithmic_work_per_launch": work, "peak_source": peaks["source"]}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        import oracle
+        oracle.build()
+        th = oracle.hardware_threads()
+        v, sample = wl.cpu_sample(oracle, th)
+        cpu = {"value": v, "unit": UNIT, "cores": th, "kind": "port", "sample": sample}
+
+    if rank == 0:
+        cfg = wl.describe()
+        cfg["parallelism"] = f"dp{world} (independent problems per rank, no collective)"
+        print(json.dumps({
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
+            "config": cfg, "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": wl.h2d,
+                    "d2h_bytes_per_step": wl.d2h},
+            "gpu_launches": wl.launches_per_step * args.steps,
+            "roofline": roofline, "cpu_baseline": cpu,
+        }))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

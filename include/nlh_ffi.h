@@ -1,0 +1,276 @@
+/*
+ * nlh_ffi.h — C ABI of libnlh_b200.so, the sm_100a implementation of the
+ * NL_Hecate memory-rule / SWA / AdamW hot path.
+ *
+ * Section 1 declares drop-in symbols: name, argument order, argument types and
+ * return type are those of the `extern "C"` block in the reference's
+ * core/src/cuda_ffi.rs (line of each Rust declaration cited). A host built
+ * against that block links against this library unchanged.
+ *
+ * Conventions (same as the reference): every pointer is DEVICE memory owned by
+ * the caller; dimensions are int32; uint16_t* is bf16 bits; outputs documented
+ * as accumulated must be zeroed by the caller. Differences, all additive:
+ *   - launches go to the stream set with nlh_set_stream() (default: the
+ *     legacy default stream, as in the reference) and never synchronise;
+ *   - private scratch comes from a grow-only per-device workspace instead of
+ *     cudaMalloc/cudaFree inside each call;
+ *   - an invalid argument or launch failure is recorded (nlh_last_status())
+ *     and printed to stderr; the process is not aborted.
+ *
+ * Section 2 declares the additive entries of this library (status-returning,
+ * per-problem outputs, recompute-style training path, multi-tensor AdamW).
+ */
+#ifndef NLH_FFI_H
+#define NLH_FFI_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ───────────────────────── runtime ───────────────────────── */
+/* No counterpart in the reference (it has no stream/handle arguments). */
+void nlh_set_stream(void* cuda_stream);
+void* nlh_get_stream(void);
+int32_t nlh_last_status(void);          /* NLH_OK (0) or the last recorded error */
+const char* nlh_last_error(void);       /* text of the last recorded error ("" if none) */
+void nlh_clear_status(void);
+int32_t nlh_workspace_reserve(int64_t bytes); /* pre-grow scratch (e.g. before graph capture) */
+void nlh_workspace_release(void);       /* free the scratch of the current device */
+int32_t nlh_abi_version(void);
+
+/* ═════════════ Section 1: drop-in symbols (core/src/cuda_ffi.rs) ═════════════ */
+
+/* cuda_ffi.rs:26 — SWA forward. q,k,v,out [B,S,H*hd] bf16; attn_weights
+ * [B,H,S,n_persistent+window] bf16 (may be NULL here: skipped). */
+void swa_forward_f32_cuda(const uint16_t* q, const uint16_t* k, const uint16_t* v, uint16_t* out,
+    uint16_t* attn_weights, int32_t seq_len, int32_t num_heads, int32_t head_dim,
+    int32_t window_size, int32_t batch_size, int32_t n_persistent);
+/* cuda_ffi.rs:62 — SWA backward. d_q,d_k,d_v f32, accumulated (caller zeroes). */
+void swa_backward_f32_cuda(const uint16_t* q, const uint16_t* k, const uint16_t* v,
+    const uint16_t* attn_weights, const float* d_attn_out, float* d_q, float* d_k, float* d_v,
+    int32_t seq_len, int32_t num_heads, int32_t head_dim, int32_t window_size, int32_t batch_size,
+    int32_t n_persistent);
+
+/* cuda_ffi.rs:86 / :109 — Delta rule, full trajectory m_states [B,(S+1),d*d]. */
+void delta_forward_f32_cuda(const float* k_mem, const float* v_mem, const float* q_mem,
+    const float* alpha, const float* theta, const float* m_initial, float* m_states, float* y,
+    int32_t seq_len, int32_t d, int32_t batch_size, int32_t input_stride, int32_t m_stride,
+    float error_clip, float m_norm_max);
+void delta_backward_f32_cuda(const float* k_mem, const float* v_mem, const float* q_mem,
+    const float* alpha, const float* theta, const float* m_states, const float* d_y,
+    float* d_k_mem, float* d_v_mem, float* d_q_mem, float* d_alpha, float* d_theta,
+    float* d_m_initial, int32_t seq_len, int32_t d, int32_t batch_size, float error_clip);
+/* cuda_ffi.rs:134 / :156 — Titans LMM. d_m_initial/d_s_initial [d*d] are summed
+ * over the batch (caller zeroes). */
+void titans_forward_f32_cuda(const float* k_mem, const float* v_mem, const float* q_mem,
+    const float* alpha, const float* theta, const float* eta, const float* m_initial,
+    const float* s_initial, float* m_states, float* s_states, float* y, int32_t seq_len, int32_t d,
+    int32_t batch_size, int32_t input_stride, int32_t m_stride, float error_clip,
+    float m_norm_max);
+void titans_backward_f32_cuda(const float* k_mem, const float* v_mem, const float* q_mem,
+    const float* alpha, const float* theta, const float* eta, const float* m_states,
+    const float* s_states, const float* d_y, float* d_k_mem, float* d_v_mem, float* d_q_mem,
+    float* d_alpha, float* d_theta, float* d_eta, float* d_m_initial, float* d_s_initial,
+    int32_t seq_len, int32_t d, int32_t batch_size, float error_clip);
+/* cuda_ffi.rs:186 / :202 — Hebbian (backward has no batch argument). */
+void hebbian_forward_f32_cuda(const float* k_mem, const float* v_mem, const float* q_mem,
+    const float* alpha, const float* m_initial, float* m_states, float* y, int32_t seq_len,
+    int32_t d, int32_t batch_size, int32_t input_stride, int32_t m_stride);
+void hebbian_backward_f32_cuda(const float* k_mem, const float* v_mem, const float* q_mem,
+    const float* alpha, const float* m_states, const float* d_y, float* d_k_mem, float* d_v_mem,
+    float* d_q_mem, float* d_alpha, float* d_m_initial, int32_t seq_len, int32_t d);
+
+/* cuda_ffi.rs:221-240 — checkpointed forwards: slot 0 = initial state, then one
+ * slot every checkpoint_interval tokens and the final state. Single problem. */
+void delta_forward_ckpt_f32_cuda(const float* k_mem, const float* v_mem, const float* q_mem,
+    const float* alpha, const float* theta, const float* m_initial, float* m_states, float* y,
+    int32_t seq_len, int32_t d, int32_t checkpoint_interval, float error_clip, float m_norm_max);
+void titans_forward_ckpt_f32_cuda(const float* k_mem, const float* v_mem, const float* q_mem,
+    const float* alpha, const float* theta, const float* eta, const float* m_initial,
+    const float* s_initial, float* m_states, float* s_states, float* y, int32_t seq_len, int32_t d,
+    int32_t checkpoint_interval, float error_clip, float m_norm_max);
+void hebbian_forward_ckpt_f32_cuda(const float* k_mem, const float* v_mem, const float* q_mem,
+    const float* alpha, const float* m_initial, float* m_states, float* y, int32_t seq_len,
+    int32_t d, int32_t checkpoint_interval);
+/* cuda_ffi.rs:250-275 — segment backwards over tokens [t_start,t_end) with a
+ * segment-local trajectory [B,(t_end-t_start+1),d*d], seeds and per-batch outputs. */
+void delta_backward_segment_f32_cuda(const float* k_mem, const float* v_mem, const float* q_mem,
+    const float* alpha, const float* theta, const float* m_states, const float* d_y,
+    const float* d_m_seed, float* d_k_mem, float* d_v_mem, float* d_q_mem, float* d_alpha,
+    float* d_theta, float* d_m_out, int32_t t_start, int32_t t_end, int32_t d, int32_t batch_size,
+    int32_t seq_len, float error_clip);
+void titans_backward_segment_f32_cuda(const float* k_mem, const float* v_mem, const float* q_mem,
+    const float* alpha, const float* theta, const float* eta, const float* m_states,
+    const float* s_states, const float* d_y, const float* d_m_seed, const float* d_s_seed,
+    float* d_k_mem, float* d_v_mem, float* d_q_mem, float* d_alpha, float* d_theta, float* d_eta,
+    float* d_m_out, float* d_s_out, int32_t t_start, int32_t t_end, int32_t d, int32_t batch_size,
+    int32_t seq_len, float error_clip);
+void hebbian_backward_segment_f32_cuda(const float* k_mem, const float* v_mem, const float* q_mem,
+    const float* alpha, const float* m_states, const float* d_y, const float* d_m_seed,
+    float* d_k_mem, float* d_v_mem, float* d_q_mem, float* d_alpha, float* d_m_out,
+    int32_t t_start, int32_t t_end, int32_t d, int32_t batch_size, int32_t seq_len);
+
+/* cuda_ffi.rs:291-337 — DGD (same math as Delta with the L2 bias). */
+void dgd_forward_f32_cuda(const float* k_mem, const float* v_mem, const float* q_mem,
+    const float* alpha, const float* theta, const float* m_initial, float* m_states, float* y,
+    int32_t seq_len, int32_t d, int32_t batch_size, int32_t input_stride, int32_t m_stride,
+    float error_clip);
+void dgd_backward_f32_cuda(const float* k_mem, const float* v_mem, const float* q_mem,
+    const float* alpha, const float* theta, const float* m_states, const float* d_y,
+    float* d_k_mem, float* d_v_mem, float* d_q_mem, float* d_alpha, float* d_theta,
+    float* d_m_initial, int32_t seq_len, int32_t d, float error_clip);
+void dgd_forward_ckpt_f32_cuda(const float* k_mem, const float* v_mem, const float* q_mem,
+    const float* alpha, const float* theta, const float* m_initial, float* m_states, float* y,
+    int32_t seq_len, int32_t d, int32_t checkpoint_interval, float error_clip);
+void dgd_backward_segment_f32_cuda(const float* k_mem, const float* v_mem, const float* q_mem,
+    const float* alpha, const float* theta, const float* m_states, const float* d_y,
+    const float* d_m_seed, float* d_k_mem, float* d_v_mem, float* d_q_mem, float* d_alpha,
+    float* d_theta, float* d_m_out, int32_t t_start, int32_t t_end, int32_t d, int32_t batch_size,
+    int32_t seq_len, float error_clip);
+
+/* cuda_ffi.rs:356-386 — frozen-M0 chunkwise rule; *_chunk_states [B,(ceil(S/C)+1),d*d]. */
+void delta_chunkwise_forward_f32_cuda(const float* k_mem, const float* v_mem, const float* q_mem,
+    const float* alpha, const float* theta, const float* m_initial, float* m_chunk_states,
+    float* y, int32_t seq_len, int32_t d, int32_t batch_size, int32_t chunk_size,
+    float error_clip, float m_norm_max);
+void delta_chunkwise_backward_f32_cuda(const float* k_mem, const float* v_mem, const float* q_mem,
+    const float* alpha, const float* theta, const float* m_chunk_states, const float* d_y,
+    float* d_k_mem, float* d_v_mem, float* d_q_mem, float* d_alpha, float* d_theta,
+    float* d_m_initial, int32_t seq_len, int32_t d, int32_t batch_size, int32_t chunk_size,
+    float error_clip, float m_norm_max);
+void titans_chunkwise_forward_f32_cuda(const float* k_mem, const float* v_mem, const float* q_mem,
+    const float* alpha, const float* theta, const float* eta, const float* m_initial,
+    const float* s_initial, float* m_chunk_states, float* s_chunk_states, float* y,
+    int32_t seq_len, int32_t d, int32_t batch_size, int32_t chunk_size, float error_clip,
+    float m_norm_max);
+void titans_chunkwise_backward_f32_cuda(const float* k_mem, const float* v_mem,
+    const float* q_mem, const float* alpha, const float* theta, const float* eta,
+    const float* m_chunk_states, const float* s_chunk_states, const float* d_y, float* d_k_mem,
+    float* d_v_mem, float* d_q_mem, float* d_alpha, float* d_theta, float* d_eta,
+    float* d_m_initial, float* d_s_initial, int32_t seq_len, int32_t d, int32_t batch_size,
+    int32_t chunk_size, float error_clip, float m_norm_max);
+
+/* cuda_ffi.rs:401-440 — phase-1 epilogue and per-chunk phase-2 kernels. */
+void error_subtract_clip_f32_cuda(float* predictions, const float* v, int32_t total_rows,
+    int32_t d, float error_clip);
+void delta_phase2_forward_f32_cuda(const float* k_mem, const float* q_mem, const float* alpha,
+    const float* theta, const float* errors, float* m_work, float* m_chunk_states, float* y,
+    int32_t seq_len, int32_t d, int32_t batch_size, int32_t chunk_size, int32_t chunk_idx,
+    float m_norm_max);
+void titans_phase2_forward_f32_cuda(const float* k_mem, const float* q_mem, const float* alpha,
+    const float* theta, const float* eta, const float* errors, float* m_work, float* s_work,
+    float* m_chunk_states, float* s_chunk_states, float* y, int32_t seq_len, int32_t d,
+    int32_t batch_size, int32_t chunk_size, int32_t chunk_idx, float m_norm_max);
+void delta_phase2_backward_f32_cuda(const float* k_mem, const float* q_mem, const float* alpha,
+    const float* theta, const float* errors, const float* m_chunk_states, const float* d_y,
+    float* d_k_mem, float* d_v_mem, float* d_q_mem, float* d_alpha, float* d_theta, float* d_M,
+    float* d_M0, float* m_recompute, int32_t seq_len, int32_t d, int32_t batch_size,
+    int32_t chunk_size, int32_t chunk_idx, float m_norm_max);
+void titans_phase2_backward_f32_cuda(const float* k_mem, const float* q_mem, const float* alpha,
+    const float* theta, const float* eta, const float* errors, const float* m_chunk_states,
+    const float* s_chunk_states, const float* d_y, float* d_k_mem, float* d_v_mem,
+    float* d_q_mem, float* d_alpha, float* d_theta, float* d_eta, float* d_M, float* d_S,
+    float* d_M0, float* m_recompute, float* s_recompute, int32_t seq_len, int32_t d,
+    int32_t batch_size, int32_t chunk_size, int32_t chunk_idx, float m_norm_max);
+
+/* cuda_ffi.rs:467 / :471 — Frobenius-norm clamp of the carried memory. */
+void m_norm_clamp_f32_cuda(float* m, int32_t d, float m_norm_max);
+void m_norm_clamp_batch_f32_cuda(float* m, int32_t d, int32_t batch_size, float m_norm_max);
+
+/* cuda_ffi.rs:674-714 — AdamW family; return value is a cudaError_t. */
+uint32_t adamw_update_cuda(float* w, const float* g, float* m, float* v, int32_t n, float lr,
+    float beta1, float beta2, float eps, float bc1_inv, float bc2_inv, float weight_decay);
+uint32_t grad_norm_sq_cuda(const float* g, float* partial_sums, int32_t n,
+    int32_t* out_num_blocks);
+uint32_t dot_product_partial_f32_cuda(const float* a, const float* b, float* partial_sums,
+    int32_t n, int32_t* out_num_blocks);
+uint32_t grad_scale_cuda(float* g, float scale, int32_t n);
+uint32_t reduce_partials_clip_cuda(const float* partial_sums, int32_t total_partials,
+    float max_grad_norm, float* out_norm, float* out_scale);
+uint32_t grad_scale_conditional_cuda(float* g, const float* scale_ptr, int32_t n);
+
+/* cuda_ffi.rs:973 / :1000 — fused forwards: L2-normalise k,q in place, compute
+ * the gates, then run the recurrence. */
+void dgd_fused_forward_f32_cuda(float* k_mem, const float* v_mem, float* q_mem,
+    const float* w_alpha, const float* b_alpha_ptr, const float* w_theta,
+    const float* b_theta_ptr, float alpha_floor, float alpha_ceil, float theta_floor,
+    float theta_ceil, const float* m_initial, float* m_states, float* y, float* alpha_out,
+    float* theta_out, float* k_norms_out, float* q_norms_out, int32_t seq_len, int32_t d,
+    int32_t batch_size, float error_clip);
+void titans_fused_forward_f32_cuda(float* k_mem, const float* v_mem, float* q_mem,
+    const float* w_alpha, const float* b_alpha_ptr, const float* w_theta,
+    const float* b_theta_ptr, const float* w_eta, const float* b_eta_ptr, float alpha_floor,
+    float alpha_ceil, float theta_floor, float theta_ceil, const float* m_initial,
+    const float* s_initial, float* m_states, float* s_states, float* y, float* alpha_out,
+    float* theta_out, float* eta_out, float* k_norms_out, float* q_norms_out, int32_t seq_len,
+    int32_t d, int32_t batch_size, float error_clip, float m_norm_max);
+
+/* ═════════════ Section 2: additive entries of this library ═════════════ */
+
+/* rule: 0 Delta/DGD, 1 Titans LMM, 2 Hebbian. All return NLH_OK or an error
+ * code; nothing is printed or aborted. */
+
+/* Training forward that keeps only what the recompute backward needs:
+ * exact rule (chunk_size = 0): checkpoints every `interval` tokens,
+ *   m_ckpt/s_ckpt [B, ceil(S/interval)+1, d*d] (slot j = state before token
+ *   j*interval; last slot = final state);
+ * frozen-M0 rule (chunk_size > 0): interval must equal chunk_size and the
+ *   buffers are the reference's *_chunk_states.
+ * Replaces the trajectory-materialising pairs core/kernels/titans_forward.cu:83
+ * + titans_backward.cu:66 (and the Delta/Hebbian twins) at the call sites
+ * core/src/gpu_forward.rs:1521 and gpu_backward.rs:459. */
+int32_t nlh_rule_forward(int32_t rule, const float* k_mem, const float* v_mem, const float* q_mem,
+    const float* alpha, const float* theta, const float* eta, const float* m_initial,
+    const float* s_initial, float* m_ckpt, float* s_ckpt, float* y, int32_t seq_len, int32_t d,
+    int32_t batch_size, int32_t interval, int32_t chunk_size, float error_clip,
+    float m_norm_max);
+/* Matching backward. d_m_initial/d_s_initial are PER PROBLEM [B,d*d] (the
+ * reference sums them over the batch with atomicAdd: titans_backward.cu:337). */
+int32_t nlh_rule_backward(int32_t rule, const float* k_mem, const float* v_mem,
+    const float* q_mem, const float* alpha, const float* theta, const float* eta,
+    const float* m_ckpt, const float* s_ckpt, const float* d_y, float* d_k_mem, float* d_v_mem,
+    float* d_q_mem, float* d_alpha, float* d_theta, float* d_eta, float* d_m_initial,
+    float* d_s_initial, int32_t seq_len, int32_t d, int32_t batch_size, int32_t interval,
+    int32_t chunk_size, float error_clip, float m_norm_max);
+
+/* SWA without the materialised weights tensor: forward writes out (bf16) and
+ * the per-row log-sum-exp lse [B,H,S] f32; backward recomputes the
+ * probabilities from lse. d_q,d_k,d_v f32 are overwritten (no pre-zeroing).
+ * Replaces core/kernels/swa_forward.cu:23 / swa_backward.cu:24. */
+int32_t nlh_swa_forward(const uint16_t* q, const uint16_t* k, const uint16_t* v, uint16_t* out,
+    float* lse, int32_t seq_len, int32_t num_heads, int32_t head_dim, int32_t window_size,
+    int32_t batch_size, int32_t n_persistent);
+int32_t nlh_swa_backward(const uint16_t* q, const uint16_t* k, const uint16_t* v,
+    const uint16_t* out, const float* lse, const float* d_attn_out, float* d_q, float* d_k,
+    float* d_v, int32_t seq_len, int32_t num_heads, int32_t head_dim, int32_t window_size,
+    int32_t batch_size, int32_t n_persistent);
+
+/* Multi-tensor AdamW over one flat arena (w,g,m,v share the layout). The
+ * per-tensor loop it replaces is core/src/gpu_stacked_optimizer.rs:554-677. */
+typedef struct nlh_adamw_tensor_desc {
+    float bc1_inv;       /* 1/(1-beta1^t), t = the tensor's own step count      */
+    float bc2_inv;       /* 1/(1-beta2^t)                                       */
+    float weight_decay;
+    float lr_scale;      /* multiplies the call's lr                            */
+    float clamp_lo;      /* post-update clamp (b_theta in [-10,2]) if has_clamp */
+    float clamp_hi;
+    int32_t has_clamp;
+    int32_t active;      /* 0: tensor skipped (CMS level not fired this step)   */
+} nlh_adamw_tensor_desc;
+
+int32_t nlh_adamw_multi_tensor(float* w, const float* g, float* m, float* v,
+    const nlh_adamw_tensor_desc* descs_dev, const int32_t* chunk_tensor_dev,
+    const int64_t* chunk_start_dev, const int32_t* chunk_len_dev, int32_t n_chunks,
+    const float* grad_scale_ptr, float lr, float beta1, float beta2, float eps);
+/* Global L2 norm of a flat gradient arena and the clip scale
+ * (norm > max ? max/norm : 1), replacing the per-tensor grad_norm_sq_cuda loop
+ * at core/src/gpu_stacked_optimizer.rs:193-345. partial: >= partial_capacity floats. */
+int32_t nlh_arena_grad_norm_clip(const float* g, int64_t n, float max_grad_norm, float* partial,
+    int32_t partial_capacity, float* out_norm, float* out_scale);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NLH_FFI_H */

@@ -1,0 +1,729 @@
+// Register-resident memory-rule kernels for head dimension D in {32, 64}.
+//
+// One CTA per independent (batch x head) problem. The D x D memory M (and the
+// momentum S) never leave the register file during the sequence: D*D/16
+// threads hold 16 elements each — one row, four float4 column chunks
+// interleaved so that shared-memory reads of k/q are conflict-free and global
+// state stores are full 32-byte sectors. Row reductions (M k, M q, dS k) are
+// 1-3 warp shuffles inside the sequential dependency chain; column reductions
+// (M^T dy, dS^T e), which only feed outputs, use a recursive-halving warp
+// reduction and a deferred cross-warp sum per token tile. The k/v/q/dy/gate
+// streams are staged tile by tile with 16-byte cp.async double buffering;
+// backward state reads use a per-thread cp.async ring so no barrier sits in
+// the token loop.
+//
+// Not covered here (generic kernels take over): error clip, Frobenius
+// projection, other head dimensions, unaligned pointers, frozen chunks > 64.
+#pragma once
+
+#include "nlh_common.cuh"
+
+namespace nlh {
+
+constexpr int FAST_TT = 16;      // tokens per forward tile
+constexpr int FAST_TB = 8;       // tokens per backward tile
+constexpr int FAST_NST = 3;      // backward state ring depth (tokens)
+constexpr int FAST_MAX_CHUNK = 64;
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc)
+{
+    unsigned s = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async4(void* smem_dst, const void* gsrc)
+{
+    unsigned s = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(s), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
+template <int TPR>
+__device__ __forceinline__ float row_allreduce(float v)
+{
+#pragma unroll
+    for (int o = 1; o < TPR; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// Column index (within a row of length D) of element i (0..15) held by column group cg.
+template <int D>
+__device__ __forceinline__ int col_of(int i, int cg) { return (i >> 2) * (D / 4) + cg * 4 + (i & 3); }
+
+// Recursive-halving reduction over the rows a warp owns. In: 16 per-thread
+// column partials. Out: NOUT = 16*TPR/32 fully warp-reduced values per lane,
+// for the consecutive element indices base..base+NOUT-1 (same column chunk).
+template <int TPR>
+struct ColReduce {
+    static constexpr int NOUT = 16 * TPR / 32;
+    __device__ static __forceinline__ int base_index(int lane)
+    {
+        int b = 0;
+        if (lane & 16) b += 8;
+        if (TPR <= 8 && (lane & 8)) b += 4;
+        if (TPR <= 4 && (lane & 4)) b += 2;
+        if (TPR <= 2 && (lane & 2)) b += 1;
+        return b;
+    }
+    __device__ static __forceinline__ void run(float (&v)[16], int lane, float (&out)[NOUT])
+    {
+        float a8[8];
+        {
+            const bool up = lane & 16;
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const float send = up ? v[i] : v[i + 8];
+                const float keep = up ? v[i + 8] : v[i];
+                a8[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+            }
+        }
+        if (TPR == 8) {
+#pragma unroll
+            for (int i = 0; i < NOUT; i++) out[i] = a8[i];  // unreachable unless NOUT == 4 (see below)
+            return;
+        }
+        float a4[4];
+        {
+            const bool up = lane & 8;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float send = up ? a8[i] : a8[i + 4];
+                const float keep = up ? a8[i + 4] : a8[i];
+                a4[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+            }
+        }
+        float a2[2];
+        {
+            const bool up = lane & 4;
+#pragma unroll
+            for (int i = 0; i < 2; i++) {
+                const float send = up ? a4[i] : a4[i + 2];
+                const float keep = up ? a4[i + 2] : a4[i];
+                a2[i] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+            }
+        }
+        if (TPR == 4) {
+            out[0] = a2[0];
+            if (NOUT > 1) out[NOUT - 1] = a2[1];
+            return;
+        }
+        {   // TPR == 2
+            const bool up = lane & 2;
+            const float send = up ? a2[0] : a2[1];
+            const float keep = up ? a2[1] : a2[0];
+            out[0] = keep + __shfl_xor_sync(0xffffffffu, send, 2);
+        }
+    }
+};
+
+template <int D>
+struct FastGeom {
+    static constexpr int TPR = D / 16;          // threads per row
+    static constexpr int NT = D * TPR;          // threads per CTA
+    static constexpr int NW = NT / 32;          // warps
+    static constexpr int RPW = 32 / TPR;        // rows per warp
+};
+
+// shared-memory floats
+template <int D>
+constexpr size_t fast_fwd_smem_floats() { return (size_t)3 * 2 * FAST_TT * D + 2 * 3 * FAST_TT + FAST_TT * D; }
+template <int D>
+constexpr size_t fast_bwd_smem_floats()
+{
+    using G = FastGeom<D>;
+    return (size_t)4 * 2 * FAST_TB * D        // k,v,q,dy tiles, double buffered
+         + 2 * 3 * FAST_TB                    // gates
+         + (size_t)FAST_NST * 2 * D * D       // state ring (M,S)
+         + (size_t)2 * G::NW * FAST_TB * D    // dq / dk warp partials
+         + (size_t)FAST_TB * D                // dv staging
+         + (size_t)3 * FAST_TB * G::NT        // per-thread scalar partials
+         + (size_t)FAST_MAX_CHUNK * D;        // errors of the current chunk (frozen rule)
+}
+
+template <int D>
+__device__ __forceinline__ void load_state16(float (&x)[16], const float* __restrict__ src, int r, int cg)
+{
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const float4 t = *reinterpret_cast<const float4*>(src + (size_t)r * D + j * (D / 4) + cg * 4);
+        x[4 * j] = t.x; x[4 * j + 1] = t.y; x[4 * j + 2] = t.z; x[4 * j + 3] = t.w;
+    }
+}
+template <int D>
+__device__ __forceinline__ void store_state16(const float (&x)[16], float* dst, int r, int cg)
+{
+#pragma unroll
+    for (int j = 0; j < 4; j++)
+        *reinterpret_cast<float4*>(dst + (size_t)r * D + j * (D / 4) + cg * 4) =
+            make_float4(x[4 * j], x[4 * j + 1], x[4 * j + 2], x[4 * j + 3]);
+}
+template <int D>
+__device__ __forceinline__ void load_vec16(float (&x)[16], const float* src /*smem row of D*/, int cg)
+{
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const float4 t = *reinterpret_cast<const float4*>(src + j * (D / 4) + cg * 4);
+        x[4 * j] = t.x; x[4 * j + 1] = t.y; x[4 * j + 2] = t.z; x[4 * j + 3] = t.w;
+    }
+}
+
+// Cooperative async copy of ntok*D contiguous floats (16-byte pieces).
+template <int D, int NT>
+__device__ __forceinline__ void tile_async(float* dst, const float* __restrict__ src, int ntok)
+{
+    const int nvec = ntok * (D / 4);
+    for (int i = threadIdx.x; i < nvec; i += NT) cp_async16(dst + 4 * i, src + 4 * i);
+}
+
+// One forward token on register state. Msrc is the matrix the error is taken
+// against (M itself, or the frozen chunk-start copy). Returns e (error or v for Hebbian).
+template <int D, int RULE>
+__device__ __forceinline__ float fast_fwd_token(float (&M)[16], float (&S)[16], const float (&Msrc)[16],
+                                                const float* krow, float vr, float alpha, float theta,
+                                                float eta, int cg)
+{
+    constexpr int TPR = FastGeom<D>::TPR;
+    float kk[16];
+    load_vec16<D>(kk, krow, cg);
+    float e = vr;
+    if (RULE != RULE_HEBBIAN) {
+        float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            p0 += Msrc[4 * j] * kk[4 * j];
+            p1 += Msrc[4 * j + 1] * kk[4 * j + 1];
+            p2 += Msrc[4 * j + 2] * kk[4 * j + 2];
+            p3 += Msrc[4 * j + 3] * kk[4 * j + 3];
+        }
+        const float p = row_allreduce<TPR>((p0 + p1) + (p2 + p3));
+        e = p - vr;
+    }
+    const float r = 1.0f - alpha;
+    const float te = theta * e;
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+        if (RULE == RULE_TITANS) {
+            S[i] = eta * S[i] - te * kk[i];
+            M[i] = r * M[i] + S[i];
+        } else if (RULE == RULE_DELTA) {
+            M[i] = r * M[i] - te * kk[i];
+        } else {
+            M[i] = r * M[i] + e * kk[i];
+        }
+    }
+    return e;
+}
+
+template <int D>
+__device__ __forceinline__ float fast_readout(const float (&M)[16], const float* qrow, int cg)
+{
+    constexpr int TPR = FastGeom<D>::TPR;
+    float qq[16];
+    load_vec16<D>(qq, qrow, cg);
+    float y0 = 0.f, y1 = 0.f, y2 = 0.f, y3 = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        y0 += M[4 * j] * qq[4 * j];
+        y1 += M[4 * j + 1] * qq[4 * j + 1];
+        y2 += M[4 * j + 2] * qq[4 * j + 2];
+        y3 += M[4 * j + 3] * qq[4 * j + 3];
+    }
+    return row_allreduce<TPR>((y0 + y1) + (y2 + y3));
+}
+
+template <int D, int RULE, bool FROZEN>
+__global__ void __launch_bounds__(FastGeom<D>::NT) fast_fwd_kernel(FwdArgs a)
+{
+    using G = FastGeom<D>;
+    constexpr int NT = G::NT, TPR = G::TPR, TT = FAST_TT;
+    extern __shared__ __align__(16) float sm[];
+    float* kt = sm;
+    float* vt = kt + 2 * TT * D;
+    float* qt = vt + 2 * TT * D;
+    float* gt = qt + 2 * TT * D;   // [2][3][TT]
+    float* ys = gt + 2 * 3 * TT;   // [TT][D]
+    const int tid = threadIdx.x, r = tid / TPR, cg = tid % TPR;
+    const size_t dd = (size_t)D * D;
+    const int b = blockIdx.x;
+    const float* k = a.k + (size_t)b * a.in_stride_tok * D;
+    const float* v = a.v + (size_t)b * a.in_stride_tok * D;
+    const float* q = a.q + (size_t)b * a.in_stride_tok * D;
+    const float* alpha = a.alpha + (size_t)b * a.in_stride_tok;
+    const float* theta = (RULE != RULE_HEBBIAN) ? a.theta + (size_t)b * a.in_stride_tok : nullptr;
+    const float* eta = (RULE == RULE_TITANS) ? a.eta + (size_t)b * a.in_stride_tok : nullptr;
+    float* y = a.y + (size_t)b * a.seq_len * D;
+    float* m_out = a.m_out + (size_t)b * a.out_stride;
+    float* s_out = (RULE == RULE_TITANS) ? a.s_out + (size_t)b * a.out_stride : nullptr;
+    const int mode = a.store_mode;
+
+    float M[16], S[16], M0[16];
+    load_state16<D>(M, a.m_init + (size_t)b * a.init_stride, r, cg);
+    if (RULE == RULE_TITANS) load_state16<D>(S, a.s_init + (size_t)b * a.init_stride, r, cg);
+    else {
+#pragma unroll
+        for (int i = 0; i < 16; i++) S[i] = 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < 16; i++) M0[i] = M[i];
+    if (mode == STORE_ALL || mode == STORE_CKPT) {
+        store_state16<D>(M, m_out, r, cg);
+        if (RULE == RULE_TITANS) store_state16<D>(S, s_out, r, cg);
+    }
+
+    const int ntiles = (a.seq_len + TT - 1) / TT;
+    auto prefetch = [&](int tile) {
+        const int t0 = tile * TT;
+        const int ntok = min(TT, a.seq_len - t0);
+        const int buf = tile & 1;
+        tile_async<D, NT>(kt + buf * TT * D, k + (size_t)t0 * D, ntok);
+        tile_async<D, NT>(vt + buf * TT * D, v + (size_t)t0 * D, ntok);
+        tile_async<D, NT>(qt + buf * TT * D, q + (size_t)t0 * D, ntok);
+        if (tid < ntok) {
+            cp_async4(gt + (buf * 3 + 0) * TT + tid, alpha + t0 + tid);
+            if (RULE != RULE_HEBBIAN) cp_async4(gt + (buf * 3 + 1) * TT + tid, theta + t0 + tid);
+            if (RULE == RULE_TITANS) cp_async4(gt + (buf * 3 + 2) * TT + tid, eta + t0 + tid);
+        }
+        cp_async_commit();
+    };
+    int slot = 1;
+    if (ntiles > 0) prefetch(0);
+    for (int tile = 0; tile < ntiles; tile++) {
+        const int t0 = tile * TT;
+        const int ntok = min(TT, a.seq_len - t0);
+        const int buf = tile & 1;
+        if (tile + 1 < ntiles) { prefetch(tile + 1); cp_async_wait<1>(); }
+        else cp_async_wait<0>();
+        __syncthreads();
+        const float* kb = kt + buf * TT * D;
+        const float* vb = vt + buf * TT * D;
+        const float* qb = qt + buf * TT * D;
+        const float* gb = gt + buf * 3 * TT;
+        for (int tl = 0; tl < ntok; tl++) {
+            const int t = t0 + tl;
+            if (mode == STORE_CHUNK && (t % a.interval) == 0) {
+                const size_t off = (size_t)(t / a.interval) * dd;
+                store_state16<D>(M, m_out + off, r, cg);
+                if (RULE == RULE_TITANS) store_state16<D>(S, s_out + off, r, cg);
+                if (FROZEN) {
+#pragma unroll
+                    for (int i = 0; i < 16; i++) M0[i] = M[i];
+                }
+            }
+            const float al = gb[tl];
+            const float th = (RULE != RULE_HEBBIAN) ? gb[TT + tl] : 0.f;
+            const float et = (RULE == RULE_TITANS) ? gb[2 * TT + tl] : 0.f;
+            if (FROZEN) fast_fwd_token<D, RULE>(M, S, M0, kb + tl * D, vb[tl * D + r], al, th, et, cg);
+            else fast_fwd_token<D, RULE>(M, S, M, kb + tl * D, vb[tl * D + r], al, th, et, cg);
+            if (mode == STORE_ALL) {
+                store_state16<D>(M, m_out + (size_t)(t + 1) * dd, r, cg);
+                if (RULE == RULE_TITANS) store_state16<D>(S, s_out + (size_t)(t + 1) * dd, r, cg);
+            } else if (mode == STORE_CKPT && (((t + 1) % a.interval) == 0 || t + 1 == a.seq_len)) {
+                store_state16<D>(M, m_out + (size_t)slot * dd, r, cg);
+                if (RULE == RULE_TITANS) store_state16<D>(S, s_out + (size_t)slot * dd, r, cg);
+                slot++;
+            }
+            const float yv = fast_readout<D>(M, qb + tl * D, cg);
+            if (cg == 0) ys[tl * D + r] = yv;
+        }
+        __syncthreads();
+        {
+            const int nvec = ntok * (D / 4);
+            float4* yd = reinterpret_cast<float4*>(y + (size_t)t0 * D);
+            const float4* ysv = reinterpret_cast<const float4*>(ys);
+            for (int i = tid; i < nvec; i += NT) yd[i] = ysv[i];
+        }
+    }
+    if (mode == STORE_CHUNK) {
+        const size_t off = (size_t)((a.seq_len + a.interval - 1) / a.interval) * dd;
+        store_state16<D>(M, m_out + off, r, cg);
+        if (RULE == RULE_TITANS) store_state16<D>(S, s_out + off, r, cg);
+    } else if (mode == STORE_FINAL) {
+        store_state16<D>(M, m_out, r, cg);
+        if (RULE == RULE_TITANS) store_state16<D>(S, s_out, r, cg);
+    }
+}
+
+// ───────────────────────────── backward ──────────────────────────────────
+// Processes, in reverse, either the token range [t_start,t_end) against a
+// stored trajectory (a.chunk == 0), or every chunk of a.chunk tokens with the
+// chunk trajectory recomputed from its boundary state into scratch (m_rec).
+template <int D, int RULE, bool FROZEN>
+__global__ void __launch_bounds__(FastGeom<D>::NT) fast_bwd_kernel(BwdArgs a)
+{
+    using G = FastGeom<D>;
+    constexpr int NT = G::NT, TPR = G::TPR, NW = G::NW, TB = FAST_TB, NST = FAST_NST;
+    constexpr int NOUT = ColReduce<TPR>::NOUT;
+    extern __shared__ __align__(16) float sm[];
+    float* kt = sm;                                   // [2][TB][D]
+    float* vt = kt + 2 * TB * D;
+    float* qt = vt + 2 * TB * D;
+    float* dyt = qt + 2 * TB * D;
+    float* gt = dyt + 2 * TB * D;                     // [2][3][TB]
+    float* ring = gt + 2 * 3 * TB;                    // [NST][2][D*D]
+    float* pq = ring + (size_t)NST * 2 * D * D;       // [NW][TB][D]
+    float* pk = pq + (size_t)NW * TB * D;             // [NW][TB][D]
+    float* dvs = pk + (size_t)NW * TB * D;            // [TB][D]
+    float* scp = dvs + TB * D;                        // [3][TB][NT]
+    float* es = scp + 3 * TB * NT;                    // [FAST_MAX_CHUNK][D]
+
+    const int tid = threadIdx.x, r = tid / TPR, cg = tid % TPR;
+    const int lane = tid & 31, warp = tid >> 5;
+    const size_t dd = (size_t)D * D;
+    const int b = blockIdx.x;
+    const size_t so = (size_t)b * a.seq_len * D, go = (size_t)b * a.seq_len;
+    const float* k = a.k + so; const float* v = a.v + so; const float* q = a.q + so;
+    const float* dy = a.d_y + so;
+    float* dk = a.d_k + so; float* dv = a.d_v + so; float* dq = a.d_q + so;
+    const float* alpha = a.alpha + go;
+    const float* theta = (RULE != RULE_HEBBIAN) ? a.theta + go : nullptr;
+    const float* eta = (RULE == RULE_TITANS) ? a.eta + go : nullptr;
+    float* dalpha = a.d_alpha + go;
+    float* dtheta = (RULE != RULE_HEBBIAN) ? a.d_theta + go : nullptr;
+    float* deta = (RULE == RULE_TITANS) ? a.d_eta + go : nullptr;
+    const float* mtraj = a.m_traj + (size_t)b * a.traj_stride;
+    const float* straj = (RULE == RULE_TITANS) ? a.s_traj + (size_t)b * a.traj_stride : nullptr;
+    const bool recompute = a.chunk > 0;
+    float* mrec = recompute ? a.m_rec + (size_t)b * (a.chunk + 1) * dd : nullptr;
+    float* srec = (recompute && RULE == RULE_TITANS) ? a.s_rec + (size_t)b * (a.chunk + 1) * dd : nullptr;
+
+    float dM[16], dS[16], dM0[16], M0[16], Mn[16];
+    if (a.d_m_seed) load_state16<D>(dM, a.d_m_seed + (size_t)b * dd, r, cg);
+    else {
+#pragma unroll
+        for (int i = 0; i < 16; i++) dM[i] = 0.f;
+    }
+    if (RULE == RULE_TITANS && a.d_s_seed) load_state16<D>(dS, a.d_s_seed + (size_t)b * dd, r, cg);
+    else {
+#pragma unroll
+        for (int i = 0; i < 16; i++) dS[i] = 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < 16; i++) { dM0[i] = 0.f; M0[i] = 0.f; }
+
+    const int nchunks = recompute ? (a.seq_len + a.chunk - 1) / a.chunk : 1;
+    for (int c = nchunks - 1; c >= 0; c--) {
+        const int t0 = recompute ? c * a.chunk : a.t_start;
+        const int t1 = recompute ? min(t0 + a.chunk, a.seq_len) : a.t_end;
+        const int len = t1 - t0;
+        const float* mt_base;   // slot j = state before token t0 + j
+        const float* st_base;
+        if (recompute) {
+            // ── recompute the chunk trajectory into scratch (slots 0..len) ──
+            float Mc[16], Sc[16];
+            load_state16<D>(Mc, mtraj + (size_t)c * dd, r, cg);
+            if (RULE == RULE_TITANS) load_state16<D>(Sc, straj + (size_t)c * dd, r, cg);
+            else {
+#pragma unroll
+                for (int i = 0; i < 16; i++) Sc[i] = 0.f;
+            }
+#pragma unroll
+            for (int i = 0; i < 16; i++) M0[i] = Mc[i];
+            store_state16<D>(Mc, mrec, r, cg);
+            if (RULE == RULE_TITANS) store_state16<D>(Sc, srec, r, cg);
+            const int ntl = (len + TB - 1) / TB;
+            for (int tile = 0; tile < ntl; tile++) {
+                const int tt0 = t0 + tile * TB;
+                const int ntok = min(TB, t1 - tt0);
+                __syncthreads();   // previous users of buffer 0 are done
+                tile_async<D, NT>(kt, k + (size_t)tt0 * D, ntok);
+                tile_async<D, NT>(vt, v + (size_t)tt0 * D, ntok);
+                cp_async_commit();
+                cp_async_wait<0>();
+                __syncthreads();
+                for (int tl = 0; tl < ntok; tl++) {
+                    const int t = tt0 + tl;
+                    const float al = alpha[t];
+                    const float th = (RULE != RULE_HEBBIAN) ? theta[t] : 0.f;
+                    const float et = (RULE == RULE_TITANS) ? eta[t] : 0.f;
+                    float e;
+                    if (FROZEN) e = fast_fwd_token<D, RULE>(Mc, Sc, M0, kt + tl * D, vt[tl * D + r], al, th, et, cg);
+                    else e = fast_fwd_token<D, RULE>(Mc, Sc, Mc, kt + tl * D, vt[tl * D + r], al, th, et, cg);
+                    if (FROZEN && cg == 0) es[(t - t0) * D + r] = e;
+                    store_state16<D>(Mc, mrec + (size_t)(t - t0 + 1) * dd, r, cg);
+                    if (RULE == RULE_TITANS) store_state16<D>(Sc, srec + (size_t)(t - t0 + 1) * dd, r, cg);
+                }
+            }
+            __syncthreads();   // es visible; staging buffers free
+            mt_base = mrec; st_base = srec;
+#pragma unroll
+            for (int i = 0; i < 16; i++) { Mn[i] = Mc[i]; dM0[i] = 0.f; }
+        } else {
+            mt_base = mtraj; st_base = straj;
+            load_state16<D>(Mn, mt_base + (size_t)len * dd, r, cg);
+        }
+
+        // ── reverse pass over the chunk, tile by tile ──
+        const int ntl = (len + TB - 1) / TB;
+        auto prefetch_tile = [&](int tile) {
+            const int tt0 = t0 + tile * TB;
+            const int ntok = min(TB, t1 - tt0);
+            const int buf = tile & 1;
+            tile_async<D, NT>(kt + buf * TB * D, k + (size_t)tt0 * D, ntok);
+            tile_async<D, NT>(vt + buf * TB * D, v + (size_t)tt0 * D, ntok);
+            tile_async<D, NT>(qt + buf * TB * D, q + (size_t)tt0 * D, ntok);
+            tile_async<D, NT>(dyt + buf * TB * D, dy + (size_t)tt0 * D, ntok);
+            if (tid < ntok) {
+                cp_async4(gt + (buf * 3 + 0) * TB + tid, alpha + tt0 + tid);
+                if (RULE != RULE_HEBBIAN) cp_async4(gt + (buf * 3 + 1) * TB + tid, theta + tt0 + tid);
+                if (RULE == RULE_TITANS) cp_async4(gt + (buf * 3 + 2) * TB + tid, eta + tt0 + tid);
+            }
+        };
+        // Thread-private async fetch of state slot j (state before token t0+j).
+        auto prefetch_state = [&](int j) {
+            if (j >= 0) {
+                // ring layout is thread-major (piece jj of thread tid at jj*NT*4 + tid*4):
+                // the data is private to the thread, so any layout works and this one
+                // makes the 16-byte shared loads conflict-free.
+                float* dst = ring + (size_t)(j % NST) * 2 * dd;
+#pragma unroll
+                for (int jj = 0; jj < 4; jj++) {
+                    const size_t o = (size_t)r * D + jj * (D / 4) + cg * 4;
+                    const int so_ = jj * NT * 4 + tid * 4;
+                    cp_async16(dst + so_, mt_base + (size_t)j * dd + o);
+                    if (RULE == RULE_TITANS) cp_async16(dst + dd + so_, st_base + (size_t)j * dd + o);
+                }
+            }
+        };
+        if (len > 0) {
+            // prologue: last tile + the first NST-1 states, one commit group each
+            prefetch_tile(ntl - 1);
+            prefetch_state(len - 1);
+            cp_async_commit();
+#pragma unroll
+            for (int s = 1; s < NST - 1; s++) { prefetch_state(len - 1 - s); cp_async_commit(); }
+        }
+        for (int tile = ntl - 1; tile >= 0; tile--) {
+            const int tt0 = t0 + tile * TB;
+            const int ntok = min(TB, t1 - tt0);
+            const int buf = tile & 1;
+            const float* kb = kt + buf * TB * D;
+            const float* vb = vt + buf * TB * D;
+            const float* qb = qt + buf * TB * D;
+            const float* dyb = dyt + buf * TB * D;
+            const float* gb = gt + buf * 3 * TB;
+            for (int tl = ntok - 1; tl >= 0; tl--) {
+                const int j = tt0 + tl - t0;   // slot of M_t
+                // keep NST-1 state groups in flight; fold the next tile's streams into this group
+                prefetch_state(j - (NST - 1));
+                if (tl == ntok - 1 && tile > 0) prefetch_tile(tile - 1);
+                cp_async_commit();
+                // This tile's streams were committed at the first token of the tile processed
+                // just before (tile+1). They are older than the NST-1 newest groups unless that
+                // tile was shorter than the pipeline depth (only the sequence tail can be).
+                if (tl == ntok - 1 && tile < ntl - 1 && (t1 - (tt0 + TB)) < NST) cp_async_wait<0>();
+                else cp_async_wait<NST - 1>();
+                if (tl == ntok - 1) __syncthreads();   // tile streams (other threads' copies) visible
+                const float* ms = ring + (size_t)(j % NST) * 2 * dd;
+                float Mt[16], St[16], kk[16], qq[16];
+#pragma unroll
+                for (int jj = 0; jj < 4; jj++) {
+                    const float4 t4 = *reinterpret_cast<const float4*>(ms + jj * NT * 4 + tid * 4);
+                    Mt[4 * jj] = t4.x; Mt[4 * jj + 1] = t4.y; Mt[4 * jj + 2] = t4.z; Mt[4 * jj + 3] = t4.w;
+                    if (RULE == RULE_TITANS) {
+                        const float4 s4 = *reinterpret_cast<const float4*>(ms + dd + jj * NT * 4 + tid * 4);
+                        St[4 * jj] = s4.x; St[4 * jj + 1] = s4.y; St[4 * jj + 2] = s4.z; St[4 * jj + 3] = s4.w;
+                    }
+                }
+                load_vec16<D>(kk, kb + tl * D, cg);
+                load_vec16<D>(qq, qb + tl * D, cg);
+                const float dyr = dyb[tl * D + r];
+                const float vr = vb[tl * D + r];
+                const float al = gb[tl];
+                const float th = (RULE != RULE_HEBBIAN) ? gb[TB + tl] : 0.f;
+                const float et = (RULE == RULE_TITANS) ? gb[2 * TB + tl] : 0.f;
+
+                float p = 0.f, u = 0.f, pa = 0.f, pe = 0.f;
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    dM[i] += dyr * qq[i];
+                    float g = dM[i];
+                    if (RULE == RULE_TITANS) { dS[i] += dM[i]; g = dS[i]; pe += St[i] * dS[i]; }
+                    pa += Mt[i] * dM[i];
+                    if (RULE != RULE_HEBBIAN && !FROZEN) p += Mt[i] * kk[i];
+                    u += g * kk[i];
+                }
+                u = row_allreduce<TPR>(u);
+                float e = 0.f;
+                if (RULE != RULE_HEBBIAN) {
+                    if (FROZEN) e = es[j * D + r];
+                    else e = row_allreduce<TPR>(p) - vr;
+                }
+                const float de = -th * u;
+                // per-thread scalar partials (summed over the CTA at tile end)
+                scp[(0 * TB + tl) * NT + tid] = pa;
+                scp[(1 * TB + tl) * NT + tid] = (RULE != RULE_HEBBIAN && cg == 0) ? e * u : 0.f;
+                scp[(2 * TB + tl) * NT + tid] = pe;
+                if (cg == 0) dvs[tl * D + r] = (RULE == RULE_HEBBIAN) ? u : th * u;
+
+                // column partials: d_q = M_{t+1}^T dy ; d_k = -theta G^T e + Mk^T de (Hebbian: dM^T v)
+                float cq[16], ck[16];
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    cq[i] = Mn[i] * dyr;
+                    if (RULE == RULE_HEBBIAN) ck[i] = dM[i] * vr;
+                    else {
+                        const float g = (RULE == RULE_TITANS) ? dS[i] : dM[i];
+                        ck[i] = (-th * g) * e + (FROZEN ? M0[i] : Mt[i]) * de;
+                    }
+                }
+                float oq[NOUT], ok[NOUT];
+                ColReduce<TPR>::run(cq, lane, oq);
+                ColReduce<TPR>::run(ck, lane, ok);
+                {
+                    const int bi = ColReduce<TPR>::base_index(lane);
+                    const int col = col_of<D>(bi, cg);
+                    float* dq_p = pq + ((size_t)warp * TB + tl) * D + col;
+                    float* dk_p = pk + ((size_t)warp * TB + tl) * D + col;
+#pragma unroll
+                    for (int i = 0; i < NOUT; i++) { dq_p[i] = oq[i]; dk_p[i] = ok[i]; }
+                }
+                // propagate to the previous token
+                const float rr = 1.0f - al;
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    if (RULE == RULE_TITANS) dS[i] *= et;
+                    float dm = rr * dM[i];
+                    if (RULE != RULE_HEBBIAN) {
+                        const float o = de * kk[i];
+                        if (FROZEN) dM0[i] += o; else dm += o;
+                    }
+                    dM[i] = dm;
+                    Mn[i] = Mt[i];
+                }
+            }
+            __syncthreads();
+            // ── tile epilogue: cross-warp sums and coalesced stores ──
+            for (int i = tid; i < ntok * D; i += NT) {
+                float sq = 0.f, sk = 0.f;
+#pragma unroll
+                for (int w = 0; w < NW; w++) { sq += pq[(size_t)w * TB * D + i]; sk += pk[(size_t)w * TB * D + i]; }
+                dq[(size_t)tt0 * D + i] = sq;
+                dk[(size_t)tt0 * D + i] = sk;
+                dv[(size_t)tt0 * D + i] = dvs[i];
+            }
+            for (int job = warp; job < 3 * ntok; job += NW) {
+                const int which = job / ntok, tl = job - which * ntok;
+                if ((which == 1 && RULE == RULE_HEBBIAN) || (which == 2 && RULE != RULE_TITANS)) continue;
+                float s = 0.f;
+                for (int i = lane; i < NT; i += 32) s += scp[(which * TB + tl) * NT + i];
+                s = warp_sum(s);
+                if (lane == 0) {
+                    if (which == 0) dalpha[tt0 + tl] = -s;
+                    else if (which == 1) dtheta[tt0 + tl] = -s;
+                    else deta[tt0 + tl] = s;
+                }
+            }
+            // the next tile's first-token barrier orders these reads before pq/pk/scp are rewritten
+        }
+        if (FROZEN) {
+#pragma unroll
+            for (int i = 0; i < 16; i++) dM[i] += dM0[i];
+        }
+        __syncthreads();
+    }
+
+    if (a.atomic_out) {
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            const size_t o = (size_t)r * D + col_of<D>(i, cg);
+            atomicAdd(&a.d_m_out[o], dM[i]);
+            if (RULE == RULE_TITANS) atomicAdd(&a.d_s_out[o], dS[i]);
+        }
+    } else {
+        store_state16<D>(dM, a.d_m_out + (size_t)b * dd, r, cg);
+        if (RULE == RULE_TITANS) store_state16<D>(dS, a.d_s_out + (size_t)b * dd, r, cg);
+    }
+}
+
+// ───────────────────────────── host dispatch ─────────────────────────────
+inline bool aligned16(const void* p) { return (((uintptr_t)p) & 15) == 0; }
+
+inline bool fast_common_ok(int d, float clip, float mmax)
+{
+    return (d == 64 || d == 32) && !(clip > 0.0f) && !m_norm_enabled(mmax);
+}
+
+template <int D, int RULE>
+static bool fast_fwd_launch(const FwdArgs& a, cudaStream_t st)
+{
+    const size_t smem = fast_fwd_smem_floats<D>() * sizeof(float);
+    if (a.frozen) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(fast_fwd_kernel<D, RULE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        fast_fwd_kernel<D, RULE, true><<<a.batch, FastGeom<D>::NT, smem, st>>>(a);
+    } else {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(fast_fwd_kernel<D, RULE, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        fast_fwd_kernel<D, RULE, false><<<a.batch, FastGeom<D>::NT, smem, st>>>(a);
+    }
+    return true;
+}
+
+// Returns true when a fast kernel was launched (caller checks the launch).
+static bool fast_forward(int rule, const FwdArgs& a, cudaStream_t st)
+{
+    if (!fast_common_ok(a.d, a.error_clip, a.m_norm_max)) return false;
+    if (a.frozen && rule == RULE_HEBBIAN) return false;
+    const bool al = aligned16(a.k) && aligned16(a.v) && aligned16(a.q) && aligned16(a.y) &&
+                    aligned16(a.m_init) && aligned16(a.m_out) &&
+                    (rule != RULE_TITANS || (aligned16(a.s_init) && aligned16(a.s_out))) &&
+                    (a.init_stride % 4 == 0) && (a.out_stride % 4 == 0);
+    if (!al) return false;
+    if (a.d == 64) {
+        if (rule == RULE_TITANS) return fast_fwd_launch<64, RULE_TITANS>(a, st);
+        if (rule == RULE_DELTA) return fast_fwd_launch<64, RULE_DELTA>(a, st);
+        if (rule == RULE_HEBBIAN) return fast_fwd_launch<64, RULE_HEBBIAN>(a, st);
+    } else {
+        if (rule == RULE_TITANS) return fast_fwd_launch<32, RULE_TITANS>(a, st);
+        if (rule == RULE_DELTA) return fast_fwd_launch<32, RULE_DELTA>(a, st);
+        if (rule == RULE_HEBBIAN) return fast_fwd_launch<32, RULE_HEBBIAN>(a, st);
+    }
+    return false;
+}
+
+template <int D, int RULE>
+static bool fast_bwd_launch(const BwdArgs& a, cudaStream_t st)
+{
+    const size_t smem = fast_bwd_smem_floats<D>() * sizeof(float);
+    if (a.frozen) {
+        cudaFuncSetAttribute(fast_bwd_kernel<D, RULE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        fast_bwd_kernel<D, RULE, true><<<a.batch, FastGeom<D>::NT, smem, st>>>(a);
+    } else {
+        cudaFuncSetAttribute(fast_bwd_kernel<D, RULE, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        fast_bwd_kernel<D, RULE, false><<<a.batch, FastGeom<D>::NT, smem, st>>>(a);
+    }
+    return true;
+}
+
+static bool fast_backward(int rule, BwdArgs& a, cudaStream_t st)
+{
+    if (!fast_common_ok(a.d, a.error_clip, a.m_norm_max)) return false;
+    if (a.frozen && (rule == RULE_HEBBIAN || a.chunk > FAST_MAX_CHUNK)) return false;
+    if (a.t_end <= a.t_start && a.chunk <= 0) return false;
+    const bool al = aligned16(a.k) && aligned16(a.v) && aligned16(a.q) && aligned16(a.d_y) &&
+                    aligned16(a.d_k) && aligned16(a.d_v) && aligned16(a.d_q) && aligned16(a.m_traj) &&
+                    (rule != RULE_TITANS || aligned16(a.s_traj)) && (a.traj_stride % 4 == 0) &&
+                    aligned16(a.d_m_out) && (rule != RULE_TITANS || aligned16(a.d_s_out)) &&
+                    (a.d_m_seed == nullptr || aligned16(a.d_m_seed)) &&
+                    (a.d_s_seed == nullptr || aligned16(a.d_s_seed));
+    if (!al) return false;
+    if (a.chunk > 0) {
+        const size_t dd = (size_t)a.d * a.d;
+        const size_t per = (((size_t)a.batch * (a.chunk + 1) * dd * sizeof(float)) + 255) & ~(size_t)255;
+        char* ws = (char*)workspace(per * 2);
+        if (!ws) return false;
+        a.m_rec = (float*)ws;
+        a.s_rec = (float*)(ws + per);
+    }
+    if (a.d == 64) {
+        if (rule == RULE_TITANS) return fast_bwd_launch<64, RULE_TITANS>(a, st);
+        if (rule == RULE_DELTA) return fast_bwd_launch<64, RULE_DELTA>(a, st);
+        if (rule == RULE_HEBBIAN) return fast_bwd_launch<64, RULE_HEBBIAN>(a, st);
+    } else {
+        if (rule == RULE_TITANS) return fast_bwd_launch<32, RULE_TITANS>(a, st);
+        if (rule == RULE_DELTA) return fast_bwd_launch<32, RULE_DELTA>(a, st);
+        if (rule == RULE_HEBBIAN) return fast_bwd_launch<32, RULE_HEBBIAN>(a, st);
+    }
+    return false;
+}
+
+}  // namespace nlh

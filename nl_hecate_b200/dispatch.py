@@ -1,0 +1,335 @@
+"""Host-side mirror of the reference's kernel dispatch layer for the hot path.
+
+``*_dd`` functions take device tensors and call the C ABI directly; they are
+the counterpart of the ``*_dd`` wrappers in core/src/dispatch.rs:2093-3404.
+``*_dispatch`` functions take host (numpy) arrays, copy them to the device, run
+the kernel and copy the results back, like the ``*_dispatch`` functions of
+core/src/dispatch.rs:330-1213 (``cuda_titans_forward`` etc.).
+
+PyTorch is used only to own device memory and the stream. Every entry raises
+if the CUDA library is missing or records an error: there is no CPU path here.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+import torch
+
+from . import ffi
+
+RULE_DELTA, RULE_TITANS, RULE_HEBBIAN = 0, 1, 2
+_PROTOS = None
+
+
+def _protos():
+    global _PROTOS
+    if _PROTOS is None:
+        _PROTOS = ffi.parse_header()
+    return _PROTOS
+
+
+def bind_stream(stream: torch.cuda.Stream | None = None) -> None:
+    """Point the library at a torch stream (default: torch's current stream)."""
+    s = stream if stream is not None else torch.cuda.current_stream()
+    ffi.lib().nlh_set_stream(C.c_void_p(s.cuda_stream))
+
+
+def call(name: str, **kw):
+    """Call a C-ABI entry by name with keyword arguments named as in include/nlh_ffi.h.
+
+    Tensors are passed as device pointers (they must be contiguous CUDA tensors),
+    None as NULL. Status-returning entries are checked; void entries are checked
+    through the library's recorded status.
+    """
+    ret, argtypes, argnames = _protos()[name]
+    missing = [a for a in argnames if a not in kw]
+    extra = [a for a in kw if a not in argnames]
+    if missing or extra:
+        raise TypeError(f"{name}: missing {missing}, unexpected {extra}")
+    args = []
+    for an, at in zip(argnames, argtypes):
+        v = kw[an]
+        if at is C.c_void_p:
+            if v is None:
+                args.append(C.c_void_p(0))
+            elif isinstance(v, torch.Tensor):
+                if not v.is_cuda or not v.is_contiguous():
+                    raise ValueError(f"{name}.{an}: need a contiguous CUDA tensor")
+                args.append(C.c_void_p(v.data_ptr()))
+            elif isinstance(v, int):
+                args.append(C.c_void_p(v))
+            else:
+                args.append(v)
+        else:
+            args.append(at(v))
+    fn = getattr(ffi.lib(), name)
+    bind_stream()
+    rc = fn(*args)
+    if ret is C.c_int32:
+        ffi.check(rc, name)
+    elif ret is C.c_uint32:
+        if rc != 0:
+            raise RuntimeError(f"{name}: cudaError {rc}")
+    elif ret is None:
+        ffi.check_void(name)
+    return rc
+
+
+def _f32(*shape, device):
+    return torch.empty(*shape, dtype=torch.float32, device=device)
+
+
+def checkpoint_count(seq_len: int, c: int) -> int:
+    """Slots written by the checkpointed forwards (core/src/gpu_forward.rs:2885-2900)."""
+    assert c > 0
+    return 1 + sum(1 for t in range(seq_len) if (t + 1) % c == 0 or t + 1 == seq_len)
+
+
+# ── memory rules, device tensors ───────────────────────────────────────────
+# Shapes: k,v,q,d_y [N,S,d]; gates [N,S]; m0,s0 [N,d*d]; states [N,(S+1),d*d].
+
+def titans_forward_dd(k, v, q, alpha, theta, eta, m0, s0, error_clip=0.0, m_norm_max=0.0):
+    n, s, d = k.shape
+    ms = _f32(n, s + 1, d * d, device=k.device)
+    ss = _f32(n, s + 1, d * d, device=k.device)
+    y = _f32(n, s, d, device=k.device)
+    call("titans_forward_f32_cuda", k_mem=k, v_mem=v, q_mem=q, alpha=alpha, theta=theta, eta=eta,
+         m_initial=m0, s_initial=s0, m_states=ms, s_states=ss, y=y, seq_len=s, d=d, batch_size=n,
+         input_stride=s, m_stride=d * d, error_clip=error_clip, m_norm_max=m_norm_max)
+    return ms, ss, y
+
+
+def titans_backward_dd(k, v, q, alpha, theta, eta, ms, ss, d_y, error_clip=0.0):
+    n, s, d = k.shape
+    dk, dv, dq = (torch.zeros_like(k) for _ in range(3))
+    da, dt, de = (torch.zeros_like(alpha) for _ in range(3))
+    dm0 = torch.zeros(d * d, dtype=torch.float32, device=k.device)
+    ds0 = torch.zeros(d * d, dtype=torch.float32, device=k.device)
+    call("titans_backward_f32_cuda", k_mem=k, v_mem=v, q_mem=q, alpha=alpha, theta=theta, eta=eta,
+         m_states=ms, s_states=ss, d_y=d_y, d_k_mem=dk, d_v_mem=dv, d_q_mem=dq, d_alpha=da,
+         d_theta=dt, d_eta=de, d_m_initial=dm0, d_s_initial=ds0, seq_len=s, d=d, batch_size=n,
+         error_clip=error_clip)
+    return dict(d_k=dk, d_v=dv, d_q=dq, d_alpha=da, d_theta=dt, d_eta=de, d_m_initial=dm0,
+                d_s_initial=ds0)
+
+
+def delta_forward_dd(k, v, q, alpha, theta, m0, error_clip=0.0, m_norm_max=0.0, dgd=False):
+    n, s, d = k.shape
+    ms = _f32(n, s + 1, d * d, device=k.device)
+    y = _f32(n, s, d, device=k.device)
+    if dgd:
+        call("dgd_forward_f32_cuda", k_mem=k, v_mem=v, q_mem=q, alpha=alpha, theta=theta,
+             m_initial=m0, m_states=ms, y=y, seq_len=s, d=d, batch_size=n, input_stride=s,
+             m_stride=d * d, error_clip=error_clip)
+    else:
+        call("delta_forward_f32_cuda", k_mem=k, v_mem=v, q_mem=q, alpha=alpha, theta=theta,
+             m_initial=m0, m_states=ms, y=y, seq_len=s, d=d, batch_size=n, input_stride=s,
+             m_stride=d * d, error_clip=error_clip, m_norm_max=m_norm_max)
+    return ms, y
+
+
+def delta_backward_dd(k, v, q, alpha, theta, ms, d_y, error_clip=0.0, dgd=False):
+    n, s, d = k.shape
+    dk, dv, dq = (torch.zeros_like(k) for _ in range(3))
+    da, dt = (torch.zeros_like(alpha) for _ in range(2))
+    dm0 = torch.zeros(d * d, dtype=torch.float32, device=k.device)
+    if dgd:
+        assert n == 1, "dgd_backward_f32_cuda has no batch argument"
+        call("dgd_backward_f32_cuda", k_mem=k, v_mem=v, q_mem=q, alpha=alpha, theta=theta,
+             m_states=ms, d_y=d_y, d_k_mem=dk, d_v_mem=dv, d_q_mem=dq, d_alpha=da, d_theta=dt,
+             d_m_initial=dm0, seq_len=s, d=d, error_clip=error_clip)
+    else:
+        call("delta_backward_f32_cuda", k_mem=k, v_mem=v, q_mem=q, alpha=alpha, theta=theta,
+             m_states=ms, d_y=d_y, d_k_mem=dk, d_v_mem=dv, d_q_mem=dq, d_alpha=da, d_theta=dt,
+             d_m_initial=dm0, seq_len=s, d=d, batch_size=n, error_clip=error_clip)
+    return dict(d_k=dk, d_v=dv, d_q=dq, d_alpha=da, d_theta=dt, d_m_initial=dm0)
+
+
+def hebbian_forward_dd(k, v, q, alpha, m0):
+    n, s, d = k.shape
+    ms = _f32(n, s + 1, d * d, device=k.device)
+    y = _f32(n, s, d, device=k.device)
+    call("hebbian_forward_f32_cuda", k_mem=k, v_mem=v, q_mem=q, alpha=alpha, m_initial=m0,
+         m_states=ms, y=y, seq_len=s, d=d, batch_size=n, input_stride=s, m_stride=d * d)
+    return ms, y
+
+
+def hebbian_backward_dd(k, v, q, alpha, ms, d_y):
+    n, s, d = k.shape
+    assert n == 1, "hebbian_backward_f32_cuda has no batch argument"
+    dk, dv, dq = (torch.zeros_like(k) for _ in range(3))
+    da = torch.zeros_like(alpha)
+    dm0 = torch.zeros(d * d, dtype=torch.float32, device=k.device)
+    call("hebbian_backward_f32_cuda", k_mem=k, v_mem=v, q_mem=q, alpha=alpha, m_states=ms, d_y=d_y,
+         d_k_mem=dk, d_v_mem=dv, d_q_mem=dq, d_alpha=da, d_m_initial=dm0, seq_len=s, d=d)
+    return dict(d_k=dk, d_v=dv, d_q=dq, d_alpha=da, d_m_initial=dm0)
+
+
+def titans_chunkwise_forward_dd(k, v, q, alpha, theta, eta, m0, s0, chunk, error_clip=0.0,
+                                m_norm_max=0.0):
+    n, s, d = k.shape
+    nc = (s + chunk - 1) // chunk
+    mc = _f32(n, nc + 1, d * d, device=k.device)
+    sc = _f32(n, nc + 1, d * d, device=k.device)
+    y = _f32(n, s, d, device=k.device)
+    call("titans_chunkwise_forward_f32_cuda", k_mem=k, v_mem=v, q_mem=q, alpha=alpha, theta=theta,
+         eta=eta, m_initial=m0, s_initial=s0, m_chunk_states=mc, s_chunk_states=sc, y=y,
+         seq_len=s, d=d, batch_size=n, chunk_size=chunk, error_clip=error_clip,
+         m_norm_max=m_norm_max)
+    return mc, sc, y
+
+
+def titans_chunkwise_backward_dd(k, v, q, alpha, theta, eta, mc, sc, d_y, chunk, error_clip=0.0,
+                                 m_norm_max=0.0):
+    n, s, d = k.shape
+    dk, dv, dq = (torch.zeros_like(k) for _ in range(3))
+    da, dt, de = (torch.zeros_like(alpha) for _ in range(3))
+    dm0 = torch.zeros(d * d, dtype=torch.float32, device=k.device)
+    ds0 = torch.zeros(d * d, dtype=torch.float32, device=k.device)
+    call("titans_chunkwise_backward_f32_cuda", k_mem=k, v_mem=v, q_mem=q, alpha=alpha, theta=theta,
+         eta=eta, m_chunk_states=mc, s_chunk_states=sc, d_y=d_y, d_k_mem=dk, d_v_mem=dv,
+         d_q_mem=dq, d_alpha=da, d_theta=dt, d_eta=de, d_m_initial=dm0, d_s_initial=ds0,
+         seq_len=s, d=d, batch_size=n, chunk_size=chunk, error_clip=error_clip,
+         m_norm_max=m_norm_max)
+    return dict(d_k=dk, d_v=dv, d_q=dq, d_alpha=da, d_theta=dt, d_eta=de, d_m_initial=dm0,
+                d_s_initial=ds0)
+
+
+def delta_chunkwise_forward_dd(k, v, q, alpha, theta, m0, chunk, error_clip=0.0, m_norm_max=0.0):
+    n, s, d = k.shape
+    nc = (s + chunk - 1) // chunk
+    mc = _f32(n, nc + 1, d * d, device=k.device)
+    y = _f32(n, s, d, device=k.device)
+    call("delta_chunkwise_forward_f32_cuda", k_mem=k, v_mem=v, q_mem=q, alpha=alpha, theta=theta,
+         m_initial=m0, m_chunk_states=mc, y=y, seq_len=s, d=d, batch_size=n, chunk_size=chunk,
+         error_clip=error_clip, m_norm_max=m_norm_max)
+    return mc, y
+
+
+def delta_chunkwise_backward_dd(k, v, q, alpha, theta, mc, d_y, chunk, error_clip=0.0,
+                                m_norm_max=0.0):
+    n, s, d = k.shape
+    dk, dv, dq = (torch.zeros_like(k) for _ in range(3))
+    da, dt = (torch.zeros_like(alpha) for _ in range(2))
+    dm0 = torch.zeros(d * d, dtype=torch.float32, device=k.device)
+    call("delta_chunkwise_backward_f32_cuda", k_mem=k, v_mem=v, q_mem=q, alpha=alpha, theta=theta,
+         m_chunk_states=mc, d_y=d_y, d_k_mem=dk, d_v_mem=dv, d_q_mem=dq, d_alpha=da, d_theta=dt,
+         d_m_initial=dm0, seq_len=s, d=d, batch_size=n, chunk_size=chunk, error_clip=error_clip,
+         m_norm_max=m_norm_max)
+    return dict(d_k=dk, d_v=dv, d_q=dq, d_alpha=da, d_theta=dt, d_m_initial=dm0)
+
+
+# ── recompute-style training pair (additive API) ───────────────────────────
+def rule_forward(rule, k, v, q, alpha, theta, eta, m0, s0, interval, chunk=0, error_clip=0.0,
+                 m_norm_max=0.0):
+    n, s, d = k.shape
+    slots = (s + interval - 1) // interval + 1
+    mc = _f32(n, slots, d * d, device=k.device)
+    sc = _f32(n, slots, d * d, device=k.device) if rule == RULE_TITANS else None
+    y = _f32(n, s, d, device=k.device)
+    call("nlh_rule_forward", rule=rule, k_mem=k, v_mem=v, q_mem=q, alpha=alpha, theta=theta,
+         eta=eta, m_initial=m0, s_initial=s0, m_ckpt=mc, s_ckpt=sc, y=y, seq_len=s, d=d,
+         batch_size=n, interval=interval, chunk_size=chunk, error_clip=error_clip,
+         m_norm_max=m_norm_max)
+    return mc, sc, y
+
+
+def rule_backward(rule, k, v, q, alpha, theta, eta, mc, sc, d_y, interval, chunk=0, error_clip=0.0,
+                  m_norm_max=0.0):
+    n, s, d = k.shape
+    dk, dv, dq = (torch.empty_like(k) for _ in range(3))
+    da = torch.empty_like(alpha)
+    dt = torch.empty_like(alpha) if rule != RULE_HEBBIAN else None
+    de = torch.empty_like(alpha) if rule == RULE_TITANS else None
+    dm0 = _f32(n, d * d, device=k.device)
+    ds0 = _f32(n, d * d, device=k.device) if rule == RULE_TITANS else None
+    call("nlh_rule_backward", rule=rule, k_mem=k, v_mem=v, q_mem=q, alpha=alpha, theta=theta,
+         eta=eta, m_ckpt=mc, s_ckpt=sc, d_y=d_y, d_k_mem=dk, d_v_mem=dv, d_q_mem=dq, d_alpha=da,
+         d_theta=dt, d_eta=de, d_m_initial=dm0, d_s_initial=ds0, seq_len=s, d=d, batch_size=n,
+         interval=interval, chunk_size=chunk, error_clip=error_clip, m_norm_max=m_norm_max)
+    return dict(d_k=dk, d_v=dv, d_q=dq, d_alpha=da, d_theta=dt, d_eta=de, d_m_initial=dm0,
+                d_s_initial=ds0)
+
+
+# ── SWA ────────────────────────────────────────────────────────────────────
+# q,k,v,out: [B,S,H*hd] bf16; attn_weights [B,H,S,n_p+W] bf16; grads f32.
+
+def swa_forward_dd(q, k, v, num_heads, head_dim, window, n_persistent=0, want_weights=True):
+    b, s, _ = q.shape
+    out = torch.empty_like(q)
+    aw = (torch.empty(b, num_heads, s, n_persistent + window, dtype=torch.bfloat16, device=q.device)
+          if want_weights else None)
+    call("swa_forward_f32_cuda", q=q, k=k, v=v, out=out, attn_weights=aw, seq_len=s,
+         num_heads=num_heads, head_dim=head_dim, window_size=window, batch_size=b,
+         n_persistent=n_persistent)
+    return out, aw
+
+
+def swa_backward_dd(q, k, v, aw, d_out, num_heads, head_dim, window, n_persistent=0):
+    b, s, td = q.shape
+    dq, dk, dv = (torch.zeros(b, s, td, dtype=torch.float32, device=q.device) for _ in range(3))
+    call("swa_backward_f32_cuda", q=q, k=k, v=v, attn_weights=aw, d_attn_out=d_out, d_q=dq, d_k=dk,
+         d_v=dv, seq_len=s, num_heads=num_heads, head_dim=head_dim, window_size=window,
+         batch_size=b, n_persistent=n_persistent)
+    return dq, dk, dv
+
+
+def swa_forward_lse(q, k, v, num_heads, head_dim, window, n_persistent=0):
+    b, s, _ = q.shape
+    out = torch.empty_like(q)
+    lse = _f32(b, num_heads, s, device=q.device)
+    call("nlh_swa_forward", q=q, k=k, v=v, out=out, lse=lse, seq_len=s, num_heads=num_heads,
+         head_dim=head_dim, window_size=window, batch_size=b, n_persistent=n_persistent)
+    return out, lse
+
+
+def swa_backward_lse(q, k, v, out, lse, d_out, num_heads, head_dim, window, n_persistent=0):
+    b, s, td = q.shape
+    dq, dk, dv = (torch.empty(b, s, td, dtype=torch.float32, device=q.device) for _ in range(3))
+    call("nlh_swa_backward", q=q, k=k, v=v, out=out, lse=lse, d_attn_out=d_out, d_q=dq, d_k=dk,
+         d_v=dv, seq_len=s, num_heads=num_heads, head_dim=head_dim, window_size=window,
+         batch_size=b, n_persistent=n_persistent)
+    return dq, dk, dv
+
+
+# ── AdamW ──────────────────────────────────────────────────────────────────
+def adamw_update_dd(w, g, m, v, lr, beta1, beta2, eps, bc1_inv, bc2_inv, weight_decay):
+    call("adamw_update_cuda", w=w, g=g, m=m, v=v, n=w.numel(), lr=lr, beta1=beta1, beta2=beta2,
+         eps=eps, bc1_inv=bc1_inv, bc2_inv=bc2_inv, weight_decay=weight_decay)
+
+
+def grad_norm_clip_dd(grads, max_norm):
+    """Global-norm clip over a list of tensors with the reference's kernel sequence
+    (core/src/gpu_stacked_optimizer.rs:193-345). Returns (norm, scale) as device scalars."""
+    dev = grads[0].device
+    total = sum((g.numel() + 255) // 256 for g in grads)
+    partial = _f32(total, device=dev)
+    off = 0
+    nb = C.c_int32(0)
+    for g in grads:
+        call("grad_norm_sq_cuda", g=g, partial_sums=partial[off:], n=g.numel(),
+             out_num_blocks=C.cast(C.pointer(nb), C.c_void_p))
+        off += nb.value
+    assert off == total
+    norm, scale = _f32(1, device=dev), _f32(1, device=dev)
+    call("reduce_partials_clip_cuda", partial_sums=partial, total_partials=total,
+         max_grad_norm=max_norm, out_norm=norm, out_scale=scale)
+    for g in grads:
+        call("grad_scale_conditional_cuda", g=g, scale_ptr=scale, n=g.numel())
+    return norm, scale
+
+
+# ── host-slice API (H2D + kernel + D2H), numpy in / numpy out ───────────────
+def _dev(a, dtype=torch.float32):
+    t = torch.from_numpy(np.ascontiguousarray(a))
+    return t.to("cuda", non_blocking=False).to(dtype) if t.dtype != dtype else t.to("cuda")
+
+
+def titans_forward_dispatch(k, v, q, alpha, theta, eta, m0, s0, error_clip=0.0, m_norm_max=0.0):
+    """Counterpart of titans_forward_dispatch (core/src/dispatch.rs:810-839), batch = 1."""
+    s, d = k.shape
+    ms, ss, y = titans_forward_dd(_dev(k)[None], _dev(v)[None], _dev(q)[None], _dev(alpha)[None],
+                                  _dev(theta)[None], _dev(eta)[None], _dev(m0)[None],
+                                  _dev(s0)[None], error_clip, m_norm_max)
+    return ms[0].cpu().numpy(), ss[0].cpu().numpy(), y[0].cpu().numpy()

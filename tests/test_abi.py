@@ -1,0 +1,96 @@
+"""CPU checks of the C-ABI boundary: the shared library loads, exports every symbol declared
+in include/nlh_ffi.h with a consistent prototype table, and the drop-in names match the
+reference's extern "C" block (no compute is launched here)."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+# the subset of core/src/cuda_ffi.rs on the hot path (names only; signatures are in the header)
+REFERENCE_SYMBOLS = """
+swa_forward_f32_cuda swa_backward_f32_cuda
+delta_forward_f32_cuda delta_backward_f32_cuda titans_forward_f32_cuda titans_backward_f32_cuda
+hebbian_forward_f32_cuda hebbian_backward_f32_cuda
+delta_forward_ckpt_f32_cuda titans_forward_ckpt_f32_cuda hebbian_forward_ckpt_f32_cuda
+delta_backward_segment_f32_cuda titans_backward_segment_f32_cuda hebbian_backward_segment_f32_cuda
+dgd_forward_f32_cuda dgd_backward_f32_cuda dgd_forward_ckpt_f32_cuda dgd_backward_segment_f32_cuda
+delta_chunkwise_forward_f32_cuda delta_chunkwise_backward_f32_cuda
+titans_chunkwise_forward_f32_cuda titans_chunkwise_backward_f32_cuda
+error_subtract_clip_f32_cuda delta_phase2_forward_f32_cuda titans_phase2_forward_f32_cuda
+delta_phase2_backward_f32_cuda titans_phase2_backward_f32_cuda
+m_norm_clamp_f32_cuda m_norm_clamp_batch_f32_cuda
+adamw_update_cuda grad_norm_sq_cuda dot_product_partial_f32_cuda grad_scale_cuda
+reduce_partials_clip_cuda grad_scale_conditional_cuda
+dgd_fused_forward_f32_cuda titans_fused_forward_f32_cuda
+""".split()
+
+
+@pytest.fixture(scope="module")
+def built():
+    from nl_hecate_b200 import build
+    return build.build()
+
+
+def test_library_exports_every_header_symbol(built):
+    from nl_hecate_b200 import ffi
+    protos = ffi.parse_header()
+    assert len(protos) >= 45
+    handle = C.CDLL(built)
+    for name in protos:
+        assert hasattr(handle, name), f"{name} declared in include/nlh_ffi.h but not exported"
+    lib = ffi.lib()
+    assert lib.nlh_abi_version() == 1
+    assert lib.nlh_last_status() == 0 and lib.nlh_last_error() == b""
+
+
+def test_reference_drop_in_names_present(built):
+    from nl_hecate_b200 import ffi
+    protos = ffi.parse_header()
+    for name in REFERENCE_SYMBOLS:
+        assert name in protos, name
+
+
+def test_drop_in_arity_matches_reference_ffi():
+    """Argument counts of a few entries, read off core/src/cuda_ffi.rs (lines cited in the header)."""
+    from nl_hecate_b200 import ffi
+    protos = ffi.parse_header()
+    arity = {"swa_forward_f32_cuda": 11, "swa_backward_f32_cuda": 14, "titans_forward_f32_cuda": 18,
+             "titans_backward_f32_cuda": 21, "delta_forward_f32_cuda": 15,
+             "hebbian_backward_f32_cuda": 13, "titans_chunkwise_backward_f32_cuda": 23,
+             "titans_phase2_backward_f32_cuda": 26, "adamw_update_cuda": 12,
+             "titans_fused_forward_f32_cuda": 28, "titans_backward_segment_f32_cuda": 25}
+    for name, n in arity.items():
+        assert len(protos[name][1]) == n, (name, len(protos[name][1]))
+    assert protos["adamw_update_cuda"][0] is C.c_uint32      # cudaError_t
+    assert protos["titans_forward_f32_cuda"][0] is None      # void
+
+
+def test_desc_struct_layout_matches_header():
+    from nl_hecate_b200 import ffi
+    text = open(os.path.join(ROOT, "include", "nlh_ffi.h")).read()
+    body = re.search(r"typedef struct nlh_adamw_tensor_desc \{(.*?)\}", text, re.S).group(1)
+    body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+    fields = re.findall(r"(float|int32_t)\s+(\w+);", body)
+    assert [f[1] for f in fields] == [f[0] for f in ffi.AdamWTensorDesc._fields_]
+    assert C.sizeof(ffi.AdamWTensorDesc) == 32
+
+
+def test_product_package_does_not_touch_the_oracle():
+    pkg = os.path.join(ROOT, "nl_hecate_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h")):
+                src = open(os.path.join(dirpath, f)).read()
+                assert "import oracle" not in src and "from oracle" not in src, f
+                assert "nlh_oracle" not in src, f
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    from nl_hecate_b200 import ffi
+    monkeypatch.setattr(ffi, "_lib", None)
+    monkeypatch.setattr(ffi, "LIB_PATH", str(tmp_path / "absent.so"))
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        ffi.lib()
