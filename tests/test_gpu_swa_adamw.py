@@ -59,7 +59,10 @@ def test_swa_compat_entries(D, orc, b, s, nh, hd, w, n_p):
     assert np.allclose(_np(aw).sum(-1), 1.0, atol=2e-2)
     dq, dk, dv = D.swa_backward_dd(q, k, v, aw, do, nh, hd, w, n_p)
     for name, got in (("d_q", dq), ("d_k", dk), ("d_v", dv)):
-        assert rel_err(_np(got), g_w[name]) <= 2e-2, (name, rel_err(_np(got), g_w[name]))
+        # window 1 makes d_q and d_k exactly zero in exact arithmetic: relative error is only
+        # meaningful when the reference is not ~0, so fall back to a tight absolute bound there
+        ok = rel_err(_np(got), g_w[name]) <= 2e-2 or max_abs(_np(got), g_w[name]) < 2e-4
+        assert ok, (name, rel_err(_np(got), g_w[name]), max_abs(_np(got), g_w[name]))
         assert max_abs(_np(got), g_w[name]) < 5e-2
 
 
