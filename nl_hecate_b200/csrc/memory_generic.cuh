@@ -578,7 +578,7 @@ __global__ void __launch_bounds__(GEN_THREADS) gen_phase2_bwd_kernel(
 
 // predictions[row,:] -= v[row,:]; optional per-row L2 clip
 // (core/kernels/error_subtract_clip.cu). One warp per row.
-__global__ void error_subtract_clip_kernel(float* pred, const float* __restrict__ v,
+static __global__ void error_subtract_clip_kernel(float* pred, const float* __restrict__ v,
                                            int rows, int d, float clip)
 {
     const int lane = threadIdx.x & 31;
@@ -602,7 +602,7 @@ __global__ void error_subtract_clip_kernel(float* pred, const float* __restrict_
 }
 
 // Frobenius clamp of each d×d matrix in a batch (core/kernels/m_norm_clamp.cu).
-__global__ void __launch_bounds__(GEN_THREADS) m_norm_clamp_kernel(float* m, size_t dd, float mmax)
+static __global__ void __launch_bounds__(GEN_THREADS) m_norm_clamp_kernel(float* m, size_t dd, float mmax)
 {
     __shared__ float red[32];
     float* mb = m + (size_t)blockIdx.x * dd;

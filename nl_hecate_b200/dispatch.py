@@ -65,6 +65,8 @@ def call(name: str, **kw):
             args.append(at(v))
     fn = getattr(ffi.lib(), name)
     bind_stream()
+    if ret is None:
+        ffi.lib().nlh_clear_status()   # void entries report through the recorded status
     rc = fn(*args)
     if ret is C.c_int32:
         ffi.check(rc, name)

@@ -86,6 +86,7 @@ def lib() -> C.CDLL:
 def check(status: int, where: str) -> None:
     if status != NLH_OK:
         err = lib().nlh_last_error()
+        lib().nlh_clear_status()   # the recorded status is sticky: do not leak it into later calls
         raise RuntimeError(f"{where} failed with status {status}: {err.decode() if err else ''}")
 
 
