@@ -373,7 +373,135 @@ class AdamWStep:
         return self.tokens_per_step / dt, f"{reps} full steps over {n} parameters, {dt * 1e3:.0f} ms each"
 
 
-def make_workload(name):
+class StackedModelStep:
+    """Full model step (configuration the headline metric is quoted on): Titans LMM + MAG + SWA
+    (window 512), CMS k=4 with periods [1,8,64,512], d_model 512, 8 heads, 4 blocks, vocab 8192,
+    seq 512, GLOBAL batch 64 split over the ranks; bf16 activations, fp32 memory state;
+    forward + backward + gradient all-reduce + clip + AdamW."""
+    GLOBAL_BATCH, S, VOCAB = 64, 512, 8192
+
+    def __init__(self, world):
+        self.name = "stacked_mag"
+        self.world = world
+        assert self.GLOBAL_BATCH % world == 0
+        self.local_batch = self.GLOBAL_BATCH // world
+        self.tokens_per_step = self.local_batch * self.S
+        self.dtype = "bf16"
+
+    def describe(self):
+        return {"workload": "full model step: Titans LMM + MAG + SWA(window 512), CMS k=4 periods "
+                            "[1,8,64,512], d_model 512, 8 heads, 4 blocks, vocab 8192, seq 512, "
+                            f"global batch {self.GLOBAL_BATCH}; fwd+bwd+all-reduce+clip+AdamW; bf16 "
+                            "activations, fp32 memory state; static projections",
+                "global_batch": self.GLOBAL_BATCH, "seq_len": self.S,
+                "tokens_per_step_per_gpu": self.tokens_per_step,
+                "l2_policy": "per-step working set (tens of GB of memory-state trajectory) >> L2"}
+
+    def zipf_tokens(self, n_seq, seed=2024):
+        g = np.random.Generator(np.random.Philox(seed))
+        ranks = np.arange(1, self.VOCAB + 1, dtype=np.float64)
+        cdf = np.cumsum(ranks ** -1.1)
+        cdf /= cdf[-1]
+        ids = np.searchsorted(cdf, g.random((n_seq, self.S + 1)), side="left").astype(np.int64)
+        return np.minimum(ids, self.VOCAB - 1)
+
+    def setup(self, torch, dispatch):
+        from nl_hecate_b200.stacked_mag import StackedMAG, StackedMAGConfig
+        self.torch, self.dd = torch, dispatch
+        rank = int(os.environ.get("RANK", "0"))
+        self.cfg = StackedMAGConfig()
+        self.model = StackedMAG(self.cfg, self.local_batch, device="cuda", seed=42)
+        ids = self.zipf_tokens(self.GLOBAL_BATCH)[rank * self.local_batch:(rank + 1) * self.local_batch]
+        self.host_tok = torch.from_numpy(np.ascontiguousarray(ids[:, :-1])).pin_memory()
+        self.host_tgt = torch.from_numpy(np.ascontiguousarray(ids[:, 1:])).pin_memory()
+        self.tok, self.tgt = self.host_tok.cuda(), self.host_tgt.cuda()
+        self.host_loss = torch.empty(1, dtype=torch.float32).pin_memory()
+        # hot-path launches per step: per block 1 SWA fwd + 3 SWA bwd + 4 levels x (fwd + bwd),
+        # plus norm (2) + AdamW (1)
+        self.launches_per_step = self.cfg.n_blocks * (4 + 2 * self.cfg.k) + 3
+        self.h2d = self.host_tok.numel() * 8 * 2
+        self.d2h = 4
+        self.pg = None
+
+    def step(self):
+        return self.model.step(self.tok, self.tgt, self.pg, self.world)
+
+    def step_e2e(self):
+        tok = self.host_tok.cuda(non_blocking=True)
+        tgt = self.host_tgt.cuda(non_blocking=True)
+        loss = self.model.step(tok, tgt, self.pg, self.world)
+        self.host_loss.copy_(loss.reshape(1), non_blocking=True)
+
+    def dominant(self):
+        """Exact Titans backward at the level-0 shapes of one block (the kernel with the largest
+        share of the step): N = local_batch x 8 heads problems, seq 512, head_dim 64."""
+        torch = self.torch
+        n, s, d = self.local_batch * self.cfg.num_heads, self.S, self.cfg.head_dim
+        g = torch.Generator(device="cuda").manual_seed(5)
+        r = lambda *sh: torch.randn(*sh, generator=g, device="cuda")
+        k, v, q, dy = (torch.nn.functional.normalize(r(n, s, d), dim=-1) for _ in range(4))
+        al, th, et = (torch.sigmoid(r(n, s)) for _ in range(3))
+        m0 = torch.zeros(n, d * d, device="cuda")
+        ms, ss, _ = self.dd.titans_forward_dd(k, v, q, al, th, et, m0, m0)
+        bytes_ = (4 + 3) * n * s * d * 4 + 6 * n * s * 4 + 2 * n * (s + 1) * d * d * 4
+        self._dom = (k, v, q, al, th, et, ms, ss, dy)
+        return ("fast_bwd_kernel<64,TITANS,exact> at level-0 shapes",
+                lambda: self.dd.titans_backward_dd(k, v, q, al, th, et, ms, ss, dy), bytes_, "hbm")
+
+    def cpu_sample(self, oracle, threads, budget_s=12.0):
+        """Hot-path operators of the step on the host: per sequence and block, SWA fwd+bwd and the
+        four CMS levels' Titans fwd+bwd (level 0 exact on 512 tokens, levels 1-3 frozen-M0 on
+        64/8/1 pooled tokens), 8 heads of 64; plus one AdamW step. Dense projections, LayerNorm
+        and cross-entropy glue are NOT included (they would only add CPU time)."""
+        import ctypes as C
+        s, nh, hd, w, nb = self.S, 8, 64, 512, 4
+        nseq = threads
+        L, ptr = oracle.lib(), oracle._p
+        g = np.random.Generator(np.random.Philox(3))
+        o = lambda *sh: np.zeros(sh, np.float32)
+        t0 = time.perf_counter()
+        for _ in range(nb):
+            sh = (nseq, s, nh * hd)
+            q, k, v = ((g.standard_normal(sh) / 8).astype(np.float32) for _ in range(3))
+            do = g.standard_normal(sh).astype(np.float32)
+            L.orc_swa_fwd_bwd_batched_mt(ptr(q), ptr(k), ptr(v), ptr(do), ptr(o(*sh)),
+                                         ptr(o(nseq, nh, s, w)), ptr(o(*sh)), ptr(o(*sh)), ptr(o(*sh)),
+                                         C.c_int(nseq), C.c_int(s), C.c_int(nh), C.c_int(hd),
+                                         C.c_int(w), C.c_int(0), C.c_int(threads))
+            for lvl, c in enumerate((1, 8, 64, 512)):
+                sf = s // c
+                n = nseq * nh
+                kk, vv, qq, dy = (g.standard_normal((n, sf, hd)).astype(np.float32) * 0.125 for _ in range(4))
+                ga = [np.full((n, sf), x, np.float32) for x in (0.05, 0.01, 0.9)]
+                z = o(n, hd * hd)
+                if lvl == 0:
+                    L.orc_titans_fwd_bwd_batched_mt(
+                        ptr(kk), ptr(vv), ptr(qq), ptr(ga[0]), ptr(ga[1]), ptr(ga[2]), ptr(z), ptr(z),
+                        ptr(dy), ptr(o(n, sf + 1, hd * hd)), ptr(o(n, sf + 1, hd * hd)), ptr(o(n, sf, hd)),
+                        ptr(o(n, sf, hd)), ptr(o(n, sf, hd)), ptr(o(n, sf, hd)), ptr(o(n, sf)), ptr(o(n, sf)),
+                        ptr(o(n, sf)), ptr(o(n, hd * hd)), ptr(o(n, hd * hd)), C.c_int(n), C.c_int(sf),
+                        C.c_int(hd), C.c_float(0.0), C.c_float(0.0), C.c_int(threads))
+                else:
+                    ch = min(c, sf)
+                    nc = (sf + ch - 1) // ch
+                    L.orc_chunkwise_fwd_bwd_batched_mt(
+                        C.c_int(1), ptr(kk), ptr(vv), ptr(qq), ptr(ga[0]), ptr(ga[1]), ptr(ga[2]), ptr(z),
+                        ptr(z), ptr(dy), ptr(o(n, nc + 1, hd * hd)), ptr(o(n, nc + 1, hd * hd)),
+                        ptr(o(n, sf, hd)), ptr(o(n, sf, hd)), ptr(o(n, sf, hd)), ptr(o(n, sf, hd)),
+                        ptr(o(n, sf)), ptr(o(n, sf)), ptr(o(n, sf)), ptr(o(n, hd * hd)), ptr(o(n, hd * hd)),
+                        C.c_int(n), C.c_int(sf), C.c_int(hd), C.c_int(ch), C.c_float(0.0),
+                        C.c_float(0.0), C.c_int(threads))
+        npar = 25_200_000
+        w_, g_, m_, v_ = (np.full(npar, x, np.float32) for x in (0.01, 0.001, 0.0, 0.0))
+        L.orc_adamw_step_mt(ptr(w_), ptr(g_), ptr(m_), ptr(v_), C.c_int64(npar), C.c_float(3e-4),
+                            C.c_float(0.9), C.c_float(0.999), C.c_float(1e-8), C.c_float(10.0),
+                            C.c_float(1000.0), C.c_float(0.1), C.c_int(threads))
+        dt = time.perf_counter() - t0
+        return nseq * s / dt, (f"{nseq} of {self.GLOBAL_BATCH} sequences, hot-path operators only (SWA, "
+                               f"4 CMS levels of Titans LMM, AdamW; 4 blocks), {dt:.1f} s incl. input generation")
+
+
+def make_workload(name, world=1):
     if name == "titans_chunkwise":
         return TitansPair(64)
     if name == "titans_exact":
@@ -382,10 +510,12 @@ def make_workload(name):
         return SwaPair()
     if name == "adamw":
         return AdamWStep()
+    if name == "stacked_mag":
+        return StackedModelStep(world)
     raise SystemExit(f"unknown workload {name}")
 
 
-DEFAULT_WORKLOAD = "titans_chunkwise"
+DEFAULT_WORKLOAD = "stacked_mag"
 METRIC = "fwd+bwd tokens/sec"
 UNIT = "tokens/s"
 
@@ -397,7 +527,7 @@ def run_reference(args):
         return
     import oracle
     oracle.build()
-    wl = make_workload(args.workload)
+    wl = make_workload(args.workload, max(1, args.gpus))
     threads = oracle.hardware_threads()
     vals = []
     sample = ""
@@ -411,8 +541,8 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": 1e3 * wl.tokens_per_step / value, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
-        "config": cfg,
+        "scaling": "strong" if args.workload == "stacked_mag" else "weak", "vs_baseline": None,
+        "dtype": wl.dtype, "data": "synthetic", "config": cfg,
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
                          "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -427,6 +557,8 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--timed-only", action="store_true",
+                    help="run only warm-up and the timed steps (for profiler launch lists)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
     if args.impl == "reference":
@@ -447,7 +579,7 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     warmup = max(args.warmup, 3)
 
-    wl = make_workload(args.workload)
+    wl = make_workload(args.workload, world)
     wl.setup(torch, dispatch)
 
     def barrier():
@@ -479,6 +611,15 @@ def main():
     clocks = sampler.stop() if sampler else None
     tokens = wl.tokens_per_step * world * args.steps
     value = tokens / (ms * 1e-3)
+
+    if args.timed_only:
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world,
+                              "steps": args.steps, "warmup": warmup, "ms_per_step": ms / args.steps,
+                              "timed_only": True, "config": wl.describe()}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     # end to end through the host-slice API
     for _ in range(2):
@@ -513,12 +654,14 @@ def main():
 
     if rank == 0:
         cfg = wl.describe()
-        cfg["parallelism"] = f"dp{world} (independent problems per rank, no collective)"
+        model_step = args.workload == "stacked_mag"
+        cfg["parallelism"] = (f"dp{world} (batch shard, one fp32 all-reduce of the gradient arena per step)"
+                              if model_step else f"dp{world} (independent problems per rank, no collective)")
         print(json.dumps({
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
-            "config": cfg, "clocks": clocks,
+            "scaling": "strong" if model_step else "weak", "vs_baseline": None, "dtype": wl.dtype,
+            "data": "synthetic", "config": cfg, "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": wl.h2d,
                     "d2h_bytes_per_step": wl.d2h},
             "gpu_launches": wl.launches_per_step * args.steps,

@@ -49,7 +49,9 @@ class FlatAdamW:
         self.chunk_len = torch.tensor(cl, dtype=torch.int32, device=dev)
         self._desc_host = (ffi.AdamWTensorDesc * len(self.sizes))()
         nbytes = C.sizeof(self._desc_host)
-        self._desc_pinned = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+        self._desc_pinned = torch.empty(nbytes, dtype=torch.uint8)
+        if dev.type == "cuda":
+            self._desc_pinned = self._desc_pinned.pin_memory()
         self._desc_dev = torch.empty(nbytes, dtype=torch.uint8, device=dev)
         self._partial = torch.empty(148 * 8, dtype=torch.float32, device=dev)
         self.norm = torch.zeros(1, dtype=torch.float32, device=dev)

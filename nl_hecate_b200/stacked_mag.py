@@ -1,0 +1,301 @@
+"""Stacked Titans-LMM + MAG + SWA model with CMS levels: the caller of the hot path.
+
+Host-side harness standing in for the reference's GPU-resident driver
+(core/src/gpu_stacked_forward.rs:1263-2038 forward_sequence, gpu_forward.rs:1197-1540
+gpu_memory_forward, gpu_stacked_backward.rs, gpu_stacked_optimizer.rs:522-700). The hot-path
+operators — memory-rule kernel pairs, SWA forward/backward, the AdamW step — are this
+library's CUDA kernels behind the C ABI; the glue around them (embedding, LayerNorm, the
+dense projections, pooling, gating, cross-entropy) is plain PyTorch/cuBLAS and autograd, which
+is what the reference does with cuBLAS and its small element-wise kernels.
+
+Block (MAG composition), per core/src/gpu_stacked_forward.rs:1656-1960:
+    h        = LN_attn(x)
+    q,k,v    = h W_q^T, h W_k^T, h W_v^T           (bf16)
+    attn     = SWA(q,k,v)  ;  attn_proj = attn W_o^T ; res1 = x + attn_proj
+    m_in     = LN_mem(res1)
+    level l  : x_l = mean_pool(m_in, c_l)            (c_l = chunk size of the level)
+               k,v,q = x_l W_{k,v,q}^T ; k,q L2-normalised over d_model
+               alpha = sigmoid([k;v].w_a + b_a), theta = softplus([k;v].w_t + b_t),
+               eta = sigmoid([k;v].w_e + b_e)        (one gate per token, shared by heads)
+               y_l  = TitansLMM per head on [B*H, s/c_l, hd]: level 0 exact per-token rule,
+                      levels >= 1 frozen-M0 chunkwise rule; M carried across steps, S0 = 0
+               y_l upsampled by repetition to full resolution
+    y        = sum_l softmax(alpha_mem)_l y_l
+    out      = x + attn_proj * sigmoid(y)            (second residual adds to the block INPUT)
+Final LayerNorm, unembedding (logits = x W_unembed, W_unembed [d, vocab]), cross-entropy.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+
+import torch
+import torch.nn.functional as F
+
+from . import dispatch as D
+from .optimizer import FlatAdamW
+
+B_ALPHA = (3.0, 4.0, 4.5, 5.0, 5.5, 6.0)      # core/src/model.rs:1081-1093
+B_THETA = (-4.6, -5.6, -6.6, -7.6, -8.6, -9.6)  # core/src/model.rs:1095-1109
+B_ETA = (1.5, 2.0, 2.5, 3.0, 3.5, 4.0)        # core/src/model.rs:1111-1122
+
+
+@dataclass
+class StackedMAGConfig:
+    d_model: int = 512
+    num_heads: int = 8
+    n_blocks: int = 4
+    k: int = 4
+    chunk_sizes: tuple = (1, 8, 64, 512)
+    seq_len: int = 512
+    window: int = 512
+    vocab: int = 8192
+    bf16: bool = True                 # bf16 activations for SWA and the dense projections
+    exact_levels: tuple = (0,)        # tape strategy: level 0 exact, others frozen-M0 (proxy)
+    lr: float = 3e-4
+    beta1: float = 0.9
+    beta2: float = 0.999
+    eps: float = 1e-8
+    weight_decay: float = 0.1
+    max_grad_norm: float = 1.0
+    tie_embeddings: bool = True
+
+    @property
+    def head_dim(self):
+        return self.d_model // self.num_heads
+
+
+class _TitansMemory(torch.autograd.Function):
+    """Per-head Titans LMM over [N, S, hd] (N = batch*heads) through the C ABI.
+    chunk == 0: exact rule (titans_forward/backward_f32_cuda, full trajectory);
+    chunk > 0 : frozen-M0 chunkwise rule (titans_chunkwise_*_f32_cuda)."""
+
+    @staticmethod
+    def forward(ctx, k, v, q, alpha, theta, eta, m0, chunk):
+        s0 = torch.zeros_like(m0)     # momentum restarts every call (gpu_forward.rs:1516-1517)
+        if chunk == 0:
+            ms, ss, y = D.titans_forward_dd(k, v, q, alpha, theta, eta, m0, s0)
+        else:
+            ms, ss, y = D.titans_chunkwise_forward_dd(k, v, q, alpha, theta, eta, m0, s0, chunk)
+        ctx.save_for_backward(k, v, q, alpha, theta, eta, ms, ss)
+        ctx.chunk = chunk
+        m_final = ms[:, -1].clone()
+        ctx.mark_non_differentiable(m_final)
+        return y, m_final
+
+    @staticmethod
+    def backward(ctx, dy, _dm):
+        k, v, q, alpha, theta, eta, ms, ss = ctx.saved_tensors
+        dy = dy.contiguous()
+        if ctx.chunk == 0:
+            g = D.titans_backward_dd(k, v, q, alpha, theta, eta, ms, ss, dy)
+        else:
+            g = D.titans_chunkwise_backward_dd(k, v, q, alpha, theta, eta, ms, ss, dy, ctx.chunk)
+        return g["d_k"], g["d_v"], g["d_q"], g["d_alpha"], g["d_theta"], g["d_eta"], None, None
+
+
+class _SWA(torch.autograd.Function):
+    """Sliding-window attention over [B, S, H*hd] bf16 (nlh_swa_forward / nlh_swa_backward)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, num_heads, head_dim, window):
+        out, lse = D.swa_forward_lse(q, k, v, num_heads, head_dim, window)
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.cfg = (num_heads, head_dim, window)
+        return out
+
+    @staticmethod
+    def backward(ctx, d_out):
+        q, k, v, out, lse = ctx.saved_tensors
+        nh, hd, w = ctx.cfg
+        dq, dk, dv = D.swa_backward_lse(q, k, v, out, lse, d_out.float().contiguous(), nh, hd, w)
+        return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), None, None, None
+
+
+def titans_memory(k, v, q, alpha, theta, eta, m0, chunk):
+    return _TitansMemory.apply(k, v, q, alpha, theta, eta, m0, chunk)
+
+
+def swa(q, k, v, num_heads, head_dim, window):
+    return _SWA.apply(q, k, v, num_heads, head_dim, window)
+
+
+class StackedMAG:
+    """Parameters live in one flat fp32 arena (FlatAdamW); tensors below are views into it."""
+
+    def __init__(self, cfg: StackedMAGConfig, batch_per_rank: int, device="cuda", seed=42,
+                 memory_fn=titans_memory, swa_fn=swa):
+        self.cfg, self.device = cfg, torch.device(device)
+        self.memory_fn, self.swa_fn = memory_fn, swa_fn
+        d, v, k = cfg.d_model, cfg.vocab, cfg.k
+        names, shapes, clamp, level_of = [], [], {}, []
+
+        def add(name, shape, level=None):
+            names.append(name); shapes.append(shape); level_of.append(level)
+            return len(names) - 1
+
+        add("w_embed", (v, d)); add("w_unembed", (d, v))
+        add("ln_final_gamma", (d,)); add("ln_final_beta", (d,))
+        for b in range(cfg.n_blocks):
+            p = f"b{b}."
+            add(p + "w_qkv", (3 * d, d)); add(p + "w_o", (d, d))
+            add(p + "ln_attn_gamma", (d,)); add(p + "ln_attn_beta", (d,))
+            add(p + "ln_mem_gamma", (d,)); add(p + "ln_mem_beta", (d,))
+            add(p + "alpha_mem", (k,))
+            for l in range(k):
+                q_ = p + f"l{l}."
+                add(q_ + "w_kvq_mem", (3 * d, d), l)
+                add(q_ + "w_gates", (3, 2 * d), l)        # rows: alpha, theta, eta
+                add(q_ + "b_alpha", (1,), l)
+                i = add(q_ + "b_theta", (1,), l)
+                clamp[i] = (-10.0, 2.0)                    # gpu_stacked_optimizer.rs:667-671
+                add(q_ + "b_eta", (1,), l)
+        self.names, self.shapes, self.level_of = names, shapes, level_of
+        self.opt = FlatAdamW([math.prod(s) for s in shapes], device=device, beta1=cfg.beta1,
+                             beta2=cfg.beta2, eps=cfg.eps, weight_decay=cfg.weight_decay,
+                             clamp=clamp)
+        self.p, self.g = {}, {}
+        for i, (n, s) in enumerate(zip(names, shapes)):
+            w = self.opt.view(self.opt.w, i).view(s)
+            w.requires_grad_(True)
+            w.grad = self.opt.view(self.opt.g, i).view(s)
+            self.p[n], self.g[n] = w, w.grad
+        self._init(seed)
+        # carried memory: one slot per (block, level, local sequence, head)
+        nh, hd = cfg.num_heads, cfg.head_dim
+        self.context = [[torch.zeros(batch_per_rank * nh, hd * hd, device=self.device)
+                         for _ in range(k)] for _ in range(cfg.n_blocks)]
+        self.global_step = 0
+        self.level_steps = [0] * k
+
+    @torch.no_grad()
+    def _init(self, seed):
+        cfg = self.cfg
+        d = cfg.d_model
+        g = torch.Generator(device=self.device).manual_seed(seed)
+        u = lambda t, sc: t.uniform_(-sc, sc, generator=g)
+        proj = math.sqrt(2.0 / (d + d))
+        depth = 1.0 / math.sqrt(2.0 * cfg.n_blocks)     # core/src/stacked_model.rs:75-79
+        gate = math.sqrt(1.0 / (2 * d))
+        for n, w in self.p.items():
+            base = n.split(".")[-1]
+            if base in ("w_embed", "w_unembed"):
+                u(w, math.sqrt(2.0 / (d + cfg.vocab)))
+            elif base == "w_qkv":
+                u(w, proj)
+            elif base in ("w_o", "w_kvq_mem"):
+                u(w, proj * depth)
+            elif base == "w_gates":
+                u(w, gate)
+            elif base.endswith("gamma"):
+                w.fill_(1.0)
+            elif base in ("b_alpha", "b_theta", "b_eta"):
+                lvl = int(n.split(".")[1][1:])
+                w.fill_({"b_alpha": B_ALPHA, "b_theta": B_THETA, "b_eta": B_ETA}[base][lvl])
+            else:
+                w.zero_()
+        if cfg.tie_embeddings:
+            self.p["w_embed"].copy_(self.p["w_unembed"].t())
+
+    # ── forward ────────────────────────────────────────────────────────────
+    def _mm(self, x, w):
+        """x [.., in] times w^T, w [out, in]; bf16 tensor-core GEMM when cfg.bf16."""
+        if self.cfg.bf16:
+            return F.linear(x.to(torch.bfloat16), w.to(torch.bfloat16))
+        return F.linear(x.float(), w)
+
+    def _level(self, b, l, m_in):
+        cfg, p = self.cfg, self.p
+        B, S, d = m_in.shape
+        nh, hd = cfg.num_heads, cfg.head_dim
+        c = min(cfg.chunk_sizes[l], S)
+        assert S % c == 0, "seq_len must be a multiple of every chunk size"
+        sf = S // c
+        x = m_in.view(B, sf, c, d).mean(2) if c > 1 else m_in
+        pre = f"b{b}.l{l}."
+        kvq = self._mm(x, p[pre + "w_kvq_mem"]).float()
+        k, v, q = kvq.split(d, dim=-1)
+        k = k / k.norm(dim=-1, keepdim=True).clamp_min(1e-8)
+        q = q / q.norm(dim=-1, keepdim=True).clamp_min(1e-8)
+        pre_g = torch.cat([k, v], dim=-1) @ p[pre + "w_gates"].t()
+        alpha = torch.sigmoid(pre_g[..., 0] + p[pre + "b_alpha"])
+        theta = F.softplus(pre_g[..., 1] + p[pre + "b_theta"])
+        eta = torch.sigmoid(pre_g[..., 2] + p[pre + "b_eta"])
+        heads = lambda t: t.reshape(B, sf, nh, hd).permute(0, 2, 1, 3).reshape(B * nh, sf, hd).contiguous()
+        bro = lambda t: t.unsqueeze(1).expand(B, nh, sf).reshape(B * nh, sf).contiguous()
+        chunk = 0 if l in cfg.exact_levels else min(cfg.chunk_sizes[l], sf)
+        y, m_final = self.memory_fn(heads(k), heads(v), heads(q), bro(alpha), bro(theta), bro(eta),
+                                    self.context[b][l], chunk)
+        self.context[b][l] = m_final.detach()
+        y = y.view(B, nh, sf, hd).permute(0, 2, 1, 3).reshape(B, sf, d)
+        return y.repeat_interleave(c, dim=1) if c > 1 else y
+
+    def forward(self, tokens, targets):
+        cfg, p = self.cfg, self.p
+        d, nh, hd = cfg.d_model, cfg.num_heads, cfg.head_dim
+        x = F.embedding(tokens, p["w_embed"])
+        for b in range(cfg.n_blocks):
+            pre = f"b{b}."
+            h = F.layer_norm(x, (d,), p[pre + "ln_attn_gamma"], p[pre + "ln_attn_beta"], 1e-5)
+            qkv = self._mm(h, p[pre + "w_qkv"]).to(torch.bfloat16)
+            q, k, v = (t.contiguous() for t in qkv.split(d, dim=-1))
+            attn = self.swa_fn(q, k, v, nh, hd, cfg.window)
+            attn_proj = self._mm(attn, p[pre + "w_o"]).float()
+            res1 = x + attn_proj
+            m_in = F.layer_norm(res1, (d,), p[pre + "ln_mem_gamma"], p[pre + "ln_mem_beta"], 1e-5)
+            wts = torch.softmax(p[pre + "alpha_mem"], dim=0)
+            y = None
+            for l in range(cfg.k):
+                yl = self._level(b, l, m_in) * wts[l]
+                y = yl if y is None else y + yl
+            x = x + attn_proj * torch.sigmoid(y)
+        x = F.layer_norm(x, (d,), p["ln_final_gamma"], p["ln_final_beta"], 1e-5)
+        logits = self._mm(x, p["w_unembed"].t()).float()
+        return F.cross_entropy(logits.view(-1, cfg.vocab), targets.reshape(-1))
+
+    # ── one training step ──────────────────────────────────────────────────
+    def pulse(self):
+        """Active CMS levels this step (core/src/conductor.rs:136-155)."""
+        cfg = self.cfg
+        return [self.global_step % cs == 0 or cfg.seq_len >= cs for cs in cfg.chunk_sizes]
+
+    def forward_backward(self, tokens, targets):
+        """Loss (mean over the local batch) and its gradients, accumulated into the arena."""
+        loss = self.forward(tokens, targets)
+        loss.backward()
+        return loss.detach()
+
+    def sync_gradients(self, process_group=None, world=1):
+        """Data-parallel gradient exchange: ONE all-reduce(SUM) over the flat gradient arena,
+        then divide by the world size (core/src/distributed.rs:121-150 does the same per
+        tensor). Inner-loop state (carried memories) is rank-local and never communicated."""
+        if world > 1:
+            torch.distributed.all_reduce(self.opt.g, group=process_group)
+            self.opt.g.mul_(1.0 / world)
+
+    def apply_update(self):
+        """Global-norm clip + AdamW with per-level step counts and pulse gating, weight tying."""
+        cfg = self.cfg
+        active = self.pulse()
+        self.global_step += 1
+        for l in range(cfg.k):
+            if active[l]:
+                self.level_steps[l] += 1
+        steps = [self.global_step if lv is None else max(self.level_steps[lv], 1)
+                 for lv in self.level_of]
+        act = [True if lv is None else active[lv] for lv in self.level_of]
+        self.opt.step(cfg.lr, steps, act, cfg.max_grad_norm)
+        if cfg.tie_embeddings:
+            with torch.no_grad():   # gpu_stacked_sync_embed_weights: w_embed <- w_unembed^T
+                self.p["w_embed"].copy_(self.p["w_unembed"].t())
+        self.opt.g.zero_()
+
+    def step(self, tokens, targets, process_group=None, world=1):
+        """forward + backward + gradient all-reduce + clip + AdamW. Returns the local loss."""
+        loss = self.forward_backward(tokens, targets)
+        self.sync_gradients(process_group, world)
+        self.apply_update()
+        return loss
+
+    def n_params(self):
+        return sum(math.prod(s) for s in self.shapes)
