@@ -270,6 +270,22 @@ int32_t nlh_adamw_multi_tensor(float* w, const float* g, float* m, float* v,
 int32_t nlh_arena_grad_norm_clip(const float* g, int64_t n, float max_grad_norm, float* partial,
     int32_t partial_capacity, float* out_norm, float* out_scale);
 
+/* No counterpart in the reference. Titans LMM backward (same arguments, layout and
+ * batch-summed d_m_initial/d_s_initial as titans_backward_f32_cuda) for callers that must
+ * not allocate device memory: its scratch is a fixed 2 MiB array inside the library image,
+ * so the call never reaches cudaMalloc/cudaFree or the workspace. Limit:
+ * batch_size*d*d <= NLH_NOALLOC_MAX_STATE_FLOATS, otherwise NLH_ERR_INVALID_ARG. All calls
+ * on a device share the array: calls that overlap on the GPU race; issue them in order on
+ * one stream. The first call on each device resolves the array's device address and should
+ * be made while the stream is not being captured. */
+#define NLH_NOALLOC_MAX_STATE_FLOATS 262144
+#define NLH_NOALLOC_SCRATCH_BYTES (2 * NLH_NOALLOC_MAX_STATE_FLOATS * 4)
+int32_t nlh_titans_backward_noalloc(const float* k_mem, const float* v_mem, const float* q_mem,
+    const float* alpha, const float* theta, const float* eta, const float* m_states,
+    const float* s_states, const float* d_y, float* d_k_mem, float* d_v_mem, float* d_q_mem,
+    float* d_alpha, float* d_theta, float* d_eta, float* d_m_initial, float* d_s_initial,
+    int32_t seq_len, int32_t d, int32_t batch_size, float error_clip);
+
 #ifdef __cplusplus
 }
 #endif
