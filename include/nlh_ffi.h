@@ -270,6 +270,46 @@ int32_t nlh_adamw_multi_tensor(float* w, const float* g, float* m, float* v,
 int32_t nlh_arena_grad_norm_clip(const float* g, int64_t n, float max_grad_norm, float* partial,
     int32_t partial_capacity, float* out_norm, float* out_scale);
 
+/* Fused rule wrapper around the recurrence (row "next" of the scope: the ~15 small launches per
+ * CMS level at core/src/gpu_forward.rs:1339-1382 and gpu_backward.rs:2047-2115 as one kernel each
+ * way). kvq: [batch*seq, 3*d_model] rows (k | v | q) as produced by the projection GEMM, fp32 or
+ * bf16. Outputs in the per-head layout the memory kernels consume: k_ph,v_ph,q_ph
+ * [batch*heads, seq, head_dim] (k,q L2-normalised over d_model), gates [batch*heads, seq]
+ * (one value per token, repeated per head); k_norm,q_norm [batch*seq] for the backward.
+ * w_gates [3, 2*d_model] rows alpha, theta, eta; biases are device scalars. */
+int32_t nlh_level_prep_forward(const void* kvq, int32_t kvq_is_bf16, const float* w_gates,
+    const float* b_alpha, const float* b_theta, const float* b_eta, float* k_ph, float* v_ph,
+    float* q_ph, float* alpha_ph, float* theta_ph, float* eta_ph, float* k_norm, float* q_norm,
+    int32_t batch, int32_t seq, int32_t d_model, int32_t num_heads);
+/* Backward twin: d_kvq [batch*seq, 3*d_model]; gate weight / bias gradients as per-CTA partial
+ * sums dw_partial [rows, 3, 2*d_model], db_partial [rows, 3] with
+ * rows = nlh_level_prep_partial_rows(batch*seq) (the caller sums over rows). */
+int32_t nlh_level_prep_partial_rows(int32_t n_tokens);
+int32_t nlh_level_prep_backward(const float* k_ph, const float* v_ph, const float* q_ph,
+    const float* alpha_ph, const float* theta_ph, const float* eta_ph, const float* k_norm,
+    const float* q_norm, const float* dk_ph, const float* dv_ph, const float* dq_ph,
+    const float* dalpha_ph, const float* dtheta_ph, const float* deta_ph, const float* w_gates,
+    void* d_kvq, int32_t kvq_is_bf16, float* dw_partial, float* db_partial, int32_t batch,
+    int32_t seq, int32_t d_model, int32_t num_heads);
+/* MAG gating of one block (core/src/gpu_stacked_forward.rs:1935-1960):
+ * out = x + attn_proj * sigmoid(sum_l w_l * upsample(y_l)), y_l [batch*heads, seq/c_l, head_dim]
+ * read in the per-head layout, level_weights [k] on the device (softmax of alpha_mem). */
+int32_t nlh_mag_combine_forward(const float* x, const void* attn_proj, int32_t attn_is_bf16,
+    const float* level_weights, const float* y0, const float* y1, const float* y2, const float* y3,
+    int32_t c0, int32_t c1, int32_t c2, int32_t c3, int32_t k, float* out, int32_t batch,
+    int32_t seq, int32_t d_model, int32_t num_heads);
+/* Backward: d_attn_proj (dtype of attn_proj), d_ycomb [batch, seq, d_model] fp32 (gradient of the
+ * weighted level sum) and dw_partial [n_partial_rows, 4] partial sums of d level_weights. */
+int32_t nlh_mag_combine_backward(const float* d_out, const void* attn_proj, int32_t attn_is_bf16,
+    const float* level_weights, const float* y0, const float* y1, const float* y2, const float* y3,
+    int32_t c0, int32_t c1, int32_t c2, int32_t c3, int32_t k, void* d_attn_proj, float* d_ycomb,
+    float* dw_partial, int32_t n_partial_rows, int32_t batch, int32_t seq, int32_t d_model,
+    int32_t num_heads);
+/* dy_ph[(b*H+h), t', :] = level_weights[level] * sum_{i<pool} d_ycomb[b, t'*pool+i, h*hd:(h+1)*hd]
+ * (adjoint of repeat_upsample_1d + head transpose, pool_ops.cu / elementwise.cu). */
+int32_t nlh_pool_to_heads(const float* d_ycomb, const float* level_weights, int32_t level,
+    int32_t pool, float* dy_ph, int32_t batch, int32_t seq, int32_t d_model, int32_t num_heads);
+
 /* No counterpart in the reference. Titans LMM backward (same arguments, layout and
  * batch-summed d_m_initial/d_s_initial as titans_backward_f32_cuda) for callers that must
  * not allocate device memory: its scratch is a fixed 2 MiB array inside the library image,

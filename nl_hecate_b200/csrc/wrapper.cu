@@ -1,0 +1,507 @@
+// Fused rule-wrapper and MAG-block glue around the memory kernels.
+//
+// level_prep   : from the projected [tokens, 3*d_model] (k | v | q) rows to what the
+//                per-head recurrence consumes: L2-normalised k,q, raw v in [B*H, s, hd]
+//                layout, and the three gates broadcast to heads — one kernel instead of
+//                the reference's l2_normalize_rows x2, gate_compute x3, clamp,
+//                transpose_heads x3, broadcast_gates x3 (core/src/gpu_forward.rs:1339-1382).
+//                Backward twin: gate activation backward, gate->k/v gradient, gate weight
+//                gradients, L2-norm backward, inverse head transpose
+//                (core/src/gpu_backward.rs:2047-2115, gate_backward.cu, l2_normalize.cu).
+// mag_combine  : out = x + attn_proj * sigmoid(sum_l w_l * upsample(y_l)) reading the
+//                per-head level outputs directly (core/src/gpu_stacked_forward.rs:1935-1960),
+//                and its backward.
+// Gate activations saturate at |x| >= 15 like core/src/tensor.rs:199-227.
+#include <cuda_bf16.h>
+
+#include "nlh_common.cuh"
+#include "../../include/nlh_ffi.h"
+
+namespace nlh {
+
+constexpr int WR_THREADS = 128;
+constexpr int WR_TOK_PER_CTA = 32;     // tokens per CTA in level_prep backward
+constexpr int WR_MAX_LEVELS = 4;
+
+__device__ __forceinline__ float wr_sigmoid(float x)
+{
+    if (x >= 15.0f) return 1.0f;
+    if (x <= -15.0f) return 0.0f;
+    return 1.0f / (1.0f + expf(-x));
+}
+__device__ __forceinline__ float wr_softplus(float x)
+{
+    if (x >= 15.0f) return x;
+    if (x <= -15.0f) return 0.0f;
+    return logf(1.0f + expf(x));
+}
+__device__ __forceinline__ float ld_as_float(const float* p) { return *p; }
+__device__ __forceinline__ float ld_as_float(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+__device__ __forceinline__ void st_from_float(float* p, float v) { *p = v; }
+__device__ __forceinline__ void st_from_float(__nv_bfloat16* p, float v) { *p = __float2bfloat16(v); }
+
+// Sum NV values over the CTA; result broadcast to every thread. red: NV * 32 floats.
+template <int NV>
+__device__ __forceinline__ void block_sum_n(float (&v)[NV], float* red)
+{
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+#pragma unroll
+    for (int i = 0; i < NV; i++) {
+        v[i] = warp_sum(v[i]);
+        if (lane == 0) red[i * 32 + warp] = v[i];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < NV; i++) {
+        float t = 0.0f;
+        for (int w = 0; w < nw; w++) t += red[i * 32 + w];
+        v[i] = t;
+    }
+    __syncthreads();
+}
+
+// ───────────────────────── level prep forward ─────────────────────────────
+// One CTA per token. kvq row = [k(d) | v(d) | q(d)].
+template <typename TIN>
+__global__ void __launch_bounds__(WR_THREADS) level_prep_fwd_kernel(
+    const TIN* __restrict__ kvq, const float* __restrict__ w_gates, const float* __restrict__ b_alpha,
+    const float* __restrict__ b_theta, const float* __restrict__ b_eta,
+    float* __restrict__ k_ph, float* __restrict__ v_ph, float* __restrict__ q_ph,
+    float* __restrict__ alpha_ph, float* __restrict__ theta_ph, float* __restrict__ eta_ph,
+    float* __restrict__ k_norm, float* __restrict__ q_norm, int sf, int d, int H)
+{
+    extern __shared__ float sm[];
+    float* ks = sm; float* vs = sm + d; float* qs = sm + 2 * d; float* red = sm + 3 * d;  // [8*32]
+    const int tok = blockIdx.x, b = tok / sf, t = tok - b * sf;
+    const int hd = d / H;
+    const TIN* row = kvq + (size_t)tok * 3 * d;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int j = threadIdx.x; j < d; j += blockDim.x) {
+        const float kj = ld_as_float(row + j), vj = ld_as_float(row + d + j), qj = ld_as_float(row + 2 * d + j);
+        ks[j] = kj; vs[j] = vj; qs[j] = qj;
+        acc[0] += kj * kj; acc[1] += qj * qj;
+#pragma unroll
+        for (int g = 0; g < 3; g++) {
+            acc[2 + g] += kj * w_gates[(size_t)g * 2 * d + j];
+            acc[5 + g] += vj * w_gates[(size_t)g * 2 * d + d + j];
+        }
+    }
+    block_sum_n<8>(acc, red);
+    const float kn = sqrtf(acc[0]), qn = sqrtf(acc[1]);
+    const float ki = 1.0f / fmaxf(kn, 1e-8f), qi = 1.0f / fmaxf(qn, 1e-8f);
+    const float al = wr_sigmoid(acc[2] * ki + acc[5] + *b_alpha);
+    const float th = wr_softplus(acc[3] * ki + acc[6] + *b_theta);
+    const float et = wr_sigmoid(acc[4] * ki + acc[7] + *b_eta);
+    for (int j = threadIdx.x; j < d; j += blockDim.x) {
+        const int h = j / hd, w = j - h * hd;
+        const size_t dst = (((size_t)b * H + h) * sf + t) * hd + w;
+        k_ph[dst] = ks[j] * ki; v_ph[dst] = vs[j]; q_ph[dst] = qs[j] * qi;
+    }
+    if (threadIdx.x < H) {
+        const size_t g = ((size_t)b * H + threadIdx.x) * sf + t;
+        alpha_ph[g] = al; theta_ph[g] = th; eta_ph[g] = et;
+    }
+    if (threadIdx.x == 0) { k_norm[tok] = kn; q_norm[tok] = qn; }
+}
+
+// ───────────────────────── level prep backward ────────────────────────────
+// One CTA per WR_TOK_PER_CTA tokens; thread owns elements j = tid + i*WR_THREADS (i < NE) of
+// each d-vector, so the gate-weight gradient accumulates in registers across the CTA's tokens
+// and is written once as a per-CTA partial [n_cta, 3, 2d] (summed by the caller).
+template <typename TIN, int NE>
+__global__ void __launch_bounds__(WR_THREADS) level_prep_bwd_kernel(
+    const float* __restrict__ k_ph, const float* __restrict__ v_ph, const float* __restrict__ q_ph,
+    const float* __restrict__ alpha_ph, const float* __restrict__ theta_ph, const float* __restrict__ eta_ph,
+    const float* __restrict__ k_norm, const float* __restrict__ q_norm,
+    const float* __restrict__ dk_ph, const float* __restrict__ dv_ph, const float* __restrict__ dq_ph,
+    const float* __restrict__ dalpha_ph, const float* __restrict__ dtheta_ph, const float* __restrict__ deta_ph,
+    const float* __restrict__ w_gates, TIN* __restrict__ d_kvq, float* __restrict__ dw_partial,
+    float* __restrict__ db_partial, int n_tok, int sf, int d, int H)
+{
+    __shared__ float red[5 * 32];
+    const int hd = d / H;
+    float dwk[3][NE], dwv[3][NE], db[3] = {0.f, 0.f, 0.f};
+#pragma unroll
+    for (int g = 0; g < 3; g++)
+#pragma unroll
+        for (int i = 0; i < NE; i++) { dwk[g][i] = 0.f; dwv[g][i] = 0.f; }
+    const int tok0 = blockIdx.x * WR_TOK_PER_CTA;
+    const int tok1 = min(tok0 + WR_TOK_PER_CTA, n_tok);
+    for (int tok = tok0; tok < tok1; tok++) {
+        const int b = tok / sf, t = tok - b * sf;
+        const size_t g0 = ((size_t)b * H) * sf + t;       // head 0 gate slot; heads are sf apart
+        const float al = alpha_ph[g0], th = theta_ph[g0], et = eta_ph[g0];
+        float kh[NE], vv[NE], qh[NE], gk[NE], gv[NE], gq[NE];
+        float s[5] = {0.f, 0.f, 0.f, 0.f, 0.f};   // d_alpha, d_theta, d_eta (head sums), dk.k, dq.q
+        if (threadIdx.x < H) {
+            const size_t gi = g0 + (size_t)threadIdx.x * sf;
+            s[0] = dalpha_ph[gi]; s[1] = dtheta_ph[gi]; s[2] = deta_ph[gi];
+        }
+#pragma unroll
+        for (int i = 0; i < NE; i++) {
+            const int j = threadIdx.x + i * WR_THREADS;
+            if (j < d) {
+                const int h = j / hd, w = j - h * hd;
+                const size_t src = (((size_t)b * H + h) * sf + t) * hd + w;
+                kh[i] = k_ph[src]; vv[i] = v_ph[src]; qh[i] = q_ph[src];
+                gk[i] = dk_ph[src]; gv[i] = dv_ph[src]; gq[i] = dq_ph[src];
+            } else { kh[i] = vv[i] = qh[i] = gk[i] = gv[i] = gq[i] = 0.f; }
+        }
+        // gate head sums first (the gate -> k gradient enters the k.dk dot product)
+        {
+            float hs[3] = {s[0], s[1], s[2]};
+            block_sum_n<3>(hs, red);
+            s[0] = hs[0]; s[1] = hs[1]; s[2] = hs[2];
+        }
+        const float dpre[3] = {s[0] * al * (1.0f - al), s[1] * (1.0f - expf(-th)), s[2] * et * (1.0f - et)};
+        float dots[2] = {0.f, 0.f};
+#pragma unroll
+        for (int i = 0; i < NE; i++) {
+            const int j = threadIdx.x + i * WR_THREADS;
+            if (j < d) {
+#pragma unroll
+                for (int g = 0; g < 3; g++) {
+                    gk[i] += dpre[g] * w_gates[(size_t)g * 2 * d + j];
+                    gv[i] += dpre[g] * w_gates[(size_t)g * 2 * d + d + j];
+                    dwk[g][i] += dpre[g] * kh[i];
+                    dwv[g][i] += dpre[g] * vv[i];
+                }
+                dots[0] += gk[i] * kh[i];
+                dots[1] += gq[i] * qh[i];
+            }
+        }
+        if (threadIdx.x == 0) { db[0] += dpre[0]; db[1] += dpre[1]; db[2] += dpre[2]; }
+        block_sum_n<2>(dots, red);
+        const float kn = k_norm[tok], qn = q_norm[tok];
+        TIN* orow = d_kvq + (size_t)tok * 3 * d;
+#pragma unroll
+        for (int i = 0; i < NE; i++) {
+            const int j = threadIdx.x + i * WR_THREADS;
+            if (j < d) {
+                // sphere Jacobian of x/||x|| (core/src/tensor.rs:320-351)
+                const float dk = (kn >= 1e-8f) ? (gk[i] - kh[i] * dots[0]) / kn : gk[i] * 1e8f;
+                const float dq = (qn >= 1e-8f) ? (gq[i] - qh[i] * dots[1]) / qn : gq[i] * 1e8f;
+                st_from_float(orow + j, dk);
+                st_from_float(orow + d + j, gv[i]);
+                st_from_float(orow + 2 * d + j, dq);
+            }
+        }
+    }
+    float* dwp = dw_partial + (size_t)blockIdx.x * 3 * 2 * d;
+#pragma unroll
+    for (int g = 0; g < 3; g++)
+#pragma unroll
+        for (int i = 0; i < NE; i++) {
+            const int j = threadIdx.x + i * WR_THREADS;
+            if (j < d) { dwp[(size_t)g * 2 * d + j] = dwk[g][i]; dwp[(size_t)g * 2 * d + d + j] = dwv[g][i]; }
+        }
+    if (threadIdx.x == 0) {
+        db_partial[blockIdx.x * 3 + 0] = db[0];
+        db_partial[blockIdx.x * 3 + 1] = db[1];
+        db_partial[blockIdx.x * 3 + 2] = db[2];
+    }
+}
+
+
+// ───────────────────────── MAG combine ────────────────────────────────────
+struct CombineLevels {
+    const float* y[WR_MAX_LEVELS];   // per-head level outputs [B*H, S/c, hd]
+    int c[WR_MAX_LEVELS];            // pooling factor of the level (tokens per level token)
+    int k;
+};
+
+// y_comb for 4 consecutive channels j..j+3 of token (b,t)
+__device__ __forceinline__ float4 combine_y(const CombineLevels& L, const float* __restrict__ wts,
+                                            int b, int t, int j, int S, int H, int hd)
+{
+    const int h = j / hd, w = j - h * hd;
+    float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int l = 0; l < L.k; l++) {
+        const int sfl = S / L.c[l];
+        const float4 v = *reinterpret_cast<const float4*>(
+            L.y[l] + (((size_t)b * H + h) * sfl + t / L.c[l]) * hd + w);
+        const float wl = wts[l];
+        y.x += wl * v.x; y.y += wl * v.y; y.z += wl * v.z; y.w += wl * v.w;
+    }
+    return y;
+}
+
+template <typename TIN>
+__device__ __forceinline__ float4 ld4(const TIN* p);
+template <>
+__device__ __forceinline__ float4 ld4<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <>
+__device__ __forceinline__ float4 ld4<__nv_bfloat16>(const __nv_bfloat16* p)
+{
+    const uint2 r = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&r.x);
+    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&r.y);
+    return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+__device__ __forceinline__ void st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void st4(__nv_bfloat16* p, float4 v)
+{
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 r;
+    r.x = *reinterpret_cast<unsigned*>(&a); r.y = *reinterpret_cast<unsigned*>(&b);
+    *reinterpret_cast<uint2*>(p) = r;
+}
+
+// out = x + attn_proj * sigmoid(y_comb)
+template <typename TIN>
+__global__ void __launch_bounds__(256) mag_combine_fwd_kernel(
+    const float* __restrict__ x, const TIN* __restrict__ attn_proj, const float* __restrict__ wts,
+    CombineLevels L, float* __restrict__ out, int B, int S, int d, int H)
+{
+    const int hd = d / H, d4 = d / 4;
+    const long long n4 = (long long)B * S * d4;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int j = (int)(i % d4) * 4;
+        const long long bt = i / d4;
+        const int t = (int)(bt % S), b = (int)(bt / S);
+        const float4 y = combine_y(L, wts, b, t, j, S, H, hd);
+        const float4 xa = ld4<float>(x + i * 4), ap = ld4<TIN>(attn_proj + i * 4);
+        float4 o;
+        o.x = xa.x + ap.x * wr_sigmoid(y.x); o.y = xa.y + ap.y * wr_sigmoid(y.y);
+        o.z = xa.z + ap.z * wr_sigmoid(y.z); o.w = xa.w + ap.w * wr_sigmoid(y.w);
+        st4(out + i * 4, o);
+    }
+}
+
+// d_attn_proj = d_out * gate ; d_ycomb = d_out * attn_proj * gate * (1 - gate) ;
+// dw_partial[cta][l] = sum d_ycomb * upsample(y_l)   (gradient of the level weights)
+template <typename TIN>
+__global__ void __launch_bounds__(256) mag_combine_bwd_kernel(
+    const float* __restrict__ d_out, const TIN* __restrict__ attn_proj, const float* __restrict__ wts,
+    CombineLevels L, TIN* __restrict__ d_attn_proj, float* __restrict__ d_ycomb,
+    float* __restrict__ dw_partial, int B, int S, int d, int H)
+{
+    __shared__ float red[WR_MAX_LEVELS * 32];
+    const int hd = d / H, d4 = d / 4;
+    const long long n4 = (long long)B * S * d4;
+    float dw[WR_MAX_LEVELS] = {0.f, 0.f, 0.f, 0.f};
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int j = (int)(i % d4) * 4;
+        const long long bt = i / d4;
+        const int t = (int)(bt % S), b = (int)(bt / S);
+        const int h = j / hd, w = j - h * hd;
+        float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
+        float4 yl[WR_MAX_LEVELS];
+#pragma unroll
+        for (int l = 0; l < WR_MAX_LEVELS; l++) {
+            if (l < L.k) {
+                const int sfl = S / L.c[l];
+                yl[l] = *reinterpret_cast<const float4*>(
+                    L.y[l] + (((size_t)b * H + h) * sfl + t / L.c[l]) * hd + w);
+                const float wl = wts[l];
+                y.x += wl * yl[l].x; y.y += wl * yl[l].y; y.z += wl * yl[l].z; y.w += wl * yl[l].w;
+            }
+        }
+        const float4 go = ld4<float>(d_out + i * 4), ap = ld4<TIN>(attn_proj + i * 4);
+        float4 g, dap, dy;
+        g.x = wr_sigmoid(y.x); g.y = wr_sigmoid(y.y); g.z = wr_sigmoid(y.z); g.w = wr_sigmoid(y.w);
+        dap.x = go.x * g.x; dap.y = go.y * g.y; dap.z = go.z * g.z; dap.w = go.w * g.w;
+        dy.x = go.x * ap.x * g.x * (1.f - g.x); dy.y = go.y * ap.y * g.y * (1.f - g.y);
+        dy.z = go.z * ap.z * g.z * (1.f - g.z); dy.w = go.w * ap.w * g.w * (1.f - g.w);
+        st4(d_attn_proj + i * 4, dap);
+        st4(d_ycomb + i * 4, dy);
+#pragma unroll
+        for (int l = 0; l < WR_MAX_LEVELS; l++)
+            if (l < L.k) dw[l] += dy.x * yl[l].x + dy.y * yl[l].y + dy.z * yl[l].z + dy.w * yl[l].w;
+    }
+    block_sum_n<WR_MAX_LEVELS>(dw, red);
+    if (threadIdx.x < WR_MAX_LEVELS) dw_partial[blockIdx.x * WR_MAX_LEVELS + threadIdx.x] = dw[threadIdx.x];
+}
+
+// dy_ph[(b*H+h), t', w] = scale * sum_{i<c} d_ycomb[b, t'*c + i, h*hd + w]  (adjoint of
+// repeat-upsample followed by the level weight), written in the per-head layout.
+__global__ void __launch_bounds__(256) pool_to_heads_kernel(
+    const float* __restrict__ d_ycomb, const float* __restrict__ wts, int level, int c,
+    float* __restrict__ dy_ph, int B, int S, int d, int H)
+{
+    const int hd = d / H, d4 = d / 4, sf = S / c;
+    const long long n4 = (long long)B * sf * d4;
+    const float scale = wts[level];
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int j = (int)(i % d4) * 4;
+        const long long bt = i / d4;
+        const int tp = (int)(bt % sf), b = (int)(bt / sf);
+        const float* src = d_ycomb + ((size_t)b * S + (size_t)tp * c) * d + j;
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int q = 0; q < c; q++) {
+            const float4 v = *reinterpret_cast<const float4*>(src + (size_t)q * d);
+            a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+        }
+        const int h = j / hd, w = j - h * hd;
+        a.x *= scale; a.y *= scale; a.z *= scale; a.w *= scale;
+        *reinterpret_cast<float4*>(dy_ph + (((size_t)b * H + h) * sf + tp) * hd + w) = a;
+    }
+}
+
+static int wr_grid(long long items, int per_cta)
+{
+    long long need = (items + per_cta - 1) / per_cta;
+    if (need < 1) need = 1;
+    const long long cap = 148LL * 16;
+    return (int)(need < cap ? need : cap);
+}
+
+}  // namespace nlh
+
+using namespace nlh;
+
+static int wr_check(const char* where, int B, int S, int d, int H)
+{
+    if (B < 0 || S <= 0 || d <= 0 || H <= 0 || d % H != 0 || (d / H) % 4 != 0 || d > 1024 ||
+        H > WR_THREADS) {
+        record_status(NLH_ERR_INVALID_ARG, where,
+                      "need d_model <= 1024, d_model % num_heads == 0, head_dim % 4 == 0");
+        return NLH_ERR_INVALID_ARG;
+    }
+    return NLH_OK;
+}
+
+extern "C" {
+
+int32_t nlh_level_prep_partial_rows(int32_t n_tokens)
+{
+    return (n_tokens + WR_TOK_PER_CTA - 1) / WR_TOK_PER_CTA;
+}
+
+int32_t nlh_level_prep_forward(const void* kvq, int32_t kvq_is_bf16, const float* w_gates,
+    const float* b_alpha, const float* b_theta, const float* b_eta, float* k_ph, float* v_ph,
+    float* q_ph, float* alpha_ph, float* theta_ph, float* eta_ph, float* k_norm, float* q_norm,
+    int32_t batch, int32_t seq, int32_t d_model, int32_t num_heads)
+{
+    int rc = wr_check("nlh_level_prep_forward", batch, seq, d_model, num_heads);
+    if (rc != NLH_OK || batch == 0) return rc;
+    const int n_tok = batch * seq;
+    const size_t smem = (size_t)(3 * d_model + 8 * 32) * sizeof(float);
+    cudaStream_t st = current_stream();
+    if (kvq_is_bf16)
+        level_prep_fwd_kernel<__nv_bfloat16><<<n_tok, WR_THREADS, smem, st>>>(
+            (const __nv_bfloat16*)kvq, w_gates, b_alpha, b_theta, b_eta, k_ph, v_ph, q_ph, alpha_ph,
+            theta_ph, eta_ph, k_norm, q_norm, seq, d_model, num_heads);
+    else
+        level_prep_fwd_kernel<float><<<n_tok, WR_THREADS, smem, st>>>(
+            (const float*)kvq, w_gates, b_alpha, b_theta, b_eta, k_ph, v_ph, q_ph, alpha_ph,
+            theta_ph, eta_ph, k_norm, q_norm, seq, d_model, num_heads);
+    return check_launch("nlh_level_prep_forward") ? NLH_OK : NLH_ERR_CUDA;
+}
+
+int32_t nlh_level_prep_backward(const float* k_ph, const float* v_ph, const float* q_ph,
+    const float* alpha_ph, const float* theta_ph, const float* eta_ph, const float* k_norm,
+    const float* q_norm, const float* dk_ph, const float* dv_ph, const float* dq_ph,
+    const float* dalpha_ph, const float* dtheta_ph, const float* deta_ph, const float* w_gates,
+    void* d_kvq, int32_t kvq_is_bf16, float* dw_partial, float* db_partial, int32_t batch,
+    int32_t seq, int32_t d_model, int32_t num_heads)
+{
+    int rc = wr_check("nlh_level_prep_backward", batch, seq, d_model, num_heads);
+    if (rc != NLH_OK || batch == 0) return rc;
+    const int n_tok = batch * seq;
+    const int grid = nlh_level_prep_partial_rows(n_tok);
+    const int ne = (d_model + WR_THREADS - 1) / WR_THREADS;
+    cudaStream_t st = current_stream();
+#define NLH_LP_BWD(T, NE)                                                                        \
+    level_prep_bwd_kernel<T, NE><<<grid, WR_THREADS, 0, st>>>(                                   \
+        k_ph, v_ph, q_ph, alpha_ph, theta_ph, eta_ph, k_norm, q_norm, dk_ph, dv_ph, dq_ph,       \
+        dalpha_ph, dtheta_ph, deta_ph, w_gates, (T*)d_kvq, dw_partial, db_partial, n_tok, seq,   \
+        d_model, num_heads)
+    if (kvq_is_bf16) {
+        if (ne <= 1) NLH_LP_BWD(__nv_bfloat16, 1);
+        else if (ne <= 2) NLH_LP_BWD(__nv_bfloat16, 2);
+        else if (ne <= 4) NLH_LP_BWD(__nv_bfloat16, 4);
+        else NLH_LP_BWD(__nv_bfloat16, 8);
+    } else {
+        if (ne <= 1) NLH_LP_BWD(float, 1);
+        else if (ne <= 2) NLH_LP_BWD(float, 2);
+        else if (ne <= 4) NLH_LP_BWD(float, 4);
+        else NLH_LP_BWD(float, 8);
+    }
+#undef NLH_LP_BWD
+    return check_launch("nlh_level_prep_backward") ? NLH_OK : NLH_ERR_CUDA;
+}
+
+static int fill_levels(CombineLevels& L, const float* y0, const float* y1, const float* y2,
+                       const float* y3, int c0, int c1, int c2, int c3, int k, int S)
+{
+    if (k < 1 || k > WR_MAX_LEVELS) return NLH_ERR_INVALID_ARG;
+    const float* ys[4] = {y0, y1, y2, y3};
+    const int cs[4] = {c0, c1, c2, c3};
+    for (int l = 0; l < WR_MAX_LEVELS; l++) {
+        L.y[l] = l < k ? ys[l] : nullptr;
+        L.c[l] = l < k ? cs[l] : 1;
+        if (l < k && (ys[l] == nullptr || cs[l] <= 0 || S % cs[l] != 0)) return NLH_ERR_INVALID_ARG;
+    }
+    L.k = k;
+    return NLH_OK;
+}
+
+int32_t nlh_mag_combine_forward(const float* x, const void* attn_proj, int32_t attn_is_bf16,
+    const float* level_weights, const float* y0, const float* y1, const float* y2, const float* y3,
+    int32_t c0, int32_t c1, int32_t c2, int32_t c3, int32_t k, float* out, int32_t batch,
+    int32_t seq, int32_t d_model, int32_t num_heads)
+{
+    int rc = wr_check("nlh_mag_combine_forward", batch, seq, d_model, num_heads);
+    if (rc != NLH_OK || batch == 0) return rc;
+    CombineLevels L;
+    if (fill_levels(L, y0, y1, y2, y3, c0, c1, c2, c3, k, seq) != NLH_OK) {
+        record_status(NLH_ERR_INVALID_ARG, "nlh_mag_combine_forward", "bad level list");
+        return NLH_ERR_INVALID_ARG;
+    }
+    const long long n4 = (long long)batch * seq * (d_model / 4);
+    const int grid = wr_grid(n4, 256 * 4);
+    cudaStream_t st = current_stream();
+    if (attn_is_bf16)
+        mag_combine_fwd_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
+            x, (const __nv_bfloat16*)attn_proj, level_weights, L, out, batch, seq, d_model, num_heads);
+    else
+        mag_combine_fwd_kernel<float><<<grid, 256, 0, st>>>(
+            x, (const float*)attn_proj, level_weights, L, out, batch, seq, d_model, num_heads);
+    return check_launch("nlh_mag_combine_forward") ? NLH_OK : NLH_ERR_CUDA;
+}
+
+int32_t nlh_mag_combine_backward(const float* d_out, const void* attn_proj, int32_t attn_is_bf16,
+    const float* level_weights, const float* y0, const float* y1, const float* y2, const float* y3,
+    int32_t c0, int32_t c1, int32_t c2, int32_t c3, int32_t k, void* d_attn_proj, float* d_ycomb,
+    float* dw_partial, int32_t n_partial_rows, int32_t batch, int32_t seq, int32_t d_model,
+    int32_t num_heads)
+{
+    int rc = wr_check("nlh_mag_combine_backward", batch, seq, d_model, num_heads);
+    if (rc != NLH_OK || batch == 0) return rc;
+    CombineLevels L;
+    if (n_partial_rows < 1 || fill_levels(L, y0, y1, y2, y3, c0, c1, c2, c3, k, seq) != NLH_OK) {
+        record_status(NLH_ERR_INVALID_ARG, "nlh_mag_combine_backward", "bad level list or partial rows");
+        return NLH_ERR_INVALID_ARG;
+    }
+    cudaStream_t st = current_stream();
+    if (attn_is_bf16)
+        mag_combine_bwd_kernel<__nv_bfloat16><<<n_partial_rows, 256, 0, st>>>(
+            d_out, (const __nv_bfloat16*)attn_proj, level_weights, L, (__nv_bfloat16*)d_attn_proj,
+            d_ycomb, dw_partial, batch, seq, d_model, num_heads);
+    else
+        mag_combine_bwd_kernel<float><<<n_partial_rows, 256, 0, st>>>(
+            d_out, (const float*)attn_proj, level_weights, L, (float*)d_attn_proj, d_ycomb,
+            dw_partial, batch, seq, d_model, num_heads);
+    return check_launch("nlh_mag_combine_backward") ? NLH_OK : NLH_ERR_CUDA;
+}
+
+int32_t nlh_pool_to_heads(const float* d_ycomb, const float* level_weights, int32_t level,
+    int32_t pool, float* dy_ph, int32_t batch, int32_t seq, int32_t d_model, int32_t num_heads)
+{
+    int rc = wr_check("nlh_pool_to_heads", batch, seq, d_model, num_heads);
+    if (rc != NLH_OK || batch == 0) return rc;
+    if (pool <= 0 || seq % pool != 0 || level < 0 || level >= WR_MAX_LEVELS) {
+        record_status(NLH_ERR_INVALID_ARG, "nlh_pool_to_heads", "bad pool factor or level");
+        return NLH_ERR_INVALID_ARG;
+    }
+    const long long n4 = (long long)batch * (seq / pool) * (d_model / 4);
+    pool_to_heads_kernel<<<wr_grid(n4, 256), 256, 0, current_stream()>>>(
+        d_ycomb, level_weights, level, pool, dy_ph, batch, seq, d_model, num_heads);
+    return check_launch("nlh_pool_to_heads") ? NLH_OK : NLH_ERR_CUDA;
+}
+
+}  // extern "C"

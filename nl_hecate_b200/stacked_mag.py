@@ -59,6 +59,7 @@ class StackedMAGConfig:
     weight_decay: float = 0.1
     max_grad_norm: float = 1.0
     tie_embeddings: bool = True
+    fused_glue: bool = True           # fused CUDA rule wrapper / MAG combine (CUDA only)
 
     @property
     def head_dim(self):
@@ -110,6 +111,98 @@ class _SWA(torch.autograd.Function):
         nh, hd, w = ctx.cfg
         dq, dk, dv = D.swa_backward_lse(q, k, v, out, lse, d_out.float().contiguous(), nh, hd, w)
         return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), None, None, None
+
+
+class _LevelPrep(torch.autograd.Function):
+    """kvq [B, s, 3d] (k|v|q rows from the projection GEMM) -> per-head k,v,q and gates
+    (nlh_level_prep_forward / _backward): L2 norm of k,q over d_model, the three gates, head
+    split, and in backward the gate/L2-norm/transposes adjoints plus gate weight gradients."""
+
+    @staticmethod
+    def forward(ctx, kvq, w_gates, b_alpha, b_theta, b_eta, num_heads):
+        kvq = kvq.contiguous()
+        B, sf, d3 = kvq.shape
+        d, H = d3 // 3, num_heads
+        hd, dev = d // H, kvq.device
+        f32 = lambda *sh: torch.empty(*sh, dtype=torch.float32, device=dev)
+        k_ph, v_ph, q_ph = f32(B * H, sf, hd), f32(B * H, sf, hd), f32(B * H, sf, hd)
+        al, th, et = f32(B * H, sf), f32(B * H, sf), f32(B * H, sf)
+        kn, qn = f32(B * sf), f32(B * sf)
+        is_bf16 = int(kvq.dtype == torch.bfloat16)
+        D.call("nlh_level_prep_forward", kvq=kvq, kvq_is_bf16=is_bf16, w_gates=w_gates,
+               b_alpha=b_alpha, b_theta=b_theta, b_eta=b_eta, k_ph=k_ph, v_ph=v_ph, q_ph=q_ph,
+               alpha_ph=al, theta_ph=th, eta_ph=et, k_norm=kn, q_norm=qn, batch=B, seq=sf,
+               d_model=d, num_heads=H)
+        ctx.save_for_backward(k_ph, v_ph, q_ph, al, th, et, kn, qn, w_gates)
+        ctx.meta = (B, sf, d, H, is_bf16, kvq.dtype)
+        return k_ph, v_ph, q_ph, al, th, et
+
+    @staticmethod
+    def backward(ctx, dk, dv, dq, da, dt, de):
+        k_ph, v_ph, q_ph, al, th, et, kn, qn, w_gates = ctx.saved_tensors
+        B, sf, d, H, is_bf16, dtype = ctx.meta
+        dev = k_ph.device
+        z = lambda g, like: torch.zeros_like(like) if g is None else g.contiguous()
+        dk, dv, dq = z(dk, k_ph), z(dv, v_ph), z(dq, q_ph)
+        da, dt, de = z(da, al), z(dt, th), z(de, et)
+        rows = int(D.ffi.lib().nlh_level_prep_partial_rows(B * sf))
+        d_kvq = torch.empty(B, sf, 3 * d, dtype=dtype, device=dev)
+        dwp = torch.empty(rows, 3, 2 * d, dtype=torch.float32, device=dev)
+        dbp = torch.empty(rows, 3, dtype=torch.float32, device=dev)
+        D.call("nlh_level_prep_backward", k_ph=k_ph, v_ph=v_ph, q_ph=q_ph, alpha_ph=al, theta_ph=th,
+               eta_ph=et, k_norm=kn, q_norm=qn, dk_ph=dk, dv_ph=dv, dq_ph=dq, dalpha_ph=da,
+               dtheta_ph=dt, deta_ph=de, w_gates=w_gates, d_kvq=d_kvq, kvq_is_bf16=is_bf16,
+               dw_partial=dwp, db_partial=dbp, batch=B, seq=sf, d_model=d, num_heads=H)
+        dw = dwp.sum(0)
+        db = dbp.sum(0)
+        return d_kvq, dw, db[0:1], db[1:2], db[2:3], None
+
+
+class _MagCombine(torch.autograd.Function):
+    """out = x + attn_proj * sigmoid(sum_l w_l upsample(y_l)) on per-head level outputs
+    (nlh_mag_combine_forward / _backward + nlh_pool_to_heads)."""
+    ROWS = 148 * 8
+
+    @staticmethod
+    def forward(ctx, x, attn_proj, wts, pools, num_heads, *ys):
+        x, attn_proj, wts = x.contiguous(), attn_proj.contiguous(), wts.contiguous().float()
+        B, S, d = x.shape
+        k = len(ys)
+        ys = [y.contiguous() for y in ys]
+        yp = ys + [None] * (4 - k)
+        cp = list(pools) + [1] * (4 - k)
+        out = torch.empty_like(x)
+        is_bf16 = int(attn_proj.dtype == torch.bfloat16)
+        D.call("nlh_mag_combine_forward", x=x, attn_proj=attn_proj, attn_is_bf16=is_bf16,
+               level_weights=wts, y0=yp[0], y1=yp[1], y2=yp[2], y3=yp[3], c0=cp[0], c1=cp[1],
+               c2=cp[2], c3=cp[3], k=k, out=out, batch=B, seq=S, d_model=d, num_heads=num_heads)
+        ctx.save_for_backward(attn_proj, wts, *ys)
+        ctx.meta = (B, S, d, num_heads, k, cp, is_bf16)
+        return out
+
+    @staticmethod
+    def backward(ctx, d_out):
+        attn_proj, wts, *ys = ctx.saved_tensors
+        B, S, d, H, k, cp, is_bf16 = ctx.meta
+        d_out = d_out.contiguous()
+        dev = d_out.device
+        yp = list(ys) + [None] * (4 - k)
+        d_ap = torch.empty_like(attn_proj)
+        d_yc = torch.empty(B, S, d, dtype=torch.float32, device=dev)
+        rows = _MagCombine.ROWS
+        dwp = torch.empty(rows, 4, dtype=torch.float32, device=dev)
+        D.call("nlh_mag_combine_backward", d_out=d_out, attn_proj=attn_proj, attn_is_bf16=is_bf16,
+               level_weights=wts, y0=yp[0], y1=yp[1], y2=yp[2], y3=yp[3], c0=cp[0], c1=cp[1],
+               c2=cp[2], c3=cp[3], k=k, d_attn_proj=d_ap, d_ycomb=d_yc, dw_partial=dwp,
+               n_partial_rows=rows, batch=B, seq=S, d_model=d, num_heads=H)
+        d_wts = dwp.sum(0)[:k]
+        dys = []
+        for l in range(k):
+            dy = torch.empty_like(ys[l])
+            D.call("nlh_pool_to_heads", d_ycomb=d_yc, level_weights=wts, level=l, pool=cp[l],
+                   dy_ph=dy, batch=B, seq=S, d_model=d, num_heads=H)
+            dys.append(dy)
+        return (d_out, d_ap, d_wts, None, None, *dys)
 
 
 def titans_memory(k, v, q, alpha, theta, eta, m0, chunk):
@@ -230,9 +323,28 @@ class StackedMAG:
         y = y.view(B, nh, sf, hd).permute(0, 2, 1, 3).reshape(B, sf, d)
         return y.repeat_interleave(c, dim=1) if c > 1 else y
 
+    def _level_fused(self, b, l, m_in):
+        """Level through the fused wrapper kernels; returns the per-head output and the pool factor."""
+        cfg, p = self.cfg, self.p
+        B, S, d = m_in.shape
+        c = min(cfg.chunk_sizes[l], S)
+        assert S % c == 0, "seq_len must be a multiple of every chunk size"
+        sf = S // c
+        x = m_in.view(B, sf, c, d).mean(2) if c > 1 else m_in
+        pre = f"b{b}.l{l}."
+        kvq = self._mm(x, p[pre + "w_kvq_mem"])
+        k, v, q, alpha, theta, eta = _LevelPrep.apply(kvq, p[pre + "w_gates"], p[pre + "b_alpha"],
+                                                      p[pre + "b_theta"], p[pre + "b_eta"],
+                                                      cfg.num_heads)
+        chunk = 0 if l in cfg.exact_levels else min(cfg.chunk_sizes[l], sf)
+        y, m_final = self.memory_fn(k, v, q, alpha, theta, eta, self.context[b][l], chunk)
+        self.context[b][l] = m_final.detach()
+        return y, c
+
     def forward(self, tokens, targets):
         cfg, p = self.cfg, self.p
         d, nh, hd = cfg.d_model, cfg.num_heads, cfg.head_dim
+        fused = (cfg.fused_glue and tokens.is_cuda and cfg.k <= 4 and d <= 1024 and hd % 4 == 0)
         x = F.embedding(tokens, p["w_embed"])
         for b in range(cfg.n_blocks):
             pre = f"b{b}."
@@ -240,15 +352,23 @@ class StackedMAG:
             qkv = self._mm(h, p[pre + "w_qkv"]).to(torch.bfloat16)
             q, k, v = (t.contiguous() for t in qkv.split(d, dim=-1))
             attn = self.swa_fn(q, k, v, nh, hd, cfg.window)
-            attn_proj = self._mm(attn, p[pre + "w_o"]).float()
-            res1 = x + attn_proj
+            attn_raw = self._mm(attn, p[pre + "w_o"])
+            res1 = x + attn_raw
             m_in = F.layer_norm(res1, (d,), p[pre + "ln_mem_gamma"], p[pre + "ln_mem_beta"], 1e-5)
             wts = torch.softmax(p[pre + "alpha_mem"], dim=0)
-            y = None
-            for l in range(cfg.k):
-                yl = self._level(b, l, m_in) * wts[l]
-                y = yl if y is None else y + yl
-            x = x + attn_proj * torch.sigmoid(y)
+            if fused:
+                ys, pools = [], []
+                for l in range(cfg.k):
+                    y_ph, c = self._level_fused(b, l, m_in)
+                    ys.append(y_ph); pools.append(c)
+                x = _MagCombine.apply(x, attn_raw, wts, tuple(pools), nh, *ys)
+            else:
+                attn_proj = attn_raw.float()
+                y = None
+                for l in range(cfg.k):
+                    yl = self._level(b, l, m_in) * wts[l]
+                    y = yl if y is None else y + yl
+                x = x + attn_proj * torch.sigmoid(y)
         x = F.layer_norm(x, (d,), p["ln_final_gamma"], p["ln_final_beta"], 1e-5)
         logits = self._mm(x, p["w_unembed"].t()).float()
         return F.cross_entropy(logits.view(-1, cfg.vocab), targets.reshape(-1))

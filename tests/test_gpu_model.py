@@ -14,10 +14,10 @@ from torch_ref import swa_ref, titans_memory_ref  # noqa: E402
 pytestmark = pytest.mark.gpu
 
 
-def _cfg(bf16):
+def _cfg(bf16, fused=True):
     from nl_hecate_b200.stacked_mag import StackedMAGConfig
     return StackedMAGConfig(d_model=128, num_heads=2, n_blocks=2, k=3, chunk_sizes=(1, 4, 16),
-                            seq_len=32, window=16, vocab=96, bf16=bf16)
+                            seq_len=32, window=16, vocab=96, bf16=bf16, fused_glue=fused)
 
 
 def _data(batch, seed=0):
@@ -63,7 +63,8 @@ def test_memory_kernels_inside_the_model_match_torch_reference():
     from nl_hecate_b200.stacked_mag import StackedMAG
     tok, tgt = _data(3)
     ours = StackedMAG(_cfg(False), 3, device="cuda", seed=1, swa_fn=swa_ref)
-    ref = StackedMAG(_cfg(False), 3, device="cuda", seed=1, memory_fn=titans_memory_ref, swa_fn=swa_ref)
+    ref = StackedMAG(_cfg(False, fused=False), 3, device="cuda", seed=1, memory_fn=titans_memory_ref,
+                     swa_fn=swa_ref)
     assert torch.equal(ours.opt.w, ref.opt.w)
     _compare(ours, ref, tok, tgt, 1e-5, 2e-3)
 
@@ -78,7 +79,8 @@ def test_full_kernel_path_matches_torch_reference_at_bf16_bar(bf16):
     from nl_hecate_b200.stacked_mag import StackedMAG
     tok, tgt = _data(3)
     ours = StackedMAG(_cfg(bf16), 3, device="cuda", seed=1)
-    ref = StackedMAG(_cfg(bf16), 3, device="cuda", seed=1, memory_fn=titans_memory_ref, swa_fn=swa_ref)
+    ref = StackedMAG(_cfg(bf16, fused=False), 3, device="cuda", seed=1, memory_fn=titans_memory_ref,
+                     swa_fn=swa_ref)
     _compare(ours, ref, tok, tgt, 1e-3, 5e-2, l2=True)
 
 
@@ -99,3 +101,20 @@ def test_training_steps_reduce_loss_and_tie_embeddings():
     for n, w in m.p.items():
         if n.endswith("b_theta"):
             assert -10.0 <= float(w.detach()) <= 2.0
+
+
+@pytest.mark.parametrize("bf16", [False, True])
+def test_fused_glue_matches_torch_glue(bf16):
+    """Same kernels for memory and SWA in both models; only the rule wrapper / MAG combine differ
+    (fused CUDA kernels vs PyTorch ops). fp32: gradients within 1e-3 of each tensor's largest
+    entry; bf16: within 3e-2 in relative L2 norm (the fused path rounds d_kvq to bf16 once)."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from nl_hecate_b200.stacked_mag import StackedMAG
+    tok, tgt = _data(3)
+    fused = StackedMAG(_cfg(bf16, True), 3, device="cuda", seed=2)
+    plain = StackedMAG(_cfg(bf16, False), 3, device="cuda", seed=2)
+    if bf16:
+        _compare(fused, plain, tok, tgt, 1e-3, 3e-2, l2=True)
+    else:
+        _compare(fused, plain, tok, tgt, 1e-5, 1e-3)

@@ -1,0 +1,108 @@
+"""GPU: fused rule-wrapper kernels (level prep, MAG combine, pool-to-heads) through the C ABI
+vs the same math written with PyTorch ops and autograd (fp32, relative error <= 1e-4)."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    return float((a.float() - b.float()).abs().max() / b.float().abs().max().clamp_min(1e-12))
+
+
+def _torch_level_prep(kvq, w_gates, b_a, b_t, b_e, H):
+    B, sf, d3 = kvq.shape
+    d = d3 // 3
+    hd = d // H
+    k, v, q = kvq.float().split(d, dim=-1)
+    k = k / k.norm(dim=-1, keepdim=True).clamp_min(1e-8)
+    q = q / q.norm(dim=-1, keepdim=True).clamp_min(1e-8)
+    pre = torch.cat([k, v], -1) @ w_gates.t()
+    al = torch.sigmoid(pre[..., 0] + b_a)
+    th = F.softplus(pre[..., 1] + b_t)
+    et = torch.sigmoid(pre[..., 2] + b_e)
+    heads = lambda t: t.reshape(B, sf, H, hd).permute(0, 2, 1, 3).reshape(B * H, sf, hd)
+    bro = lambda t: t.unsqueeze(1).expand(B, H, sf).reshape(B * H, sf)
+    return heads(k), heads(v), heads(q), bro(al), bro(th), bro(et)
+
+
+@pytest.mark.parametrize("B,sf,d,H", [(2, 5, 128, 2), (3, 33, 512, 8), (1, 1, 64, 1), (2, 40, 192, 3)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_level_prep_forward_backward(B, sf, d, H, dtype):
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from nl_hecate_b200.stacked_mag import _LevelPrep
+    g = torch.Generator(device="cuda").manual_seed(B * 100 + sf)
+    r = lambda *sh: torch.randn(*sh, generator=g, device="cuda")
+    kvq = r(B, sf, 3 * d).to(dtype)
+    w = 0.05 * r(3, 2 * d)
+    ba, bt, be = r(1), r(1) - 2.0, r(1)
+    ups = [r(B * H, sf, d // H) for _ in range(3)] + [r(B * H, sf) for _ in range(3)]
+
+    def run(fn):
+        leaves = [t.clone().requires_grad_(True) for t in (kvq, w, ba, bt, be)]
+        outs = fn(*leaves)
+        loss = sum((o * u).sum() for o, u in zip(outs, ups))
+        loss.backward()
+        return [o.detach() for o in outs], [t.grad for t in leaves]
+
+    o1, g1 = run(lambda kvq_, w_, a_, t_, e_: _LevelPrep.apply(kvq_, w_, a_, t_, e_, H))
+    o2, g2 = run(lambda kvq_, w_, a_, t_, e_: _torch_level_prep(kvq_, w_, a_, t_, e_, H))
+    for a, b in zip(o1, o2):
+        assert _rel(a, b) <= 1e-5
+    tol = 1e-4 if dtype == torch.float32 else 1e-2   # d_kvq is rounded to bf16 in that mode
+    for name, a, b in zip(("d_kvq", "d_w_gates", "d_b_alpha", "d_b_theta", "d_b_eta"), g1, g2):
+        assert a.dtype == b.dtype
+        assert _rel(a, b) <= (tol if name == "d_kvq" else 1e-4), (name, _rel(a, b))
+
+
+def _torch_combine(x, ap, wts, pools, H, ys):
+    B, S, d = x.shape
+    hd = d // H
+    y = 0
+    for l, (yl, c) in enumerate(zip(ys, pools)):
+        sf = S // c
+        full = yl.view(B, H, sf, hd).permute(0, 2, 1, 3).reshape(B, sf, d).repeat_interleave(c, dim=1)
+        y = y + wts[l] * full
+    return x + ap.float() * torch.sigmoid(y)
+
+
+@pytest.mark.parametrize("B,S,d,H,pools", [(2, 16, 128, 2, (1, 4, 16)), (2, 64, 512, 8, (1, 8, 64, 64)),
+                                           (1, 8, 64, 1, (1,)), (3, 24, 192, 3, (1, 2, 8, 24))])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_mag_combine_forward_backward(B, S, d, H, pools, dtype):
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from nl_hecate_b200.stacked_mag import _MagCombine
+    g = torch.Generator(device="cuda").manual_seed(S + d)
+    r = lambda *sh: torch.randn(*sh, generator=g, device="cuda")
+    x, ap = r(B, S, d), r(B, S, d).to(dtype)
+    alpha_mem = r(len(pools))
+    ys = [r(B * H, S // c, d // H) for c in pools]
+    up = r(B, S, d)
+
+    def run(fn):
+        leaves = [t.clone().requires_grad_(True) for t in [x, ap, alpha_mem] + ys]
+        wts = torch.softmax(leaves[2], 0)
+        out = fn(leaves[0], leaves[1], wts, leaves[3:])
+        (out * up).sum().backward()
+        return out.detach(), [t.grad for t in leaves]
+
+    o1, g1 = run(lambda x_, ap_, w_, ys_: _MagCombine.apply(x_, ap_, w_, pools, H, *ys_))
+    o2, g2 = run(lambda x_, ap_, w_, ys_: _torch_combine(x_, ap_, w_, pools, H, ys_))
+    assert _rel(o1, o2) <= 1e-5
+    names = ["d_x", "d_attn_proj", "d_alpha_mem"] + [f"d_y{l}" for l in range(len(pools))]
+    for name, a, b in zip(names, g1, g2):
+        tol = 1e-2 if (name == "d_attn_proj" and dtype == torch.bfloat16) else 1e-4
+        assert _rel(a, b) <= tol, (name, _rel(a, b))
+
+
+def test_wrapper_rejects_unsupported_shapes():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from nl_hecate_b200 import dispatch as D
+    z = torch.zeros(16, device="cuda")
+    with pytest.raises(RuntimeError):   # head_dim 6 is not a multiple of 4
+        D.call("nlh_pool_to_heads", d_ycomb=z, level_weights=z, level=0, pool=1, dy_ph=z, batch=1,
+               seq=1, d_model=12, num_heads=2)
