@@ -416,20 +416,26 @@ class StackedModelStep:
         self.host_tgt = torch.from_numpy(np.ascontiguousarray(ids[:, 1:])).pin_memory()
         self.tok, self.tgt = self.host_tok.cuda(), self.host_tgt.cuda()
         self.host_loss = torch.empty(1, dtype=torch.float32).pin_memory()
-        # hot-path launches per step: per block 1 SWA fwd + 3 SWA bwd + 4 levels x (fwd + bwd),
-        # plus norm (2) + AdamW (1)
-        self.launches_per_step = self.cfg.n_blocks * (4 + 2 * self.cfg.k) + 3
+        # this library's launches per step: per block SWA fwd (1) + bwd (3), MAG combine fwd+bwd (2),
+        # per level: prep fwd+bwd (2), memory fwd+bwd (2), pool-to-heads (1); norm (2) + AdamW (1)
+        self.launches_per_step = self.cfg.n_blocks * (4 + 2 + 5 * self.cfg.k) + 3
         self.h2d = self.host_tok.numel() * 8 * 2
         self.d2h = 4
         self.pg = None
+        self.use_graph = os.environ.get("NLH_BENCH_NO_GRAPH", "0") != "1"
 
     def step(self):
+        if self.use_graph:
+            return self.model.step_graphed(self.tok, self.tgt, self.pg, self.world)
         return self.model.step(self.tok, self.tgt, self.pg, self.world)
 
     def step_e2e(self):
-        tok = self.host_tok.cuda(non_blocking=True)
-        tgt = self.host_tgt.cuda(non_blocking=True)
-        loss = self.model.step(tok, tgt, self.pg, self.world)
+        if self.use_graph:   # pinned host ids -> static device buffers -> graph replay -> loss to host
+            loss = self.model.step_graphed(self.host_tok, self.host_tgt, self.pg, self.world)
+        else:
+            tok = self.host_tok.cuda(non_blocking=True)
+            tgt = self.host_tgt.cuda(non_blocking=True)
+            loss = self.model.step(tok, tgt, self.pg, self.world)
         self.host_loss.copy_(loss.reshape(1), non_blocking=True)
 
     def dominant(self):
@@ -442,11 +448,12 @@ class StackedModelStep:
         k, v, q, dy = (torch.nn.functional.normalize(r(n, s, d), dim=-1) for _ in range(4))
         al, th, et = (torch.sigmoid(r(n, s)) for _ in range(3))
         m0 = torch.zeros(n, d * d, device="cuda")
-        ms, ss, _ = self.dd.titans_forward_dd(k, v, q, al, th, et, m0, m0)
-        bytes_ = (4 + 3) * n * s * d * 4 + 6 * n * s * 4 + 2 * n * (s + 1) * d * d * 4
-        self._dom = (k, v, q, al, th, et, ms, ss, dy)
-        return ("fast_bwd_kernel<64,TITANS,exact> at level-0 shapes",
-                lambda: self.dd.titans_backward_dd(k, v, q, al, th, et, ms, ss, dy), bytes_, "hbm")
+        # as the model runs it: M trajectory only (s_states = NULL), S derived in the kernel
+        ms, _, _ = self.dd.titans_forward_dd(k, v, q, al, th, et, m0, m0, store_s=False)
+        bytes_ = (4 + 3) * n * s * d * 4 + 6 * n * s * 4 + n * (s + 1) * d * d * 4
+        self._dom = (k, v, q, al, th, et, ms, dy)
+        return ("fast_bwd_kernel<64,TITANS,exact,S-derived> at level-0 shapes",
+                lambda: self.dd.titans_backward_dd(k, v, q, al, th, et, ms, None, dy), bytes_, "hbm")
 
     def cpu_sample(self, oracle, threads, budget_s=12.0):
         """Hot-path operators of the step on the host: per sequence and block, SWA fwd+bwd and the

@@ -63,7 +63,9 @@ void delta_backward_f32_cuda(const float* k_mem, const float* v_mem, const float
     float* d_k_mem, float* d_v_mem, float* d_q_mem, float* d_alpha, float* d_theta,
     float* d_m_initial, int32_t seq_len, int32_t d, int32_t batch_size, float error_clip);
 /* cuda_ffi.rs:134 / :156 — Titans LMM. d_m_initial/d_s_initial [d*d] are summed
- * over the batch (caller zeroes). */
+ * over the batch (caller zeroes). Additive: s_states may be NULL in both calls (head_dim 32/64,
+ * no clip/projection): the forward then writes only the M trajectory and the backward derives
+ * S_t = M_t - (1-alpha_{t-1}) M_{t-1} from it (needs eta_t > 0), halving the state traffic. */
 void titans_forward_f32_cuda(const float* k_mem, const float* v_mem, const float* q_mem,
     const float* alpha, const float* theta, const float* eta, const float* m_initial,
     const float* s_initial, float* m_states, float* s_states, float* y, int32_t seq_len, int32_t d,

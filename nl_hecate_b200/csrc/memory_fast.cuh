@@ -254,7 +254,8 @@ __global__ void __launch_bounds__(FastGeom<D>::NT) fast_fwd_kernel(FwdArgs a)
     const float* eta = (RULE == RULE_TITANS) ? a.eta + (size_t)b * a.in_stride_tok : nullptr;
     float* y = a.y + (size_t)b * a.seq_len * D;
     float* m_out = a.m_out + (size_t)b * a.out_stride;
-    float* s_out = (RULE == RULE_TITANS) ? a.s_out + (size_t)b * a.out_stride : nullptr;
+    // s_out == NULL: the momentum trajectory is not stored (the backward derives S from M)
+    float* s_out = (RULE == RULE_TITANS && a.s_out != nullptr) ? a.s_out + (size_t)b * a.out_stride : nullptr;
     const int mode = a.store_mode;
 
     float M[16], S[16], M0[16];
@@ -268,7 +269,7 @@ __global__ void __launch_bounds__(FastGeom<D>::NT) fast_fwd_kernel(FwdArgs a)
     for (int i = 0; i < 16; i++) M0[i] = M[i];
     if (mode == STORE_ALL || mode == STORE_CKPT) {
         store_state16<D>(M, m_out, r, cg);
-        if (RULE == RULE_TITANS) store_state16<D>(S, s_out, r, cg);
+        if (RULE == RULE_TITANS && s_out != nullptr) store_state16<D>(S, s_out, r, cg);
     }
 
     const int ntiles = (a.seq_len + TT - 1) / TT;
@@ -304,7 +305,7 @@ __global__ void __launch_bounds__(FastGeom<D>::NT) fast_fwd_kernel(FwdArgs a)
             if (mode == STORE_CHUNK && (t % a.interval) == 0) {
                 const size_t off = (size_t)(t / a.interval) * dd;
                 store_state16<D>(M, m_out + off, r, cg);
-                if (RULE == RULE_TITANS) store_state16<D>(S, s_out + off, r, cg);
+                if (RULE == RULE_TITANS && s_out != nullptr) store_state16<D>(S, s_out + off, r, cg);
                 if (FROZEN) {
 #pragma unroll
                     for (int i = 0; i < 16; i++) M0[i] = M[i];
@@ -317,10 +318,10 @@ __global__ void __launch_bounds__(FastGeom<D>::NT) fast_fwd_kernel(FwdArgs a)
             else fast_fwd_token<D, RULE>(M, S, M, kb + tl * D, vb[tl * D + r], al, th, et, cg);
             if (mode == STORE_ALL) {
                 store_state16<D>(M, m_out + (size_t)(t + 1) * dd, r, cg);
-                if (RULE == RULE_TITANS) store_state16<D>(S, s_out + (size_t)(t + 1) * dd, r, cg);
+                if (RULE == RULE_TITANS && s_out != nullptr) store_state16<D>(S, s_out + (size_t)(t + 1) * dd, r, cg);
             } else if (mode == STORE_CKPT && (((t + 1) % a.interval) == 0 || t + 1 == a.seq_len)) {
                 store_state16<D>(M, m_out + (size_t)slot * dd, r, cg);
-                if (RULE == RULE_TITANS) store_state16<D>(S, s_out + (size_t)slot * dd, r, cg);
+                if (RULE == RULE_TITANS && s_out != nullptr) store_state16<D>(S, s_out + (size_t)slot * dd, r, cg);
                 slot++;
             }
             const float yv = fast_readout<D>(M, qb + tl * D, cg);
@@ -337,10 +338,10 @@ __global__ void __launch_bounds__(FastGeom<D>::NT) fast_fwd_kernel(FwdArgs a)
     if (mode == STORE_CHUNK) {
         const size_t off = (size_t)((a.seq_len + a.interval - 1) / a.interval) * dd;
         store_state16<D>(M, m_out + off, r, cg);
-        if (RULE == RULE_TITANS) store_state16<D>(S, s_out + off, r, cg);
+        if (RULE == RULE_TITANS && s_out != nullptr) store_state16<D>(S, s_out + off, r, cg);
     } else if (mode == STORE_FINAL) {
         store_state16<D>(M, m_out, r, cg);
-        if (RULE == RULE_TITANS) store_state16<D>(S, s_out, r, cg);
+        if (RULE == RULE_TITANS && s_out != nullptr) store_state16<D>(S, s_out, r, cg);
     }
 }
 
@@ -348,7 +349,11 @@ __global__ void __launch_bounds__(FastGeom<D>::NT) fast_fwd_kernel(FwdArgs a)
 // Processes, in reverse, either the token range [t_start,t_end) against a
 // stored trajectory (a.chunk == 0), or every chunk of a.chunk tokens with the
 // chunk trajectory recomputed from its boundary state into scratch (m_rec).
-template <int D, int RULE, bool FROZEN>
+// SDER (Titans, stored-trajectory mode only): no S trajectory is given; since
+// S_{t+1} = M_{t+1} - (1-alpha_t) M_t and S_{t+1} = eta_t S_t - theta_t e k^T,
+//   d_eta_t = <S_t, dS> = ( <M_{t+1} - (1-alpha_t) M_t, dS> + theta_t (e . dS k) ) / eta_t,
+// which needs eta_t > 0 (gates far below ~1e-3 lose accuracy to the division).
+template <int D, int RULE, bool FROZEN, bool SDER = false>
 __global__ void __launch_bounds__(FastGeom<D>::NT) fast_bwd_kernel(BwdArgs a)
 {
     using G = FastGeom<D>;
@@ -382,7 +387,7 @@ __global__ void __launch_bounds__(FastGeom<D>::NT) fast_bwd_kernel(BwdArgs a)
     float* dtheta = (RULE != RULE_HEBBIAN) ? a.d_theta + go : nullptr;
     float* deta = (RULE == RULE_TITANS) ? a.d_eta + go : nullptr;
     const float* mtraj = a.m_traj + (size_t)b * a.traj_stride;
-    const float* straj = (RULE == RULE_TITANS) ? a.s_traj + (size_t)b * a.traj_stride : nullptr;
+    const float* straj = (RULE == RULE_TITANS && !SDER) ? a.s_traj + (size_t)b * a.traj_stride : nullptr;
     const bool recompute = a.chunk > 0;
     float* mrec = recompute ? a.m_rec + (size_t)b * (a.chunk + 1) * dd : nullptr;
     float* srec = (recompute && RULE == RULE_TITANS) ? a.s_rec + (size_t)b * (a.chunk + 1) * dd : nullptr;
@@ -481,7 +486,7 @@ __global__ void __launch_bounds__(FastGeom<D>::NT) fast_bwd_kernel(BwdArgs a)
                     const size_t o = (size_t)r * D + jj * (D / 4) + cg * 4;
                     const int so_ = jj * NT * 4 + tid * 4;
                     cp_async16(dst + so_, mt_base + (size_t)j * dd + o);
-                    if (RULE == RULE_TITANS) cp_async16(dst + dd + so_, st_base + (size_t)j * dd + o);
+                    if (RULE == RULE_TITANS && !SDER) cp_async16(dst + dd + so_, st_base + (size_t)j * dd + o);
                 }
             }
         };
@@ -520,7 +525,7 @@ __global__ void __launch_bounds__(FastGeom<D>::NT) fast_bwd_kernel(BwdArgs a)
                 for (int jj = 0; jj < 4; jj++) {
                     const float4 t4 = *reinterpret_cast<const float4*>(ms + jj * NT * 4 + tid * 4);
                     Mt[4 * jj] = t4.x; Mt[4 * jj + 1] = t4.y; Mt[4 * jj + 2] = t4.z; Mt[4 * jj + 3] = t4.w;
-                    if (RULE == RULE_TITANS) {
+                    if (RULE == RULE_TITANS && !SDER) {
                         const float4 s4 = *reinterpret_cast<const float4*>(ms + dd + jj * NT * 4 + tid * 4);
                         St[4 * jj] = s4.x; St[4 * jj + 1] = s4.y; St[4 * jj + 2] = s4.z; St[4 * jj + 3] = s4.w;
                     }
@@ -534,11 +539,16 @@ __global__ void __launch_bounds__(FastGeom<D>::NT) fast_bwd_kernel(BwdArgs a)
                 const float et = (RULE == RULE_TITANS) ? gb[2 * TB + tl] : 0.f;
 
                 float p = 0.f, u = 0.f, pa = 0.f, pe = 0.f;
+                const float rr0 = 1.0f - al;
 #pragma unroll
                 for (int i = 0; i < 16; i++) {
                     dM[i] += dyr * qq[i];
                     float g = dM[i];
-                    if (RULE == RULE_TITANS) { dS[i] += dM[i]; g = dS[i]; pe += St[i] * dS[i]; }
+                    if (RULE == RULE_TITANS) {
+                        dS[i] += dM[i]; g = dS[i];
+                        if (SDER) pe += (Mn[i] - rr0 * Mt[i]) * dS[i];
+                        else pe += St[i] * dS[i];
+                    }
                     pa += Mt[i] * dM[i];
                     if (RULE != RULE_HEBBIAN && !FROZEN) p += Mt[i] * kk[i];
                     u += g * kk[i];
@@ -553,6 +563,7 @@ __global__ void __launch_bounds__(FastGeom<D>::NT) fast_bwd_kernel(BwdArgs a)
                 // per-thread scalar partials (summed over the CTA at tile end)
                 scp[(0 * TB + tl) * NT + tid] = pa;
                 scp[(1 * TB + tl) * NT + tid] = (RULE != RULE_HEBBIAN && cg == 0) ? e * u : 0.f;
+                if (SDER) pe = (et > 1e-30f) ? (pe + ((cg == 0) ? th * e * u : 0.f)) / et : 0.f;
                 scp[(2 * TB + tl) * NT + tid] = pe;
                 if (cg == 0) dvs[tl * D + r] = (RULE == RULE_HEBBIAN) ? u : th * u;
 
@@ -666,6 +677,7 @@ static bool fast_forward(int rule, const FwdArgs& a, cudaStream_t st)
     const bool al = aligned16(a.k) && aligned16(a.v) && aligned16(a.q) && aligned16(a.y) &&
                     aligned16(a.m_init) && aligned16(a.m_out) &&
                     (rule != RULE_TITANS || (aligned16(a.s_init) && aligned16(a.s_out))) &&
+                    (a.s_out != nullptr || rule != RULE_TITANS || a.store_mode == STORE_ALL) &&
                     (a.init_stride % 4 == 0) && (a.out_stride % 4 == 0);
     if (!al) return false;
     if (a.d == 64) {
@@ -684,6 +696,11 @@ template <int D, int RULE>
 static bool fast_bwd_launch(const BwdArgs& a, cudaStream_t st)
 {
     const size_t smem = fast_bwd_smem_floats<D>() * sizeof(float);
+    if (RULE == RULE_TITANS && a.s_traj == nullptr) {   // checked by the caller: stored-trajectory mode
+        cudaFuncSetAttribute(fast_bwd_kernel<D, RULE, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        fast_bwd_kernel<D, RULE, false, true><<<a.batch, FastGeom<D>::NT, smem, st>>>(a);
+        return true;
+    }
     if (a.frozen) {
         cudaFuncSetAttribute(fast_bwd_kernel<D, RULE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         fast_bwd_kernel<D, RULE, true><<<a.batch, FastGeom<D>::NT, smem, st>>>(a);
@@ -702,6 +719,7 @@ static bool fast_backward(int rule, BwdArgs& a, cudaStream_t st)
     const bool al = aligned16(a.k) && aligned16(a.v) && aligned16(a.q) && aligned16(a.d_y) &&
                     aligned16(a.d_k) && aligned16(a.d_v) && aligned16(a.d_q) && aligned16(a.m_traj) &&
                     (rule != RULE_TITANS || aligned16(a.s_traj)) && (a.traj_stride % 4 == 0) &&
+                    (a.s_traj != nullptr || rule != RULE_TITANS || (a.chunk <= 0 && !a.frozen)) &&
                     aligned16(a.d_m_out) && (rule != RULE_TITANS || aligned16(a.d_s_out)) &&
                     (a.d_m_seed == nullptr || aligned16(a.d_m_seed)) &&
                     (a.d_s_seed == nullptr || aligned16(a.d_s_seed));

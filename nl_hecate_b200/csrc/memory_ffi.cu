@@ -67,6 +67,11 @@ static int run_forward(int rule, FwdArgs a, const char* where)
     }
     cudaStream_t st = current_stream();
     if (fast_forward(rule, a, st)) return check_launch(where) ? NLH_OK : NLH_ERR_CUDA;
+    if (rule == RULE_TITANS && a.s_out == nullptr) {
+        record_status(NLH_ERR_UNSUPPORTED, where,
+                      "s_states == NULL needs the register-resident path (head_dim 32/64, no clip/projection, aligned)");
+        return NLH_ERR_UNSUPPORTED;
+    }
     const size_t dd = (size_t)a.d * a.d;
     if (a.store_mode != STORE_ALL) {
         const size_t per = WsCarver::need((size_t)a.batch * dd);
@@ -94,6 +99,11 @@ static int run_backward(int rule, BwdArgs a, const char* where)
     }
     cudaStream_t st = current_stream();
     if (fast_backward(rule, a, st)) return check_launch(where) ? NLH_OK : NLH_ERR_CUDA;
+    if (rule == RULE_TITANS && a.s_traj == nullptr) {
+        record_status(NLH_ERR_UNSUPPORTED, where,
+                      "s_states == NULL needs the register-resident path (head_dim 32/64, no clip/projection, aligned)");
+        return NLH_ERR_UNSUPPORTED;
+    }
     const size_t dd = (size_t)a.d * a.d;
     const size_t nb = (size_t)a.batch * dd;
     size_t bytes = WsCarver::need(nb) * 3;

@@ -91,10 +91,13 @@ def checkpoint_count(seq_len: int, c: int) -> int:
 # ── memory rules, device tensors ───────────────────────────────────────────
 # Shapes: k,v,q,d_y [N,S,d]; gates [N,S]; m0,s0 [N,d*d]; states [N,(S+1),d*d].
 
-def titans_forward_dd(k, v, q, alpha, theta, eta, m0, s0, error_clip=0.0, m_norm_max=0.0):
+def titans_forward_dd(k, v, q, alpha, theta, eta, m0, s0, error_clip=0.0, m_norm_max=0.0,
+                      store_s=True):
+    """store_s=False passes s_states = NULL: the momentum trajectory is not written (half the
+    HBM traffic); titans_backward_dd(..., ss=None) then derives S_t from consecutive M states."""
     n, s, d = k.shape
     ms = _f32(n, s + 1, d * d, device=k.device)
-    ss = _f32(n, s + 1, d * d, device=k.device)
+    ss = _f32(n, s + 1, d * d, device=k.device) if store_s else None
     y = _f32(n, s, d, device=k.device)
     call("titans_forward_f32_cuda", k_mem=k, v_mem=v, q_mem=q, alpha=alpha, theta=theta, eta=eta,
          m_initial=m0, s_initial=s0, m_states=ms, s_states=ss, y=y, seq_len=s, d=d, batch_size=n,

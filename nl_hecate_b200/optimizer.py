@@ -61,10 +61,10 @@ class FlatAdamW:
         o, n = self.slices[i]
         return arena[o:o + n]
 
-    def step(self, lr, steps, active=None, max_grad_norm=0.0):
-        """One optimizer step. ``steps[i]`` is tensor i's own 1-based step count (bias
-        correction), ``active[i]`` False skips it. Returns the device scalar holding the
-        pre-clip global gradient norm (valid only when max_grad_norm > 0)."""
+    def prepare(self, steps, active=None, lr_scale=1.0):
+        """Host part of a step: fill the per-tensor descriptor table (bias corrections from each
+        tensor's own 1-based step count, activity, clamp, learning-rate scale) in pinned memory.
+        The device reads it in launch(); do not call prepare() again before that copy has run."""
         nt = len(self.sizes)
         active = [True] * nt if active is None else active
         for i in range(nt):
@@ -73,12 +73,17 @@ class FlatAdamW:
             d.bc1_inv = 1.0 / (1.0 - self.beta1 ** t)
             d.bc2_inv = 1.0 / (1.0 - self.beta2 ** t)
             d.weight_decay = 0.0 if i in self.no_decay else self.weight_decay
-            d.lr_scale = 1.0
+            d.lr_scale = lr_scale
             lo, hi = self.clamp.get(i, (0.0, 0.0))
             d.clamp_lo, d.clamp_hi, d.has_clamp = lo, hi, int(i in self.clamp)
             d.active = int(bool(active[i]))
         C.memmove(self._desc_pinned.data_ptr(), C.addressof(self._desc_host),
                   C.sizeof(self._desc_host))
+
+    def launch(self, lr, max_grad_norm=0.0):
+        """Device part of a step (stream-ordered, capturable in a CUDA graph): descriptor upload,
+        global-norm clip scale, multi-tensor AdamW. Returns the device scalar with the pre-clip
+        gradient norm (valid only when max_grad_norm > 0)."""
         self._desc_dev.copy_(self._desc_pinned, non_blocking=True)
         scale_ptr = None
         if max_grad_norm > 0.0:
@@ -92,3 +97,9 @@ class FlatAdamW:
              n_chunks=self.n_chunks, grad_scale_ptr=scale_ptr, lr=lr, beta1=self.beta1,
              beta2=self.beta2, eps=self.eps)
         return self.norm
+
+    def step(self, lr, steps, active=None, max_grad_norm=0.0):
+        """One optimizer step. ``steps[i]`` is tensor i's own 1-based step count (bias
+        correction), ``active[i]`` False skips it."""
+        self.prepare(steps, active)
+        return self.launch(lr, max_grad_norm)

@@ -75,10 +75,12 @@ class _TitansMemory(torch.autograd.Function):
     def forward(ctx, k, v, q, alpha, theta, eta, m0, chunk):
         s0 = torch.zeros_like(m0)     # momentum restarts every call (gpu_forward.rs:1516-1517)
         if chunk == 0:
-            ms, ss, y = D.titans_forward_dd(k, v, q, alpha, theta, eta, m0, s0)
+            # M trajectory only: the backward derives S_t = M_t - (1-alpha_{t-1}) M_{t-1}
+            ms, ss, y = D.titans_forward_dd(k, v, q, alpha, theta, eta, m0, s0, store_s=False)
+            ctx.save_for_backward(k, v, q, alpha, theta, eta, ms)
         else:
             ms, ss, y = D.titans_chunkwise_forward_dd(k, v, q, alpha, theta, eta, m0, s0, chunk)
-        ctx.save_for_backward(k, v, q, alpha, theta, eta, ms, ss)
+            ctx.save_for_backward(k, v, q, alpha, theta, eta, ms, ss)
         ctx.chunk = chunk
         m_final = ms[:, -1].clone()
         ctx.mark_non_differentiable(m_final)
@@ -86,11 +88,12 @@ class _TitansMemory(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy, _dm):
-        k, v, q, alpha, theta, eta, ms, ss = ctx.saved_tensors
         dy = dy.contiguous()
         if ctx.chunk == 0:
-            g = D.titans_backward_dd(k, v, q, alpha, theta, eta, ms, ss, dy)
+            k, v, q, alpha, theta, eta, ms = ctx.saved_tensors
+            g = D.titans_backward_dd(k, v, q, alpha, theta, eta, ms, None, dy)
         else:
+            k, v, q, alpha, theta, eta, ms, ss = ctx.saved_tensors
             g = D.titans_chunkwise_backward_dd(k, v, q, alpha, theta, eta, ms, ss, dy, ctx.chunk)
         return g["d_k"], g["d_v"], g["d_q"], g["d_alpha"], g["d_theta"], g["d_eta"], None, None
 
@@ -319,7 +322,7 @@ class StackedMAG:
         chunk = 0 if l in cfg.exact_levels else min(cfg.chunk_sizes[l], sf)
         y, m_final = self.memory_fn(heads(k), heads(v), heads(q), bro(alpha), bro(theta), bro(eta),
                                     self.context[b][l], chunk)
-        self.context[b][l] = m_final.detach()
+        self.context[b][l].copy_(m_final.detach())
         y = y.view(B, nh, sf, hd).permute(0, 2, 1, 3).reshape(B, sf, d)
         return y.repeat_interleave(c, dim=1) if c > 1 else y
 
@@ -338,7 +341,7 @@ class StackedMAG:
                                                       cfg.num_heads)
         chunk = 0 if l in cfg.exact_levels else min(cfg.chunk_sizes[l], sf)
         y, m_final = self.memory_fn(k, v, q, alpha, theta, eta, self.context[b][l], chunk)
-        self.context[b][l] = m_final.detach()
+        self.context[b][l].copy_(m_final.detach())   # in place: addresses stay fixed for graph replay
         return y, c
 
     def forward(self, tokens, targets):
@@ -393,8 +396,8 @@ class StackedMAG:
             torch.distributed.all_reduce(self.opt.g, group=process_group)
             self.opt.g.mul_(1.0 / world)
 
-    def apply_update(self):
-        """Global-norm clip + AdamW with per-level step counts and pulse gating, weight tying."""
+    def _host_schedule(self):
+        """Host bookkeeping of one step: pulse, global and per-level step counts, descriptors."""
         cfg = self.cfg
         active = self.pulse()
         self.global_step += 1
@@ -404,11 +407,20 @@ class StackedMAG:
         steps = [self.global_step if lv is None else max(self.level_steps[lv], 1)
                  for lv in self.level_of]
         act = [True if lv is None else active[lv] for lv in self.level_of]
-        self.opt.step(cfg.lr, steps, act, cfg.max_grad_norm)
+        self.opt.prepare(steps, act)
+
+    def _device_update(self):
+        cfg = self.cfg
+        self.opt.launch(cfg.lr, cfg.max_grad_norm)
         if cfg.tie_embeddings:
             with torch.no_grad():   # gpu_stacked_sync_embed_weights: w_embed <- w_unembed^T
                 self.p["w_embed"].copy_(self.p["w_unembed"].t())
         self.opt.g.zero_()
+
+    def apply_update(self):
+        """Global-norm clip + AdamW with per-level step counts and pulse gating, weight tying."""
+        self._host_schedule()
+        self._device_update()
 
     def step(self, tokens, targets, process_group=None, world=1):
         """forward + backward + gradient all-reduce + clip + AdamW. Returns the local loss."""
@@ -416,6 +428,41 @@ class StackedMAG:
         self.sync_gradients(process_group, world)
         self.apply_update()
         return loss
+
+    def step_graphed(self, tokens, targets, process_group=None, world=1):
+        """Same as step(), replayed from one CUDA graph (forward, backward, gradient all-reduce,
+        clip, AdamW, weight tying): removes the per-launch host cost, which dominates when the
+        per-rank batch is small. The first call runs two eager steps (sizes every allocation and
+        the library workspace) and captures; later calls copy the inputs into static buffers and
+        replay. Shapes must not change between calls."""
+        if getattr(self, "_graph", None) is None:
+            self._static_tok = tokens.clone()
+            self._static_tgt = targets.clone()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for _ in range(2):
+                    self.step(self._static_tok, self._static_tgt, process_group, world)
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            torch.cuda.empty_cache()
+            self._host_schedule()
+            self._graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self._graph):
+                self._static_loss = self.forward_backward(self._static_tok, self._static_tgt)
+                self.sync_gradients(process_group, world)
+                self._device_update()
+            self._graph.replay()            # capture records only: run the scheduled step now
+            self._graph_done = torch.cuda.Event()
+            self._graph_done.record()
+            return self._static_loss
+        self._static_tok.copy_(tokens, non_blocking=True)
+        self._static_tgt.copy_(targets, non_blocking=True)
+        self._graph_done.synchronize()      # the previous replay has consumed the descriptors
+        self._host_schedule()
+        self._graph.replay()
+        self._graph_done.record()
+        return self._static_loss
 
     def n_params(self):
         return sum(math.prod(s) for s in self.shapes)

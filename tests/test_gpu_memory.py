@@ -456,3 +456,28 @@ def test_empty_and_invalid_inputs(D):
                eta=z, m_initial=z, s_initial=z, m_chunk_states=z, s_chunk_states=z, y=z,
                seq_len=4, d=8, batch_size=1, chunk_size=0, error_clip=0.0, m_norm_max=0.0)
     assert ffi.lib().nlh_last_status() == 0   # cleared by the wrapper after raising
+
+
+@pytest.mark.parametrize("d,s,n", [(64, 40, 3), (32, 17, 2), (64, 1, 1)])
+def test_titans_exact_without_momentum_trajectory(D, orc, d, s, n):
+    """s_states = NULL: forward stores only M; backward derives S_t from consecutive M states
+    (d_eta = (<M_{t+1} - (1-alpha) M_t, dS> + theta e.(dS k)) / eta)."""
+    p = make_problem(orc, n, s, d, 2900 + d + s, "rand")
+    w = oracle_exact(orc, "titans", p)
+    t = to_dev(p)
+    ms, ss, y = D.titans_forward_dd(t["k"], t["v"], t["q"], t["alpha"], t["theta"], t["eta"],
+                                    t["m0"], t["s0"], store_s=False)
+    assert ss is None
+    assert rel_err(_np(y), w["y"]) <= REL and rel_err(_np(ms), w["m_states"]) <= REL
+    g = D.titans_backward_dd(t["k"], t["v"], t["q"], t["alpha"], t["theta"], t["eta"], ms, None,
+                             t["dy"])
+    _check_bwd(g, w, ["d_k", "d_v", "d_q", "d_alpha", "d_theta", "d_eta", "d_m_initial",
+                      "d_s_initial"])
+
+
+def test_null_momentum_trajectory_rejected_off_the_fast_path(D, orc):
+    p = make_problem(orc, 1, 6, 16, 2990, "rand")   # d = 16 runs the generic kernels
+    t = to_dev(p)
+    with pytest.raises(RuntimeError, match="register-resident"):
+        D.titans_forward_dd(t["k"], t["v"], t["q"], t["alpha"], t["theta"], t["eta"], t["m0"],
+                            t["s0"], store_s=False)

@@ -118,3 +118,28 @@ def test_fused_glue_matches_torch_glue(bf16):
         _compare(fused, plain, tok, tgt, 1e-3, 3e-2, l2=True)
     else:
         _compare(fused, plain, tok, tgt, 1e-5, 1e-3)
+
+
+def test_graph_replayed_step_matches_eager_steps():
+    """step_graphed = 2 eager steps + capture + replay on the first call, replay afterwards: after
+    the same number of steps the parameters agree with a model stepped eagerly."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from nl_hecate_b200.stacked_mag import StackedMAG
+    tok, tgt = _data(4, seed=9)
+    eager = StackedMAG(_cfg(True), 4, device="cuda", seed=7)
+    graph = StackedMAG(_cfg(True), 4, device="cuda", seed=7)
+    for _ in range(5):
+        le = eager.step(tok, tgt)
+    lg = graph.step_graphed(tok, tgt)        # steps 1-3
+    for _ in range(2):
+        lg = graph.step_graphed(tok, tgt)    # steps 4, 5
+    torch.cuda.synchronize()
+    assert graph.global_step == eager.global_step == 5
+    assert abs(float(le) - float(lg)) <= 1e-3 * abs(float(le))
+    err = float((eager.opt.w - graph.opt.w).abs().max())
+    assert err <= 1e-4, err
+    for b in range(2):
+        for l in range(3):
+            a, r = graph.context[b][l], eager.context[b][l]
+            assert float((a - r).abs().max()) <= 1e-3 * max(float(r.abs().max()), 1e-6)
