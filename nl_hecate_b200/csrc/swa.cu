@@ -17,6 +17,7 @@
 #include <cuda_bf16.h>
 
 #include "nlh_common.cuh"
+#include "swa_tc.cuh"
 #include "../../include/nlh_ffi.h"
 
 namespace nlh {
@@ -558,6 +559,7 @@ __global__ void __launch_bounds__(SWA_THREADS) swa_bwd_dq_kernel(
 }
 
 // ───────────────────────────── host side ──────────────────────────────────
+static int g_swa_use_tcgen05 = 0;   // nlh_set_option(NLH_OPT_SWA_TCGEN05, 1) switches the head_dim-64 forward
 template <int HD>
 static size_t swa_fwd_smem() { return (size_t)(SWA_BM + 4 * SWA_BN) * (HD + SWA_PAD) * sizeof(bf16); }
 template <int HD>
@@ -584,12 +586,21 @@ static int swa_forward_impl(const bf16* q, const bf16* k, const bf16* v, bf16* o
 {
     cudaStream_t st = current_stream();
     const float scale = 1.0f / sqrtf((float)HD);
-    const size_t smem = swa_fwd_smem<HD>();
-    if (smem > 48 * 1024)
-        cudaFuncSetAttribute(swa_fwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    dim3 grid((S + SWA_BM - 1) / SWA_BM, B * H);
-    swa_fwd_kernel<HD><<<grid, SWA_THREADS, smem, st>>>(q, k, v, out, lse, S, H, W, n_p, scale);
-    if (!check_launch("swa_fwd_kernel")) return NLH_ERR_CUDA;
+    const bool aligned = ((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15) == 0);
+    if (HD == 64 && g_swa_use_tcgen05 && aligned) {
+        // tcgen05 / TMEM kernel: 128 query rows per CTA
+        cudaFuncSetAttribute(tc::swa_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM_BYTES);
+        dim3 grid((S + tc::BM - 1) / tc::BM, B * H);
+        tc::swa_fwd_tc_kernel<<<grid, tc::THREADS, tc::SMEM_BYTES, st>>>(q, k, v, out, lse, S, H, W, n_p, scale);
+        if (!check_launch("swa_fwd_tc_kernel")) return NLH_ERR_CUDA;
+    } else {
+        const size_t smem = swa_fwd_smem<HD>();
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(swa_fwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        dim3 grid((S + SWA_BM - 1) / SWA_BM, B * H);
+        swa_fwd_kernel<HD><<<grid, SWA_THREADS, smem, st>>>(q, k, v, out, lse, S, H, W, n_p, scale);
+        if (!check_launch("swa_fwd_kernel")) return NLH_ERR_CUDA;
+    }
     if (aw != nullptr) {
         const long long rows = (long long)B * H * S;
         swa_weights_kernel<HD><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(q, k, lse, aw, S, H, W, n_p, B, scale);
@@ -643,6 +654,19 @@ static int swa_backward_impl(const bf16* q, const bf16* k, const bf16* v, const 
 using namespace nlh;
 
 extern "C" {
+
+int32_t nlh_set_option(int32_t option, int32_t value)
+{
+    if (option == NLH_OPT_SWA_TCGEN05) { g_swa_use_tcgen05 = value ? 1 : 0; return NLH_OK; }
+    return NLH_ERR_INVALID_ARG;
+}
+
+int32_t nlh_swa_tc_timeout_flag(void)
+{
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, tc::g_swa_tc_timeout, sizeof(int)) != cudaSuccess) return -1;
+    return v;
+}
 
 int32_t nlh_swa_forward(const uint16_t* q, const uint16_t* k, const uint16_t* v, uint16_t* out,
     float* lse, int32_t seq_len, int32_t num_heads, int32_t head_dim, int32_t window_size,
