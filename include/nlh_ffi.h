@@ -249,8 +249,8 @@ int32_t nlh_swa_backward(const uint16_t* q, const uint16_t* k, const uint16_t* v
     float* d_v, int32_t seq_len, int32_t num_heads, int32_t head_dim, int32_t window_size,
     int32_t batch_size, int32_t n_persistent);
 
-/* Library options (no counterpart in the reference). NLH_OPT_SWA_TCGEN05 = 1 runs the head_dim-64
- * SWA forward on the tcgen05/TMEM kernel instead of the mma.sync one. nlh_swa_tc_timeout_flag()
+/* Library options (no counterpart in the reference). NLH_OPT_SWA_TCGEN05 (default 1) runs the
+ * head_dim-64 SWA forward on the tcgen05/TMEM kernel; 0 selects the mma.sync kernel instead. nlh_swa_tc_timeout_flag()
  * synchronously reads a device flag that the tcgen05 kernel sets if one of its bounded mbarrier
  * waits ran out (0 = never, 1 = a wait expired and results are invalid, -1 = read failed). */
 #define NLH_OPT_SWA_TCGEN05 1

@@ -559,7 +559,7 @@ __global__ void __launch_bounds__(SWA_THREADS) swa_bwd_dq_kernel(
 }
 
 // ───────────────────────────── host side ──────────────────────────────────
-static int g_swa_use_tcgen05 = 0;   // nlh_set_option(NLH_OPT_SWA_TCGEN05, 1) switches the head_dim-64 forward
+static int g_swa_use_tcgen05 = 1;   // nlh_set_option(NLH_OPT_SWA_TCGEN05, 0) switches the head_dim-64 forward
 template <int HD>
 static size_t swa_fwd_smem() { return (size_t)(SWA_BM + 4 * SWA_BN) * (HD + SWA_PAD) * sizeof(bf16); }
 template <int HD>

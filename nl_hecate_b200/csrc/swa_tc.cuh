@@ -6,10 +6,11 @@
 //                  the thread its 64 scores, so max / exp / sum need no shuffles at all
 //   P (bf16)     : written to shared memory in the tensor core's K-major core-matrix layout
 //   PV = P V     : tcgen05.mma M=128 N=64 K=64, V consumed MN-major straight from its tile,
-//                  fp32 in TMEM cols [64,128); loaded back and folded into the running output
-//                  (kept in registers so that the online-softmax rescale costs no TMEM traffic)
+//                  accumulated across key tiles in TMEM cols [64,128); when a row's running
+//                  maximum moves, its warp rescales the accumulator in place (tcgen05.ld / st)
 // Operands are staged with 16-byte cp.async into the canonical no-swizzle core-matrix layouts
-// (8 rows x 16 bytes contiguous), so no tensor map is needed; K/V tiles are double buffered.
+// (8 rows x 16 bytes contiguous), so no tensor map is needed; K and V tiles are double buffered
+// and the score MMA of tile i+1 is issued before the softmax of tile i so the two overlap.
 // A single thread issues the MMAs; completion is tracked with tcgen05.commit -> mbarrier. Every
 // mbarrier wait is bounded: on expiry the CTA sets a global error flag, stops waiting, frees its
 // TMEM and returns.
@@ -26,7 +27,7 @@ constexpr int BN = 64;           // keys per tile
 constexpr int HD = 64;
 constexpr int THREADS = 128;
 constexpr unsigned TMEM_COLS = 128;
-constexpr unsigned WAIT_LIMIT = 1u << 24;
+constexpr unsigned WAIT_LIMIT = 1u << 20;
 
 // shared-memory byte offsets
 constexpr int Q_BYTES = BM * HD * 2;        // 16 KB
@@ -36,9 +37,9 @@ constexpr int OFF_Q = 0;
 constexpr int OFF_K = OFF_Q + Q_BYTES;              // 2 buffers
 constexpr int OFF_V = OFF_K + 2 * KV_BYTES;         // 2 buffers
 constexpr int OFF_P = OFF_V + 2 * KV_BYTES;
-constexpr int OFF_BAR = OFF_P + P_BYTES;            // 8-byte mbarrier
-constexpr int OFF_TMEM = OFF_BAR + 8;               // 4-byte TMEM base address
-constexpr int SMEM_BYTES = OFF_TMEM + 8;
+constexpr int OFF_BAR = OFF_P + P_BYTES;            // two 8-byte mbarriers (S ready, O updated)
+constexpr int OFF_TMEM = OFF_BAR + 16;              // 4-byte TMEM base address
+constexpr int SMEM_BYTES = OFF_TMEM + 16;
 
 // Canonical no-swizzle core-matrix layouts (core matrix = 8 rows x 16 bytes, contiguous):
 //  K-major operand (rows = M or N index, 16-byte chunks along K):
@@ -127,11 +128,28 @@ __device__ __forceinline__ void tmem_ld_32x32b_x64(unsigned (&r)[64], unsigned t
                  : "r"(taddr));
 }
 
+// 64 registers -> 32 TMEM lanes x 64 consecutive columns (inverse of tmem_ld_32x32b_x64).
+__device__ __forceinline__ void tmem_st_32x32b_x64(unsigned taddr, const unsigned (&r)[64])
+{
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x64.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63, %64};\n"
+                 :
+                 : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]), "r"(r[32]), "r"(r[33]), "r"(r[34]), "r"(r[35]), "r"(r[36]), "r"(r[37]), "r"(r[38]), "r"(r[39]), "r"(r[40]), "r"(r[41]), "r"(r[42]), "r"(r[43]), "r"(r[44]), "r"(r[45]), "r"(r[46]), "r"(r[47]), "r"(r[48]), "r"(r[49]), "r"(r[50]), "r"(r[51]), "r"(r[52]), "r"(r[53]), "r"(r[54]), "r"(r[55]), "r"(r[56]), "r"(r[57]), "r"(r[58]), "r"(r[59]), "r"(r[60]), "r"(r[61]), "r"(r[62]), "r"(r[63])
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ float ex2_approx(float x)
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+
 __device__ __forceinline__ void cp16_tc(void* smem_dst, const void* gsrc)
 {
     unsigned s = smem_u32(smem_dst);
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gsrc) : "memory");
 }
+__device__ __forceinline__ void cp_commit_tc() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 
 // Stage n_rows rows of 64 bf16 (row stride rs elements) into the core-matrix layout:
 // 16-byte chunk c of row r goes to (r/8)*GROUP + c*CORE + (r%8)*16. Rows >= n_valid are zeroed.
@@ -148,6 +166,15 @@ __device__ __forceinline__ void stage_rows(unsigned char* dst, const __nv_bfloat
 
 __device__ int g_swa_tc_timeout = 0;   // set when a bounded mbarrier wait ran out
 
+// Pipeline per key tile i (S and O live in TMEM, columns [0,64) and [64,128)):
+//   A  wait S(i) ready, every thread pulls its row of 64 scores into registers
+//   B  wait PV(i-1) done  -> P buffer, V(i-1) buffer and O are free
+//   C  prefetch K(i+2) and V(i+1) with cp.async (K two tiles ahead, V one tile ahead: two
+//      buffers each are enough because K(i) is dead once S(i) is ready)
+//   D  barrier; one thread issues S(i+1) = Q K(i+1)^T  -> runs under the softmax of tile i
+//   E  softmax of tile i in registers (masks only on boundary tiles), P -> shared memory;
+//      O is rescaled in TMEM only by warps whose running maximum moved (tcgen05.ld/st)
+//   F  barrier; one thread issues O += P V(i)
 __global__ void __launch_bounds__(THREADS) swa_fwd_tc_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
     const __nv_bfloat16* __restrict__ v, __nv_bfloat16* __restrict__ out, float* __restrict__ lse,
@@ -162,10 +189,10 @@ __global__ void __launch_bounds__(THREADS) swa_fwd_tc_kernel(
     const int q0 = qt * BM;
     const int q_hi = min(q0 + BM - 1, S - 1);
     const float sl2 = scale * 1.4426950408889634f;
-    const unsigned bar = smem_u32(smem + OFF_BAR);
+    const unsigned bar_s = smem_u32(smem + OFF_BAR), bar_o = bar_s + 8;
     volatile unsigned* tmem_slot = reinterpret_cast<volatile unsigned*>(smem + OFF_TMEM);
 
-    if (tid == 0) mbar_init(bar, 1);
+    if (tid == 0) { mbar_init(bar_s, 1); mbar_init(bar_o, 1); }
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
                      ::"r"(smem_u32(smem + OFF_TMEM)), "r"(TMEM_COLS) : "memory");
@@ -177,78 +204,102 @@ __global__ void __launch_bounds__(THREADS) swa_fwd_tc_kernel(
     const unsigned tmem_base = *tmem_slot;
     const unsigned tmem_row = tmem_base + ((unsigned)(warp * 32) << 16);   // this warp's 32 lanes
 
-    stage_rows(smem + OFF_Q, q + base + (size_t)q0 * rs, rs, BM, min(BM, S - q0));
     const int kt_last = q_hi / BN;
-    auto needed = [&](int t) {
-        const int k_lo = t * BN, k_hi2 = k_lo + BN - 1;
-        if (k_lo > q_hi) return false;
-        if (k_lo < n_p) return true;
-        return k_hi2 >= q0 + 1 - window;
-    };
     auto next_tile = [&](int cur) {
-        for (int t = cur + 1; t <= kt_last; t++)
-            if (needed(t)) return t;
+        for (int t = cur + 1; t <= kt_last; t++) {
+            const int k_lo = t * BN;
+            if (k_lo < n_p || k_lo + BN - 1 >= q0 + 1 - window) return t;
+        }
         return -1;
     };
-    auto issue = [&](int tile, int bufi) {
+    auto load_k = [&](int tile, int bufi) {
         const int k0 = tile * BN;
         stage_rows(smem + OFF_K + bufi * KV_BYTES, k + base + (size_t)k0 * rs, rs, BN, min(BN, S - k0));
+    };
+    auto load_v = [&](int tile, int bufi) {
+        const int k0 = tile * BN;
         stage_rows(smem + OFF_V + bufi * KV_BYTES, v + base + (size_t)k0 * rs, rs, BN, min(BN, S - k0));
     };
-    int kt = next_tile(-1);
-    if (kt >= 0) issue(kt, 0);
-    asm volatile("cp.async.commit_group;\n" ::: "memory");
-
     const unsigned idesc_qk = make_idesc(false), idesc_pv = make_idesc(true);
     const unsigned q_addr = smem_u32(smem + OFF_Q), p_addr = smem_u32(smem + OFF_P);
-    float o[HD];
+    auto issue_qk = [&](int bufi) {     // S = Q K^T, both operands K-major, 2 chunks per K=16 step
+        const unsigned k_addr = smem_u32(smem + OFF_K + bufi * KV_BYTES);
 #pragma unroll
-    for (int j = 0; j < HD; j++) o[j] = 0.f;
+        for (int ks = 0; ks < HD / 16; ks++)
+            mma_bf16(tmem_base, make_desc(q_addr + ks * 2 * CORE, CORE, GROUP),
+                     make_desc(k_addr + ks * 2 * CORE, CORE, GROUP), idesc_qk, ks > 0 ? 1u : 0u);
+        mma_commit(bar_s);
+    };
+
+    int kt = next_tile(-1);
+    int nxt = (kt >= 0) ? next_tile(kt) : -1;
+    stage_rows(smem + OFF_Q, q + base + (size_t)q0 * rs, rs, BM, min(BM, S - q0));
+    if (kt >= 0) { load_k(kt, 0); load_v(kt, 0); }
+    if (nxt >= 0) load_k(nxt, 1);
+    cp_commit_tc();
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    fence_async_proxy();
+    fence_before_sync();
+    __syncthreads();
+    if (tid == 0 && kt >= 0) { fence_after_sync(); issue_qk(0); }
+
     float m_run = -INFINITY, l_run = 0.f;
     const int qp = q0 + tid;
-    unsigned parity = 0;
+    unsigned par_s = 0, par_o = 0;
     bool dead = false;
-    int buf = 0;
+    int it = 0;
 
     while (kt >= 0) {
-        const int nxt = next_tile(kt);
-        asm volatile("cp.async.wait_group 0;\n" ::: "memory");
-        fence_async_proxy();
-        fence_before_sync();
-        __syncthreads();
-        if (nxt >= 0) issue(nxt, buf ^ 1);
-        asm volatile("cp.async.commit_group;\n" ::: "memory");
-        const unsigned k_addr = smem_u32(smem + OFF_K + buf * KV_BYTES);
-        const unsigned v_addr = smem_u32(smem + OFF_V + buf * KV_BYTES);
-        if (tid == 0) {
-            fence_after_sync();
-#pragma unroll
-            for (int ks = 0; ks < HD / 16; ks++)      // K-major A (Q) and B (K): 2 chunks per step
-                mma_bf16(tmem_base, make_desc(q_addr + ks * 2 * CORE, CORE, GROUP),
-                         make_desc(k_addr + ks * 2 * CORE, CORE, GROUP), idesc_qk, ks > 0 ? 1u : 0u);
-            mma_commit(bar);
-        }
-        if (!dead) dead = !mbar_wait(bar, parity, WAIT_LIMIT);
-        parity ^= 1;
+        const int nxt2 = (nxt >= 0) ? next_tile(nxt) : -1;
+        // A: scores of this tile
+        if (!dead) dead = !mbar_wait(bar_s, par_s, WAIT_LIMIT);
+        par_s ^= 1;
         fence_after_sync();
         unsigned sr[64];
         tmem_ld_32x32b_x64(sr, tmem_row);
         tmem_wait_ld();
+        fence_before_sync();
+        // B: previous P V product has been folded into O
+        if (it > 0) {
+            if (!dead) dead = !mbar_wait(bar_o, par_o, WAIT_LIMIT);
+            par_o ^= 1;
+            fence_after_sync();
+        }
+        // C: prefetch
+        if (nxt2 >= 0) load_k(nxt2, it & 1);            // K(it+2) over K(it)
+        if (nxt >= 0) load_v(nxt, (it + 1) & 1);        // V(it+1) over V(it-1)
+        cp_commit_tc();
+        // D: K(it+1) (committed one tile ago) has landed; start the next score tile
+        asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+        fence_async_proxy();
+        fence_before_sync();
+        __syncthreads();
+        if (tid == 0 && nxt >= 0) { fence_after_sync(); issue_qk((it + 1) & 1); }
 
+        // E: softmax
         const int k0 = kt * BN;
+        const bool interior = (k0 + BN - 1 <= q0) && (k0 + BN - 1 < S) &&
+                              ((k0 >= q0 + BM - window) || (k0 + BN - 1 < n_p));
         float mx = -INFINITY;
+        if (interior) {
 #pragma unroll
-        for (int j = 0; j < BN; j++) {
-            const int kp = k0 + j;
-            const bool ok = kp < S && kp <= qp && (kp < n_p || kp >= qp + 1 - window);
-            const float s = ok ? __uint_as_float(sr[j]) : -INFINITY;
-            sr[j] = __float_as_uint(s);
-            mx = fmaxf(mx, s);
+            for (int j = 0; j < BN; j++) mx = fmaxf(mx, __uint_as_float(sr[j]));
+        } else {
+#pragma unroll
+            for (int j = 0; j < BN; j++) {
+                const int kp = k0 + j;
+                const bool ok = kp < S && kp <= qp && (kp < n_p || kp >= qp + 1 - window);
+                const float s = ok ? __uint_as_float(sr[j]) : -INFINITY;
+                sr[j] = __float_as_uint(s);
+                mx = fmaxf(mx, s);
+            }
         }
         const float m_new = fmaxf(m_run, mx);
         const float mu = (m_new == -INFINITY) ? 0.f : m_new;
-        const float corr = exp2f((m_run - mu) * sl2);
+        const float corr = ex2_approx((m_run - mu) * sl2);
+        const bool moved = (m_new != m_run);
         m_run = m_new;
+        const float mus = mu * sl2;
         float ls = 0.f;
         unsigned char* prow = smem + OFF_P + (tid >> 3) * GROUP + (tid & 7) * 16;
 #pragma unroll
@@ -256,7 +307,7 @@ __global__ void __launch_bounds__(THREADS) swa_fwd_tc_kernel(
             float p[8];
 #pragma unroll
             for (int e = 0; e < 8; e++) {
-                p[e] = exp2f((__uint_as_float(sr[c * 8 + e]) - mu) * sl2);
+                p[e] = ex2_approx(fmaf(__uint_as_float(sr[c * 8 + e]), sl2, -mus));
                 ls += p[e];
             }
             uint4 w;
@@ -267,47 +318,57 @@ __global__ void __launch_bounds__(THREADS) swa_fwd_tc_kernel(
             *reinterpret_cast<uint4*>(prow + c * CORE) = w;
         }
         l_run = l_run * corr + ls;
+        // rescale O in TMEM, only in warps where some row's maximum moved (never on the first tile:
+        // O is not initialised yet and the first product overwrites it)
+        if (it > 0 && __any_sync(0xffffffffu, moved)) {
+            tmem_ld_32x32b_x64(sr, tmem_row + 64);
+            tmem_wait_ld();
 #pragma unroll
-        for (int j = 0; j < HD; j++) o[j] *= corr;
-
+            for (int j = 0; j < HD; j++) sr[j] = __float_as_uint(__uint_as_float(sr[j]) * corr);
+            tmem_st_32x32b_x64(tmem_row + 64, sr);
+            tmem_wait_st();
+        }
+        // F: O (+)= P V
         fence_async_proxy();
         fence_before_sync();
         __syncthreads();
         if (tid == 0) {
             fence_after_sync();
+            const unsigned v_addr = smem_u32(smem + OFF_V + (it & 1) * KV_BYTES);
 #pragma unroll
             for (int ks = 0; ks < BN / 16; ks++)      // A = P (K-major over keys), B = V (MN-major)
                 mma_bf16(tmem_base + 64, make_desc(p_addr + ks * 2 * CORE, CORE, GROUP),
-                         make_desc(v_addr + ks * 2 * GROUP, GROUP, CORE), idesc_pv, ks > 0 ? 1u : 0u);
-            mma_commit(bar);
+                         make_desc(v_addr + ks * 2 * GROUP, GROUP, CORE), idesc_pv,
+                         (it > 0 || ks > 0) ? 1u : 0u);
+            mma_commit(bar_o);
         }
-        if (!dead) dead = !mbar_wait(bar, parity, WAIT_LIMIT);
-        parity ^= 1;
-        fence_after_sync();
-        tmem_ld_32x32b_x64(sr, tmem_row + 64);
-        tmem_wait_ld();
-#pragma unroll
-        for (int j = 0; j < HD; j++) o[j] += __uint_as_float(sr[j]);
-        fence_before_sync();
         kt = nxt;
-        buf ^= 1;
+        nxt = nxt2;
+        it++;
     }
     asm volatile("cp.async.wait_group 0;\n" ::: "memory");
-    if (qp < S) {
-        const float inv = (l_run > 0.f) ? 1.0f / l_run : 0.f;
-        __nv_bfloat16* orow = out + base + (size_t)qp * rs;
+    if (it > 0) {
+        if (!dead) dead = !mbar_wait(bar_o, par_o, WAIT_LIMIT);
+        fence_after_sync();
+        unsigned orr[64];
+        tmem_ld_32x32b_x64(orr, tmem_row + 64);
+        tmem_wait_ld();
+        if (qp < S) {
+            const float inv = (l_run > 0.f) ? 1.0f / l_run : 0.f;
+            __nv_bfloat16* orow = out + base + (size_t)qp * rs;
 #pragma unroll
-        for (int c = 0; c < HD / 8; c++) {
-            uint4 w;
-            __nv_bfloat162 t0 = __floats2bfloat162_rn(o[c * 8] * inv, o[c * 8 + 1] * inv);
-            __nv_bfloat162 t1 = __floats2bfloat162_rn(o[c * 8 + 2] * inv, o[c * 8 + 3] * inv);
-            __nv_bfloat162 t2 = __floats2bfloat162_rn(o[c * 8 + 4] * inv, o[c * 8 + 5] * inv);
-            __nv_bfloat162 t3 = __floats2bfloat162_rn(o[c * 8 + 6] * inv, o[c * 8 + 7] * inv);
-            w.x = *reinterpret_cast<unsigned*>(&t0); w.y = *reinterpret_cast<unsigned*>(&t1);
-            w.z = *reinterpret_cast<unsigned*>(&t2); w.w = *reinterpret_cast<unsigned*>(&t3);
-            *reinterpret_cast<uint4*>(orow + c * 8) = w;
+            for (int c = 0; c < HD / 8; c++) {
+                uint4 w;
+                __nv_bfloat162 t0 = __floats2bfloat162_rn(__uint_as_float(orr[c * 8]) * inv, __uint_as_float(orr[c * 8 + 1]) * inv);
+                __nv_bfloat162 t1 = __floats2bfloat162_rn(__uint_as_float(orr[c * 8 + 2]) * inv, __uint_as_float(orr[c * 8 + 3]) * inv);
+                __nv_bfloat162 t2 = __floats2bfloat162_rn(__uint_as_float(orr[c * 8 + 4]) * inv, __uint_as_float(orr[c * 8 + 5]) * inv);
+                __nv_bfloat162 t3 = __floats2bfloat162_rn(__uint_as_float(orr[c * 8 + 6]) * inv, __uint_as_float(orr[c * 8 + 7]) * inv);
+                w.x = *reinterpret_cast<unsigned*>(&t0); w.y = *reinterpret_cast<unsigned*>(&t1);
+                w.z = *reinterpret_cast<unsigned*>(&t2); w.w = *reinterpret_cast<unsigned*>(&t3);
+                *reinterpret_cast<uint4*>(orow + c * 8) = w;
+            }
+            if (lse != nullptr) lse[((size_t)b * H + h) * S + qp] = m_run * scale + logf(l_run);
         }
-        if (lse != nullptr) lse[((size_t)b * H + h) * S + qp] = m_run * scale + logf(l_run);
     }
     if (dead && (tid & 31) == 0) atomicExch(&g_swa_tc_timeout, 1);
     fence_before_sync();

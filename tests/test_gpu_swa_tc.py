@@ -16,7 +16,7 @@ def tc_on():
     from nl_hecate_b200 import dispatch as D
     D.call("nlh_set_option", option=1, value=1)
     yield D
-    D.call("nlh_set_option", option=1, value=0)
+    D.call("nlh_set_option", option=1, value=1)   # the library default
 
 
 def _np(t):
