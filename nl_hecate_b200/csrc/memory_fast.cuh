@@ -128,17 +128,19 @@ struct FastGeom {
 // shared-memory floats
 template <int D>
 constexpr size_t fast_fwd_smem_floats() { return (size_t)3 * 2 * FAST_TT * D + 2 * 3 * FAST_TT + FAST_TT * D; }
+// ring_mats: matrices per ring slot (2 when a stored S trajectory is read, else 1);
+// frozen: the per-chunk error buffer is only needed by the frozen rules.
 template <int D>
-constexpr size_t fast_bwd_smem_floats()
+constexpr size_t fast_bwd_smem_floats(int ring_mats, bool frozen)
 {
     using G = FastGeom<D>;
     return (size_t)4 * 2 * FAST_TB * D        // k,v,q,dy tiles, double buffered
          + 2 * 3 * FAST_TB                    // gates
-         + (size_t)FAST_NST * 2 * D * D       // state ring (M,S)
+         + (size_t)FAST_NST * ring_mats * D * D   // state ring
          + (size_t)2 * G::NW * FAST_TB * D    // dq / dk warp partials
          + (size_t)FAST_TB * D                // dv staging
-         + (size_t)3 * FAST_TB * G::NT        // per-thread scalar partials
-         + (size_t)FAST_MAX_CHUNK * D;        // errors of the current chunk (frozen rule)
+         + (size_t)3 * FAST_TB * D            // per-row scalar partials
+         + (frozen ? (size_t)FAST_MAX_CHUNK * D : 0);   // errors of the current chunk
 }
 
 template <int D>
@@ -232,8 +234,10 @@ __device__ __forceinline__ float fast_readout(const float (&M)[16], const float*
     return row_allreduce<TPR>((y0 + y1) + (y2 + y3));
 }
 
+// D = 64, exact rules: capped at 64 registers so that four CTAs share an SM (the level-0 problem
+// count of the stacked model, batch x heads = 512, then fits in one wave of 148 x 4).
 template <int D, int RULE, bool FROZEN>
-__global__ void __launch_bounds__(FastGeom<D>::NT) fast_fwd_kernel(FwdArgs a)
+__global__ void __launch_bounds__(FastGeom<D>::NT, (D == 64 && !FROZEN) ? 4 : 1) fast_fwd_kernel(FwdArgs a)
 {
     using G = FastGeom<D>;
     constexpr int NT = G::NT, TPR = G::TPR, TT = FAST_TT;
@@ -365,12 +369,13 @@ __global__ void __launch_bounds__(FastGeom<D>::NT) fast_bwd_kernel(BwdArgs a)
     float* qt = vt + 2 * TB * D;
     float* dyt = qt + 2 * TB * D;
     float* gt = dyt + 2 * TB * D;                     // [2][3][TB]
-    float* ring = gt + 2 * 3 * TB;                    // [NST][2][D*D]
-    float* pq = ring + (size_t)NST * 2 * D * D;       // [NW][TB][D]
+    constexpr int RM = (RULE == RULE_TITANS && !SDER) ? 2 : 1;   // matrices per ring slot
+    float* ring = gt + 2 * 3 * TB;                    // [NST][RM][D*D]
+    float* pq = ring + (size_t)NST * RM * D * D;      // [NW][TB][D]
     float* pk = pq + (size_t)NW * TB * D;             // [NW][TB][D]
     float* dvs = pk + (size_t)NW * TB * D;            // [TB][D]
-    float* scp = dvs + TB * D;                        // [3][TB][NT]
-    float* es = scp + 3 * TB * NT;                    // [FAST_MAX_CHUNK][D]
+    float* scp = dvs + TB * D;                        // [3][TB][D] per-row partials
+    float* es = scp + 3 * TB * D;                     // [FAST_MAX_CHUNK][D], frozen rules only
 
     const int tid = threadIdx.x, r = tid / TPR, cg = tid % TPR;
     const int lane = tid & 31, warp = tid >> 5;
@@ -480,7 +485,7 @@ __global__ void __launch_bounds__(FastGeom<D>::NT) fast_bwd_kernel(BwdArgs a)
                 // ring layout is thread-major (piece jj of thread tid at jj*NT*4 + tid*4):
                 // the data is private to the thread, so any layout works and this one
                 // makes the 16-byte shared loads conflict-free.
-                float* dst = ring + (size_t)(j % NST) * 2 * dd;
+                float* dst = ring + (size_t)(j % NST) * RM * dd;
 #pragma unroll
                 for (int jj = 0; jj < 4; jj++) {
                     const size_t o = (size_t)r * D + jj * (D / 4) + cg * 4;
@@ -519,7 +524,7 @@ __global__ void __launch_bounds__(FastGeom<D>::NT) fast_bwd_kernel(BwdArgs a)
                 if (tl == ntok - 1 && tile < ntl - 1 && (t1 - (tt0 + TB)) < NST) cp_async_wait<0>();
                 else cp_async_wait<NST - 1>();
                 if (tl == ntok - 1) __syncthreads();   // tile streams (other threads' copies) visible
-                const float* ms = ring + (size_t)(j % NST) * 2 * dd;
+                const float* ms = ring + (size_t)(j % NST) * RM * dd;
                 float Mt[16], St[16], kk[16], qq[16];
 #pragma unroll
                 for (int jj = 0; jj < 4; jj++) {
@@ -560,11 +565,15 @@ __global__ void __launch_bounds__(FastGeom<D>::NT) fast_bwd_kernel(BwdArgs a)
                     else e = row_allreduce<TPR>(p) - vr;
                 }
                 const float de = -th * u;
-                // per-thread scalar partials (summed over the CTA at tile end)
-                scp[(0 * TB + tl) * NT + tid] = pa;
-                scp[(1 * TB + tl) * NT + tid] = (RULE != RULE_HEBBIAN && cg == 0) ? e * u : 0.f;
-                if (SDER) pe = (et > 1e-30f) ? (pe + ((cg == 0) ? th * e * u : 0.f)) / et : 0.f;
-                scp[(2 * TB + tl) * NT + tid] = pe;
+                // per-row scalar partials (summed over the rows at tile end)
+                pa = row_allreduce<TPR>(pa);
+                if (RULE == RULE_TITANS) pe = row_allreduce<TPR>(pe);
+                if (cg == 0) {
+                    scp[(0 * TB + tl) * D + r] = pa;
+                    scp[(1 * TB + tl) * D + r] = (RULE != RULE_HEBBIAN) ? e * u : 0.f;
+                    if (SDER) pe = (et > 1e-30f) ? (pe + th * e * u) / et : 0.f;
+                    scp[(2 * TB + tl) * D + r] = pe;
+                }
                 if (cg == 0) dvs[tl * D + r] = (RULE == RULE_HEBBIAN) ? u : th * u;
 
                 // column partials: d_q = M_{t+1}^T dy ; d_k = -theta G^T e + Mk^T de (Hebbian: dM^T v)
@@ -617,7 +626,7 @@ __global__ void __launch_bounds__(FastGeom<D>::NT) fast_bwd_kernel(BwdArgs a)
                 const int which = job / ntok, tl = job - which * ntok;
                 if ((which == 1 && RULE == RULE_HEBBIAN) || (which == 2 && RULE != RULE_TITANS)) continue;
                 float s = 0.f;
-                for (int i = lane; i < NT; i += 32) s += scp[(which * TB + tl) * NT + i];
+                for (int i = lane; i < D; i += 32) s += scp[(which * TB + tl) * D + i];
                 s = warp_sum(s);
                 if (lane == 0) {
                     if (which == 0) dalpha[tt0 + tl] = -s;
@@ -695,8 +704,9 @@ static bool fast_forward(int rule, const FwdArgs& a, cudaStream_t st)
 template <int D, int RULE>
 static bool fast_bwd_launch(const BwdArgs& a, cudaStream_t st)
 {
-    const size_t smem = fast_bwd_smem_floats<D>() * sizeof(float);
-    if (RULE == RULE_TITANS && a.s_traj == nullptr) {   // checked by the caller: stored-trajectory mode
+    const bool sder = (RULE == RULE_TITANS && a.s_traj == nullptr);
+    const size_t smem = fast_bwd_smem_floats<D>((RULE == RULE_TITANS && !sder) ? 2 : 1, a.frozen) * sizeof(float);
+    if (sder) {   // checked by the caller: stored-trajectory mode
         cudaFuncSetAttribute(fast_bwd_kernel<D, RULE, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         fast_bwd_kernel<D, RULE, false, true><<<a.batch, FastGeom<D>::NT, smem, st>>>(a);
         return true;
