@@ -51,9 +51,27 @@ __device__ __forceinline__ float row_allreduce(float v)
 template <int D>
 __device__ __forceinline__ int col_of(int i, int cg) { return (i >> 2) * (D / 4) + cg * 4 + (i & 3); }
 
-// Recursive-halving reduction over the rows a warp owns. In: 16 per-thread
-// column partials. Out: NOUT = 16*TPR/32 fully warp-reduced values per lane,
-// for the consecutive element indices base..base+NOUT-1 (same column chunk).
+// Packed fp32x2 arithmetic (one instruction for two lanes of a 64-bit register pair on sm_100).
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ float2 bc2(float s) { return make_float2(s, s); }
+__device__ __forceinline__ float2 shfl_xor2(float2 v, int o)
+{
+    return make_float2(__shfl_xor_sync(0xffffffffu, v.x, o), __shfl_xor_sync(0xffffffffu, v.y, o));
+}
+
+// A thread keeps its 16 elements of a row as 8 float2: pair p holds logical elements 2p, 2p+1;
+// logical element i lives in 16-byte chunk i>>2. In the backward kernel the chunks are stored
+// PERMUTED per lane: physical chunk j holds logical chunk j ^ xc, with
+//   xc = 2*(lane bit 4) + (lane bit 3).
+// With that layout the first two steps of the recursive-halving column reduction below always
+// keep the low half of the registers and send the high half, so they need no selects.
+__device__ __forceinline__ int chunk_perm(int lane) { return (((lane >> 4) & 1) << 1) | ((lane >> 3) & 1); }
+
+// Recursive-halving reduction over the rows a warp owns. In: 16 per-thread column partials in
+// the permuted layout. Out: NOUT = 16*TPR/32 fully warp-reduced values per lane, for the
+// consecutive LOGICAL element indices base..base+NOUT-1 (same column chunk).
 template <int TPR>
 struct ColReduce {
     static constexpr int NOUT = 16 * TPR / 32;
@@ -66,52 +84,29 @@ struct ColReduce {
         if (TPR <= 2 && (lane & 2)) b += 1;
         return b;
     }
-    __device__ static __forceinline__ void run(float (&v)[16], int lane, float (&out)[NOUT])
+    __device__ static __forceinline__ void run(const float2 (&v)[8], int lane, float (&out)[NOUT])
     {
-        float a8[8];
-        {
-            const bool up = lane & 16;
+        static_assert(TPR == 4 || TPR == 2, "column reduction is written for 2 or 4 threads per row");
+        float2 a4[4], a2[2];
 #pragma unroll
-            for (int i = 0; i < 8; i++) {
-                const float send = up ? v[i] : v[i + 8];
-                const float keep = up ? v[i + 8] : v[i];
-                a8[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
-            }
-        }
-        if (TPR == 8) {
+        for (int i = 0; i < 4; i++) a4[i] = add2(v[i], shfl_xor2(v[i + 4], 16));   // lane bit 4 <-> chunk bit 1
 #pragma unroll
-            for (int i = 0; i < NOUT; i++) out[i] = a8[i];  // unreachable unless NOUT == 4 (see below)
-            return;
-        }
-        float a4[4];
-        {
-            const bool up = lane & 8;
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const float send = up ? a8[i] : a8[i + 4];
-                const float keep = up ? a8[i + 4] : a8[i];
-                a4[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
-            }
-        }
-        float a2[2];
-        {
+        for (int i = 0; i < 2; i++) a2[i] = add2(a4[i], shfl_xor2(a4[i + 2], 8));  // lane bit 3 <-> chunk bit 0
+        {   // lane bit 2 <-> pair within the chunk (not permuted: select)
             const bool up = lane & 4;
-#pragma unroll
-            for (int i = 0; i < 2; i++) {
-                const float send = up ? a4[i] : a4[i + 2];
-                const float keep = up ? a4[i + 2] : a4[i];
-                a2[i] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
-            }
+            const float2 send = up ? a2[0] : a2[1];
+            const float2 keep = up ? a2[1] : a2[0];
+            a2[0] = add2(keep, shfl_xor2(send, 4));
         }
         if (TPR == 4) {
-            out[0] = a2[0];
-            if (NOUT > 1) out[NOUT - 1] = a2[1];
+            out[0] = a2[0].x;
+            if (NOUT > 1) out[NOUT - 1] = a2[0].y;
             return;
         }
-        {   // TPR == 2
+        {   // TPR == 2: lane bit 1 <-> element within the pair
             const bool up = lane & 2;
-            const float send = up ? a2[0] : a2[1];
-            const float keep = up ? a2[1] : a2[0];
+            const float send = up ? a2[0].x : a2[0].y;
+            const float keep = up ? a2[0].y : a2[0].x;
             out[0] = keep + __shfl_xor_sync(0xffffffffu, send, 2);
         }
     }
@@ -143,31 +138,49 @@ constexpr size_t fast_bwd_smem_floats(int ring_mats, bool frozen)
          + (frozen ? (size_t)FAST_MAX_CHUNK * D : 0);   // errors of the current chunk
 }
 
+// xc: chunk permutation of the calling thread (0 = logical order).
 template <int D>
-__device__ __forceinline__ void load_state16(float (&x)[16], const float* __restrict__ src, int r, int cg)
+__device__ __forceinline__ void load_state8(float2 (&x)[8], const float* __restrict__ src, int r, int cg, int xc = 0)
 {
 #pragma unroll
     for (int j = 0; j < 4; j++) {
-        const float4 t = *reinterpret_cast<const float4*>(src + (size_t)r * D + j * (D / 4) + cg * 4);
-        x[4 * j] = t.x; x[4 * j + 1] = t.y; x[4 * j + 2] = t.z; x[4 * j + 3] = t.w;
+        const float4 t = *reinterpret_cast<const float4*>(src + (size_t)r * D + (j ^ xc) * (D / 4) + cg * 4);
+        x[2 * j] = make_float2(t.x, t.y); x[2 * j + 1] = make_float2(t.z, t.w);
     }
 }
 template <int D>
-__device__ __forceinline__ void store_state16(const float (&x)[16], float* dst, int r, int cg)
+__device__ __forceinline__ void store_state8(const float2 (&x)[8], float* dst, int r, int cg, int xc = 0)
 {
 #pragma unroll
     for (int j = 0; j < 4; j++)
-        *reinterpret_cast<float4*>(dst + (size_t)r * D + j * (D / 4) + cg * 4) =
-            make_float4(x[4 * j], x[4 * j + 1], x[4 * j + 2], x[4 * j + 3]);
+        *reinterpret_cast<float4*>(dst + (size_t)r * D + (j ^ xc) * (D / 4) + cg * 4) =
+            make_float4(x[2 * j].x, x[2 * j].y, x[2 * j + 1].x, x[2 * j + 1].y);
 }
 template <int D>
-__device__ __forceinline__ void load_vec16(float (&x)[16], const float* src /*smem row of D*/, int cg)
+__device__ __forceinline__ void load_vec8(float2 (&x)[8], const float* src /*smem row of D*/, int cg, int xc = 0)
 {
 #pragma unroll
     for (int j = 0; j < 4; j++) {
-        const float4 t = *reinterpret_cast<const float4*>(src + j * (D / 4) + cg * 4);
-        x[4 * j] = t.x; x[4 * j + 1] = t.y; x[4 * j + 2] = t.z; x[4 * j + 3] = t.w;
+        const float4 t = *reinterpret_cast<const float4*>(src + (j ^ xc) * (D / 4) + cg * 4);
+        x[2 * j] = make_float2(t.x, t.y); x[2 * j + 1] = make_float2(t.z, t.w);
     }
+}
+__device__ __forceinline__ void zero8(float2 (&x)[8])
+{
+#pragma unroll
+    for (int i = 0; i < 8; i++) x[i] = make_float2(0.f, 0.f);
+}
+__device__ __forceinline__ void copy8(float2 (&d)[8], const float2 (&s)[8])
+{
+#pragma unroll
+    for (int i = 0; i < 8; i++) d[i] = s[i];
+}
+__device__ __forceinline__ float hsum8(const float2 (&x)[8])
+{
+    const float2 a = add2(add2(x[0], x[1]), add2(x[2], x[3]));
+    const float2 b = add2(add2(x[4], x[5]), add2(x[6], x[7]));
+    const float2 c = add2(a, b);
+    return c.x + c.y;
 }
 
 // Cooperative async copy of ntok*D contiguous floats (16-byte pieces).
@@ -181,57 +194,54 @@ __device__ __forceinline__ void tile_async(float* dst, const float* __restrict__
 // One forward token on register state. Msrc is the matrix the error is taken
 // against (M itself, or the frozen chunk-start copy). Returns e (error or v for Hebbian).
 template <int D, int RULE>
-__device__ __forceinline__ float fast_fwd_token(float (&M)[16], float (&S)[16], const float (&Msrc)[16],
+__device__ __forceinline__ float fast_fwd_token(float2 (&M)[8], float2 (&S)[8], const float2 (&Msrc)[8],
                                                 const float* krow, float vr, float alpha, float theta,
-                                                float eta, int cg)
+                                                float eta, int cg, int xc = 0)
 {
     constexpr int TPR = FastGeom<D>::TPR;
-    float kk[16];
-    load_vec16<D>(kk, krow, cg);
+    float2 kk[8];
+    load_vec8<D>(kk, krow, cg, xc);
     float e = vr;
     if (RULE != RULE_HEBBIAN) {
-        float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
+        float2 pa = make_float2(0.f, 0.f), pb = make_float2(0.f, 0.f);
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            p0 += Msrc[4 * j] * kk[4 * j];
-            p1 += Msrc[4 * j + 1] * kk[4 * j + 1];
-            p2 += Msrc[4 * j + 2] * kk[4 * j + 2];
-            p3 += Msrc[4 * j + 3] * kk[4 * j + 3];
+        for (int i = 0; i < 4; i++) {
+            pa = fma2(Msrc[2 * i], kk[2 * i], pa);
+            pb = fma2(Msrc[2 * i + 1], kk[2 * i + 1], pb);
         }
-        const float p = row_allreduce<TPR>((p0 + p1) + (p2 + p3));
-        e = p - vr;
+        const float2 ps = add2(pa, pb);
+        e = row_allreduce<TPR>(ps.x + ps.y) - vr;
     }
-    const float r = 1.0f - alpha;
-    const float te = theta * e;
+    const float2 r2 = bc2(1.0f - alpha);
+    if (RULE == RULE_TITANS) {
+        const float2 nte = bc2(-theta * e), et2 = bc2(eta);
 #pragma unroll
-    for (int i = 0; i < 16; i++) {
-        if (RULE == RULE_TITANS) {
-            S[i] = eta * S[i] - te * kk[i];
-            M[i] = r * M[i] + S[i];
-        } else if (RULE == RULE_DELTA) {
-            M[i] = r * M[i] - te * kk[i];
-        } else {
-            M[i] = r * M[i] + e * kk[i];
+        for (int i = 0; i < 8; i++) {
+            S[i] = fma2(et2, S[i], mul2(nte, kk[i]));
+            M[i] = fma2(r2, M[i], S[i]);
         }
+    } else {
+        const float2 c2 = bc2(RULE == RULE_DELTA ? -theta * e : e);
+#pragma unroll
+        for (int i = 0; i < 8; i++) M[i] = fma2(r2, M[i], mul2(c2, kk[i]));
     }
     return e;
 }
 
 template <int D>
-__device__ __forceinline__ float fast_readout(const float (&M)[16], const float* qrow, int cg)
+__device__ __forceinline__ float fast_readout(const float2 (&M)[8], const float* qrow, int cg, int xc = 0)
 {
     constexpr int TPR = FastGeom<D>::TPR;
-    float qq[16];
-    load_vec16<D>(qq, qrow, cg);
-    float y0 = 0.f, y1 = 0.f, y2 = 0.f, y3 = 0.f;
+    float2 qq[8];
+    load_vec8<D>(qq, qrow, cg, xc);
+    float2 ya = make_float2(0.f, 0.f), yb = make_float2(0.f, 0.f);
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
-        y0 += M[4 * j] * qq[4 * j];
-        y1 += M[4 * j + 1] * qq[4 * j + 1];
-        y2 += M[4 * j + 2] * qq[4 * j + 2];
-        y3 += M[4 * j + 3] * qq[4 * j + 3];
+    for (int i = 0; i < 4; i++) {
+        ya = fma2(M[2 * i], qq[2 * i], ya);
+        yb = fma2(M[2 * i + 1], qq[2 * i + 1], yb);
     }
-    return row_allreduce<TPR>((y0 + y1) + (y2 + y3));
+    const float2 ys = add2(ya, yb);
+    return row_allreduce<TPR>(ys.x + ys.y);
 }
 
 // D = 64, exact rules: capped at 64 registers so that four CTAs share an SM (the level-0 problem
@@ -262,18 +272,14 @@ __global__ void __launch_bounds__(FastGeom<D>::NT, (D == 64 && !FROZEN) ? 4 : 1)
     float* s_out = (RULE == RULE_TITANS && a.s_out != nullptr) ? a.s_out + (size_t)b * a.out_stride : nullptr;
     const int mode = a.store_mode;
 
-    float M[16], S[16], M0[16];
-    load_state16<D>(M, a.m_init + (size_t)b * a.init_stride, r, cg);
-    if (RULE == RULE_TITANS) load_state16<D>(S, a.s_init + (size_t)b * a.init_stride, r, cg);
-    else {
-#pragma unroll
-        for (int i = 0; i < 16; i++) S[i] = 0.f;
-    }
-#pragma unroll
-    for (int i = 0; i < 16; i++) M0[i] = M[i];
+    float2 M[8], S[8], M0[8];
+    load_state8<D>(M, a.m_init + (size_t)b * a.init_stride, r, cg);
+    if (RULE == RULE_TITANS) load_state8<D>(S, a.s_init + (size_t)b * a.init_stride, r, cg);
+    else zero8(S);
+    copy8(M0, M);
     if (mode == STORE_ALL || mode == STORE_CKPT) {
-        store_state16<D>(M, m_out, r, cg);
-        if (RULE == RULE_TITANS && s_out != nullptr) store_state16<D>(S, s_out, r, cg);
+        store_state8<D>(M, m_out, r, cg);
+        if (RULE == RULE_TITANS && s_out != nullptr) store_state8<D>(S, s_out, r, cg);
     }
 
     const int ntiles = (a.seq_len + TT - 1) / TT;
@@ -308,12 +314,9 @@ __global__ void __launch_bounds__(FastGeom<D>::NT, (D == 64 && !FROZEN) ? 4 : 1)
             const int t = t0 + tl;
             if (mode == STORE_CHUNK && (t % a.interval) == 0) {
                 const size_t off = (size_t)(t / a.interval) * dd;
-                store_state16<D>(M, m_out + off, r, cg);
-                if (RULE == RULE_TITANS && s_out != nullptr) store_state16<D>(S, s_out + off, r, cg);
-                if (FROZEN) {
-#pragma unroll
-                    for (int i = 0; i < 16; i++) M0[i] = M[i];
-                }
+                store_state8<D>(M, m_out + off, r, cg);
+                if (RULE == RULE_TITANS && s_out != nullptr) store_state8<D>(S, s_out + off, r, cg);
+                if (FROZEN) copy8(M0, M);
             }
             const float al = gb[tl];
             const float th = (RULE != RULE_HEBBIAN) ? gb[TT + tl] : 0.f;
@@ -321,11 +324,11 @@ __global__ void __launch_bounds__(FastGeom<D>::NT, (D == 64 && !FROZEN) ? 4 : 1)
             if (FROZEN) fast_fwd_token<D, RULE>(M, S, M0, kb + tl * D, vb[tl * D + r], al, th, et, cg);
             else fast_fwd_token<D, RULE>(M, S, M, kb + tl * D, vb[tl * D + r], al, th, et, cg);
             if (mode == STORE_ALL) {
-                store_state16<D>(M, m_out + (size_t)(t + 1) * dd, r, cg);
-                if (RULE == RULE_TITANS && s_out != nullptr) store_state16<D>(S, s_out + (size_t)(t + 1) * dd, r, cg);
+                store_state8<D>(M, m_out + (size_t)(t + 1) * dd, r, cg);
+                if (RULE == RULE_TITANS && s_out != nullptr) store_state8<D>(S, s_out + (size_t)(t + 1) * dd, r, cg);
             } else if (mode == STORE_CKPT && (((t + 1) % a.interval) == 0 || t + 1 == a.seq_len)) {
-                store_state16<D>(M, m_out + (size_t)slot * dd, r, cg);
-                if (RULE == RULE_TITANS && s_out != nullptr) store_state16<D>(S, s_out + (size_t)slot * dd, r, cg);
+                store_state8<D>(M, m_out + (size_t)slot * dd, r, cg);
+                if (RULE == RULE_TITANS && s_out != nullptr) store_state8<D>(S, s_out + (size_t)slot * dd, r, cg);
                 slot++;
             }
             const float yv = fast_readout<D>(M, qb + tl * D, cg);
@@ -341,11 +344,11 @@ __global__ void __launch_bounds__(FastGeom<D>::NT, (D == 64 && !FROZEN) ? 4 : 1)
     }
     if (mode == STORE_CHUNK) {
         const size_t off = (size_t)((a.seq_len + a.interval - 1) / a.interval) * dd;
-        store_state16<D>(M, m_out + off, r, cg);
-        if (RULE == RULE_TITANS && s_out != nullptr) store_state16<D>(S, s_out + off, r, cg);
+        store_state8<D>(M, m_out + off, r, cg);
+        if (RULE == RULE_TITANS && s_out != nullptr) store_state8<D>(S, s_out + off, r, cg);
     } else if (mode == STORE_FINAL) {
-        store_state16<D>(M, m_out, r, cg);
-        if (RULE == RULE_TITANS && s_out != nullptr) store_state16<D>(S, s_out, r, cg);
+        store_state8<D>(M, m_out, r, cg);
+        if (RULE == RULE_TITANS && s_out != nullptr) store_state8<D>(S, s_out, r, cg);
     }
 }
 
@@ -358,7 +361,7 @@ __global__ void __launch_bounds__(FastGeom<D>::NT, (D == 64 && !FROZEN) ? 4 : 1)
 //   d_eta_t = <S_t, dS> = ( <M_{t+1} - (1-alpha_t) M_t, dS> + theta_t (e . dS k) ) / eta_t,
 // which needs eta_t > 0 (gates far below ~1e-3 lose accuracy to the division).
 template <int D, int RULE, bool FROZEN, bool SDER = false>
-__global__ void __launch_bounds__(FastGeom<D>::NT) fast_bwd_kernel(BwdArgs a)
+__global__ void __launch_bounds__(FastGeom<D>::NT, (D == 64 && !FROZEN) ? 2 : 1) fast_bwd_kernel(BwdArgs a)
 {
     using G = FastGeom<D>;
     constexpr int NT = G::NT, TPR = G::TPR, NW = G::NW, TB = FAST_TB, NST = FAST_NST;
@@ -397,19 +400,20 @@ __global__ void __launch_bounds__(FastGeom<D>::NT) fast_bwd_kernel(BwdArgs a)
     float* mrec = recompute ? a.m_rec + (size_t)b * (a.chunk + 1) * dd : nullptr;
     float* srec = (recompute && RULE == RULE_TITANS) ? a.s_rec + (size_t)b * (a.chunk + 1) * dd : nullptr;
 
-    float dM[16], dS[16], dM0[16], M0[16], Mn[16];
-    if (a.d_m_seed) load_state16<D>(dM, a.d_m_seed + (size_t)b * dd, r, cg);
-    else {
+    // All register state of this kernel uses the per-lane chunk permutation xc (see chunk_perm).
+    const int xc = chunk_perm(lane);
+    constexpr int DD = D * D;
+    int co[4];   // float offsets, within a row, of the four chunks this thread holds
 #pragma unroll
-        for (int i = 0; i < 16; i++) dM[i] = 0.f;
-    }
-    if (RULE == RULE_TITANS && a.d_s_seed) load_state16<D>(dS, a.d_s_seed + (size_t)b * dd, r, cg);
-    else {
-#pragma unroll
-        for (int i = 0; i < 16; i++) dS[i] = 0.f;
-    }
-#pragma unroll
-    for (int i = 0; i < 16; i++) { dM0[i] = 0.f; M0[i] = 0.f; }
+    for (int jj = 0; jj < 4; jj++) co[jj] = (jj ^ xc) * (D / 4) + cg * 4;
+    float* const ring_t = ring + tid * 4;
+    float2 dM[8], dS[8], dM0[8], M0[8], Mn[8];
+    if (a.d_m_seed) load_state8<D>(dM, a.d_m_seed + (size_t)b * dd, r, cg, xc);
+    else zero8(dM);
+    if (RULE == RULE_TITANS && a.d_s_seed) load_state8<D>(dS, a.d_s_seed + (size_t)b * dd, r, cg, xc);
+    else zero8(dS);
+    zero8(dM0);
+    zero8(M0);
 
     const int nchunks = recompute ? (a.seq_len + a.chunk - 1) / a.chunk : 1;
     for (int c = nchunks - 1; c >= 0; c--) {
@@ -420,17 +424,13 @@ __global__ void __launch_bounds__(FastGeom<D>::NT) fast_bwd_kernel(BwdArgs a)
         const float* st_base;
         if (recompute) {
             // ── recompute the chunk trajectory into scratch (slots 0..len) ──
-            float Mc[16], Sc[16];
-            load_state16<D>(Mc, mtraj + (size_t)c * dd, r, cg);
-            if (RULE == RULE_TITANS) load_state16<D>(Sc, straj + (size_t)c * dd, r, cg);
-            else {
-#pragma unroll
-                for (int i = 0; i < 16; i++) Sc[i] = 0.f;
-            }
-#pragma unroll
-            for (int i = 0; i < 16; i++) M0[i] = Mc[i];
-            store_state16<D>(Mc, mrec, r, cg);
-            if (RULE == RULE_TITANS) store_state16<D>(Sc, srec, r, cg);
+            float2 Mc[8], Sc[8];
+            load_state8<D>(Mc, mtraj + (size_t)c * dd, r, cg, xc);
+            if (RULE == RULE_TITANS) load_state8<D>(Sc, straj + (size_t)c * dd, r, cg, xc);
+            else zero8(Sc);
+            copy8(M0, Mc);
+            store_state8<D>(Mc, mrec, r, cg, xc);
+            if (RULE == RULE_TITANS) store_state8<D>(Sc, srec, r, cg, xc);
             const int ntl = (len + TB - 1) / TB;
             for (int tile = 0; tile < ntl; tile++) {
                 const int tt0 = t0 + tile * TB;
@@ -447,20 +447,20 @@ __global__ void __launch_bounds__(FastGeom<D>::NT) fast_bwd_kernel(BwdArgs a)
                     const float th = (RULE != RULE_HEBBIAN) ? theta[t] : 0.f;
                     const float et = (RULE == RULE_TITANS) ? eta[t] : 0.f;
                     float e;
-                    if (FROZEN) e = fast_fwd_token<D, RULE>(Mc, Sc, M0, kt + tl * D, vt[tl * D + r], al, th, et, cg);
-                    else e = fast_fwd_token<D, RULE>(Mc, Sc, Mc, kt + tl * D, vt[tl * D + r], al, th, et, cg);
+                    if (FROZEN) e = fast_fwd_token<D, RULE>(Mc, Sc, M0, kt + tl * D, vt[tl * D + r], al, th, et, cg, xc);
+                    else e = fast_fwd_token<D, RULE>(Mc, Sc, Mc, kt + tl * D, vt[tl * D + r], al, th, et, cg, xc);
                     if (FROZEN && cg == 0) es[(t - t0) * D + r] = e;
-                    store_state16<D>(Mc, mrec + (size_t)(t - t0 + 1) * dd, r, cg);
-                    if (RULE == RULE_TITANS) store_state16<D>(Sc, srec + (size_t)(t - t0 + 1) * dd, r, cg);
+                    store_state8<D>(Mc, mrec + (size_t)(t - t0 + 1) * dd, r, cg, xc);
+                    if (RULE == RULE_TITANS) store_state8<D>(Sc, srec + (size_t)(t - t0 + 1) * dd, r, cg, xc);
                 }
             }
             __syncthreads();   // es visible; staging buffers free
             mt_base = mrec; st_base = srec;
-#pragma unroll
-            for (int i = 0; i < 16; i++) { Mn[i] = Mc[i]; dM0[i] = 0.f; }
+            copy8(Mn, Mc);
+            zero8(dM0);
         } else {
             mt_base = mtraj; st_base = straj;
-            load_state16<D>(Mn, mt_base + (size_t)len * dd, r, cg);
+            load_state8<D>(Mn, mt_base + (size_t)len * dd, r, cg, xc);
         }
 
         // ── reverse pass over the chunk, tile by tile ──
@@ -479,43 +479,46 @@ __global__ void __launch_bounds__(FastGeom<D>::NT) fast_bwd_kernel(BwdArgs a)
                 if (RULE == RULE_TITANS) cp_async4(gt + (buf * 3 + 2) * TB + tid, eta + tt0 + tid);
             }
         };
-        // Thread-private async fetch of state slot j (state before token t0+j).
-        auto prefetch_state = [&](int j) {
-            if (j >= 0) {
-                // ring layout is thread-major (piece jj of thread tid at jj*NT*4 + tid*4):
-                // the data is private to the thread, so any layout works and this one
-                // makes the 16-byte shared loads conflict-free.
-                float* dst = ring + (size_t)(j % NST) * RM * dd;
+        // Thread-private async fetch of the next state slot, walking down from slot len-1 (slot
+        // j = state before token t0+j). The ring is thread-major (piece jj of thread tid at
+        // jj*NT*4 + tid*4): the data is private to the thread, so any layout works and this
+        // one makes the 16-byte shared loads conflict-free. Ring slot = j mod NST, kept as a
+        // counter; the global source pointer walks down by one state per call.
+        int jp = len - 1;
+        int pslot = (len > 0) ? (len - 1) % NST : 0;
+        int cslot = pslot;
+        const float* gpre = mt_base + (size_t)max(len - 1, 0) * DD + r * D;
+        const ptrdiff_t sdiff = (RULE == RULE_TITANS && !SDER) ? (st_base - mt_base) : 0;
+        auto prefetch_state = [&]() {
+            if (jp >= 0) {
+                float* dst = ring_t + pslot * (RM * DD);
 #pragma unroll
                 for (int jj = 0; jj < 4; jj++) {
-                    const size_t o = (size_t)r * D + jj * (D / 4) + cg * 4;
-                    const int so_ = jj * NT * 4 + tid * 4;
-                    cp_async16(dst + so_, mt_base + (size_t)j * dd + o);
-                    if (RULE == RULE_TITANS && !SDER) cp_async16(dst + dd + so_, st_base + (size_t)j * dd + o);
+                    cp_async16(dst + jj * NT * 4, gpre + co[jj]);
+                    if (RULE == RULE_TITANS && !SDER) cp_async16(dst + DD + jj * NT * 4, gpre + sdiff + co[jj]);
                 }
             }
+            jp--;
+            gpre -= DD;
+            pslot = (pslot == 0) ? NST - 1 : pslot - 1;
         };
         if (len > 0) {
             // prologue: last tile + the first NST-1 states, one commit group each
             prefetch_tile(ntl - 1);
-            prefetch_state(len - 1);
+            prefetch_state();
             cp_async_commit();
 #pragma unroll
-            for (int s = 1; s < NST - 1; s++) { prefetch_state(len - 1 - s); cp_async_commit(); }
+            for (int s = 1; s < NST - 1; s++) { prefetch_state(); cp_async_commit(); }
         }
         for (int tile = ntl - 1; tile >= 0; tile--) {
             const int tt0 = t0 + tile * TB;
             const int ntok = min(TB, t1 - tt0);
             const int buf = tile & 1;
-            const float* kb = kt + buf * TB * D;
-            const float* vb = vt + buf * TB * D;
-            const float* qb = qt + buf * TB * D;
-            const float* dyb = dyt + buf * TB * D;
             const float* gb = gt + buf * 3 * TB;
             for (int tl = ntok - 1; tl >= 0; tl--) {
                 const int j = tt0 + tl - t0;   // slot of M_t
                 // keep NST-1 state groups in flight; fold the next tile's streams into this group
-                prefetch_state(j - (NST - 1));
+                prefetch_state();
                 if (tl == ntok - 1 && tile > 0) prefetch_tile(tile - 1);
                 cp_async_commit();
                 // This tile's streams were committed at the first token of the tile processed
@@ -524,92 +527,99 @@ __global__ void __launch_bounds__(FastGeom<D>::NT) fast_bwd_kernel(BwdArgs a)
                 if (tl == ntok - 1 && tile < ntl - 1 && (t1 - (tt0 + TB)) < NST) cp_async_wait<0>();
                 else cp_async_wait<NST - 1>();
                 if (tl == ntok - 1) __syncthreads();   // tile streams (other threads' copies) visible
-                const float* ms = ring + (size_t)(j % NST) * RM * dd;
-                float Mt[16], St[16], kk[16], qq[16];
+                const float* ms = ring_t + cslot * (RM * DD);
+                cslot = (cslot == 0) ? NST - 1 : cslot - 1;
+                float2 Mt[8], St[8], kk[8], qq[8];
 #pragma unroll
                 for (int jj = 0; jj < 4; jj++) {
-                    const float4 t4 = *reinterpret_cast<const float4*>(ms + jj * NT * 4 + tid * 4);
-                    Mt[4 * jj] = t4.x; Mt[4 * jj + 1] = t4.y; Mt[4 * jj + 2] = t4.z; Mt[4 * jj + 3] = t4.w;
+                    const float4 t4 = *reinterpret_cast<const float4*>(ms + jj * NT * 4);
+                    Mt[2 * jj] = make_float2(t4.x, t4.y); Mt[2 * jj + 1] = make_float2(t4.z, t4.w);
                     if (RULE == RULE_TITANS && !SDER) {
-                        const float4 s4 = *reinterpret_cast<const float4*>(ms + dd + jj * NT * 4 + tid * 4);
-                        St[4 * jj] = s4.x; St[4 * jj + 1] = s4.y; St[4 * jj + 2] = s4.z; St[4 * jj + 3] = s4.w;
+                        const float4 s4 = *reinterpret_cast<const float4*>(ms + DD + jj * NT * 4);
+                        St[2 * jj] = make_float2(s4.x, s4.y); St[2 * jj + 1] = make_float2(s4.z, s4.w);
                     }
                 }
-                load_vec16<D>(kk, kb + tl * D, cg);
-                load_vec16<D>(qq, qb + tl * D, cg);
-                const float dyr = dyb[tl * D + r];
-                const float vr = vb[tl * D + r];
+                // the k, v, q, dy tiles live in one array: row tl of buffer buf, constant strides
+                const float* trow = kt + (buf * TB + tl) * D;
+                constexpr int VOFF = 2 * TB * D, QOFF = 4 * TB * D, DYOFF = 6 * TB * D;
+#pragma unroll
+                for (int jj = 0; jj < 4; jj++) {
+                    const float4 k4 = *reinterpret_cast<const float4*>(trow + co[jj]);
+                    const float4 q4 = *reinterpret_cast<const float4*>(trow + QOFF + co[jj]);
+                    kk[2 * jj] = make_float2(k4.x, k4.y); kk[2 * jj + 1] = make_float2(k4.z, k4.w);
+                    qq[2 * jj] = make_float2(q4.x, q4.y); qq[2 * jj + 1] = make_float2(q4.z, q4.w);
+                }
+                const float dyr = trow[DYOFF + r];
+                const float vr = trow[VOFF + r];
                 const float al = gb[tl];
                 const float th = (RULE != RULE_HEBBIAN) ? gb[TB + tl] : 0.f;
                 const float et = (RULE == RULE_TITANS) ? gb[2 * TB + tl] : 0.f;
+                const float rr = 1.0f - al;
 
-                float p = 0.f, u = 0.f, pa = 0.f, pe = 0.f;
-                const float rr0 = 1.0f - al;
+                // pass 1: fold dy into dM (and dS); dot products of this row
+                const float2 dy2 = bc2(dyr), nrr2 = bc2(-rr);
+                float2 p2 = make_float2(0.f, 0.f), ua = make_float2(0.f, 0.f), ub = make_float2(0.f, 0.f);
+                float2 pa2 = make_float2(0.f, 0.f), pe2 = make_float2(0.f, 0.f);
 #pragma unroll
-                for (int i = 0; i < 16; i++) {
-                    dM[i] += dyr * qq[i];
-                    float g = dM[i];
+                for (int i = 0; i < 8; i++) {
+                    dM[i] = fma2(dy2, qq[i], dM[i]);
+                    float2 g = dM[i];
                     if (RULE == RULE_TITANS) {
-                        dS[i] += dM[i]; g = dS[i];
-                        if (SDER) pe += (Mn[i] - rr0 * Mt[i]) * dS[i];
-                        else pe += St[i] * dS[i];
+                        dS[i] = add2(dS[i], dM[i]);
+                        g = dS[i];
+                        if (SDER) pe2 = fma2(fma2(nrr2, Mt[i], Mn[i]), dS[i], pe2);   // S_{t+1} = M_{t+1} - (1-alpha) M_t
+                        else pe2 = fma2(St[i], dS[i], pe2);
                     }
-                    pa += Mt[i] * dM[i];
-                    if (RULE != RULE_HEBBIAN && !FROZEN) p += Mt[i] * kk[i];
-                    u += g * kk[i];
+                    pa2 = fma2(Mt[i], dM[i], pa2);
+                    if (RULE != RULE_HEBBIAN && !FROZEN) p2 = fma2(Mt[i], kk[i], p2);
+                    if (i & 1) ub = fma2(g, kk[i], ub); else ua = fma2(g, kk[i], ua);
                 }
-                u = row_allreduce<TPR>(u);
+                const float2 us = add2(ua, ub);
+                const float u = row_allreduce<TPR>(us.x + us.y);
                 float e = 0.f;
                 if (RULE != RULE_HEBBIAN) {
                     if (FROZEN) e = es[j * D + r];
-                    else e = row_allreduce<TPR>(p) - vr;
+                    else e = row_allreduce<TPR>(p2.x + p2.y) - vr;
                 }
                 const float de = -th * u;
                 // per-row scalar partials (summed over the rows at tile end)
-                pa = row_allreduce<TPR>(pa);
-                if (RULE == RULE_TITANS) pe = row_allreduce<TPR>(pe);
+                const float pa = row_allreduce<TPR>(pa2.x + pa2.y);
+                float pe = 0.f;
+                if (RULE == RULE_TITANS) pe = row_allreduce<TPR>(pe2.x + pe2.y);
                 if (cg == 0) {
                     scp[(0 * TB + tl) * D + r] = pa;
                     scp[(1 * TB + tl) * D + r] = (RULE != RULE_HEBBIAN) ? e * u : 0.f;
-                    if (SDER) pe = (et > 1e-30f) ? (pe + th * e * u) / et : 0.f;
+                    if (SDER) pe = (et > 1e-30f) ? __fdividef(pe + th * e * u, et) : 0.f;
                     scp[(2 * TB + tl) * D + r] = pe;
+                    dvs[tl * D + r] = (RULE == RULE_HEBBIAN) ? u : th * u;
                 }
-                if (cg == 0) dvs[tl * D + r] = (RULE == RULE_HEBBIAN) ? u : th * u;
 
-                // column partials: d_q = M_{t+1}^T dy ; d_k = -theta G^T e + Mk^T de (Hebbian: dM^T v)
-                float cq[16], ck[16];
+                // pass 2: column partials d_q = M_{t+1}^T dy ; d_k = -theta G^T e + Mk^T de
+                // (Hebbian: dM^T v), then propagate dM / dS to the previous token
+                float2 cq[8], ck[8];
+                const float2 de2 = bc2(de), nthe2 = bc2(-th * e), vr2 = bc2(vr), et2 = bc2(et), rr2 = bc2(rr);
 #pragma unroll
-                for (int i = 0; i < 16; i++) {
-                    cq[i] = Mn[i] * dyr;
-                    if (RULE == RULE_HEBBIAN) ck[i] = dM[i] * vr;
-                    else {
-                        const float g = (RULE == RULE_TITANS) ? dS[i] : dM[i];
-                        ck[i] = (-th * g) * e + (FROZEN ? M0[i] : Mt[i]) * de;
+                for (int i = 0; i < 8; i++) {
+                    cq[i] = mul2(Mn[i], dy2);
+                    if (RULE == RULE_HEBBIAN) ck[i] = mul2(dM[i], vr2);
+                    else ck[i] = fma2((RULE == RULE_TITANS) ? dS[i] : dM[i], nthe2, mul2(FROZEN ? M0[i] : Mt[i], de2));
+                    if (RULE == RULE_TITANS) dS[i] = mul2(dS[i], et2);
+                    float2 dm = mul2(dM[i], rr2);
+                    if (RULE != RULE_HEBBIAN) {
+                        if (FROZEN) dM0[i] = fma2(kk[i], de2, dM0[i]);
+                        else dm = fma2(kk[i], de2, dm);
                     }
+                    dM[i] = dm;
+                    Mn[i] = Mt[i];
                 }
                 float oq[NOUT], ok[NOUT];
                 ColReduce<TPR>::run(cq, lane, oq);
                 ColReduce<TPR>::run(ck, lane, ok);
                 {
                     const int bi = ColReduce<TPR>::base_index(lane);
-                    const int col = col_of<D>(bi, cg);
-                    float* dq_p = pq + ((size_t)warp * TB + tl) * D + col;
-                    float* dk_p = pk + ((size_t)warp * TB + tl) * D + col;
+                    const int pcol = (warp * TB + tl) * D + col_of<D>(bi, cg);
 #pragma unroll
-                    for (int i = 0; i < NOUT; i++) { dq_p[i] = oq[i]; dk_p[i] = ok[i]; }
-                }
-                // propagate to the previous token
-                const float rr = 1.0f - al;
-#pragma unroll
-                for (int i = 0; i < 16; i++) {
-                    if (RULE == RULE_TITANS) dS[i] *= et;
-                    float dm = rr * dM[i];
-                    if (RULE != RULE_HEBBIAN) {
-                        const float o = de * kk[i];
-                        if (FROZEN) dM0[i] += o; else dm += o;
-                    }
-                    dM[i] = dm;
-                    Mn[i] = Mt[i];
+                    for (int i = 0; i < NOUT; i++) { pq[pcol + i] = oq[i]; pk[pcol + i] = ok[i]; }
                 }
             }
             __syncthreads();
@@ -638,21 +648,23 @@ __global__ void __launch_bounds__(FastGeom<D>::NT) fast_bwd_kernel(BwdArgs a)
         }
         if (FROZEN) {
 #pragma unroll
-            for (int i = 0; i < 16; i++) dM[i] += dM0[i];
+            for (int i = 0; i < 8; i++) dM[i] = add2(dM[i], dM0[i]);
         }
         __syncthreads();
     }
 
     if (a.atomic_out) {
 #pragma unroll
-        for (int i = 0; i < 16; i++) {
-            const size_t o = (size_t)r * D + col_of<D>(i, cg);
-            atomicAdd(&a.d_m_out[o], dM[i]);
-            if (RULE == RULE_TITANS) atomicAdd(&a.d_s_out[o], dS[i]);
+        for (int i = 0; i < 8; i++) {
+            // physical pair i holds logical elements 2i ^ (xc << 2) and the next one
+            const size_t o = (size_t)r * D + col_of<D>((2 * i) ^ (xc << 2), cg);
+            atomicAdd(&a.d_m_out[o], dM[i].x);
+            atomicAdd(&a.d_m_out[o + 1], dM[i].y);
+            if (RULE == RULE_TITANS) { atomicAdd(&a.d_s_out[o], dS[i].x); atomicAdd(&a.d_s_out[o + 1], dS[i].y); }
         }
     } else {
-        store_state16<D>(dM, a.d_m_out + (size_t)b * dd, r, cg);
-        if (RULE == RULE_TITANS) store_state16<D>(dS, a.d_s_out + (size_t)b * dd, r, cg);
+        store_state8<D>(dM, a.d_m_out + (size_t)b * dd, r, cg, xc);
+        if (RULE == RULE_TITANS) store_state8<D>(dS, a.d_s_out + (size_t)b * dd, r, cg, xc);
     }
 }
 
