@@ -309,16 +309,62 @@ int32_t nlh_mag_combine_forward(const float* x, const void* attn_proj, int32_t a
     int32_t c0, int32_t c1, int32_t c2, int32_t c3, int32_t k, float* out, int32_t batch,
     int32_t seq, int32_t d_model, int32_t num_heads);
 /* Backward: d_attn_proj (dtype of attn_proj), d_ycomb [batch, seq, d_model] fp32 (gradient of the
- * weighted level sum) and dw_partial [n_partial_rows, 4] partial sums of d level_weights. */
+ * weighted level sum) and dw_partial [n_partial_rows, 4] partial sums of d level_weights.
+ * dy0..dy3 (each may be NULL): for a level with pool factor 1, receives that level's output
+ * gradient level_weights[l] * d_ycomb in the per-head layout, saving its nlh_pool_to_heads pass. */
 int32_t nlh_mag_combine_backward(const float* d_out, const void* attn_proj, int32_t attn_is_bf16,
     const float* level_weights, const float* y0, const float* y1, const float* y2, const float* y3,
     int32_t c0, int32_t c1, int32_t c2, int32_t c3, int32_t k, void* d_attn_proj, float* d_ycomb,
-    float* dw_partial, int32_t n_partial_rows, int32_t batch, int32_t seq, int32_t d_model,
-    int32_t num_heads);
+    float* dw_partial, int32_t n_partial_rows, float* dy0, float* dy1, float* dy2, float* dy3,
+    int32_t batch, int32_t seq, int32_t d_model, int32_t num_heads);
 /* dy_ph[(b*H+h), t', :] = level_weights[level] * sum_{i<pool} d_ycomb[b, t'*pool+i, h*hd:(h+1)*hd]
  * (adjoint of repeat_upsample_1d + head transpose, pool_ops.cu / elementwise.cu). */
 int32_t nlh_pool_to_heads(const float* d_ycomb, const float* level_weights, int32_t level,
     int32_t pool, float* dy_ph, int32_t batch, int32_t seq, int32_t d_model, int32_t num_heads);
+
+/* ── Stacked-block glue (drop-in) ─────────────────────────────────────────────────────────────
+ * LayerNorm over the last axis of x [n, d]; mean/rstd caches [n] feed the backward
+ * (core/src/cuda_ffi.rs:487-491, kernels core/kernels/layer_norm.cu; CPU statement
+ * core/src/mag.rs:396-449). Backward ACCUMULATES into d_gamma/d_beta (caller zeroes). */
+void layer_norm_forward_cuda(const float* x, const float* gamma, const float* beta, float* out,
+    float* mean_cache, float* rstd_cache, int32_t n, int32_t d, float eps);
+/* core/src/cuda_ffi.rs:495-500 */
+void layer_norm_backward_cuda(const float* d_out, const float* x, const float* gamma,
+    const float* mean_cache, const float* rstd_cache, float* d_x, float* d_gamma, float* d_beta,
+    int32_t n, int32_t d);
+/* output[t, :] = w_embed[input_ids[t], :] (core/src/cuda_ffi.rs:523-529, embedding.cu). */
+void embedding_gather_cuda(const float* w_embed, const int32_t* input_ids, float* output,
+    int32_t seq_len, int32_t d);
+/* d_embed[input_ids[t], :] += d_embedded[t, :] (core/src/cuda_ffi.rs:532-538). */
+void embedding_scatter_add_cuda(const float* d_embedded, const int32_t* input_ids, float* d_embed,
+    int32_t seq_len, int32_t d);
+/* loss_out[0] = sum over positions with 0 <= target < vocab of -log softmax(logits[t])[target];
+ * the entry zeroes loss_out first (core/src/cuda_ffi.rs:766-770, cross_entropy.cu:20-96). */
+void cross_entropy_forward_cuda(const float* logits, const int32_t* target_ids, float* loss_out,
+    int32_t seq_len, int32_t vocab);
+/* d_logits = (softmax - onehot) * inv_count; rows with an invalid target are zeroed
+ * (core/src/cuda_ffi.rs:772-775, cross_entropy.cu:99-176). */
+void cross_entropy_backward_cuda(const float* logits, const int32_t* target_ids, float* d_logits,
+    int32_t seq_len, int32_t vocab, float inv_count);
+
+/* ── Stacked-block glue (additive, no counterpart in the reference) ───────────────────────────
+ * LayerNorm that can also emit a bf16 copy of its output (either output pointer may be NULL)
+ * and whose backward takes the upstream gradient as an fp32 part plus a bf16 part (either may be
+ * NULL; they are summed), so the bf16 GEMMs on both sides need no separate cast kernels. */
+int32_t nlh_layer_norm_forward(const float* x, const float* gamma, const float* beta, float* out_f32,
+    uint16_t* out_bf16, float* mean_cache, float* rstd_cache, int32_t n, int32_t d, float eps);
+int32_t nlh_layer_norm_backward(const float* d_out_f32, const uint16_t* d_out_bf16, const float* x,
+    const float* gamma, const float* mean_cache, const float* rstd_cache, float* d_x, float* d_gamma,
+    float* d_beta, int32_t n, int32_t d);
+/* Cross-entropy on fp32 or bf16 logits [n, vocab]. Forward ACCUMULATES the loss sum into
+ * loss_sum[0] and the number of valid targets into valid_count[0] (optional) and stores the
+ * per-row log-sum-exp in lse [n] (optional). Backward writes
+ * (softmax - onehot) * inv_count * grad_scale[0] (grad_scale NULL = 1) in the logits' type;
+ * d_logits may alias logits; lse NULL = recompute. */
+int32_t nlh_cross_entropy_forward(const void* logits, int32_t logits_is_bf16, const int32_t* target_ids,
+    float* loss_sum, float* lse, int32_t* valid_count, int32_t n, int32_t vocab);
+int32_t nlh_cross_entropy_backward(const void* logits, int32_t logits_is_bf16, const int32_t* target_ids,
+    const float* lse, const float* grad_scale, void* d_logits, int32_t n, int32_t vocab, float inv_count);
 
 /* No counterpart in the reference. Titans LMM backward (same arguments, layout and
  * batch-summed d_m_initial/d_s_initial as titans_backward_f32_cuda) for callers that must

@@ -20,7 +20,7 @@
 namespace nlh {
 
 constexpr int WR_THREADS = 128;
-constexpr int WR_TOK_PER_CTA = 32;     // tokens per CTA in level_prep backward
+constexpr int WR_TOK_PER_CTA = 32;     // most tokens per CTA in level_prep backward
 constexpr int WR_MAX_LEVELS = 4;
 
 __device__ __forceinline__ float wr_sigmoid(float x)
@@ -105,7 +105,7 @@ __global__ void __launch_bounds__(WR_THREADS) level_prep_fwd_kernel(
 }
 
 // ───────────────────────── level prep backward ────────────────────────────
-// One CTA per WR_TOK_PER_CTA tokens; thread owns elements j = tid + i*WR_THREADS (i < NE) of
+// One CTA per tok_per_cta tokens (see lp_tok_per_cta); thread owns elements j = tid + i*WR_THREADS (i < NE) of
 // each d-vector, so the gate-weight gradient accumulates in registers across the CTA's tokens
 // and is written once as a per-CTA partial [n_cta, 3, 2d] (summed by the caller).
 template <typename TIN, int NE>
@@ -116,7 +116,7 @@ __global__ void __launch_bounds__(WR_THREADS) level_prep_bwd_kernel(
     const float* __restrict__ dk_ph, const float* __restrict__ dv_ph, const float* __restrict__ dq_ph,
     const float* __restrict__ dalpha_ph, const float* __restrict__ dtheta_ph, const float* __restrict__ deta_ph,
     const float* __restrict__ w_gates, TIN* __restrict__ d_kvq, float* __restrict__ dw_partial,
-    float* __restrict__ db_partial, int n_tok, int sf, int d, int H)
+    float* __restrict__ db_partial, int n_tok, int sf, int d, int H, int tok_per_cta)
 {
     __shared__ float red[5 * 32];
     const int hd = d / H;
@@ -125,8 +125,8 @@ __global__ void __launch_bounds__(WR_THREADS) level_prep_bwd_kernel(
     for (int g = 0; g < 3; g++)
 #pragma unroll
         for (int i = 0; i < NE; i++) { dwk[g][i] = 0.f; dwv[g][i] = 0.f; }
-    const int tok0 = blockIdx.x * WR_TOK_PER_CTA;
-    const int tok1 = min(tok0 + WR_TOK_PER_CTA, n_tok);
+    const int tok0 = blockIdx.x * tok_per_cta;
+    const int tok1 = min(tok0 + tok_per_cta, n_tok);
     for (int tok = tok0; tok < tok1; tok++) {
         const int b = tok / sf, t = tok - b * sf;
         const size_t g0 = ((size_t)b * H) * sf + t;       // head 0 gate slot; heads are sf apart
@@ -269,13 +269,19 @@ __global__ void __launch_bounds__(256) mag_combine_fwd_kernel(
     }
 }
 
+// Optional per-level outputs of the combine backward: for a level with pool factor 1,
+// dy[l] [B*H, S, hd] receives w_l * d_ycomb in the per-head layout (NULL = not wanted).
+struct CombineGrads {
+    float* dy[WR_MAX_LEVELS];
+};
+
 // d_attn_proj = d_out * gate ; d_ycomb = d_out * attn_proj * gate * (1 - gate) ;
 // dw_partial[cta][l] = sum d_ycomb * upsample(y_l)   (gradient of the level weights)
 template <typename TIN>
 __global__ void __launch_bounds__(256) mag_combine_bwd_kernel(
     const float* __restrict__ d_out, const TIN* __restrict__ attn_proj, const float* __restrict__ wts,
     CombineLevels L, TIN* __restrict__ d_attn_proj, float* __restrict__ d_ycomb,
-    float* __restrict__ dw_partial, int B, int S, int d, int H)
+    float* __restrict__ dw_partial, CombineGrads G, int B, int S, int d, int H)
 {
     __shared__ float red[WR_MAX_LEVELS * 32];
     const int hd = d / H, d4 = d / 4;
@@ -308,8 +314,16 @@ __global__ void __launch_bounds__(256) mag_combine_bwd_kernel(
         st4(d_attn_proj + i * 4, dap);
         st4(d_ycomb + i * 4, dy);
 #pragma unroll
-        for (int l = 0; l < WR_MAX_LEVELS; l++)
-            if (l < L.k) dw[l] += dy.x * yl[l].x + dy.y * yl[l].y + dy.z * yl[l].z + dy.w * yl[l].w;
+        for (int l = 0; l < WR_MAX_LEVELS; l++) {
+            if (l < L.k) {
+                dw[l] += dy.x * yl[l].x + dy.y * yl[l].y + dy.z * yl[l].z + dy.w * yl[l].w;
+                if (G.dy[l] != nullptr) {   // unpooled level: its gradient needs no pooling pass
+                    const float wl = wts[l];
+                    *reinterpret_cast<float4*>(G.dy[l] + (((size_t)b * H + h) * S + t) * hd + w) =
+                        make_float4(wl * dy.x, wl * dy.y, wl * dy.z, wl * dy.w);
+                }
+            }
+        }
     }
     block_sum_n<WR_MAX_LEVELS>(dw, red);
     if (threadIdx.x < WR_MAX_LEVELS) dw_partial[blockIdx.x * WR_MAX_LEVELS + threadIdx.x] = dw[threadIdx.x];
@@ -366,9 +380,18 @@ static int wr_check(const char* where, int B, int S, int d, int H)
 
 extern "C" {
 
+// Tokens a CTA of the level_prep backward walks through: its per-token block reductions are
+// serial, so short inputs (the pooled levels) get fewer tokens per CTA and more CTAs.
+static int lp_tok_per_cta(int n_tokens)
+{
+    int t = (n_tokens + 1023) / 1024;
+    return t < 1 ? 1 : (t > WR_TOK_PER_CTA ? WR_TOK_PER_CTA : t);
+}
+
 int32_t nlh_level_prep_partial_rows(int32_t n_tokens)
 {
-    return (n_tokens + WR_TOK_PER_CTA - 1) / WR_TOK_PER_CTA;
+    const int t = lp_tok_per_cta(n_tokens);
+    return (n_tokens + t - 1) / t;
 }
 
 int32_t nlh_level_prep_forward(const void* kvq, int32_t kvq_is_bf16, const float* w_gates,
@@ -409,7 +432,7 @@ int32_t nlh_level_prep_backward(const float* k_ph, const float* v_ph, const floa
     level_prep_bwd_kernel<T, NE><<<grid, WR_THREADS, 0, st>>>(                                   \
         k_ph, v_ph, q_ph, alpha_ph, theta_ph, eta_ph, k_norm, q_norm, dk_ph, dv_ph, dq_ph,       \
         dalpha_ph, dtheta_ph, deta_ph, w_gates, (T*)d_kvq, dw_partial, db_partial, n_tok, seq,   \
-        d_model, num_heads)
+        d_model, num_heads, lp_tok_per_cta(n_tok))
     if (kvq_is_bf16) {
         if (ne <= 1) NLH_LP_BWD(__nv_bfloat16, 1);
         else if (ne <= 2) NLH_LP_BWD(__nv_bfloat16, 2);
@@ -467,8 +490,8 @@ int32_t nlh_mag_combine_forward(const float* x, const void* attn_proj, int32_t a
 int32_t nlh_mag_combine_backward(const float* d_out, const void* attn_proj, int32_t attn_is_bf16,
     const float* level_weights, const float* y0, const float* y1, const float* y2, const float* y3,
     int32_t c0, int32_t c1, int32_t c2, int32_t c3, int32_t k, void* d_attn_proj, float* d_ycomb,
-    float* dw_partial, int32_t n_partial_rows, int32_t batch, int32_t seq, int32_t d_model,
-    int32_t num_heads)
+    float* dw_partial, int32_t n_partial_rows, float* dy0, float* dy1, float* dy2, float* dy3,
+    int32_t batch, int32_t seq, int32_t d_model, int32_t num_heads)
 {
     int rc = wr_check("nlh_mag_combine_backward", batch, seq, d_model, num_heads);
     if (rc != NLH_OK || batch == 0) return rc;
@@ -478,14 +501,23 @@ int32_t nlh_mag_combine_backward(const float* d_out, const void* attn_proj, int3
         return NLH_ERR_INVALID_ARG;
     }
     cudaStream_t st = current_stream();
+    CombineGrads G;
+    float* dys[4] = {dy0, dy1, dy2, dy3};
+    for (int l = 0; l < WR_MAX_LEVELS; l++) {
+        G.dy[l] = (l < k) ? dys[l] : nullptr;
+        if (G.dy[l] != nullptr && L.c[l] != 1) {
+            record_status(NLH_ERR_INVALID_ARG, "nlh_mag_combine_backward", "dy output given for a pooled level");
+            return NLH_ERR_INVALID_ARG;
+        }
+    }
     if (attn_is_bf16)
         mag_combine_bwd_kernel<__nv_bfloat16><<<n_partial_rows, 256, 0, st>>>(
             d_out, (const __nv_bfloat16*)attn_proj, level_weights, L, (__nv_bfloat16*)d_attn_proj,
-            d_ycomb, dw_partial, batch, seq, d_model, num_heads);
+            d_ycomb, dw_partial, G, batch, seq, d_model, num_heads);
     else
         mag_combine_bwd_kernel<float><<<n_partial_rows, 256, 0, st>>>(
             d_out, (const float*)attn_proj, level_weights, L, (float*)d_attn_proj, d_ycomb,
-            dw_partial, batch, seq, d_model, num_heads);
+            dw_partial, G, batch, seq, d_model, num_heads);
     return check_launch("nlh_mag_combine_backward") ? NLH_OK : NLH_ERR_CUDA;
 }
 

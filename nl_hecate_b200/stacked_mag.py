@@ -194,18 +194,91 @@ class _MagCombine(torch.autograd.Function):
         d_yc = torch.empty(B, S, d, dtype=torch.float32, device=dev)
         rows = _MagCombine.ROWS
         dwp = torch.empty(rows, 4, dtype=torch.float32, device=dev)
+        dys = [torch.empty_like(ys[l]) for l in range(k)]
+        direct = [dys[l] if cp[l] == 1 else None for l in range(k)] + [None] * (4 - k)
         D.call("nlh_mag_combine_backward", d_out=d_out, attn_proj=attn_proj, attn_is_bf16=is_bf16,
                level_weights=wts, y0=yp[0], y1=yp[1], y2=yp[2], y3=yp[3], c0=cp[0], c1=cp[1],
                c2=cp[2], c3=cp[3], k=k, d_attn_proj=d_ap, d_ycomb=d_yc, dw_partial=dwp,
-               n_partial_rows=rows, batch=B, seq=S, d_model=d, num_heads=H)
+               n_partial_rows=rows, dy0=direct[0], dy1=direct[1], dy2=direct[2], dy3=direct[3],
+               batch=B, seq=S, d_model=d, num_heads=H)
         d_wts = dwp.sum(0)[:k]
-        dys = []
         for l in range(k):
-            dy = torch.empty_like(ys[l])
-            D.call("nlh_pool_to_heads", d_ycomb=d_yc, level_weights=wts, level=l, pool=cp[l],
-                   dy_ph=dy, batch=B, seq=S, d_model=d, num_heads=H)
-            dys.append(dy)
+            if cp[l] != 1:
+                D.call("nlh_pool_to_heads", d_ycomb=d_yc, level_weights=wts, level=l, pool=cp[l],
+                       dy_ph=dys[l], batch=B, seq=S, d_model=d, num_heads=H)
         return (d_out, d_ap, d_wts, None, None, *dys)
+
+
+class _LayerNorm(torch.autograd.Function):
+    """Row LayerNorm through nlh_layer_norm_forward / _backward. mode 0: fp32 output, 1: bf16
+    output, 2: both (fp32 for the pooled levels, bf16 for the GEMM that follows)."""
+
+    @staticmethod
+    def forward(ctx, x, gamma, beta, eps, mode):
+        x = x.contiguous()
+        d = x.shape[-1]
+        n = x.numel() // d
+        dev = x.device
+        o32 = torch.empty_like(x) if mode in (0, 2) else None
+        o16 = torch.empty(x.shape, dtype=torch.bfloat16, device=dev) if mode in (1, 2) else None
+        mean = torch.empty(n, dtype=torch.float32, device=dev)
+        rstd = torch.empty(n, dtype=torch.float32, device=dev)
+        D.call("nlh_layer_norm_forward", x=x, gamma=gamma.contiguous(), beta=beta.contiguous(),
+               out_f32=o32, out_bf16=o16, mean_cache=mean, rstd_cache=rstd, n=n, d=d, eps=eps)
+        ctx.save_for_backward(x, gamma, mean, rstd)
+        ctx.mode = mode
+        return o32 if mode == 0 else o16 if mode == 1 else (o32, o16)
+
+    @staticmethod
+    def backward(ctx, *grads):
+        x, gamma, mean, rstd = ctx.saved_tensors
+        d = x.shape[-1]
+        n = x.numel() // d
+        g32 = g16 = None
+        for g in grads:
+            if g is None:
+                continue
+            if g.dtype == torch.bfloat16:
+                g16 = g.contiguous()
+            else:
+                g32 = g.contiguous()
+        d_x = torch.empty_like(x)
+        d_gb = torch.zeros(2, d, dtype=torch.float32, device=x.device)
+        if g32 is None and g16 is None:
+            return d_x.zero_(), d_gb[0], d_gb[1], None, None
+        D.call("nlh_layer_norm_backward", d_out_f32=g32, d_out_bf16=g16, x=x, gamma=gamma.contiguous(),
+               mean_cache=mean, rstd_cache=rstd, d_x=d_x, d_gamma=d_gb[0], d_beta=d_gb[1], n=n, d=d)
+        return d_x, d_gb[0], d_gb[1], None, None
+
+
+class _CrossEntropy(torch.autograd.Function):
+    """Mean cross-entropy over valid targets on fp32 or bf16 logits [n, vocab]
+    (nlh_cross_entropy_forward / _backward). The backward overwrites the logits with their
+    gradient, so the logits must not be used again after the loss."""
+
+    @staticmethod
+    def forward(ctx, logits, targets):
+        n, vocab = logits.shape
+        dev = logits.device
+        acc = torch.zeros(2, dtype=torch.float32, device=dev)          # loss sum | (int) valid count
+        cnt = acc[1:2].view(torch.int32)
+        lse = torch.empty(n, dtype=torch.float32, device=dev)
+        is_bf16 = int(logits.dtype == torch.bfloat16)
+        D.call("nlh_cross_entropy_forward", logits=logits, logits_is_bf16=is_bf16, target_ids=targets,
+               loss_sum=acc[0:1], lse=lse, valid_count=cnt, n=n, vocab=vocab)
+        inv = 1.0 / cnt.float().clamp_min(1.0)
+        ctx.save_for_backward(logits, targets, lse, inv)
+        ctx.meta = (n, vocab, is_bf16)
+        return (acc[0:1] * inv).reshape(())
+
+    @staticmethod
+    def backward(ctx, g):
+        logits, targets, lse, inv = ctx.saved_tensors
+        n, vocab, is_bf16 = ctx.meta
+        scale = (g.float().reshape(1) * inv).contiguous()
+        D.call("nlh_cross_entropy_backward", logits=logits, logits_is_bf16=is_bf16, target_ids=targets,
+               lse=lse, grad_scale=scale, d_logits=logits, n=n, vocab=vocab, inv_count=1.0)
+        return logits, None
 
 
 def titans_memory(k, v, q, alpha, theta, eta, m0, chunk):
@@ -326,14 +399,16 @@ class StackedMAG:
         y = y.view(B, nh, sf, hd).permute(0, 2, 1, 3).reshape(B, sf, d)
         return y.repeat_interleave(c, dim=1) if c > 1 else y
 
-    def _level_fused(self, b, l, m_in):
-        """Level through the fused wrapper kernels; returns the per-head output and the pool factor."""
+    def _level_fused(self, b, l, m_in, m_in_gemm):
+        """Level through the fused wrapper kernels; returns the per-head output and the pool
+        factor. m_in: LayerNorm output in fp32 (pooled levels average it); m_in_gemm: the same
+        in the GEMM's input type (used as is by the unpooled level)."""
         cfg, p = self.cfg, self.p
         B, S, d = m_in.shape
         c = min(cfg.chunk_sizes[l], S)
         assert S % c == 0, "seq_len must be a multiple of every chunk size"
         sf = S // c
-        x = m_in.view(B, sf, c, d).mean(2) if c > 1 else m_in
+        x = m_in.view(B, sf, c, d).mean(2) if c > 1 else m_in_gemm
         pre = f"b{b}.l{l}."
         kvq = self._mm(x, p[pre + "w_kvq_mem"])
         k, v, q, alpha, theta, eta = _LevelPrep.apply(kvq, p[pre + "w_gates"], p[pre + "b_alpha"],
@@ -344,37 +419,49 @@ class StackedMAG:
         self.context[b][l].copy_(m_final.detach())   # in place: addresses stay fixed for graph replay
         return y, c
 
+    def _ln(self, x, name, mode, fused):
+        p = self.p
+        if fused:
+            return _LayerNorm.apply(x, p[name + "gamma"], p[name + "beta"], 1e-5, mode)
+        out = F.layer_norm(x, (x.shape[-1],), p[name + "gamma"], p[name + "beta"], 1e-5)
+        return (out, out) if mode == 2 else out
+
     def forward(self, tokens, targets):
         cfg, p = self.cfg, self.p
         d, nh, hd = cfg.d_model, cfg.num_heads, cfg.head_dim
         fused = (cfg.fused_glue and tokens.is_cuda and cfg.k <= 4 and d <= 1024 and hd % 4 == 0)
+        lp = 1 if (fused and cfg.bf16) else 0           # LayerNorm output feeding only a GEMM
         x = F.embedding(tokens, p["w_embed"])
         for b in range(cfg.n_blocks):
             pre = f"b{b}."
-            h = F.layer_norm(x, (d,), p[pre + "ln_attn_gamma"], p[pre + "ln_attn_beta"], 1e-5)
+            h = self._ln(x, pre + "ln_attn_", lp, fused)
             qkv = self._mm(h, p[pre + "w_qkv"]).to(torch.bfloat16)
             q, k, v = (t.contiguous() for t in qkv.split(d, dim=-1))
             attn = self.swa_fn(q, k, v, nh, hd, cfg.window)
             attn_raw = self._mm(attn, p[pre + "w_o"])
             res1 = x + attn_raw
-            m_in = F.layer_norm(res1, (d,), p[pre + "ln_mem_gamma"], p[pre + "ln_mem_beta"], 1e-5)
             wts = torch.softmax(p[pre + "alpha_mem"], dim=0)
             if fused:
+                m32, m16 = self._ln(res1, pre + "ln_mem_", 2, True) if cfg.bf16 else \
+                    (self._ln(res1, pre + "ln_mem_", 0, True),) * 2
                 ys, pools = [], []
                 for l in range(cfg.k):
-                    y_ph, c = self._level_fused(b, l, m_in)
+                    y_ph, c = self._level_fused(b, l, m32, m16)
                     ys.append(y_ph); pools.append(c)
                 x = _MagCombine.apply(x, attn_raw, wts, tuple(pools), nh, *ys)
             else:
+                m_in = self._ln(res1, pre + "ln_mem_", 0, False)
                 attn_proj = attn_raw.float()
                 y = None
                 for l in range(cfg.k):
                     yl = self._level(b, l, m_in) * wts[l]
                     y = yl if y is None else y + yl
                 x = x + attn_proj * torch.sigmoid(y)
-        x = F.layer_norm(x, (d,), p["ln_final_gamma"], p["ln_final_beta"], 1e-5)
-        logits = self._mm(x, p["w_unembed"].t()).float()
-        return F.cross_entropy(logits.view(-1, cfg.vocab), targets.reshape(-1))
+        x = self._ln(x, "ln_final_", lp, fused)
+        logits = self._mm(x, p["w_unembed"].t())
+        if fused:
+            return _CrossEntropy.apply(logits.view(-1, cfg.vocab), targets.reshape(-1).to(torch.int32))
+        return F.cross_entropy(logits.float().view(-1, cfg.vocab), targets.reshape(-1))
 
     # ── one training step ──────────────────────────────────────────────────
     def pulse(self):

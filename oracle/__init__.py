@@ -301,3 +301,66 @@ def grad_norm_clip(g, max_norm):
 
 def hardware_threads() -> int:
     return int(lib().orc_hardware_threads())
+
+
+# ── block glue: LayerNorm, cross-entropy, embedding ────────────────────────
+def _pi(a):
+    assert a.dtype == np.int32 and a.flags["C_CONTIGUOUS"]
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def layer_norm_forward(x, gamma, beta, eps=1e-5):
+    """(out, mean, rstd) of row-wise LayerNorm over the last axis; x is [n, d]."""
+    x = _f(x)
+    n, d = x.shape
+    out, mean, rstd = np.empty_like(x), np.empty(n, np.float32), np.empty(n, np.float32)
+    lib().orc_layer_norm_forward(_p(x), _p(_f(gamma)), _p(_f(beta)), _p(out), _p(mean), _p(rstd),
+                                 C.c_int(n), C.c_int(d), _cf(eps))
+    return out, mean, rstd
+
+
+def layer_norm_backward(d_out, x, gamma, mean, rstd):
+    """(d_x, d_gamma, d_beta); the parameter gradients start from zero."""
+    x, d_out = _f(x), _f(d_out)
+    n, d = x.shape
+    d_x, d_gamma, d_beta = np.empty_like(x), np.zeros(d, np.float32), np.zeros(d, np.float32)
+    lib().orc_layer_norm_backward(_p(d_out), _p(x), _p(_f(gamma)), _p(_f(mean)), _p(_f(rstd)),
+                                  _p(d_x), _p(d_gamma), _p(d_beta), C.c_int(n), C.c_int(d))
+    return d_x, d_gamma, d_beta
+
+
+def cross_entropy_sum(logits, targets):
+    """(sum of negative log-likelihoods over valid targets, number of valid targets)."""
+    logits = _f(logits)
+    t = np.ascontiguousarray(targets, dtype=np.int32)
+    n, v = logits.shape
+    cnt = C.c_int(0)
+    f = lib().orc_cross_entropy_sum
+    f.restype = C.c_float
+    s = f(_p(logits), _pi(t), C.c_int(n), C.c_int(v), C.byref(cnt))
+    return float(s), int(cnt.value)
+
+
+def cross_entropy_backward(logits, targets, inv_count):
+    logits = _f(logits)
+    t = np.ascontiguousarray(targets, dtype=np.int32)
+    n, v = logits.shape
+    d = np.empty_like(logits)
+    lib().orc_cross_entropy_backward(_p(logits), _pi(t), _p(d), C.c_int(n), C.c_int(v), _cf(inv_count))
+    return d
+
+
+def embedding_gather(w_embed, ids):
+    w = _f(w_embed)
+    ids = np.ascontiguousarray(ids, dtype=np.int32)
+    out = np.empty((ids.size, w.shape[1]), np.float32)
+    lib().orc_embedding_gather(_p(w), _pi(ids), _p(out), C.c_int(ids.size), C.c_int(w.shape[1]))
+    return out
+
+
+def embedding_scatter_add(d_embedded, ids, vocab):
+    g = _f(d_embedded)
+    ids = np.ascontiguousarray(ids, dtype=np.int32)
+    d_embed = np.zeros((vocab, g.shape[1]), np.float32)
+    lib().orc_embedding_scatter_add(_p(g), _pi(ids), _p(d_embed), C.c_int(ids.size), C.c_int(g.shape[1]))
+    return d_embed

@@ -292,3 +292,81 @@ def test_grad_norm_clip(orc):
     assert abs(np.linalg.norm(g2) - 1.0) < 1e-4 and scale < 1.0
     g3, _, scale3 = orc.grad_norm_clip(g, 0.0)
     assert scale3 == 1.0 and np.array_equal(g3, g)
+
+
+# ── block glue (LayerNorm, cross-entropy, embedding): float64 closed forms and FD ──
+def test_layer_norm_matches_float64_closed_form(orc):
+    n, d = 7, 48
+    x = orc.rand_buf(n * d, 901, 1.5).reshape(n, d)
+    gamma = 1.0 + orc.rand_buf(d, 902, 0.3)
+    beta = orc.rand_buf(d, 903, 0.2)
+    out, mean, rstd = orc.layer_norm_forward(x, gamma, beta, 1e-5)
+    x64 = x.astype(np.float64)
+    mu = x64.mean(1, keepdims=True)
+    var = ((x64 - mu) ** 2).mean(1, keepdims=True)
+    ref = gamma * (x64 - mu) / np.sqrt(var + 1e-5) + beta
+    assert np.abs(out - ref).max() < 5e-6
+    assert np.abs(mean - mu[:, 0]).max() < 1e-6
+    assert np.abs(rstd - 1 / np.sqrt(var[:, 0] + 1e-5)).max() < 1e-5
+
+
+def test_layer_norm_backward_matches_finite_differences(orc):
+    n, d = 3, 16
+    x = orc.rand_buf(n * d, 911, 1.0).reshape(n, d).astype(np.float64)
+    gamma = (1.0 + orc.rand_buf(d, 912, 0.3)).astype(np.float64)
+    beta = orc.rand_buf(d, 913, 0.2).astype(np.float64)
+    w = orc.rand_buf(n * d, 914, 1.0).reshape(n, d).astype(np.float64)
+
+    def loss(x_, g_, b_):
+        mu = x_.mean(1, keepdims=True)
+        var = ((x_ - mu) ** 2).mean(1, keepdims=True)
+        return float((w * (g_ * (x_ - mu) / np.sqrt(var + 1e-5) + b_)).sum())
+
+    _, mean, rstd = orc.layer_norm_forward(x, gamma, beta, 1e-5)
+    d_x, d_gamma, d_beta = orc.layer_norm_backward(w, x, gamma, mean, rstd)
+    h = 1e-5
+    for (i, j) in [(0, 0), (1, 5), (2, 15)]:
+        xp, xm = x.copy(), x.copy()
+        xp[i, j] += h; xm[i, j] -= h
+        fd = (loss(xp, gamma, beta) - loss(xm, gamma, beta)) / (2 * h)
+        assert abs(d_x[i, j] - fd) < 2e-3 * max(1.0, abs(fd))
+    for j in (0, 7):
+        gp, gm = gamma.copy(), gamma.copy()
+        gp[j] += h; gm[j] -= h
+        fd = (loss(x, gp, beta) - loss(x, gm, beta)) / (2 * h)
+        assert abs(d_gamma[j] - fd) < 2e-3 * max(1.0, abs(fd))
+        assert abs(d_beta[j] - w[:, j].sum()) < 1e-4
+
+
+def test_cross_entropy_sum_and_gradient(orc):
+    n, v = 6, 37
+    logits = orc.rand_buf(n * v, 921, 3.0).reshape(n, v)
+    targets = np.array([0, 36, 5, -1, 40, 12], dtype=np.int32)   # two invalid targets are skipped
+    s, cnt = orc.cross_entropy_sum(logits, targets)
+    l64 = logits.astype(np.float64)
+    lse = np.log(np.exp(l64 - l64.max(1, keepdims=True)).sum(1)) + l64.max(1)
+    valid = [i for i in range(n) if 0 <= targets[i] < v]
+    ref = sum(lse[i] - l64[i, targets[i]] for i in valid)
+    assert cnt == len(valid)
+    assert abs(s - ref) < 1e-4
+    g = orc.cross_entropy_backward(logits, targets, 1.0 / cnt)
+    p = np.exp(l64 - lse[:, None])
+    for i in range(n):
+        if i in valid:
+            e = p[i].copy(); e[targets[i]] -= 1.0
+            assert np.abs(g[i] - e / cnt).max() < 1e-6
+        else:
+            assert np.all(g[i] == 0.0)
+
+
+def test_embedding_gather_scatter_are_adjoint(orc):
+    vocab, d, n = 11, 8, 9
+    w = orc.rand_buf(vocab * d, 931, 1.0).reshape(vocab, d)
+    ids = np.array([3, 3, 0, 10, 7, 3, 0, 1, 10], dtype=np.int32)
+    out = orc.embedding_gather(w, ids)
+    assert np.array_equal(out, w[ids])
+    g = orc.rand_buf(n * d, 932, 1.0).reshape(n, d)
+    dw = orc.embedding_scatter_add(g, ids, vocab)
+    ref = np.zeros((vocab, d), np.float64)
+    np.add.at(ref, ids, g.astype(np.float64))
+    assert np.abs(dw - ref).max() < 1e-6
