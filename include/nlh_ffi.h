@@ -320,7 +320,14 @@ int32_t nlh_mag_combine_backward(const float* d_out, const void* attn_proj, int3
 /* dy_ph[(b*H+h), t', :] = level_weights[level] * sum_{i<pool} d_ycomb[b, t'*pool+i, h*hd:(h+1)*hd]
  * (adjoint of repeat_upsample_1d + head transpose, pool_ops.cu / elementwise.cu). */
 int32_t nlh_pool_to_heads(const float* d_ycomb, const float* level_weights, int32_t level,
-    int32_t pool, float* dy_ph, int32_t batch, int32_t seq, int32_t d_model, int32_t num_heads);
+    int32_t pool, float* dy_ph, float* sum_out, int32_t batch, int32_t seq, int32_t d_model,
+    int32_t num_heads);
+/* A coarser level from a finer level's UNSCALED sums (sum_out of nlh_pool_to_heads or of this
+ * entry; optional, same layout as dy_ph), both per-head: src_sums [rows, src_seq, head_dim] ->
+ * dy_ph [rows, src_seq/factor, head_dim] = level_weights[level] * sum over factor source rows.
+ * Pooling by 512 then reads 1/64 of the data a direct pass over d_ycomb would. */
+int32_t nlh_pool_heads(const float* src_sums, const float* level_weights, int32_t level,
+    int32_t factor, float* dy_ph, float* sum_out, int32_t rows, int32_t src_seq, int32_t head_dim);
 
 /* ── Stacked-block glue (drop-in) ─────────────────────────────────────────────────────────────
  * LayerNorm over the last axis of x [n, d]; mean/rstd caches [n] feed the backward

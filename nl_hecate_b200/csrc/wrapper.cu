@@ -104,6 +104,89 @@ __global__ void __launch_bounds__(WR_THREADS) level_prep_fwd_kernel(
     if (threadIdx.x == 0) { k_norm[tok] = kn; q_norm[tok] = qn; }
 }
 
+// Warp-per-token variant for d % 8 == 0, head_dim % 8 == 0, d <= 1024: lane owns the 8-element
+// chunks c = lane + 32*i (i < NC) of each of k, v, q in registers, so the token is read once with
+// 16-byte loads, reduced with shuffles only (no barrier), and written with 16-byte stores.
+__device__ __forceinline__ void ld8(const float* p, float (&x)[8])
+{
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+}
+__device__ __forceinline__ void ld8(const __nv_bfloat16* p, float (&x)[8])
+{
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const unsigned w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]));
+        x[2 * i] = f.x; x[2 * i + 1] = f.y;
+    }
+}
+__device__ __forceinline__ void st8(float* p, const float (&x)[8], float s)
+{
+    *reinterpret_cast<float4*>(p) = make_float4(x[0] * s, x[1] * s, x[2] * s, x[3] * s);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(x[4] * s, x[5] * s, x[6] * s, x[7] * s);
+}
+
+constexpr int LPW_WARPS = 4;
+
+template <typename TIN, int NC>
+__global__ void __launch_bounds__(LPW_WARPS * 32) level_prep_fwd_warp_kernel(
+    const TIN* __restrict__ kvq, const float* __restrict__ w_gates, const float* __restrict__ b_alpha,
+    const float* __restrict__ b_theta, const float* __restrict__ b_eta,
+    float* __restrict__ k_ph, float* __restrict__ v_ph, float* __restrict__ q_ph,
+    float* __restrict__ alpha_ph, float* __restrict__ theta_ph, float* __restrict__ eta_ph,
+    float* __restrict__ k_norm, float* __restrict__ q_norm, int n_tok, int sf, int d, int H)
+{
+    const int lane = threadIdx.x & 31;
+    const int tok = blockIdx.x * LPW_WARPS + (threadIdx.x >> 5);
+    if (tok >= n_tok) return;
+    const int b = tok / sf, t = tok - b * sf;
+    const int hd = d / H, nc = d >> 3;
+    const TIN* row = kvq + (size_t)tok * 3 * d;
+    float kk[NC][8], vv[NC][8], qq[NC][8];
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < NC; i++) {
+        const int c = lane + 32 * i;
+        if (c < nc) {
+            ld8(row + 8 * c, kk[i]); ld8(row + d + 8 * c, vv[i]); ld8(row + 2 * d + 8 * c, qq[i]);
+            float wk[3][8], wv[3][8];
+#pragma unroll
+            for (int g = 0; g < 3; g++) {
+                ld8(w_gates + (size_t)g * 2 * d + 8 * c, wk[g]);
+                ld8(w_gates + (size_t)g * 2 * d + d + 8 * c, wv[g]);
+            }
+#pragma unroll
+            for (int e = 0; e < 8; e++) {
+                acc[0] += kk[i][e] * kk[i][e]; acc[1] += qq[i][e] * qq[i][e];
+#pragma unroll
+                for (int g = 0; g < 3; g++) { acc[2 + g] += kk[i][e] * wk[g][e]; acc[5 + g] += vv[i][e] * wv[g][e]; }
+            }
+        }
+    }
+#pragma unroll
+    for (int a = 0; a < 8; a++) acc[a] = warp_sum(acc[a]);
+    const float kn = sqrtf(acc[0]), qn = sqrtf(acc[1]);
+    const float ki = 1.0f / fmaxf(kn, 1e-8f), qi = 1.0f / fmaxf(qn, 1e-8f);
+#pragma unroll
+    for (int i = 0; i < NC; i++) {
+        const int c = lane + 32 * i;
+        if (c < nc) {
+            const int j = 8 * c, h = j / hd, w = j - h * hd;
+            const size_t dst = (((size_t)b * H + h) * sf + t) * hd + w;
+            st8(k_ph + dst, kk[i], ki); st8(v_ph + dst, vv[i], 1.0f); st8(q_ph + dst, qq[i], qi);
+        }
+    }
+    if (lane < H) {
+        const size_t g = ((size_t)b * H + lane) * sf + t;
+        alpha_ph[g] = wr_sigmoid(acc[2] * ki + acc[5] + *b_alpha);
+        theta_ph[g] = wr_softplus(acc[3] * ki + acc[6] + *b_theta);
+        eta_ph[g] = wr_sigmoid(acc[4] * ki + acc[7] + *b_eta);
+    }
+    if (lane == 0) { k_norm[tok] = kn; q_norm[tok] = qn; }
+}
+
 // ───────────────────────── level prep backward ────────────────────────────
 // One CTA per tok_per_cta tokens (see lp_tok_per_cta); thread owns elements j = tid + i*WR_THREADS (i < NE) of
 // each d-vector, so the gate-weight gradient accumulates in registers across the CTA's tokens
@@ -202,6 +285,137 @@ __global__ void __launch_bounds__(WR_THREADS) level_prep_bwd_kernel(
     }
 }
 
+
+// Warp-per-token backward (same conditions as level_prep_fwd_warp_kernel). A CTA covers
+// tok_per_cta consecutive tokens, warp w takes every LPW_WARPS-th of them; gate-weight gradients
+// accumulate in registers per lane and are combined over the CTA's warps through shared memory
+// into ONE partial row per CTA.
+__device__ __forceinline__ void st8_as(float* p, const float (&x)[8]) { st8(p, x, 1.0f); }
+__device__ __forceinline__ void st8_as(__nv_bfloat16* p, const float (&x)[8])
+{
+    uint4 u;
+    __nv_bfloat162 a = __floats2bfloat162_rn(x[0], x[1]), b = __floats2bfloat162_rn(x[2], x[3]);
+    __nv_bfloat162 c = __floats2bfloat162_rn(x[4], x[5]), e = __floats2bfloat162_rn(x[6], x[7]);
+    u.x = *reinterpret_cast<unsigned*>(&a); u.y = *reinterpret_cast<unsigned*>(&b);
+    u.z = *reinterpret_cast<unsigned*>(&c); u.w = *reinterpret_cast<unsigned*>(&e);
+    *reinterpret_cast<uint4*>(p) = u;
+}
+
+template <typename TIN, int NC>
+__global__ void __launch_bounds__(LPW_WARPS * 32) level_prep_bwd_warp_kernel(
+    const float* __restrict__ k_ph, const float* __restrict__ v_ph, const float* __restrict__ q_ph,
+    const float* __restrict__ alpha_ph, const float* __restrict__ theta_ph, const float* __restrict__ eta_ph,
+    const float* __restrict__ k_norm, const float* __restrict__ q_norm,
+    const float* __restrict__ dk_ph, const float* __restrict__ dv_ph, const float* __restrict__ dq_ph,
+    const float* __restrict__ dalpha_ph, const float* __restrict__ dtheta_ph, const float* __restrict__ deta_ph,
+    const float* __restrict__ w_gates, TIN* __restrict__ d_kvq, float* __restrict__ dw_partial,
+    float* __restrict__ db_partial, int n_tok, int sf, int d, int H, int tok_per_cta)
+{
+    __shared__ float sdw[6 * 1024];
+    __shared__ float sdb[3];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int hd = d / H, nc = d >> 3;
+    float dwk[3][NC][8], dwv[3][NC][8], db[3] = {0.f, 0.f, 0.f};
+#pragma unroll
+    for (int g = 0; g < 3; g++)
+#pragma unroll
+        for (int i = 0; i < NC; i++)
+#pragma unroll
+            for (int e = 0; e < 8; e++) { dwk[g][i][e] = 0.f; dwv[g][i][e] = 0.f; }
+    const int tok0 = blockIdx.x * tok_per_cta;
+    const int tok1 = min(tok0 + tok_per_cta, n_tok);
+    for (int tok = tok0 + warp; tok < tok1; tok += LPW_WARPS) {
+        const int b = tok / sf, t = tok - b * sf;
+        const size_t g0 = ((size_t)b * H) * sf + t;       // head 0 gate slot; heads are sf apart
+        const float al = alpha_ph[g0], th = theta_ph[g0], et = eta_ph[g0];
+        float s0 = 0.f, s1 = 0.f, s2 = 0.f;
+        if (lane < H) {
+            const size_t gi = g0 + (size_t)lane * sf;
+            s0 = dalpha_ph[gi]; s1 = dtheta_ph[gi]; s2 = deta_ph[gi];
+        }
+        s0 = warp_sum(s0); s1 = warp_sum(s1); s2 = warp_sum(s2);
+        const float dpre[3] = {s0 * al * (1.0f - al), s1 * (1.0f - expf(-th)), s2 * et * (1.0f - et)};
+        float kh[NC][8], qh[NC][8], gk[NC][8], gq[NC][8];
+        float dot_k = 0.f, dot_q = 0.f;
+        TIN* orow = d_kvq + (size_t)tok * 3 * d;
+#pragma unroll
+        for (int i = 0; i < NC; i++) {
+            const int c = lane + 32 * i;
+            if (c < nc) {
+                const int j = 8 * c, h = j / hd, w = j - h * hd;
+                const size_t src = (((size_t)b * H + h) * sf + t) * hd + w;
+                float vv[8], gv[8];
+                ld8(k_ph + src, kh[i]); ld8(v_ph + src, vv); ld8(q_ph + src, qh[i]);
+                ld8(dk_ph + src, gk[i]); ld8(dv_ph + src, gv); ld8(dq_ph + src, gq[i]);
+#pragma unroll
+                for (int g = 0; g < 3; g++) {
+                    float wk[8], wv[8];
+                    ld8(w_gates + (size_t)g * 2 * d + j, wk);
+                    ld8(w_gates + (size_t)g * 2 * d + d + j, wv);
+#pragma unroll
+                    for (int e = 0; e < 8; e++) {
+                        gk[i][e] += dpre[g] * wk[e];
+                        gv[e] += dpre[g] * wv[e];
+                        dwk[g][i][e] += dpre[g] * kh[i][e];
+                        dwv[g][i][e] += dpre[g] * vv[e];
+                    }
+                }
+#pragma unroll
+                for (int e = 0; e < 8; e++) { dot_k += gk[i][e] * kh[i][e]; dot_q += gq[i][e] * qh[i][e]; }
+                st8_as(orow + d + j, gv);
+            }
+        }
+        dot_k = warp_sum(dot_k);
+        dot_q = warp_sum(dot_q);
+        if (lane == 0) { db[0] += dpre[0]; db[1] += dpre[1]; db[2] += dpre[2]; }
+        const float kn = k_norm[tok], qn = q_norm[tok];
+        const float kinv = (kn >= 1e-8f) ? 1.0f / kn : 1e8f, qinv = (qn >= 1e-8f) ? 1.0f / qn : 1e8f;
+        const float kd = (kn >= 1e-8f) ? dot_k : 0.f, qd = (qn >= 1e-8f) ? dot_q : 0.f;
+#pragma unroll
+        for (int i = 0; i < NC; i++) {
+            const int c = lane + 32 * i;
+            if (c < nc) {
+                // sphere Jacobian of x/||x|| (core/src/tensor.rs:320-351)
+                float ok[8], oq[8];
+#pragma unroll
+                for (int e = 0; e < 8; e++) {
+                    ok[e] = (gk[i][e] - kh[i][e] * kd) * kinv;
+                    oq[e] = (gq[i][e] - qh[i][e] * qd) * qinv;
+                }
+                st8_as(orow + 8 * c, ok);
+                st8_as(orow + 2 * d + 8 * c, oq);
+            }
+        }
+    }
+    // combine the warps' gate-weight gradients: warp after warp into shared memory
+    for (int w = 0; w < LPW_WARPS; w++) {
+        if (warp == w) {
+#pragma unroll
+            for (int g = 0; g < 3; g++)
+#pragma unroll
+                for (int i = 0; i < NC; i++) {
+                    const int c = lane + 32 * i;
+                    if (c < nc) {
+#pragma unroll
+                        for (int e = 0; e < 8; e++) {
+                            float* pk = sdw + g * 2 * d + 8 * c + e;
+                            float* pv = pk + d;
+                            if (w == 0) { *pk = dwk[g][i][e]; *pv = dwv[g][i][e]; }
+                            else { *pk += dwk[g][i][e]; *pv += dwv[g][i][e]; }
+                        }
+                    }
+                }
+            if (lane == 0) {
+#pragma unroll
+                for (int g = 0; g < 3; g++) { if (w == 0) sdb[g] = db[g]; else sdb[g] += db[g]; }
+            }
+        }
+        __syncthreads();
+    }
+    float* dwp = dw_partial + (size_t)blockIdx.x * 3 * 2 * d;
+    for (int i = threadIdx.x; i < 6 * d; i += blockDim.x) dwp[i] = sdw[i];
+    if (threadIdx.x < 3) db_partial[blockIdx.x * 3 + threadIdx.x] = sdb[threadIdx.x];
+}
 
 // ───────────────────────── MAG combine ────────────────────────────────────
 struct CombineLevels {
@@ -333,7 +547,7 @@ __global__ void __launch_bounds__(256) mag_combine_bwd_kernel(
 // repeat-upsample followed by the level weight), written in the per-head layout.
 __global__ void __launch_bounds__(256) pool_to_heads_kernel(
     const float* __restrict__ d_ycomb, const float* __restrict__ wts, int level, int c,
-    float* __restrict__ dy_ph, int B, int S, int d, int H)
+    float* __restrict__ dy_ph, float* __restrict__ sum_out, int B, int S, int d, int H)
 {
     const int hd = d / H, d4 = d / 4, sf = S / c;
     const long long n4 = (long long)B * sf * d4;
@@ -350,8 +564,33 @@ __global__ void __launch_bounds__(256) pool_to_heads_kernel(
             a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
         }
         const int h = j / hd, w = j - h * hd;
+        const size_t o = (((size_t)b * H + h) * sf + tp) * hd + w;
+        if (sum_out != nullptr) *reinterpret_cast<float4*>(sum_out + o) = a;
         a.x *= scale; a.y *= scale; a.z *= scale; a.w *= scale;
-        *reinterpret_cast<float4*>(dy_ph + (((size_t)b * H + h) * sf + tp) * hd + w) = a;
+        *reinterpret_cast<float4*>(dy_ph + o) = a;
+    }
+}
+
+// Coarser level from a finer level's unscaled sums, both in the per-head layout:
+// dy_ph[n, t', :] = scale * sum_{i<f} src[n, t'*f + i, :]  (n = batch*heads rows of hd floats).
+__global__ void __launch_bounds__(256) pool_heads_kernel(
+    const float* __restrict__ src, const float* __restrict__ wts, int level, int f,
+    float* __restrict__ dy_ph, float* __restrict__ sum_out, long long n_out4, int hd4)
+{
+    const float scale = wts[level];
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_out4;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long row = i / hd4;                 // output row (n, t')
+        const int w4 = (int)(i - row * hd4);
+        const float4* sp = reinterpret_cast<const float4*>(src) + row * f * hd4 + w4;
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int q = 0; q < f; q++) {
+            const float4 v = sp[(size_t)q * hd4];
+            a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+        }
+        if (sum_out != nullptr) reinterpret_cast<float4*>(sum_out)[i] = a;
+        a.x *= scale; a.y *= scale; a.z *= scale; a.w *= scale;
+        reinterpret_cast<float4*>(dy_ph)[i] = a;
     }
 }
 
@@ -404,6 +643,22 @@ int32_t nlh_level_prep_forward(const void* kvq, int32_t kvq_is_bf16, const float
     const int n_tok = batch * seq;
     const size_t smem = (size_t)(3 * d_model + 8 * 32) * sizeof(float);
     cudaStream_t st = current_stream();
+    const bool al16 = ((((uintptr_t)kvq | (uintptr_t)w_gates | (uintptr_t)k_ph | (uintptr_t)v_ph | (uintptr_t)q_ph) & 15) == 0);
+    if (d_model % 8 == 0 && (d_model / num_heads) % 8 == 0 && num_heads <= 32 && al16) {
+        const int grid = (n_tok + LPW_WARPS - 1) / LPW_WARPS;
+        const int ncl = (d_model / 8 + 31) / 32;     // chunks per lane, <= 4 because d_model <= 1024
+#define NLH_LP_FWD(T, NC)                                                                         \
+    level_prep_fwd_warp_kernel<T, NC><<<grid, LPW_WARPS * 32, 0, st>>>(                              \
+        (const T*)kvq, w_gates, b_alpha, b_theta, b_eta, k_ph, v_ph, q_ph, alpha_ph, theta_ph,    \
+        eta_ph, k_norm, q_norm, n_tok, seq, d_model, num_heads)
+        if (kvq_is_bf16) {
+            if (ncl <= 1) NLH_LP_FWD(__nv_bfloat16, 1); else if (ncl <= 2) NLH_LP_FWD(__nv_bfloat16, 2); else NLH_LP_FWD(__nv_bfloat16, 4);
+        } else {
+            if (ncl <= 1) NLH_LP_FWD(float, 1); else if (ncl <= 2) NLH_LP_FWD(float, 2); else NLH_LP_FWD(float, 4);
+        }
+#undef NLH_LP_FWD
+        return check_launch("nlh_level_prep_forward") ? NLH_OK : NLH_ERR_CUDA;
+    }
     if (kvq_is_bf16)
         level_prep_fwd_kernel<__nv_bfloat16><<<n_tok, WR_THREADS, smem, st>>>(
             (const __nv_bfloat16*)kvq, w_gates, b_alpha, b_theta, b_eta, k_ph, v_ph, q_ph, alpha_ph,
@@ -428,6 +683,24 @@ int32_t nlh_level_prep_backward(const float* k_ph, const float* v_ph, const floa
     const int grid = nlh_level_prep_partial_rows(n_tok);
     const int ne = (d_model + WR_THREADS - 1) / WR_THREADS;
     cudaStream_t st = current_stream();
+    const bool al16 = ((((uintptr_t)k_ph | (uintptr_t)v_ph | (uintptr_t)q_ph | (uintptr_t)dk_ph | (uintptr_t)dv_ph |
+                         (uintptr_t)dq_ph | (uintptr_t)w_gates | (uintptr_t)d_kvq) & 15) == 0);
+    // the register-resident gate-weight gradients fit for up to 2 chunks per lane (d_model <= 512)
+    if (d_model % 8 == 0 && d_model <= 512 && (d_model / num_heads) % 8 == 0 && num_heads <= 32 && al16) {
+        const int ncl = (d_model / 8 + 31) / 32;
+#define NLH_LP_BWDW(T, NC)                                                                       \
+    level_prep_bwd_warp_kernel<T, NC><<<grid, LPW_WARPS * 32, 0, st>>>(                             \
+        k_ph, v_ph, q_ph, alpha_ph, theta_ph, eta_ph, k_norm, q_norm, dk_ph, dv_ph, dq_ph,       \
+        dalpha_ph, dtheta_ph, deta_ph, w_gates, (T*)d_kvq, dw_partial, db_partial, n_tok, seq,   \
+        d_model, num_heads, lp_tok_per_cta(n_tok))
+        if (kvq_is_bf16) {
+            if (ncl <= 1) NLH_LP_BWDW(__nv_bfloat16, 1); else NLH_LP_BWDW(__nv_bfloat16, 2);
+        } else {
+            if (ncl <= 1) NLH_LP_BWDW(float, 1); else NLH_LP_BWDW(float, 2);
+        }
+#undef NLH_LP_BWDW
+        return check_launch("nlh_level_prep_backward") ? NLH_OK : NLH_ERR_CUDA;
+    }
 #define NLH_LP_BWD(T, NE)                                                                        \
     level_prep_bwd_kernel<T, NE><<<grid, WR_THREADS, 0, st>>>(                                   \
         k_ph, v_ph, q_ph, alpha_ph, theta_ph, eta_ph, k_norm, q_norm, dk_ph, dv_ph, dq_ph,       \
@@ -522,7 +795,8 @@ int32_t nlh_mag_combine_backward(const float* d_out, const void* attn_proj, int3
 }
 
 int32_t nlh_pool_to_heads(const float* d_ycomb, const float* level_weights, int32_t level,
-    int32_t pool, float* dy_ph, int32_t batch, int32_t seq, int32_t d_model, int32_t num_heads)
+    int32_t pool, float* dy_ph, float* sum_out, int32_t batch, int32_t seq, int32_t d_model,
+    int32_t num_heads)
 {
     int rc = wr_check("nlh_pool_to_heads", batch, seq, d_model, num_heads);
     if (rc != NLH_OK || batch == 0) return rc;
@@ -532,8 +806,23 @@ int32_t nlh_pool_to_heads(const float* d_ycomb, const float* level_weights, int3
     }
     const long long n4 = (long long)batch * (seq / pool) * (d_model / 4);
     pool_to_heads_kernel<<<wr_grid(n4, 256), 256, 0, current_stream()>>>(
-        d_ycomb, level_weights, level, pool, dy_ph, batch, seq, d_model, num_heads);
+        d_ycomb, level_weights, level, pool, dy_ph, sum_out, batch, seq, d_model, num_heads);
     return check_launch("nlh_pool_to_heads") ? NLH_OK : NLH_ERR_CUDA;
+}
+
+int32_t nlh_pool_heads(const float* src_sums, const float* level_weights, int32_t level,
+    int32_t factor, float* dy_ph, float* sum_out, int32_t rows, int32_t src_seq, int32_t head_dim)
+{
+    if (rows < 0 || src_seq <= 0 || head_dim <= 0 || head_dim % 4 != 0 || factor <= 0 ||
+        src_seq % factor != 0 || level < 0 || level >= WR_MAX_LEVELS) {
+        record_status(NLH_ERR_INVALID_ARG, "nlh_pool_heads", "bad dimensions, factor or level");
+        return NLH_ERR_INVALID_ARG;
+    }
+    if (rows == 0) return NLH_OK;
+    const long long n4 = (long long)rows * (src_seq / factor) * (head_dim / 4);
+    pool_heads_kernel<<<wr_grid(n4, 256), 256, 0, current_stream()>>>(
+        src_sums, level_weights, level, factor, dy_ph, sum_out, n4, head_dim / 4);
+    return check_launch("nlh_pool_heads") ? NLH_OK : NLH_ERR_CUDA;
 }
 
 }  // extern "C"

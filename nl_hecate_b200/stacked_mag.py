@@ -202,10 +202,22 @@ class _MagCombine(torch.autograd.Function):
                n_partial_rows=rows, dy0=direct[0], dy1=direct[1], dy2=direct[2], dy3=direct[3],
                batch=B, seq=S, d_model=d, num_heads=H)
         d_wts = dwp.sum(0)[:k]
-        for l in range(k):
-            if cp[l] != 1:
+        # pooled levels, finest first; a level whose pool factor is a multiple of the previous
+        # pooled level's is reduced from that level's unscaled sums instead of from d_ycomb
+        order = sorted((l for l in range(k) if cp[l] != 1), key=lambda l: cp[l])
+        prev = None                                        # (pool factor, unscaled sums)
+        for i, l in enumerate(order):
+            later = any(cp[m] % cp[l] == 0 for m in order[i + 1:])
+            sums = torch.empty_like(dys[l]) if later else None
+            if prev is not None and cp[l] % prev[0] == 0:
+                D.call("nlh_pool_heads", src_sums=prev[1], level_weights=wts, level=l,
+                       factor=cp[l] // prev[0], dy_ph=dys[l], sum_out=sums, rows=B * H,
+                       src_seq=S // prev[0], head_dim=d // H)
+            else:
                 D.call("nlh_pool_to_heads", d_ycomb=d_yc, level_weights=wts, level=l, pool=cp[l],
-                       dy_ph=dys[l], batch=B, seq=S, d_model=d, num_heads=H)
+                       dy_ph=dys[l], sum_out=sums, batch=B, seq=S, d_model=d, num_heads=H)
+            if sums is not None:
+                prev = (cp[l], sums)
         return (d_out, d_ap, d_wts, None, None, *dys)
 
 

@@ -104,5 +104,33 @@ def test_wrapper_rejects_unsupported_shapes():
     from nl_hecate_b200 import dispatch as D
     z = torch.zeros(16, device="cuda")
     with pytest.raises(RuntimeError):   # head_dim 6 is not a multiple of 4
-        D.call("nlh_pool_to_heads", d_ycomb=z, level_weights=z, level=0, pool=1, dy_ph=z, batch=1,
-               seq=1, d_model=12, num_heads=2)
+        D.call("nlh_pool_to_heads", d_ycomb=z, level_weights=z, level=0, pool=1, dy_ph=z, sum_out=None,
+               batch=1, seq=1, d_model=12, num_heads=2)
+    with pytest.raises(RuntimeError):   # 6 source rows cannot be pooled by 4
+        D.call("nlh_pool_heads", src_sums=z, level_weights=z, level=1, factor=4, dy_ph=z, sum_out=None,
+               rows=1, src_seq=6, head_dim=4)
+
+
+def test_hierarchical_pooling_equals_direct_pooling():
+    """Pooling by 64 from the by-8 sums gives what a direct pass over d_ycomb gives."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from nl_hecate_b200 import dispatch as D
+    B, S, d, H = 3, 128, 64, 4
+    g = torch.Generator(device="cuda").manual_seed(5)
+    dyc = torch.randn(B, S, d, device="cuda", generator=g)
+    wts = torch.tensor([0.1, 0.2, 0.3, 0.4], device="cuda")
+    hd = d // H
+    fine = torch.empty(B * H, S // 8, hd, device="cuda")
+    sums = torch.empty_like(fine)
+    D.call("nlh_pool_to_heads", d_ycomb=dyc, level_weights=wts, level=1, pool=8, dy_ph=fine, sum_out=sums,
+           batch=B, seq=S, d_model=d, num_heads=H)
+    ref8 = dyc.view(B, S // 8, 8, H, hd).sum(2).permute(0, 2, 1, 3).reshape(B * H, S // 8, hd)
+    assert _rel(sums, ref8) <= 1e-6 and _rel(fine, 0.2 * ref8) <= 1e-6
+    direct = torch.empty(B * H, S // 64, hd, device="cuda")
+    D.call("nlh_pool_to_heads", d_ycomb=dyc, level_weights=wts, level=2, pool=64, dy_ph=direct, sum_out=None,
+           batch=B, seq=S, d_model=d, num_heads=H)
+    chained = torch.empty_like(direct)
+    D.call("nlh_pool_heads", src_sums=sums, level_weights=wts, level=2, factor=8, dy_ph=chained, sum_out=None,
+           rows=B * H, src_seq=S // 8, head_dim=hd)
+    assert _rel(chained, direct) <= 1e-5
