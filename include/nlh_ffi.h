@@ -329,6 +329,18 @@ int32_t nlh_pool_to_heads(const float* d_ycomb, const float* level_weights, int3
 int32_t nlh_pool_heads(const float* src_sums, const float* level_weights, int32_t level,
     int32_t factor, float* dy_ph, float* sum_out, int32_t rows, int32_t src_seq, int32_t head_dim);
 
+/* Mean pooling of consecutive token rows (the input of a coarser CMS level,
+ * core/src/gpu_stacked_forward.rs:1879-1890, pool_ops.cu): src [rows_out*factor, d_model] fp32 ->
+ * out [rows_out, d_model] (fp32 or bf16) = scale * sum of factor rows; sum_out (optional, fp32)
+ * keeps the unscaled sums so that the next coarser level pools those instead of src. */
+int32_t nlh_mean_pool(const float* src, int32_t factor, float scale, void* out, int32_t out_is_bf16,
+    float* sum_out, int32_t rows_out, int32_t d_model);
+/* Adjoint of up to three mean pools in one pass: out[b, t, :] = sum_l g_l[b, t / c_l, :] / c_l,
+ * g_l [batch, seq/c_l, d_model] fp32 or bf16. */
+int32_t nlh_unpool_sum(const void* g0, int32_t c0, int32_t g0_is_bf16, const void* g1, int32_t c1,
+    int32_t g1_is_bf16, const void* g2, int32_t c2, int32_t g2_is_bf16, int32_t n_src, float* out,
+    int32_t batch, int32_t seq, int32_t d_model);
+
 /* ── Stacked-block glue (drop-in) ─────────────────────────────────────────────────────────────
  * LayerNorm over the last axis of x [n, d]; mean/rstd caches [n] feed the backward
  * (core/src/cuda_ffi.rs:487-491, kernels core/kernels/layer_norm.cu; CPU statement

@@ -594,6 +594,62 @@ __global__ void __launch_bounds__(256) pool_heads_kernel(
     }
 }
 
+// Mean pooling of token rows for the coarser levels (core/kernels/pool_ops.cu mean_pool_1d):
+// out[r, :] = scale * sum_{i<f} src[r*f + i, :], optional unscaled sums for the next level.
+template <typename TOUT>
+__global__ void __launch_bounds__(256) mean_pool_kernel(const float* __restrict__ src, int f, float scale,
+    TOUT* __restrict__ out, float* __restrict__ sum_out, long long n_out4, int d4)
+{
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_out4;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long row = i / d4;
+        const int c4 = (int)(i - row * d4);
+        const float4* sp = reinterpret_cast<const float4*>(src) + row * f * d4 + c4;
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+        for (int q = 0; q < f; q++) {
+            const float4 v = sp[(size_t)q * d4];
+            a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+        }
+        if (sum_out != nullptr) reinterpret_cast<float4*>(sum_out)[i] = a;
+        a.x *= scale; a.y *= scale; a.z *= scale; a.w *= scale;
+        st4(out + i * 4, a);
+    }
+}
+
+// Adjoint of the mean pools of up to three levels in one pass:
+// out[b, t, :] = sum_l g_l[b, t / c_l, :] / c_l  (core/kernels/pool_ops.cu repeat_upsample_1d + scale).
+struct UnpoolSrc {
+    const void* g[3];
+    int c[3];
+    int is_bf16[3];
+    int n;
+};
+__global__ void __launch_bounds__(256) unpool_sum_kernel(UnpoolSrc P, float* __restrict__ out,
+                                                         long long n4, int S, int d4)
+{
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long bt = i / d4;
+        const int c4 = (int)(i - bt * d4);
+        const long long b = bt / S;
+        const int t = (int)(bt - b * S);
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int l = 0; l < 3; l++) {
+            if (l < P.n) {
+                const long long row = b * (S / P.c[l]) + t / P.c[l];
+                const size_t o = ((size_t)row * d4 + c4) * 4;
+                const float4 v = P.is_bf16[l] ? ld4<__nv_bfloat16>((const __nv_bfloat16*)P.g[l] + o)
+                                              : ld4<float>((const float*)P.g[l] + o);
+                const float inv = 1.0f / (float)P.c[l];
+                a.x += v.x * inv; a.y += v.y * inv; a.z += v.z * inv; a.w += v.w * inv;
+            }
+        }
+        *reinterpret_cast<float4*>(out + i * 4) = a;
+    }
+}
+
 static int wr_grid(long long items, int per_cta)
 {
     long long need = (items + per_cta - 1) / per_cta;
@@ -823,6 +879,50 @@ int32_t nlh_pool_heads(const float* src_sums, const float* level_weights, int32_
     pool_heads_kernel<<<wr_grid(n4, 256), 256, 0, current_stream()>>>(
         src_sums, level_weights, level, factor, dy_ph, sum_out, n4, head_dim / 4);
     return check_launch("nlh_pool_heads") ? NLH_OK : NLH_ERR_CUDA;
+}
+
+int32_t nlh_mean_pool(const float* src, int32_t factor, float scale, void* out, int32_t out_is_bf16,
+    float* sum_out, int32_t rows_out, int32_t d_model)
+{
+    if (rows_out < 0 || factor <= 0 || d_model <= 0 || d_model % 4 != 0 || !src || !out ||
+        ((((uintptr_t)src | (uintptr_t)out | (uintptr_t)sum_out) & 15) != 0)) {
+        record_status(NLH_ERR_INVALID_ARG, "nlh_mean_pool", "bad dimensions, factor or alignment");
+        return NLH_ERR_INVALID_ARG;
+    }
+    if (rows_out == 0) return NLH_OK;
+    const long long n4 = (long long)rows_out * (d_model / 4);
+    cudaStream_t st = current_stream();
+    if (out_is_bf16)
+        mean_pool_kernel<__nv_bfloat16><<<wr_grid(n4, 256), 256, 0, st>>>(src, factor, scale, (__nv_bfloat16*)out, sum_out, n4, d_model / 4);
+    else
+        mean_pool_kernel<float><<<wr_grid(n4, 256), 256, 0, st>>>(src, factor, scale, (float*)out, sum_out, n4, d_model / 4);
+    return check_launch("nlh_mean_pool") ? NLH_OK : NLH_ERR_CUDA;
+}
+
+int32_t nlh_unpool_sum(const void* g0, int32_t c0, int32_t g0_is_bf16, const void* g1, int32_t c1,
+    int32_t g1_is_bf16, const void* g2, int32_t c2, int32_t g2_is_bf16, int32_t n_src, float* out,
+    int32_t batch, int32_t seq, int32_t d_model)
+{
+    UnpoolSrc P;
+    const void* gs[3] = {g0, g1, g2};
+    const int cs[3] = {c0, c1, c2}, bs[3] = {g0_is_bf16, g1_is_bf16, g2_is_bf16};
+    bool ok = batch >= 0 && seq > 0 && d_model > 0 && d_model % 8 == 0 && n_src >= 1 && n_src <= 3 && out &&
+              (((uintptr_t)out & 15) == 0);
+    for (int l = 0; l < 3; l++) {
+        P.g[l] = l < n_src ? gs[l] : nullptr;
+        P.c[l] = l < n_src ? cs[l] : 1;
+        P.is_bf16[l] = bs[l];
+        if (l < n_src && (gs[l] == nullptr || cs[l] <= 0 || seq % cs[l] != 0 || ((uintptr_t)gs[l] & 15) != 0)) ok = false;
+    }
+    P.n = n_src;
+    if (!ok) {
+        record_status(NLH_ERR_INVALID_ARG, "nlh_unpool_sum", "bad dimensions, pool factors or alignment");
+        return NLH_ERR_INVALID_ARG;
+    }
+    if (batch == 0) return NLH_OK;
+    const long long n4 = (long long)batch * seq * (d_model / 4);
+    unpool_sum_kernel<<<wr_grid(n4, 256), 256, 0, current_stream()>>>(P, out, n4, seq, d_model / 4);
+    return check_launch("nlh_unpool_sum") ? NLH_OK : NLH_ERR_CUDA;
 }
 
 }  // extern "C"

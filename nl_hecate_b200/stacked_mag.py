@@ -221,6 +221,54 @@ class _MagCombine(torch.autograd.Function):
         return (d_out, d_ap, d_wts, None, None, *dys)
 
 
+class _PoolLevels(torch.autograd.Function):
+    """Inputs of the pooled CMS levels: mean over c_l consecutive tokens of m_in [B, S, d] for each
+    pool factor (ascending), coarser levels reduced from the finer level's sums when divisible
+    (nlh_mean_pool); the backward adds all levels' upsampled gradients in one pass
+    (nlh_unpool_sum). Outputs are bf16 when out_bf16 (they feed the projection GEMM)."""
+
+    @staticmethod
+    def forward(ctx, m_in, pools, out_bf16):
+        m_in = m_in.contiguous()
+        B, S, d = m_in.shape
+        dt = torch.bfloat16 if out_bf16 else torch.float32
+        outs, prev = [], None                       # prev = (pool factor, unscaled sums)
+        for i, c in enumerate(pools):
+            later = any(c2 % c == 0 for c2 in pools[i + 1:])
+            out = torch.empty(B, S // c, d, dtype=dt, device=m_in.device)
+            sums = torch.empty(B, S // c, d, dtype=torch.float32, device=m_in.device) if later else None
+            if prev is not None and c % prev[0] == 0:
+                src, f = prev[1], c // prev[0]
+            else:
+                src, f = m_in, c
+            D.call("nlh_mean_pool", src=src, factor=f, scale=1.0 / c, out=out, out_is_bf16=int(out_bf16),
+                   sum_out=sums, rows_out=B * (S // c), d_model=d)
+            if sums is not None:
+                prev = (c, sums)
+            outs.append(out)
+        ctx.meta = (B, S, d, tuple(pools))
+        return tuple(outs)
+
+    @staticmethod
+    def backward(ctx, *grads):
+        B, S, d, pools = ctx.meta
+        dev = next(g for g in grads if g is not None).device
+        out = torch.empty(B, S, d, dtype=torch.float32, device=dev)
+        src = [(g.contiguous(), c) for g, c in zip(grads, pools) if g is not None]
+        first = True
+        for i in range(0, len(src), 3):              # three levels per pass
+            part = src[i:i + 3] + [(None, 1)] * (3 - len(src[i:i + 3]))
+            dst = out if first else torch.empty_like(out)
+            D.call("nlh_unpool_sum", g0=part[0][0], c0=part[0][1], g0_is_bf16=int(part[0][0].dtype == torch.bfloat16),
+                   g1=part[1][0], c1=part[1][1], g1_is_bf16=int(part[1][0] is not None and part[1][0].dtype == torch.bfloat16),
+                   g2=part[2][0], c2=part[2][1], g2_is_bf16=int(part[2][0] is not None and part[2][0].dtype == torch.bfloat16),
+                   n_src=len(src[i:i + 3]), out=dst, batch=B, seq=S, d_model=d)
+            if not first:
+                out += dst
+            first = False
+        return out, None, None
+
+
 class _LayerNorm(torch.autograd.Function):
     """Row LayerNorm through nlh_layer_norm_forward / _backward. mode 0: fp32 output, 1: bf16
     output, 2: both (fp32 for the pooled levels, bf16 for the GEMM that follows)."""
@@ -411,16 +459,11 @@ class StackedMAG:
         y = y.view(B, nh, sf, hd).permute(0, 2, 1, 3).reshape(B, sf, d)
         return y.repeat_interleave(c, dim=1) if c > 1 else y
 
-    def _level_fused(self, b, l, m_in, m_in_gemm):
-        """Level through the fused wrapper kernels; returns the per-head output and the pool
-        factor. m_in: LayerNorm output in fp32 (pooled levels average it); m_in_gemm: the same
-        in the GEMM's input type (used as is by the unpooled level)."""
+    def _level_fused(self, b, l, x):
+        """Level through the fused wrapper kernels; x is the level's (already pooled) input
+        [B, S/c, d]. Returns the per-head output."""
         cfg, p = self.cfg, self.p
-        B, S, d = m_in.shape
-        c = min(cfg.chunk_sizes[l], S)
-        assert S % c == 0, "seq_len must be a multiple of every chunk size"
-        sf = S // c
-        x = m_in.view(B, sf, c, d).mean(2) if c > 1 else m_in_gemm
+        sf = x.shape[1]
         pre = f"b{b}.l{l}."
         kvq = self._mm(x, p[pre + "w_kvq_mem"])
         k, v, q, alpha, theta, eta = _LevelPrep.apply(kvq, p[pre + "w_gates"], p[pre + "b_alpha"],
@@ -429,7 +472,7 @@ class StackedMAG:
         chunk = 0 if l in cfg.exact_levels else min(cfg.chunk_sizes[l], sf)
         y, m_final = self.memory_fn(k, v, q, alpha, theta, eta, self.context[b][l], chunk)
         self.context[b][l].copy_(m_final.detach())   # in place: addresses stay fixed for graph replay
-        return y, c
+        return y
 
     def _ln(self, x, name, mode, fused):
         p = self.p
@@ -456,10 +499,14 @@ class StackedMAG:
             if fused:
                 m32, m16 = self._ln(res1, pre + "ln_mem_", 2, True) if cfg.bf16 else \
                     (self._ln(res1, pre + "ln_mem_", 0, True),) * 2
-                ys, pools = [], []
-                for l in range(cfg.k):
-                    y_ph, c = self._level_fused(b, l, m32, m16)
-                    ys.append(y_ph); pools.append(c)
+                S = res1.shape[1]
+                cs = [min(c, S) for c in cfg.chunk_sizes[:cfg.k]]
+                uniq = sorted({c for c in cs if c > 1})
+                pooled = dict(zip(uniq, _PoolLevels.apply(m32, tuple(uniq), cfg.bf16))) if uniq else {}
+                for c in cs:
+                    assert S % c == 0, "seq_len must be a multiple of every chunk size"
+                ys = [self._level_fused(b, l, pooled.get(cs[l], m16)) for l in range(cfg.k)]
+                pools = cs
                 x = _MagCombine.apply(x, attn_raw, wts, tuple(pools), nh, *ys)
             else:
                 m_in = self._ln(res1, pre + "ln_mem_", 0, False)

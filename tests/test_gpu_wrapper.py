@@ -134,3 +134,26 @@ def test_hierarchical_pooling_equals_direct_pooling():
     D.call("nlh_pool_heads", src_sums=sums, level_weights=wts, level=2, factor=8, dy_ph=chained, sum_out=None,
            rows=B * H, src_seq=S // 8, head_dim=hd)
     assert _rel(chained, direct) <= 1e-5
+
+
+@pytest.mark.parametrize("pools,dtype", [((8, 64, 512), torch.bfloat16), ((2, 8, 24), torch.float32),
+                                         ((4,), torch.float32), ((2, 3, 4, 12), torch.bfloat16)])
+def test_pool_levels_forward_backward(pools, dtype):
+    """Mean pooling of the level inputs and its fused adjoint vs torch."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from nl_hecate_b200.stacked_mag import _PoolLevels
+    B, d = 2, 64
+    S = 512 if 512 in pools else 48
+    g = torch.Generator(device="cuda").manual_seed(S)
+    x1 = torch.randn(B, S, d, device="cuda", generator=g, requires_grad=True)
+    x2 = x1.detach().clone().requires_grad_(True)
+    outs = _PoolLevels.apply(x1, pools, dtype == torch.bfloat16)
+    refs = [x2.view(B, S // c, c, d).mean(2).to(dtype) for c in pools]
+    ws = [torch.randn(o.shape, device="cuda", generator=g) for o in refs]
+    tol = 1e-2 if dtype == torch.bfloat16 else 1e-5
+    for o, r in zip(outs, refs):
+        assert o.dtype == dtype and _rel(o, r) <= tol
+    sum((o.float() * w).sum() for o, w in zip(outs, ws)).backward()
+    sum((r.float() * w).sum() for r, w in zip(refs, ws)).backward()
+    assert _rel(x1.grad, x2.grad) <= tol
