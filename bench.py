@@ -452,7 +452,7 @@ class StackedModelStep:
         ms, _, _ = self.dd.titans_forward_dd(k, v, q, al, th, et, m0, m0, store_s=False)
         bytes_ = (4 + 3) * n * s * d * 4 + 6 * n * s * 4 + n * (s + 1) * d * d * 4
         self._dom = (k, v, q, al, th, et, ms, dy)
-        return ("fast_bwd_kernel<64,TITANS,exact,S-derived> at level-0 shapes",
+        return ("titans_exact_bwd_kernel<64> (exact Titans backward, M-only trajectory) at level-0 shapes",
                 lambda: self.dd.titans_backward_dd(k, v, q, al, th, et, ms, None, dy), bytes_, "hbm")
 
     def cpu_sample(self, oracle, threads, budget_s=12.0):

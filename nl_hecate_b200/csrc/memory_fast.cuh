@@ -51,10 +51,13 @@ __device__ __forceinline__ float row_allreduce(float v)
 template <int D>
 __device__ __forceinline__ int col_of(int i, int cg) { return (i >> 2) * (D / 4) + cg * 4 + (i & 3); }
 
-// Packed fp32x2 arithmetic (one instruction for two lanes of a 64-bit register pair on sm_100).
-__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
-__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
-__device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
+// Two-lane arithmetic on float2 values. Written as two scalar operations on purpose: the
+// sm_100 packed-pair intrinsics (__ffma2_rn and friends) were measured on these kernels and
+// lost — the compiler spent as many moves forming aligned register pairs as the packed
+// instructions saved (same instruction total, 9 % longer run time).
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return make_float2(fmaf(a.x, b.x, c.x), fmaf(a.y, b.y, c.y)); }
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return make_float2(a.x * b.x, a.y * b.y); }
+__device__ __forceinline__ float2 add2(float2 a, float2 b) { return make_float2(a.x + b.x, a.y + b.y); }
 __device__ __forceinline__ float2 bc2(float s) { return make_float2(s, s); }
 __device__ __forceinline__ float2 shfl_xor2(float2 v, int o)
 {
@@ -713,16 +716,16 @@ static bool fast_forward(int rule, const FwdArgs& a, cudaStream_t st)
     return false;
 }
 
+// Exact Titans backward on an M-only trajectory (defined in memory_exact_bwd.cuh).
+template <int D>
+static bool exact_bwd_launch(const BwdArgs& a, cudaStream_t st);
+
 template <int D, int RULE>
 static bool fast_bwd_launch(const BwdArgs& a, cudaStream_t st)
 {
     const bool sder = (RULE == RULE_TITANS && a.s_traj == nullptr);
     const size_t smem = fast_bwd_smem_floats<D>((RULE == RULE_TITANS && !sder) ? 2 : 1, a.frozen) * sizeof(float);
-    if (sder) {   // checked by the caller: stored-trajectory mode
-        cudaFuncSetAttribute(fast_bwd_kernel<D, RULE, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        fast_bwd_kernel<D, RULE, false, true><<<a.batch, FastGeom<D>::NT, smem, st>>>(a);
-        return true;
-    }
+    if (sder) return exact_bwd_launch<D>(a, st);   // checked by the caller: stored-trajectory mode
     if (a.frozen) {
         cudaFuncSetAttribute(fast_bwd_kernel<D, RULE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         fast_bwd_kernel<D, RULE, true><<<a.batch, FastGeom<D>::NT, smem, st>>>(a);

@@ -5,7 +5,7 @@
 // Dispatch: register-resident kernels (memory_fast.cuh) when the head
 // dimension and options allow it, the generic-d kernels otherwise.
 #include "memory_generic.cuh"
-#include "memory_fast.cuh"
+#include "memory_exact_bwd.cuh"
 #include "../../include/nlh_ffi.h"
 
 namespace nlh {
