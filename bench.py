@@ -624,8 +624,7 @@ def main():
             print(json.dumps({"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world,
                               "steps": args.steps, "warmup": warmup, "ms_per_step": ms / args.steps,
                               "timed_only": True, "config": wl.describe()}))
-        if world > 1:
-            dist.destroy_process_group()
+        finish(world, barrier, wl)
         return
 
     # end to end through the host-slice API
@@ -674,8 +673,28 @@ def main():
             "gpu_launches": wl.launches_per_step * args.steps,
             "roofline": roofline, "cpu_baseline": cpu,
         }))
-    if world > 1:
-        dist.destroy_process_group()
+    finish(world, barrier, wl)
+
+
+def finish(world, barrier, wl):
+    """End of a run. With several ranks: wait for everyone, drop the captured step graph (it
+    holds the communicator's resources) and leave without running NCCL's teardown, which can
+    block forever once a captured collective has been replayed."""
+    sys.stdout.flush()
+    sys.stderr.flush()
+    if world <= 1:
+        return
+    # the result line is out: whatever happens below, leave within a minute
+    watchdog = threading.Timer(60.0, lambda: os._exit(0))
+    watchdog.daemon = True
+    watchdog.start()
+    barrier()
+    model = getattr(wl, "model", None)
+    if model is not None and getattr(model, "_graph", None) is not None:
+        model._graph = None
+    import torch
+    torch.cuda.synchronize()
+    os._exit(0)
 
 
 if __name__ == "__main__":
