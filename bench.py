@@ -452,6 +452,10 @@ class StackedModelStep:
         ms, _, _ = self.dd.titans_forward_dd(k, v, q, al, th, et, m0, m0, store_s=False)
         bytes_ = (4 + 3) * n * s * d * 4 + 6 * n * s * 4 + n * (s + 1) * d * d * 4
         self._dom = (k, v, q, al, th, et, ms, dy)
+        # DRAM bytes of one launch from the profiler capture of this kernel on a smaller case
+        # (296 problems x 128 tokens: 664.94 MB read + 28.05 MB written), scaled by problem-tokens
+        # (traffic is proportional to them); see profiles/titans_exact_level0_kernels.md
+        self.dominant_traffic = (664_938_496 + 28_052_224) / (296 * 128) * n * s
         return ("titans_exact_bwd_kernel<64> (exact Titans backward, M-only trajectory) at level-0 shapes",
                 lambda: self.dd.titans_backward_dd(k, v, q, al, th, et, ms, None, dy), bytes_, "hbm")
 
@@ -647,7 +651,8 @@ def main():
         achieved = work / (ms_dom * 1e-3) / 1e12
         peak, runit = peaks["bf16_tflops"], "TFLOP/s"
     roofline = {"kernel": name, "bound": bound, "achieved": achieved, "peak": peak, "unit": runit,
-                "frac": achieved / peak, "traffic": None, "ms_per_launch": ms_dom,
+                "frac": achieved / peak, "traffic": getattr(wl, "dominant_traffic", None),
+                "ms_per_launch": ms_dom,
                 "algorithmic_work_per_launch": work, "peak_source": peaks["source"]}
 
     cpu = None
