@@ -249,6 +249,16 @@ int32_t nlh_swa_backward(const uint16_t* q, const uint16_t* k, const uint16_t* v
     float* d_v, int32_t seq_len, int32_t num_heads, int32_t head_dim, int32_t window_size,
     int32_t batch_size, int32_t n_persistent);
 
+/* Packed variants for callers that keep q|k|v as the rows of one projection output
+ * qkv [batch, seq, 3*heads*head_dim] bf16: no split copies before the forward, and the backward
+ * takes d_attn_out in bf16 and OVERWRITES d_qkv (same packed layout, bf16) — no casts or
+ * concatenation around the attention. out and d_attn_out are dense [batch, seq, heads*head_dim]. */
+int32_t nlh_swa_forward_packed(const uint16_t* qkv, uint16_t* out, float* lse, int32_t seq_len,
+    int32_t num_heads, int32_t head_dim, int32_t window_size, int32_t batch_size, int32_t n_persistent);
+int32_t nlh_swa_backward_packed(const uint16_t* qkv, const uint16_t* out, const float* lse,
+    const uint16_t* d_attn_out, uint16_t* d_qkv, int32_t seq_len, int32_t num_heads, int32_t head_dim,
+    int32_t window_size, int32_t batch_size, int32_t n_persistent);
+
 /* Library options (no counterpart in the reference). NLH_OPT_SWA_TCGEN05 (default 1) runs the
  * head_dim-64 SWA forward on the tcgen05/TMEM kernel; 0 selects the mma.sync kernel instead. nlh_swa_tc_timeout_flag()
  * synchronously reads a device flag that the tcgen05 kernel sets if one of its bounded mbarrier

@@ -110,6 +110,33 @@ __device__ __forceinline__ void load_tile_f32_as_bf16(bf16* dst, const float* __
     }
 }
 
+// d_out tile in either storage type
+template <int HD>
+__device__ __forceinline__ void load_tile_do(bf16* dst, const float* src, size_t row_stride, int n_valid)
+{
+    load_tile_f32_as_bf16<HD>(dst, src, row_stride, n_valid);
+}
+template <int HD>
+__device__ __forceinline__ void load_tile_do(bf16* dst, const bf16* src, size_t row_stride, int n_valid)
+{
+    load_tile_bf16<HD>(dst, src, row_stride, n_valid);
+}
+__device__ __forceinline__ float do_as_float(float x) { return x; }
+__device__ __forceinline__ float do_as_float(bf16 x) { return __bfloat162float(x); }
+// two adjacent gradient elements, in either storage type
+template <bool ACCUM>
+__device__ __forceinline__ void store_grad2(float* p, float a, float b)
+{
+    float2 o = make_float2(a, b);
+    if (ACCUM) { const float2 old = *reinterpret_cast<float2*>(p); o.x += old.x; o.y += old.y; }
+    *reinterpret_cast<float2*>(p) = o;
+}
+template <bool ACCUM>
+__device__ __forceinline__ void store_grad2(bf16* p, float a, float b)
+{
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);   // packed gradients are never accumulated
+}
+
 // acc[nt][4] (16 x 64, fp32) = A(16 x HD, rows a_row0.. of As) * B^T, with B
 // stored [64 rows(n)][HD(k)] (row-major n x k): used for Q K^T, K Q^T, dO V^T, V dO^T.
 template <int HD>
@@ -164,7 +191,8 @@ __device__ __forceinline__ void c_to_a(unsigned (&pa)[4][4], const float (&c)[8]
 template <int HD>
 __global__ void __launch_bounds__(SWA_THREADS) swa_fwd_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v,
-    bf16* __restrict__ out, float* __restrict__ lse, int S, int H, int window, int n_p, float scale)
+    bf16* __restrict__ out, float* __restrict__ lse, int S, int H, int window, int n_p, float scale,
+    int rs_in, int rs_o)
 {
     constexpr int LD = HD + SWA_PAD;
     extern __shared__ __align__(16) unsigned char smraw[];
@@ -175,11 +203,11 @@ __global__ void __launch_bounds__(SWA_THREADS) swa_fwd_kernel(
     const int g = lane >> 2, t4 = lane & 3;
     const int qt = (gridDim.x - 1) - blockIdx.x;   // long tiles first
     const int bh = blockIdx.y, b = bh / H, h = bh - b * H;
-    const size_t rs = (size_t)H * HD;
+    const size_t rs = (size_t)rs_in;               // row stride of q, k, v (elements)
     const bf16* qb = q + (size_t)b * S * rs + (size_t)h * HD;
     const bf16* kb = k + (size_t)b * S * rs + (size_t)h * HD;
     const bf16* vb = v + (size_t)b * S * rs + (size_t)h * HD;
-    bf16* ob = out + (size_t)b * S * rs + (size_t)h * HD;
+    bf16* ob = out + (size_t)b * S * rs_o + (size_t)h * HD;
     const int q0 = qt * SWA_BM;
     const int q_hi = min(q0 + SWA_BM - 1, S - 1);
     const float sl2 = scale * 1.4426950408889634f;
@@ -278,7 +306,7 @@ __global__ void __launch_bounds__(SWA_THREADS) swa_fwd_kernel(
 #pragma unroll
             for (int i = 0; i < HD / 8; i++) {
                 __nv_bfloat162 w = __floats2bfloat162_rn(o[i][2 * r2] * inv, o[i][2 * r2 + 1] * inv);
-                *reinterpret_cast<__nv_bfloat162*>(ob + (size_t)qp * rs + i * 8 + 2 * t4) = w;
+                *reinterpret_cast<__nv_bfloat162*>(ob + (size_t)qp * rs_o + i * 8 + 2 * t4) = w;
             }
             if (t4 == 0 && lse != nullptr)
                 lse[((size_t)b * H + h) * S + qp] = m_run[r2] * scale + logf(l_run[r2]);
@@ -332,10 +360,10 @@ __global__ void __launch_bounds__(256) swa_weights_kernel(
 }
 
 // delta[b,h,q] = sum_d dO[q,d] * O[q,d]
-template <int HD>
-__global__ void __launch_bounds__(256) swa_delta_kernel(const float* __restrict__ d_out,
+template <int HD, typename TDO>
+__global__ void __launch_bounds__(256) swa_delta_kernel(const TDO* __restrict__ d_out,
                                                         const bf16* __restrict__ out,
-                                                        float* __restrict__ delta, int S, int H, int B)
+                                                        float* __restrict__ delta, int S, int H, int B, int rs_o)
 {
     const int lane = threadIdx.x & 31;
     const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -343,9 +371,9 @@ __global__ void __launch_bounds__(256) swa_delta_kernel(const float* __restrict_
     const int qp = (int)(row % S);
     const int h = (int)((row / S) % H);
     const int b = (int)(row / ((long long)S * H));
-    const size_t off = ((size_t)b * S + qp) * H * HD + (size_t)h * HD;
+    const size_t off = ((size_t)b * S + qp) * rs_o + (size_t)h * HD;
     float s = 0.f;
-    for (int i = lane; i < HD; i += 32) s += d_out[off + i] * __bfloat162float(out[off + i]);
+    for (int i = lane; i < HD; i += 32) s += do_as_float(d_out[off + i]) * __bfloat162float(out[off + i]);
     s = warp_sum(s);
     if (lane == 0) delta[row] = s;
 }
@@ -353,11 +381,12 @@ __global__ void __launch_bounds__(256) swa_delta_kernel(const float* __restrict_
 // ───────────────────────────── backward: dK, dV ───────────────────────────
 // CTA = one tile of 64 keys; warp = 16 keys (rows of S^T). Loops over the
 // query tiles that can see the key tile.
-template <int HD, bool ACCUM>
+template <int HD, bool ACCUM, typename TDO, typename TG>
 __global__ void __launch_bounds__(SWA_THREADS) swa_bwd_dkv_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v,
-    const float* __restrict__ d_out, const float* __restrict__ lse, const float* __restrict__ delta,
-    float* __restrict__ d_k, float* __restrict__ d_v, int S, int H, int window, int n_p, float scale)
+    const TDO* __restrict__ d_out, const float* __restrict__ lse, const float* __restrict__ delta,
+    TG* __restrict__ d_k, TG* __restrict__ d_v, int S, int H, int window, int n_p, float scale,
+    int rs_in, int rs_o)
 {
     constexpr int LD = HD + SWA_PAD;
     extern __shared__ __align__(16) unsigned char smraw[];
@@ -371,8 +400,9 @@ __global__ void __launch_bounds__(SWA_THREADS) swa_bwd_dkv_kernel(
     const int g = lane >> 2, t4 = lane & 3;
     const int kt = blockIdx.x;
     const int bh = blockIdx.y, b = bh / H, h = bh - b * H;
-    const size_t rs = (size_t)H * HD;
+    const size_t rs = (size_t)rs_in;                      // row stride of q, k, v and their gradients
     const size_t base = (size_t)b * S * rs + (size_t)h * HD;
+    const size_t base_o = (size_t)b * S * rs_o + (size_t)h * HD;   // d_out rows
     const int k0 = kt * SWA_BN;
     const int k_hi = min(k0 + SWA_BN - 1, S - 1);
     const float sl2 = scale * 1.4426950408889634f;
@@ -397,8 +427,8 @@ __global__ void __launch_bounds__(SWA_THREADS) swa_bwd_dkv_kernel(
         const int nq = min(SWA_BM, S - q0);
         __syncthreads();   // previous iteration's readers are done with Qs/dOs/lse_s
         load_tile_bf16<HD>(Qs, q + base + (size_t)q0 * rs, rs, nq);
+        load_tile_do<HD>(dOs, d_out + base_o + (size_t)q0 * rs_o, (size_t)rs_o, nq);
         cp_commit();
-        load_tile_f32_as_bf16<HD>(dOs, d_out + base + (size_t)q0 * rs, rs, nq);
         if (threadIdx.x < SWA_BM) {
             const int qp = q0 + threadIdx.x;
             lse_s[threadIdx.x] = (qp < S) ? lse[((size_t)b * H + h) * S + qp] : 0.f;
@@ -439,31 +469,24 @@ __global__ void __launch_bounds__(SWA_THREADS) swa_bwd_dkv_kernel(
     for (int r2 = 0; r2 < 2; r2++) {
         const int kp = krow0 + r2 * 8;
         if (kp < S) {
-            float* dkr = d_k + base + (size_t)kp * rs;
-            float* dvr = d_v + base + (size_t)kp * rs;
+            TG* dkr = d_k + base + (size_t)kp * rs;
+            TG* dvr = d_v + base + (size_t)kp * rs;
 #pragma unroll
             for (int i = 0; i < HD / 8; i++) {
                 const int c = i * 8 + 2 * t4;
-                float2 a = make_float2(dk[i][2 * r2], dk[i][2 * r2 + 1]);
-                float2 bb = make_float2(dv[i][2 * r2], dv[i][2 * r2 + 1]);
-                if (ACCUM) {
-                    const float2 oa = *reinterpret_cast<float2*>(dkr + c);
-                    const float2 ob = *reinterpret_cast<float2*>(dvr + c);
-                    a.x += oa.x; a.y += oa.y; bb.x += ob.x; bb.y += ob.y;
-                }
-                *reinterpret_cast<float2*>(dkr + c) = a;
-                *reinterpret_cast<float2*>(dvr + c) = bb;
+                store_grad2<ACCUM>(dkr + c, dk[i][2 * r2], dk[i][2 * r2 + 1]);
+                store_grad2<ACCUM>(dvr + c, dv[i][2 * r2], dv[i][2 * r2 + 1]);
             }
         }
     }
 }
 
 // ───────────────────────────── backward: dQ ───────────────────────────────
-template <int HD>
+template <int HD, typename TDO, typename TG>
 __global__ void __launch_bounds__(SWA_THREADS) swa_bwd_dq_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v,
-    const float* __restrict__ d_out, const float* __restrict__ lse, const float* __restrict__ delta,
-    float* __restrict__ d_q, int S, int H, int window, int n_p, float scale)
+    const TDO* __restrict__ d_out, const float* __restrict__ lse, const float* __restrict__ delta,
+    TG* __restrict__ d_q, int S, int H, int window, int n_p, float scale, int rs_in, int rs_o)
 {
     constexpr int LD = HD + SWA_PAD;
     extern __shared__ __align__(16) unsigned char smraw[];
@@ -475,15 +498,16 @@ __global__ void __launch_bounds__(SWA_THREADS) swa_bwd_dq_kernel(
     const int g = lane >> 2, t4 = lane & 3;
     const int qt = (gridDim.x - 1) - blockIdx.x;
     const int bh = blockIdx.y, b = bh / H, h = bh - b * H;
-    const size_t rs = (size_t)H * HD;
+    const size_t rs = (size_t)rs_in;
     const size_t base = (size_t)b * S * rs + (size_t)h * HD;
+    const size_t base_o = (size_t)b * S * rs_o + (size_t)h * HD;
     const int q0 = qt * SWA_BM;
     const int q_hi = min(q0 + SWA_BM - 1, S - 1);
     const float sl2 = scale * 1.4426950408889634f;
     const int nq = min(SWA_BM, S - q0);
 
     load_tile_bf16<HD>(Qs, q + base + (size_t)q0 * rs, rs, nq);
-    load_tile_f32_as_bf16<HD>(dOs, d_out + base + (size_t)q0 * rs, rs, nq);
+    load_tile_do<HD>(dOs, d_out + base_o + (size_t)q0 * rs_o, (size_t)rs_o, nq);
     const int kt_last = q_hi / SWA_BN;
     auto next_tile = [&](int cur) {
         for (int t = cur + 1; t <= kt_last; t++)
@@ -550,10 +574,10 @@ __global__ void __launch_bounds__(SWA_THREADS) swa_bwd_dq_kernel(
     for (int r2 = 0; r2 < 2; r2++) {
         const int qp = row0 + r2 * 8;
         if (qp < S) {
-            float* dqr = d_q + base + (size_t)qp * rs;
+            TG* dqr = d_q + base + (size_t)qp * rs;
 #pragma unroll
             for (int i = 0; i < HD / 8; i++)
-                *reinterpret_cast<float2*>(dqr + i * 8 + 2 * t4) = make_float2(dq[i][2 * r2], dq[i][2 * r2 + 1]);
+                store_grad2<false>(dqr + i * 8 + 2 * t4, dq[i][2 * r2], dq[i][2 * r2 + 1]);
         }
     }
 }
@@ -582,23 +606,25 @@ static int swa_check(const char* where, int S, int H, int hd, int W, int B, int 
 
 template <int HD>
 static int swa_forward_impl(const bf16* q, const bf16* k, const bf16* v, bf16* out, float* lse,
-                            bf16* aw, int S, int H, int W, int B, int n_p)
+                            bf16* aw, int S, int H, int W, int B, int n_p, int rs_in = 0, int rs_o = 0)
 {
     cudaStream_t st = current_stream();
     const float scale = 1.0f / sqrtf((float)HD);
+    if (rs_in == 0) rs_in = H * HD;     // dense [B, S, H*hd] rows unless the caller packs q|k|v
+    if (rs_o == 0) rs_o = H * HD;
     const bool aligned = ((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15) == 0);
     if (HD == 64 && g_swa_use_tcgen05 && aligned) {
         // tcgen05 / TMEM kernel: 128 query rows per CTA
         cudaFuncSetAttribute(tc::swa_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM_BYTES);
         dim3 grid((S + tc::BM - 1) / tc::BM, B * H);
-        tc::swa_fwd_tc_kernel<<<grid, tc::THREADS, tc::SMEM_BYTES, st>>>(q, k, v, out, lse, S, H, W, n_p, scale);
+        tc::swa_fwd_tc_kernel<<<grid, tc::THREADS, tc::SMEM_BYTES, st>>>(q, k, v, out, lse, S, H, W, n_p, scale, rs_in, rs_o);
         if (!check_launch("swa_fwd_tc_kernel")) return NLH_ERR_CUDA;
     } else {
         const size_t smem = swa_fwd_smem<HD>();
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(swa_fwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         dim3 grid((S + SWA_BM - 1) / SWA_BM, B * H);
-        swa_fwd_kernel<HD><<<grid, SWA_THREADS, smem, st>>>(q, k, v, out, lse, S, H, W, n_p, scale);
+        swa_fwd_kernel<HD><<<grid, SWA_THREADS, smem, st>>>(q, k, v, out, lse, S, H, W, n_p, scale, rs_in, rs_o);
         if (!check_launch("swa_fwd_kernel")) return NLH_ERR_CUDA;
     }
     if (aw != nullptr) {
@@ -609,44 +635,47 @@ static int swa_forward_impl(const bf16* q, const bf16* k, const bf16* v, bf16* o
     return NLH_OK;
 }
 
-template <int HD>
+template <int HD, typename TDO, typename TG>
 static int swa_backward_impl(const bf16* q, const bf16* k, const bf16* v, const bf16* out,
-                             const float* lse, const float* d_out, float* delta, float* d_q,
-                             float* d_k, float* d_v, int S, int H, int W, int B, int n_p, bool accum)
+                             const float* lse, const TDO* d_out, float* delta, TG* d_q,
+                             TG* d_k, TG* d_v, int S, int H, int W, int B, int n_p, bool accum,
+                             int rs_in = 0, int rs_o = 0)
 {
     cudaStream_t st = current_stream();
     const float scale = 1.0f / sqrtf((float)HD);
+    if (rs_in == 0) rs_in = H * HD;
+    if (rs_o == 0) rs_o = H * HD;
     const long long rows = (long long)B * H * S;
-    swa_delta_kernel<HD><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(d_out, out, delta, S, H, B);
+    swa_delta_kernel<HD, TDO><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(d_out, out, delta, S, H, B, rs_o);
     if (!check_launch("swa_delta_kernel")) return NLH_ERR_CUDA;
     {
         const size_t smem = swa_dkv_smem<HD>();
         dim3 grid((S + SWA_BN - 1) / SWA_BN, B * H);
         if (accum) {
-            if (smem > 48 * 1024) cudaFuncSetAttribute(swa_bwd_dkv_kernel<HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            swa_bwd_dkv_kernel<HD, true><<<grid, SWA_THREADS, smem, st>>>(q, k, v, d_out, lse, delta, d_k, d_v, S, H, W, n_p, scale);
+            if (smem > 48 * 1024) cudaFuncSetAttribute(swa_bwd_dkv_kernel<HD, true, TDO, TG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            swa_bwd_dkv_kernel<HD, true, TDO, TG><<<grid, SWA_THREADS, smem, st>>>(q, k, v, d_out, lse, delta, d_k, d_v, S, H, W, n_p, scale, rs_in, rs_o);
         } else {
-            if (smem > 48 * 1024) cudaFuncSetAttribute(swa_bwd_dkv_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            swa_bwd_dkv_kernel<HD, false><<<grid, SWA_THREADS, smem, st>>>(q, k, v, d_out, lse, delta, d_k, d_v, S, H, W, n_p, scale);
+            if (smem > 48 * 1024) cudaFuncSetAttribute(swa_bwd_dkv_kernel<HD, false, TDO, TG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            swa_bwd_dkv_kernel<HD, false, TDO, TG><<<grid, SWA_THREADS, smem, st>>>(q, k, v, d_out, lse, delta, d_k, d_v, S, H, W, n_p, scale, rs_in, rs_o);
         }
         if (!check_launch("swa_bwd_dkv_kernel")) return NLH_ERR_CUDA;
     }
     {
         const size_t smem = swa_dq_smem<HD>();
-        if (smem > 48 * 1024) cudaFuncSetAttribute(swa_bwd_dq_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (smem > 48 * 1024) cudaFuncSetAttribute(swa_bwd_dq_kernel<HD, TDO, TG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         dim3 grid((S + SWA_BM - 1) / SWA_BM, B * H);
-        swa_bwd_dq_kernel<HD><<<grid, SWA_THREADS, smem, st>>>(q, k, v, d_out, lse, delta, d_q, S, H, W, n_p, scale);
+        swa_bwd_dq_kernel<HD, TDO, TG><<<grid, SWA_THREADS, smem, st>>>(q, k, v, d_out, lse, delta, d_q, S, H, W, n_p, scale, rs_in, rs_o);
         if (!check_launch("swa_bwd_dq_kernel")) return NLH_ERR_CUDA;
     }
     return NLH_OK;
 }
 
-#define SWA_DISPATCH_HD(hd, CALL)                 \
-    switch (hd) {                                 \
-        case 16: { constexpr int HD_ = 16; CALL; } break;   \
-        case 32: { constexpr int HD_ = 32; CALL; } break;   \
-        case 64: { constexpr int HD_ = 64; CALL; } break;   \
-        default: { constexpr int HD_ = 128; CALL; } break;  \
+#define SWA_DISPATCH_HD(hd, ...)                         \
+    switch (hd) {                                        \
+        case 16: { constexpr int HD_ = 16; __VA_ARGS__; } break;   \
+        case 32: { constexpr int HD_ = 32; __VA_ARGS__; } break;   \
+        case 64: { constexpr int HD_ = 64; __VA_ARGS__; } break;   \
+        default: { constexpr int HD_ = 128; __VA_ARGS__; } break;  \
     }
 
 }  // namespace nlh
@@ -689,9 +718,39 @@ int32_t nlh_swa_backward(const uint16_t* q, const uint16_t* k, const uint16_t* v
     const size_t rows = (size_t)batch_size * num_heads * seq_len;
     float* delta = (float*)workspace(rows * sizeof(float));
     if (!delta) return NLH_ERR_WORKSPACE;
-    SWA_DISPATCH_HD(head_dim, rc = swa_backward_impl<HD_>((const bf16*)q, (const bf16*)k, (const bf16*)v,
+    SWA_DISPATCH_HD(head_dim, rc = swa_backward_impl<HD_, float, float>((const bf16*)q, (const bf16*)k, (const bf16*)v,
         (const bf16*)out, lse, d_attn_out, delta, d_q, d_k, d_v, seq_len, num_heads, window_size,
         batch_size, n_persistent, false));
+    return rc;
+}
+
+int32_t nlh_swa_forward_packed(const uint16_t* qkv, uint16_t* out, float* lse, int32_t seq_len,
+    int32_t num_heads, int32_t head_dim, int32_t window_size, int32_t batch_size, int32_t n_persistent)
+{
+    int rc = swa_check("nlh_swa_forward_packed", seq_len, num_heads, head_dim, window_size, batch_size, n_persistent);
+    if (rc != NLH_OK || batch_size == 0) return rc;
+    const int dm = num_heads * head_dim;
+    const bf16* p = (const bf16*)qkv;
+    SWA_DISPATCH_HD(head_dim, rc = swa_forward_impl<HD_>(p, p + dm, p + 2 * dm, (bf16*)out, lse, nullptr,
+        seq_len, num_heads, window_size, batch_size, n_persistent, 3 * dm, dm));
+    return rc;
+}
+
+int32_t nlh_swa_backward_packed(const uint16_t* qkv, const uint16_t* out, const float* lse,
+    const uint16_t* d_attn_out, uint16_t* d_qkv, int32_t seq_len, int32_t num_heads, int32_t head_dim,
+    int32_t window_size, int32_t batch_size, int32_t n_persistent)
+{
+    int rc = swa_check("nlh_swa_backward_packed", seq_len, num_heads, head_dim, window_size, batch_size, n_persistent);
+    if (rc != NLH_OK || batch_size == 0) return rc;
+    const size_t rows = (size_t)batch_size * num_heads * seq_len;
+    float* delta = (float*)workspace(rows * sizeof(float));
+    if (!delta) return NLH_ERR_WORKSPACE;
+    const int dm = num_heads * head_dim;
+    const bf16* p = (const bf16*)qkv;
+    bf16* g = (bf16*)d_qkv;
+    SWA_DISPATCH_HD(head_dim, rc = (swa_backward_impl<HD_, bf16, bf16>(p, p + dm, p + 2 * dm,
+        (const bf16*)out, lse, (const bf16*)d_attn_out, delta, g, g + dm, g + 2 * dm, seq_len, num_heads,
+        window_size, batch_size, n_persistent, false, 3 * dm, dm)));
     return rc;
 }
 
@@ -730,7 +789,7 @@ void swa_backward_f32_cuda(const uint16_t* q, const uint16_t* k, const uint16_t*
     SWA_DISPATCH_HD(head_dim, rc = swa_forward_impl<HD_>((const bf16*)q, (const bf16*)k, (const bf16*)v,
         out, lse, nullptr, seq_len, num_heads, window_size, batch_size, n_persistent));
     if (rc != NLH_OK) return;
-    SWA_DISPATCH_HD(head_dim, rc = swa_backward_impl<HD_>((const bf16*)q, (const bf16*)k, (const bf16*)v,
+    SWA_DISPATCH_HD(head_dim, rc = swa_backward_impl<HD_, float, float>((const bf16*)q, (const bf16*)k, (const bf16*)v,
         out, lse, d_attn_out, delta, d_q, d_k, d_v, seq_len, num_heads, window_size, batch_size,
         n_persistent, true));
 }

@@ -178,14 +178,15 @@ __device__ int g_swa_tc_timeout = 0;   // set when a bounded mbarrier wait ran o
 __global__ void __launch_bounds__(THREADS) swa_fwd_tc_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
     const __nv_bfloat16* __restrict__ v, __nv_bfloat16* __restrict__ out, float* __restrict__ lse,
-    int S, int H, int window, int n_p, float scale)
+    int S, int H, int window, int n_p, float scale, int rs_in, int rs_o)
 {
     extern __shared__ __align__(128) unsigned char smem[];
     const int tid = threadIdx.x, warp = tid >> 5;
     const int qt = (gridDim.x - 1) - blockIdx.x;
     const int bh = blockIdx.y, b = bh / H, h = bh - b * H;
-    const size_t rs = (size_t)H * HD;
+    const size_t rs = (size_t)rs_in;                       // row stride of q, k, v (elements)
     const size_t base = (size_t)b * S * rs + (size_t)h * HD;
+    const size_t base_o = (size_t)b * S * rs_o + (size_t)h * HD;   // output rows
     const int q0 = qt * BM;
     const int q_hi = min(q0 + BM - 1, S - 1);
     const float sl2 = scale * 1.4426950408889634f;
@@ -355,7 +356,7 @@ __global__ void __launch_bounds__(THREADS) swa_fwd_tc_kernel(
         tmem_wait_ld();
         if (qp < S) {
             const float inv = (l_run > 0.f) ? 1.0f / l_run : 0.f;
-            __nv_bfloat16* orow = out + base + (size_t)qp * rs;
+            __nv_bfloat16* orow = out + base_o + (size_t)qp * rs_o;
 #pragma unroll
             for (int c = 0; c < HD / 8; c++) {
                 uint4 w;

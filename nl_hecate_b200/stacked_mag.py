@@ -3,10 +3,11 @@
 Host-side harness standing in for the reference's GPU-resident driver
 (core/src/gpu_stacked_forward.rs:1263-2038 forward_sequence, gpu_forward.rs:1197-1540
 gpu_memory_forward, gpu_stacked_backward.rs, gpu_stacked_optimizer.rs:522-700). The hot-path
-operators — memory-rule kernel pairs, SWA forward/backward, the AdamW step — are this
-library's CUDA kernels behind the C ABI; the glue around them (embedding, LayerNorm, the
-dense projections, pooling, gating, cross-entropy) is plain PyTorch/cuBLAS and autograd, which
-is what the reference does with cuBLAS and its small element-wise kernels.
+operators — memory-rule kernel pairs, SWA forward/backward, the AdamW step — and the glue
+around them (rule wrapper, level pooling, MAG gating, LayerNorm, cross-entropy) are this
+library's CUDA kernels behind the C ABI, registered as opaque blocks of PyTorch's tape; the
+dense projections and the embedding stay cuBLAS / PyTorch. With fused_glue = False (and on
+CPU) the glue runs as plain PyTorch operators, which the tests use as the second statement.
 
 Block (MAG composition), per core/src/gpu_stacked_forward.rs:1656-1960:
     h        = LN_attn(x)
@@ -114,6 +115,35 @@ class _SWA(torch.autograd.Function):
         nh, hd, w = ctx.cfg
         dq, dk, dv = D.swa_backward_lse(q, k, v, out, lse, d_out.float().contiguous(), nh, hd, w)
         return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), None, None, None
+
+
+class _SWAPacked(torch.autograd.Function):
+    """Sliding-window attention straight on the projection output qkv [B, S, 3*H*hd] bf16
+    (nlh_swa_forward_packed / nlh_swa_backward_packed): no q/k/v split copies, bf16 gradient in,
+    packed bf16 gradient out."""
+
+    @staticmethod
+    def forward(ctx, qkv, num_heads, head_dim, window):
+        qkv = qkv.contiguous()
+        B, S, _ = qkv.shape
+        out = torch.empty(B, S, num_heads * head_dim, dtype=torch.bfloat16, device=qkv.device)
+        lse = torch.empty(B, num_heads, S, dtype=torch.float32, device=qkv.device)
+        D.call("nlh_swa_forward_packed", qkv=qkv, out=out, lse=lse, seq_len=S, num_heads=num_heads,
+               head_dim=head_dim, window_size=window, batch_size=B, n_persistent=0)
+        ctx.save_for_backward(qkv, out, lse)
+        ctx.cfg = (num_heads, head_dim, window)
+        return out
+
+    @staticmethod
+    def backward(ctx, d_out):
+        qkv, out, lse = ctx.saved_tensors
+        nh, hd, w = ctx.cfg
+        B, S, _ = qkv.shape
+        d_qkv = torch.empty_like(qkv)
+        D.call("nlh_swa_backward_packed", qkv=qkv, out=out, lse=lse,
+               d_attn_out=d_out.to(torch.bfloat16).contiguous(), d_qkv=d_qkv, seq_len=S, num_heads=nh,
+               head_dim=hd, window_size=w, batch_size=B, n_persistent=0)
+        return d_qkv, None, None, None
 
 
 class _LevelPrep(torch.autograd.Function):
@@ -491,8 +521,11 @@ class StackedMAG:
             pre = f"b{b}."
             h = self._ln(x, pre + "ln_attn_", lp, fused)
             qkv = self._mm(h, p[pre + "w_qkv"]).to(torch.bfloat16)
-            q, k, v = (t.contiguous() for t in qkv.split(d, dim=-1))
-            attn = self.swa_fn(q, k, v, nh, hd, cfg.window)
+            if fused and self.swa_fn is swa:
+                attn = _SWAPacked.apply(qkv, nh, hd, cfg.window)
+            else:
+                q, k, v = (t.contiguous() for t in qkv.split(d, dim=-1))
+                attn = self.swa_fn(q, k, v, nh, hd, cfg.window)
             attn_raw = self._mm(attn, p[pre + "w_o"])
             res1 = x + attn_raw
             wts = torch.softmax(p[pre + "alpha_mem"], dim=0)

@@ -8,7 +8,8 @@ pytestmark = pytest.mark.gpu
 
 
 def _rel(a, b):
-    return float((a.float() - b.float()).abs().max() / b.float().abs().max().clamp_min(1e-12))
+    a, b = a.detach().float(), b.detach().float()
+    return float((a - b).abs().max() / b.abs().max().clamp_min(1e-12))
 
 
 def _torch_level_prep(kvq, w_gates, b_a, b_t, b_e, H):
