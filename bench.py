@@ -454,7 +454,7 @@ class StackedModelStep:
         self._dom = (k, v, q, al, th, et, ms, dy)
         # DRAM bytes of one launch from the profiler capture of this kernel on a smaller case
         # (296 problems x 128 tokens: 664.94 MB read + 28.05 MB written), scaled by problem-tokens
-        # (traffic is proportional to them); see profiles/titans_exact_level0_kernels.md
+        # (the kernel reads each stored state once and streams the rest: traffic is proportional to them)
         self.dominant_traffic = (664_938_496 + 28_052_224) / (296 * 128) * n * s
         return ("titans_exact_bwd_kernel<64> (exact Titans backward, M-only trajectory) at level-0 shapes",
                 lambda: self.dd.titans_backward_dd(k, v, q, al, th, et, ms, None, dy), bytes_, "hbm")

@@ -395,6 +395,28 @@ int32_t nlh_cross_entropy_forward(const void* logits, int32_t logits_is_bf16, co
 int32_t nlh_cross_entropy_backward(const void* logits, int32_t logits_is_bf16, const int32_t* target_ids,
     const float* lse, const float* grad_scale, void* d_logits, int32_t n, int32_t vocab, float inv_count);
 
+/* ── Opaque-VJP registry over the C ABI (boundary of core/src/tape.rs:98-182) ────────────────
+ * Keys number the variants of the reference's OpaqueKey enum in declaration order
+ * (core/src/tape.rs:100-134). nlh_opaque_backward is the C form of OpaqueBackwardFn
+ * (tape.rs:141-145): HOST pointers, d_outputs[i] of out_len[i] floats, saved[i] of saved_len[i]
+ * floats (saved[0] is the float-encoded meta buffer), d_inputs[i] of in_len[i] floats
+ * caller-allocated and overwritten. GPU adapters exist for NLH_KEY_DGD
+ * (opaque_adapters.rs:1680-1725), NLH_KEY_SWA (:952-997; q,k,v are rounded to bf16 on the device,
+ * attn_weights is not read) and the frozen reads NLH_KEY_FROZEN_{DELTA_RULE,TITANS_LMM,
+ * HEBBIAN_RULE} with the identity feature map (:999-1069); every other key returns
+ * NLH_ERR_UNSUPPORTED. The call synchronises its stream before returning. */
+#define NLH_KEY_DELTA_RULE 0
+#define NLH_KEY_TITANS_LMM 1
+#define NLH_KEY_HEBBIAN_RULE 2
+#define NLH_KEY_DGD 9
+#define NLH_KEY_SWA 10
+#define NLH_KEY_FROZEN_DELTA_RULE 11
+#define NLH_KEY_FROZEN_TITANS_LMM 12
+#define NLH_KEY_FROZEN_HEBBIAN_RULE 13
+int32_t nlh_opaque_backward(int32_t key, int32_t n_out, const float* const* d_outputs,
+    const int64_t* out_len, int32_t n_saved, const float* const* saved, const int64_t* saved_len,
+    int32_t n_in, float* const* d_inputs, const int64_t* in_len);
+
 /* No counterpart in the reference. Titans LMM backward (same arguments, layout and
  * batch-summed d_m_initial/d_s_initial as titans_backward_f32_cuda) for callers that must
  * not allocate device memory: its scratch is a fixed 2 MiB array inside the library image,

@@ -348,3 +348,31 @@ def titans_forward_dispatch(k, v, q, alpha, theta, eta, m0, s0, error_clip=0.0, 
                                   _dev(theta)[None], _dev(eta)[None], _dev(m0)[None],
                                   _dev(s0)[None], error_clip, m_norm_max)
     return ms[0].cpu().numpy(), ss[0].cpu().numpy(), y[0].cpu().numpy()
+
+
+# ── opaque-VJP registry over the C ABI (host slices, as on the reference's tape) ──
+OPAQUE_KEYS = {"DeltaRule": 0, "TitansLMM": 1, "HebbianRule": 2, "DGD": 9, "SWA": 10,
+               "FrozenDeltaRule": 11, "FrozenTitansLMM": 12, "FrozenHebbianRule": 13}
+
+
+def opaque_backward(key, d_outputs, saved, in_lens):
+    """Counterpart of an ``OpaqueBackwardFn`` (core/src/tape.rs:141-145): host float32 arrays in,
+    list of host float32 input gradients out (lengths ``in_lens``). ``key`` is an OpaqueKey name
+    or number; keys without a GPU adapter raise."""
+    if isinstance(key, str):
+        key = OPAQUE_KEYS[key]
+    d_outputs = [np.ascontiguousarray(a, dtype=np.float32).ravel() for a in d_outputs]
+    saved = [np.ascontiguousarray(a, dtype=np.float32).ravel() for a in saved]
+    d_inputs = [np.zeros(int(n), dtype=np.float32) for n in in_lens]
+
+    def pack(arrs):
+        ptrs = (C.c_void_p * len(arrs))(*[a.ctypes.data for a in arrs])
+        lens = (C.c_int64 * len(arrs))(*[a.size for a in arrs])
+        return ptrs, lens
+
+    po, lo = pack(d_outputs)
+    ps, ls = pack(saved)
+    pi, li = pack(d_inputs)
+    call("nlh_opaque_backward", key=key, n_out=len(d_outputs), d_outputs=po, out_len=lo,
+         n_saved=len(saved), saved=ps, saved_len=ls, n_in=len(d_inputs), d_inputs=pi, in_len=li)
+    return d_inputs
