@@ -286,10 +286,9 @@ __global__ void __launch_bounds__(WR_THREADS) level_prep_bwd_kernel(
 }
 
 
-// Warp-per-token backward (same conditions as level_prep_fwd_warp_kernel). A CTA covers
-// tok_per_cta consecutive tokens, warp w takes every LPW_WARPS-th of them; gate-weight gradients
-// accumulate in registers per lane and are combined over the CTA's warps through shared memory
-// into ONE partial row per CTA.
+// Warp-per-token backward (same conditions as level_prep_fwd_warp_kernel): writes d_kvq and the
+// gate pre-activation gradients dpre [tokens, 3] (alpha, theta, eta); the gate-weight gradient,
+// a reduction over tokens, is left to gate_wgrad_kernel so that this kernel stays light.
 __device__ __forceinline__ void st8_as(float* p, const float (&x)[8]) { st8(p, x, 1.0f); }
 __device__ __forceinline__ void st8_as(__nv_bfloat16* p, const float (&x)[8])
 {
@@ -308,113 +307,135 @@ __global__ void __launch_bounds__(LPW_WARPS * 32) level_prep_bwd_warp_kernel(
     const float* __restrict__ k_norm, const float* __restrict__ q_norm,
     const float* __restrict__ dk_ph, const float* __restrict__ dv_ph, const float* __restrict__ dq_ph,
     const float* __restrict__ dalpha_ph, const float* __restrict__ dtheta_ph, const float* __restrict__ deta_ph,
-    const float* __restrict__ w_gates, TIN* __restrict__ d_kvq, float* __restrict__ dw_partial,
-    float* __restrict__ db_partial, int n_tok, int sf, int d, int H, int tok_per_cta)
+    const float* __restrict__ w_gates, TIN* __restrict__ d_kvq, float* __restrict__ dpre_out,
+    int n_tok, int sf, int d, int H)
 {
-    __shared__ float sdw[6 * 1024];
-    __shared__ float sdb[3];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int tok = blockIdx.x * LPW_WARPS + (threadIdx.x >> 5);
+    if (tok >= n_tok) return;
     const int hd = d / H, nc = d >> 3;
-    float dwk[3][NC][8], dwv[3][NC][8], db[3] = {0.f, 0.f, 0.f};
+    const int b = tok / sf, t = tok - b * sf;
+    const size_t g0 = ((size_t)b * H) * sf + t;       // head 0 gate slot; heads are sf apart
+    const float al = alpha_ph[g0], th = theta_ph[g0], et = eta_ph[g0];
+    const float kn = k_norm[tok], qn = q_norm[tok];
+    float s0 = 0.f, s1 = 0.f, s2 = 0.f;
+    if (lane < H) {
+        const size_t gi = g0 + (size_t)lane * sf;
+        s0 = dalpha_ph[gi]; s1 = dtheta_ph[gi]; s2 = deta_ph[gi];
+    }
+    float kh[NC][8], qh[NC][8], gk[NC][8], gq[NC][8], gv[NC][8];
 #pragma unroll
-    for (int g = 0; g < 3; g++)
+    for (int i = 0; i < NC; i++) {
+        const int c = lane + 32 * i;
+        if (c < nc) {
+            const int j = 8 * c, h = j / hd, w = j - h * hd;
+            const size_t src = (((size_t)b * H + h) * sf + t) * hd + w;
+            ld8(k_ph + src, kh[i]); ld8(q_ph + src, qh[i]);
+            ld8(dk_ph + src, gk[i]); ld8(dv_ph + src, gv[i]); ld8(dq_ph + src, gq[i]);
+        }
+    }
+    s0 = warp_sum(s0); s1 = warp_sum(s1); s2 = warp_sum(s2);
+    const float dpre[3] = {s0 * al * (1.0f - al), s1 * (1.0f - expf(-th)), s2 * et * (1.0f - et)};
+    if (lane < 3) dpre_out[(size_t)tok * 3 + lane] = lane == 0 ? dpre[0] : lane == 1 ? dpre[1] : dpre[2];
+    float dot_k = 0.f, dot_q = 0.f;
+    TIN* orow = d_kvq + (size_t)tok * 3 * d;
 #pragma unroll
-        for (int i = 0; i < NC; i++)
+    for (int i = 0; i < NC; i++) {
+        const int c = lane + 32 * i;
+        if (c < nc) {
+            const int j = 8 * c;
 #pragma unroll
-            for (int e = 0; e < 8; e++) { dwk[g][i][e] = 0.f; dwv[g][i][e] = 0.f; }
+            for (int g = 0; g < 3; g++) {
+                float wk[8], wv[8];
+                ld8(w_gates + (size_t)g * 2 * d + j, wk);
+                ld8(w_gates + (size_t)g * 2 * d + d + j, wv);
+#pragma unroll
+                for (int e = 0; e < 8; e++) { gk[i][e] += dpre[g] * wk[e]; gv[i][e] += dpre[g] * wv[e]; }
+            }
+#pragma unroll
+            for (int e = 0; e < 8; e++) { dot_k += gk[i][e] * kh[i][e]; dot_q += gq[i][e] * qh[i][e]; }
+            st8_as(orow + d + j, gv[i]);
+        }
+    }
+    dot_k = warp_sum(dot_k);
+    dot_q = warp_sum(dot_q);
+    const float kinv = (kn >= 1e-8f) ? 1.0f / kn : 1e8f, qinv = (qn >= 1e-8f) ? 1.0f / qn : 1e8f;
+    const float kd = (kn >= 1e-8f) ? dot_k : 0.f, qd = (qn >= 1e-8f) ? dot_q : 0.f;
+#pragma unroll
+    for (int i = 0; i < NC; i++) {
+        const int c = lane + 32 * i;
+        if (c < nc) {
+            // sphere Jacobian of x/||x|| (core/src/tensor.rs:320-351)
+            float ok[8], oq[8];
+#pragma unroll
+            for (int e = 0; e < 8; e++) {
+                ok[e] = (gk[i][e] - kh[i][e] * kd) * kinv;
+                oq[e] = (gq[i][e] - qh[i][e] * qd) * qinv;
+            }
+            st8_as(orow + 8 * c, ok);
+            st8_as(orow + 2 * d + 8 * c, oq);
+        }
+    }
+}
+
+// Gate-weight and gate-bias gradients: dw[g, :] = sum_tok dpre[tok, g] * [k_hat(tok) | v(tok)],
+// db[g] = sum_tok dpre[tok, g]. One CTA per tok_per_cta consecutive tokens writes one partial
+// row [3, 2d] (+ [3]); the caller sums the rows. Thread owns 4 consecutive columns of k and of v
+// per pass (d <= 4 * blockDim.x * WG_PASSES).
+constexpr int WG_THREADS = 128;
+constexpr int WG_PASSES = 2;      // d_model <= 1024
+__global__ void __launch_bounds__(WG_THREADS) gate_wgrad_kernel(
+    const float* __restrict__ dpre, const float* __restrict__ k_ph, const float* __restrict__ v_ph,
+    float* __restrict__ dw_partial, float* __restrict__ db_partial, int n_tok, int sf, int d, int H,
+    int tok_per_cta)
+{
+    const int hd = d / H;
     const int tok0 = blockIdx.x * tok_per_cta;
     const int tok1 = min(tok0 + tok_per_cta, n_tok);
-    for (int tok = tok0 + warp; tok < tok1; tok += LPW_WARPS) {
+    float4 ak[WG_PASSES][3], av[WG_PASSES][3];
+#pragma unroll
+    for (int p = 0; p < WG_PASSES; p++)
+#pragma unroll
+        for (int g = 0; g < 3; g++) { ak[p][g] = make_float4(0.f, 0.f, 0.f, 0.f); av[p][g] = make_float4(0.f, 0.f, 0.f, 0.f); }
+    float db[3] = {0.f, 0.f, 0.f};
+    for (int tok = tok0; tok < tok1; tok++) {
         const int b = tok / sf, t = tok - b * sf;
-        const size_t g0 = ((size_t)b * H) * sf + t;       // head 0 gate slot; heads are sf apart
-        const float al = alpha_ph[g0], th = theta_ph[g0], et = eta_ph[g0];
-        float s0 = 0.f, s1 = 0.f, s2 = 0.f;
-        if (lane < H) {
-            const size_t gi = g0 + (size_t)lane * sf;
-            s0 = dalpha_ph[gi]; s1 = dtheta_ph[gi]; s2 = deta_ph[gi];
-        }
-        s0 = warp_sum(s0); s1 = warp_sum(s1); s2 = warp_sum(s2);
-        const float dpre[3] = {s0 * al * (1.0f - al), s1 * (1.0f - expf(-th)), s2 * et * (1.0f - et)};
-        float kh[NC][8], qh[NC][8], gk[NC][8], gq[NC][8];
-        float dot_k = 0.f, dot_q = 0.f;
-        TIN* orow = d_kvq + (size_t)tok * 3 * d;
+        const float p0 = dpre[(size_t)tok * 3], p1 = dpre[(size_t)tok * 3 + 1], p2 = dpre[(size_t)tok * 3 + 2];
+        db[0] += p0; db[1] += p1; db[2] += p2;
 #pragma unroll
-        for (int i = 0; i < NC; i++) {
-            const int c = lane + 32 * i;
-            if (c < nc) {
-                const int j = 8 * c, h = j / hd, w = j - h * hd;
+        for (int p = 0; p < WG_PASSES; p++) {
+            const int j = 4 * (threadIdx.x + p * WG_THREADS);
+            if (j < d) {
+                const int h = j / hd, w = j - h * hd;
                 const size_t src = (((size_t)b * H + h) * sf + t) * hd + w;
-                float vv[8], gv[8];
-                ld8(k_ph + src, kh[i]); ld8(v_ph + src, vv); ld8(q_ph + src, qh[i]);
-                ld8(dk_ph + src, gk[i]); ld8(dv_ph + src, gv); ld8(dq_ph + src, gq[i]);
-#pragma unroll
-                for (int g = 0; g < 3; g++) {
-                    float wk[8], wv[8];
-                    ld8(w_gates + (size_t)g * 2 * d + j, wk);
-                    ld8(w_gates + (size_t)g * 2 * d + d + j, wv);
-#pragma unroll
-                    for (int e = 0; e < 8; e++) {
-                        gk[i][e] += dpre[g] * wk[e];
-                        gv[e] += dpre[g] * wv[e];
-                        dwk[g][i][e] += dpre[g] * kh[i][e];
-                        dwv[g][i][e] += dpre[g] * vv[e];
-                    }
-                }
-#pragma unroll
-                for (int e = 0; e < 8; e++) { dot_k += gk[i][e] * kh[i][e]; dot_q += gq[i][e] * qh[i][e]; }
-                st8_as(orow + d + j, gv);
+                const float4 kv = *reinterpret_cast<const float4*>(k_ph + src);
+                const float4 vv = *reinterpret_cast<const float4*>(v_ph + src);
+                ak[p][0].x += p0 * kv.x; ak[p][0].y += p0 * kv.y; ak[p][0].z += p0 * kv.z; ak[p][0].w += p0 * kv.w;
+                ak[p][1].x += p1 * kv.x; ak[p][1].y += p1 * kv.y; ak[p][1].z += p1 * kv.z; ak[p][1].w += p1 * kv.w;
+                ak[p][2].x += p2 * kv.x; ak[p][2].y += p2 * kv.y; ak[p][2].z += p2 * kv.z; ak[p][2].w += p2 * kv.w;
+                av[p][0].x += p0 * vv.x; av[p][0].y += p0 * vv.y; av[p][0].z += p0 * vv.z; av[p][0].w += p0 * vv.w;
+                av[p][1].x += p1 * vv.x; av[p][1].y += p1 * vv.y; av[p][1].z += p1 * vv.z; av[p][1].w += p1 * vv.w;
+                av[p][2].x += p2 * vv.x; av[p][2].y += p2 * vv.y; av[p][2].z += p2 * vv.z; av[p][2].w += p2 * vv.w;
             }
         }
-        dot_k = warp_sum(dot_k);
-        dot_q = warp_sum(dot_q);
-        if (lane == 0) { db[0] += dpre[0]; db[1] += dpre[1]; db[2] += dpre[2]; }
-        const float kn = k_norm[tok], qn = q_norm[tok];
-        const float kinv = (kn >= 1e-8f) ? 1.0f / kn : 1e8f, qinv = (qn >= 1e-8f) ? 1.0f / qn : 1e8f;
-        const float kd = (kn >= 1e-8f) ? dot_k : 0.f, qd = (qn >= 1e-8f) ? dot_q : 0.f;
-#pragma unroll
-        for (int i = 0; i < NC; i++) {
-            const int c = lane + 32 * i;
-            if (c < nc) {
-                // sphere Jacobian of x/||x|| (core/src/tensor.rs:320-351)
-                float ok[8], oq[8];
-#pragma unroll
-                for (int e = 0; e < 8; e++) {
-                    ok[e] = (gk[i][e] - kh[i][e] * kd) * kinv;
-                    oq[e] = (gq[i][e] - qh[i][e] * qd) * qinv;
-                }
-                st8_as(orow + 8 * c, ok);
-                st8_as(orow + 2 * d + 8 * c, oq);
-            }
-        }
-    }
-    // combine the warps' gate-weight gradients: warp after warp into shared memory
-    for (int w = 0; w < LPW_WARPS; w++) {
-        if (warp == w) {
-#pragma unroll
-            for (int g = 0; g < 3; g++)
-#pragma unroll
-                for (int i = 0; i < NC; i++) {
-                    const int c = lane + 32 * i;
-                    if (c < nc) {
-#pragma unroll
-                        for (int e = 0; e < 8; e++) {
-                            float* pk = sdw + g * 2 * d + 8 * c + e;
-                            float* pv = pk + d;
-                            if (w == 0) { *pk = dwk[g][i][e]; *pv = dwv[g][i][e]; }
-                            else { *pk += dwk[g][i][e]; *pv += dwv[g][i][e]; }
-                        }
-                    }
-                }
-            if (lane == 0) {
-#pragma unroll
-                for (int g = 0; g < 3; g++) { if (w == 0) sdb[g] = db[g]; else sdb[g] += db[g]; }
-            }
-        }
-        __syncthreads();
     }
     float* dwp = dw_partial + (size_t)blockIdx.x * 3 * 2 * d;
-    for (int i = threadIdx.x; i < 6 * d; i += blockDim.x) dwp[i] = sdw[i];
-    if (threadIdx.x < 3) db_partial[blockIdx.x * 3 + threadIdx.x] = sdb[threadIdx.x];
+#pragma unroll
+    for (int p = 0; p < WG_PASSES; p++) {
+        const int j = 4 * (threadIdx.x + p * WG_THREADS);
+        if (j < d) {
+#pragma unroll
+            for (int g = 0; g < 3; g++) {
+                *reinterpret_cast<float4*>(dwp + (size_t)g * 2 * d + j) = ak[p][g];
+                *reinterpret_cast<float4*>(dwp + (size_t)g * 2 * d + d + j) = av[p][g];
+            }
+        }
+    }
+    if (threadIdx.x == 0) {
+        db_partial[blockIdx.x * 3 + 0] = db[0];
+        db_partial[blockIdx.x * 3 + 1] = db[1];
+        db_partial[blockIdx.x * 3 + 2] = db[2];
+    }
 }
 
 // ───────────────────────── MAG combine ────────────────────────────────────
@@ -741,20 +762,25 @@ int32_t nlh_level_prep_backward(const float* k_ph, const float* v_ph, const floa
     cudaStream_t st = current_stream();
     const bool al16 = ((((uintptr_t)k_ph | (uintptr_t)v_ph | (uintptr_t)q_ph | (uintptr_t)dk_ph | (uintptr_t)dv_ph |
                          (uintptr_t)dq_ph | (uintptr_t)w_gates | (uintptr_t)d_kvq) & 15) == 0);
-    // the register-resident gate-weight gradients fit for up to 2 chunks per lane (d_model <= 512)
-    if (d_model % 8 == 0 && d_model <= 512 && (d_model / num_heads) % 8 == 0 && num_heads <= 32 && al16) {
-        const int ncl = (d_model / 8 + 31) / 32;
+    if (d_model % 8 == 0 && (d_model / num_heads) % 8 == 0 && num_heads <= 32 && al16 &&
+        ((uintptr_t)dw_partial & 15) == 0) {
+        float* dpre = (float*)workspace((size_t)n_tok * 3 * sizeof(float));
+        if (!dpre) return NLH_ERR_WORKSPACE;
+        const int wgrid = (n_tok + LPW_WARPS - 1) / LPW_WARPS;
+        const int ncl = (d_model / 8 + 31) / 32;     // chunks per lane, <= 4 because d_model <= 1024
 #define NLH_LP_BWDW(T, NC)                                                                       \
-    level_prep_bwd_warp_kernel<T, NC><<<grid, LPW_WARPS * 32, 0, st>>>(                             \
+    level_prep_bwd_warp_kernel<T, NC><<<wgrid, LPW_WARPS * 32, 0, st>>>(                            \
         k_ph, v_ph, q_ph, alpha_ph, theta_ph, eta_ph, k_norm, q_norm, dk_ph, dv_ph, dq_ph,       \
-        dalpha_ph, dtheta_ph, deta_ph, w_gates, (T*)d_kvq, dw_partial, db_partial, n_tok, seq,   \
-        d_model, num_heads, lp_tok_per_cta(n_tok))
+        dalpha_ph, dtheta_ph, deta_ph, w_gates, (T*)d_kvq, dpre, n_tok, seq, d_model, num_heads)
         if (kvq_is_bf16) {
-            if (ncl <= 1) NLH_LP_BWDW(__nv_bfloat16, 1); else NLH_LP_BWDW(__nv_bfloat16, 2);
+            if (ncl <= 1) NLH_LP_BWDW(__nv_bfloat16, 1); else if (ncl <= 2) NLH_LP_BWDW(__nv_bfloat16, 2); else NLH_LP_BWDW(__nv_bfloat16, 4);
         } else {
-            if (ncl <= 1) NLH_LP_BWDW(float, 1); else NLH_LP_BWDW(float, 2);
+            if (ncl <= 1) NLH_LP_BWDW(float, 1); else if (ncl <= 2) NLH_LP_BWDW(float, 2); else NLH_LP_BWDW(float, 4);
         }
 #undef NLH_LP_BWDW
+        if (!check_launch("nlh_level_prep_backward")) return NLH_ERR_CUDA;
+        gate_wgrad_kernel<<<grid, WG_THREADS, 0, st>>>(dpre, k_ph, v_ph, dw_partial, db_partial, n_tok, seq,
+                                                       d_model, num_heads, lp_tok_per_cta(n_tok));
         return check_launch("nlh_level_prep_backward") ? NLH_OK : NLH_ERR_CUDA;
     }
 #define NLH_LP_BWD(T, NE)                                                                        \
