@@ -444,7 +444,7 @@ static int ln_backward(const char* where, const float* d_out, const __nv_bfloat1
         const int nv = (d / 4 + 31) / 32;
         // persistent: a few CTAs per SM, each warp walks rows so that the parameter gradients
         // are reduced once per CTA
-        const int grid = need < 148 * 4 ? need : 148 * 4;
+        const int grid = need < 148 * 2 ? need : 148 * 2;
 #define NLH_LN_BWD(NV) ln_bwd_kernel<NV><<<grid, LN_WARPS * 32, 0, st>>>(d_out, d_out_bf16, x, gamma, mean_cache, rstd_cache, d_x, d_gamma, d_beta, n, d)
         if (nv <= 1) NLH_LN_BWD(1); else if (nv <= 2) NLH_LN_BWD(2); else if (nv <= 4) NLH_LN_BWD(4); else NLH_LN_BWD(8);
 #undef NLH_LN_BWD

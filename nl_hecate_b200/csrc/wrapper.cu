@@ -482,6 +482,25 @@ __device__ __forceinline__ void st4(__nv_bfloat16* p, float4 v)
     *reinterpret_cast<uint2*>(p) = r;
 }
 
+// Element-wise passes over [rows, d] walk whole rows: a thread keeps one float4 column chunk
+// and steps over rows, so the per-element index arithmetic is one 32-bit division per row
+// instead of 64-bit divisions per element. Needs d/4 <= blockDim.x.
+struct RowWalk {
+    int c4;      // float4 column chunk of this thread
+    int row;     // first row (INT_MAX for threads beyond the last whole row of the CTA)
+    int step;    // rows between passes
+};
+__device__ __forceinline__ RowWalk row_walk(int d4)
+{
+    const int rpc = blockDim.x / d4;
+    const int r = threadIdx.x / d4;
+    RowWalk w;
+    w.c4 = threadIdx.x - r * d4;
+    w.row = (r < rpc) ? blockIdx.x * rpc + r : 0x7fffffff;
+    w.step = gridDim.x * rpc;
+    return w;
+}
+
 // out = x + attn_proj * sigmoid(y_comb)
 template <typename TIN>
 __global__ void __launch_bounds__(256) mag_combine_fwd_kernel(
@@ -489,12 +508,12 @@ __global__ void __launch_bounds__(256) mag_combine_fwd_kernel(
     CombineLevels L, float* __restrict__ out, int B, int S, int d, int H)
 {
     const int hd = d / H, d4 = d / 4;
-    const long long n4 = (long long)B * S * d4;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4;
-         i += (long long)gridDim.x * blockDim.x) {
-        const int j = (int)(i % d4) * 4;
-        const long long bt = i / d4;
-        const int t = (int)(bt % S), b = (int)(bt / S);
+    const int n_rows = B * S;
+    const RowWalk rw = row_walk(d4);
+    const int j = rw.c4 * 4;
+    for (int row = rw.row; row < n_rows; row += rw.step) {
+        const int b = row / S, t = row - b * S;
+        const size_t i = (size_t)row * d4 + rw.c4;
         const float4 y = combine_y(L, wts, b, t, j, S, H, hd);
         const float4 xa = ld4<float>(x + i * 4), ap = ld4<TIN>(attn_proj + i * 4);
         float4 o;
@@ -520,14 +539,14 @@ __global__ void __launch_bounds__(256) mag_combine_bwd_kernel(
 {
     __shared__ float red[WR_MAX_LEVELS * 32];
     const int hd = d / H, d4 = d / 4;
-    const long long n4 = (long long)B * S * d4;
+    const int n_rows = B * S;
     float dw[WR_MAX_LEVELS] = {0.f, 0.f, 0.f, 0.f};
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4;
-         i += (long long)gridDim.x * blockDim.x) {
-        const int j = (int)(i % d4) * 4;
-        const long long bt = i / d4;
-        const int t = (int)(bt % S), b = (int)(bt / S);
-        const int h = j / hd, w = j - h * hd;
+    const RowWalk rw = row_walk(d4);
+    const int j = rw.c4 * 4;
+    const int h = j / hd, w = j - h * hd;
+    for (int row = rw.row; row < n_rows; row += rw.step) {
+        const int b = row / S, t = row - b * S;
+        const size_t i = (size_t)row * d4 + rw.c4;
         float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
         float4 yl[WR_MAX_LEVELS];
 #pragma unroll
@@ -649,17 +668,17 @@ struct UnpoolSrc {
 __global__ void __launch_bounds__(256) unpool_sum_kernel(UnpoolSrc P, float* __restrict__ out,
                                                          long long n4, int S, int d4)
 {
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4;
-         i += (long long)gridDim.x * blockDim.x) {
-        const long long bt = i / d4;
-        const int c4 = (int)(i - bt * d4);
-        const long long b = bt / S;
-        const int t = (int)(bt - b * S);
+    const int n_rows = (int)(n4 / d4);
+    const RowWalk rw = row_walk(d4);
+    const int c4 = rw.c4;
+    for (int r = rw.row; r < n_rows; r += rw.step) {
+        const int b = r / S, t = r - b * S;
+        const size_t i = (size_t)r * d4 + c4;
         float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
         for (int l = 0; l < 3; l++) {
             if (l < P.n) {
-                const long long row = b * (S / P.c[l]) + t / P.c[l];
+                const long long row = (long long)b * (S / P.c[l]) + t / P.c[l];
                 const size_t o = ((size_t)row * d4 + c4) * 4;
                 const float4 v = P.is_bf16[l] ? ld4<__nv_bfloat16>((const __nv_bfloat16*)P.g[l] + o)
                                               : ld4<float>((const float*)P.g[l] + o);
