@@ -416,9 +416,14 @@ class StackedModelStep:
         self.host_tgt = torch.from_numpy(np.ascontiguousarray(ids[:, 1:])).pin_memory()
         self.tok, self.tgt = self.host_tok.cuda(), self.host_tgt.cuda()
         self.host_loss = torch.empty(1, dtype=torch.float32).pin_memory()
-        # this library's launches per step: per block SWA fwd (1) + bwd (3), MAG combine fwd+bwd (2),
-        # per level: prep fwd+bwd (2), memory fwd+bwd (2), pool-to-heads (1); norm (2) + AdamW (1)
-        self.launches_per_step = self.cfg.n_blocks * (4 + 2 + 5 * self.cfg.k) + 3
+        # this library's launches per step (the profiler's launch list shows the same kernels).
+        # Per block: SWA fwd (1) + bwd (3); MAG combine fwd + bwd (2); two LayerNorms fwd + bwd (4);
+        # pooled-level inputs: one mean pool per pooled level + their fused adjoint (p + 1);
+        # pooled-level output gradients (p); per level: prep fwd (1) + bwd (2: d_kvq, gate
+        # weights), memory fwd + bwd (2). Once: final LayerNorm (2), cross-entropy (2), gradient
+        # norm (1), AdamW (1).
+        p = sum(1 for c in self.cfg.chunk_sizes[:self.cfg.k] if min(c, self.S) > 1)
+        self.launches_per_step = self.cfg.n_blocks * (4 + 2 + 4 + (p + 1) + p + 5 * self.cfg.k) + 6
         self.h2d = self.host_tok.numel() * 8 * 2
         self.d2h = 4
         self.pg = None
