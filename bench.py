@@ -409,7 +409,7 @@ class StackedModelStep:
         from nl_hecate_b200.stacked_mag import StackedMAG, StackedMAGConfig
         self.torch, self.dd = torch, dispatch
         rank = int(os.environ.get("RANK", "0"))
-        self.cfg = StackedMAGConfig()
+        self.cfg = StackedMAGConfig(level_streams=os.environ.get("NLH_BENCH_LEVEL_STREAMS", "1") == "1")
         self.model = StackedMAG(self.cfg, self.local_batch, device="cuda", seed=42)
         ids = self.zipf_tokens(self.GLOBAL_BATCH)[rank * self.local_batch:(rank + 1) * self.local_batch]
         self.host_tok = torch.from_numpy(np.ascontiguousarray(ids[:, :-1])).pin_memory()

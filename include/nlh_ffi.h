@@ -38,6 +38,9 @@ const char* nlh_last_error(void);       /* text of the last recorded error ("" i
 void nlh_clear_status(void);
 int32_t nlh_workspace_reserve(int64_t bytes); /* pre-grow scratch (e.g. before graph capture) */
 void nlh_workspace_release(void);       /* free the scratch of the current device */
+/* Scratch slot (0..7, default 0) used by the following calls. Launches that may overlap on the
+ * GPU (different streams) must use different slots; each slot grows on its own. */
+int32_t nlh_set_workspace_slot(int32_t slot);
 int32_t nlh_abi_version(void);
 
 /* ═════════════ Section 1: drop-in symbols (core/src/cuda_ffi.rs) ═════════════ */

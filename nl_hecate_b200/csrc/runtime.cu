@@ -14,8 +14,16 @@ static char g_error[512] = "";
 static std::mutex g_mu;
 
 constexpr int MAX_DEVICES = 64;
-static void* g_ws[MAX_DEVICES] = {nullptr};
-static size_t g_ws_bytes[MAX_DEVICES] = {0};
+// Scratch is grow-only, per device and per SLOT. All launches use slot 0 unless the caller
+// selects another one (nlh_set_workspace_slot): a caller that runs launches on several streams
+// concurrently gives each stream its own slot so that they do not share scratch.
+constexpr int WS_SLOTS = 8;
+struct WsSlot {
+    void* ptr;
+    size_t bytes;
+};
+static int g_ws_slot = 0;
+static WsSlot g_ws[MAX_DEVICES][WS_SLOTS] = {};
 
 cudaStream_t current_stream() { return g_stream; }
 
@@ -34,9 +42,10 @@ void* workspace(size_t bytes)
         record_status(NLH_ERR_WORKSPACE, "workspace", "cudaGetDevice failed");
         return nullptr;
     }
-    if (bytes <= g_ws_bytes[dev] && g_ws[dev] != nullptr) return g_ws[dev];
+    WsSlot* slot = &g_ws[dev][g_ws_slot];
+    if (bytes <= slot->bytes && slot->ptr != nullptr) return slot->ptr;
     // cudaFree synchronises the device, so kernels still using the old block finish first.
-    if (g_ws[dev] != nullptr) { cudaFree(g_ws[dev]); g_ws[dev] = nullptr; g_ws_bytes[dev] = 0; }
+    if (slot->ptr != nullptr) { cudaFree(slot->ptr); slot->ptr = nullptr; slot->bytes = 0; }
     size_t want = (bytes + ((size_t)1 << 20) - 1) & ~(((size_t)1 << 20) - 1);
     void* p = nullptr;
     cudaError_t e = cudaMalloc(&p, want);
@@ -44,8 +53,8 @@ void* workspace(size_t bytes)
         record_status(NLH_ERR_WORKSPACE, "workspace cudaMalloc", cudaGetErrorString(e));
         return nullptr;
     }
-    g_ws[dev] = p;
-    g_ws_bytes[dev] = want;
+    slot->ptr = p;
+    slot->bytes = want;
     return p;
 }
 
@@ -67,7 +76,17 @@ void nlh_workspace_release(void)
 {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= nlh::MAX_DEVICES) return;
-    if (nlh::g_ws[dev]) { cudaFree(nlh::g_ws[dev]); nlh::g_ws[dev] = nullptr; nlh::g_ws_bytes[dev] = 0; }
+    for (int i = 0; i < nlh::WS_SLOTS; i++) {
+        nlh::WsSlot& s = nlh::g_ws[dev][i];
+        if (s.ptr) cudaFree(s.ptr);
+        s = nlh::WsSlot{};
+    }
+}
+int32_t nlh_set_workspace_slot(int32_t slot)
+{
+    if (slot < 0 || slot >= nlh::WS_SLOTS) return NLH_ERR_INVALID_ARG;
+    nlh::g_ws_slot = slot;
+    return NLH_OK;
 }
 int32_t nlh_abi_version(void) { return 1; }
 

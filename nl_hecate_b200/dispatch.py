@@ -78,6 +78,24 @@ def call(name: str, **kw):
     return rc
 
 
+class workspace_slot:
+    """Context manager: the library calls inside use scratch slot ``slot`` (launches that may
+    overlap on the GPU, i.e. run on different streams, must not share a slot)."""
+
+    def __init__(self, slot: int):
+        self.slot = int(slot)
+
+    def __enter__(self):
+        if self.slot:
+            ffi.check(ffi.lib().nlh_set_workspace_slot(self.slot), "nlh_set_workspace_slot")
+        return self
+
+    def __exit__(self, *exc):
+        if self.slot:
+            ffi.lib().nlh_set_workspace_slot(0)
+        return False
+
+
 def _f32(*shape, device):
     return torch.empty(*shape, dtype=torch.float32, device=device)
 

@@ -61,6 +61,7 @@ class StackedMAGConfig:
     max_grad_norm: float = 1.0
     tie_embeddings: bool = True
     fused_glue: bool = True           # fused CUDA rule wrapper / MAG combine (CUDA only)
+    level_streams: bool = True        # run CMS levels >= 1 on side streams next to level 0
 
     @property
     def head_dim(self):
@@ -73,8 +74,14 @@ class _TitansMemory(torch.autograd.Function):
     chunk > 0 : frozen-M0 chunkwise rule (titans_chunkwise_*_f32_cuda)."""
 
     @staticmethod
-    def forward(ctx, k, v, q, alpha, theta, eta, m0, chunk):
+    def forward(ctx, k, v, q, alpha, theta, eta, m0, chunk, slot=0):
         s0 = torch.zeros_like(m0)     # momentum restarts every call (gpu_forward.rs:1516-1517)
+        ctx.slot = slot
+        with D.workspace_slot(slot):
+            return _TitansMemory._forward(ctx, k, v, q, alpha, theta, eta, m0, s0, chunk)
+
+    @staticmethod
+    def _forward(ctx, k, v, q, alpha, theta, eta, m0, s0, chunk):
         if chunk == 0:
             # M trajectory only: the backward derives S_t = M_t - (1-alpha_{t-1}) M_{t-1}
             ms, ss, y = D.titans_forward_dd(k, v, q, alpha, theta, eta, m0, s0, store_s=False)
@@ -90,13 +97,14 @@ class _TitansMemory(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy, _dm):
         dy = dy.contiguous()
-        if ctx.chunk == 0:
-            k, v, q, alpha, theta, eta, ms = ctx.saved_tensors
-            g = D.titans_backward_dd(k, v, q, alpha, theta, eta, ms, None, dy)
-        else:
-            k, v, q, alpha, theta, eta, ms, ss = ctx.saved_tensors
-            g = D.titans_chunkwise_backward_dd(k, v, q, alpha, theta, eta, ms, ss, dy, ctx.chunk)
-        return g["d_k"], g["d_v"], g["d_q"], g["d_alpha"], g["d_theta"], g["d_eta"], None, None
+        with D.workspace_slot(ctx.slot):
+            if ctx.chunk == 0:
+                k, v, q, alpha, theta, eta, ms = ctx.saved_tensors
+                g = D.titans_backward_dd(k, v, q, alpha, theta, eta, ms, None, dy)
+            else:
+                k, v, q, alpha, theta, eta, ms, ss = ctx.saved_tensors
+                g = D.titans_chunkwise_backward_dd(k, v, q, alpha, theta, eta, ms, ss, dy, ctx.chunk)
+        return g["d_k"], g["d_v"], g["d_q"], g["d_alpha"], g["d_theta"], g["d_eta"], None, None, None
 
 
 class _SWA(torch.autograd.Function):
@@ -152,8 +160,9 @@ class _LevelPrep(torch.autograd.Function):
     split, and in backward the gate/L2-norm/transposes adjoints plus gate weight gradients."""
 
     @staticmethod
-    def forward(ctx, kvq, w_gates, b_alpha, b_theta, b_eta, num_heads):
+    def forward(ctx, kvq, w_gates, b_alpha, b_theta, b_eta, num_heads, slot=0):
         kvq = kvq.contiguous()
+        ctx.slot = slot
         B, sf, d3 = kvq.shape
         d, H = d3 // 3, num_heads
         hd, dev = d // H, kvq.device
@@ -182,13 +191,14 @@ class _LevelPrep(torch.autograd.Function):
         d_kvq = torch.empty(B, sf, 3 * d, dtype=dtype, device=dev)
         dwp = torch.empty(rows, 3, 2 * d, dtype=torch.float32, device=dev)
         dbp = torch.empty(rows, 3, dtype=torch.float32, device=dev)
-        D.call("nlh_level_prep_backward", k_ph=k_ph, v_ph=v_ph, q_ph=q_ph, alpha_ph=al, theta_ph=th,
-               eta_ph=et, k_norm=kn, q_norm=qn, dk_ph=dk, dv_ph=dv, dq_ph=dq, dalpha_ph=da,
-               dtheta_ph=dt, deta_ph=de, w_gates=w_gates, d_kvq=d_kvq, kvq_is_bf16=is_bf16,
-               dw_partial=dwp, db_partial=dbp, batch=B, seq=sf, d_model=d, num_heads=H)
+        with D.workspace_slot(ctx.slot):
+            D.call("nlh_level_prep_backward", k_ph=k_ph, v_ph=v_ph, q_ph=q_ph, alpha_ph=al, theta_ph=th,
+                   eta_ph=et, k_norm=kn, q_norm=qn, dk_ph=dk, dv_ph=dv, dq_ph=dq, dalpha_ph=da,
+                   dtheta_ph=dt, deta_ph=de, w_gates=w_gates, d_kvq=d_kvq, kvq_is_bf16=is_bf16,
+                   dw_partial=dwp, db_partial=dbp, batch=B, seq=sf, d_model=d, num_heads=H)
         dw = dwp.sum(0)
         db = dbp.sum(0)
-        return d_kvq, dw, db[0:1], db[1:2], db[2:3], None
+        return d_kvq, dw, db[0:1], db[1:2], db[2:3], None, None
 
 
 class _MagCombine(torch.autograd.Function):
@@ -371,8 +381,8 @@ class _CrossEntropy(torch.autograd.Function):
         return logits, None
 
 
-def titans_memory(k, v, q, alpha, theta, eta, m0, chunk):
-    return _TitansMemory.apply(k, v, q, alpha, theta, eta, m0, chunk)
+def titans_memory(k, v, q, alpha, theta, eta, m0, chunk, slot=0):
+    return _TitansMemory.apply(k, v, q, alpha, theta, eta, m0, chunk, slot)
 
 
 def swa(q, k, v, num_heads, head_dim, window):
@@ -489,20 +499,47 @@ class StackedMAG:
         y = y.view(B, nh, sf, hd).permute(0, 2, 1, 3).reshape(B, sf, d)
         return y.repeat_interleave(c, dim=1) if c > 1 else y
 
-    def _level_fused(self, b, l, x):
+    def _level_fused(self, b, l, x, slot=0):
         """Level through the fused wrapper kernels; x is the level's (already pooled) input
-        [B, S/c, d]. Returns the per-head output."""
+        [B, S/c, d]. Returns the per-head output. slot: scratch slot of the library calls (a
+        level that runs on a side stream must not share scratch with the other streams)."""
         cfg, p = self.cfg, self.p
         sf = x.shape[1]
         pre = f"b{b}.l{l}."
         kvq = self._mm(x, p[pre + "w_kvq_mem"])
         k, v, q, alpha, theta, eta = _LevelPrep.apply(kvq, p[pre + "w_gates"], p[pre + "b_alpha"],
                                                       p[pre + "b_theta"], p[pre + "b_eta"],
-                                                      cfg.num_heads)
+                                                      cfg.num_heads, slot)
         chunk = 0 if l in cfg.exact_levels else min(cfg.chunk_sizes[l], sf)
-        y, m_final = self.memory_fn(k, v, q, alpha, theta, eta, self.context[b][l], chunk)
+        if self.memory_fn is titans_memory:
+            y, m_final = titans_memory(k, v, q, alpha, theta, eta, self.context[b][l], chunk, slot)
+        else:
+            y, m_final = self.memory_fn(k, v, q, alpha, theta, eta, self.context[b][l], chunk)
         self.context[b][l].copy_(m_final.detach())   # in place: addresses stay fixed for graph replay
         return y
+
+    def _levels(self, b, inputs):
+        """Outputs of all CMS levels of block b. With cfg.level_streams the levels >= 1 (short,
+        latency-bound kernels) are issued on side streams and overlap level 0 on the GPU; the
+        autograd engine replays the same stream assignment in the backward pass."""
+        cfg = self.cfg
+        if not cfg.level_streams or cfg.k < 2:
+            return [self._level_fused(b, l, inputs[l]) for l in range(cfg.k)]
+        main = torch.cuda.current_stream()
+        if getattr(self, "_side", None) is None:
+            self._side = [torch.cuda.Stream() for _ in range(cfg.k)]
+        ys = [None] * cfg.k
+        for l in range(1, cfg.k):
+            st = self._side[l]
+            st.wait_stream(main)
+            with torch.cuda.stream(st):
+                ys[l] = self._level_fused(b, l, inputs[l], slot=l)
+            inputs[l].record_stream(st)
+        ys[0] = self._level_fused(b, 0, inputs[0])
+        for l in range(1, cfg.k):
+            main.wait_stream(self._side[l])
+            ys[l].record_stream(main)
+        return ys
 
     def _ln(self, x, name, mode, fused):
         p = self.p
@@ -538,7 +575,7 @@ class StackedMAG:
                 pooled = dict(zip(uniq, _PoolLevels.apply(m32, tuple(uniq), cfg.bf16))) if uniq else {}
                 for c in cs:
                     assert S % c == 0, "seq_len must be a multiple of every chunk size"
-                ys = [self._level_fused(b, l, pooled.get(cs[l], m16)) for l in range(cfg.k)]
+                ys = self._levels(b, [pooled.get(cs[l], m16) for l in range(cfg.k)])
                 pools = cs
                 x = _MagCombine.apply(x, attn_raw, wts, tuple(pools), nh, *ys)
             else:

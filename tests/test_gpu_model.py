@@ -143,3 +143,29 @@ def test_graph_replayed_step_matches_eager_steps():
         for l in range(3):
             a, r = graph.context[b][l], eager.context[b][l]
             assert float((a - r).abs().max()) <= 1e-3 * max(float(r.abs().max()), 1e-6)
+
+
+def test_level_streams_match_single_stream_eager_and_graphed():
+    """cfg.level_streams issues CMS levels >= 1 on side streams (own scratch slots): the same
+    kernels run, so gradients agree with the single-stream model to rounding (only the order of
+    the atomic adds into shared gradients can differ), eagerly and replayed from the graph."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    import dataclasses
+    from nl_hecate_b200.stacked_mag import StackedMAG
+    tok, tgt = _data(4, seed=21)
+    cfg_s = dataclasses.replace(_cfg(True), level_streams=True)
+    cfg_1 = dataclasses.replace(_cfg(True), level_streams=False)
+    multi = StackedMAG(cfg_s, 4, device="cuda", seed=5)
+    single = StackedMAG(cfg_1, 4, device="cuda", seed=5)
+    _compare(multi, single, tok, tgt, 1e-6, 1e-4)
+    multi = StackedMAG(cfg_s, 4, device="cuda", seed=6)
+    single = StackedMAG(cfg_1, 4, device="cuda", seed=6)
+    for _ in range(5):
+        le = single.step(tok, tgt)
+    for _ in range(3):
+        lg = multi.step_graphed(tok, tgt)     # steps 1-3 on the first call, then 4 and 5
+    torch.cuda.synchronize()
+    assert multi.global_step == single.global_step == 5
+    assert abs(float(le) - float(lg)) <= 1e-3 * abs(float(le))
+    assert float((single.opt.w - multi.opt.w).abs().max()) <= 1e-4
