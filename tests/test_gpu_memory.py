@@ -481,3 +481,26 @@ def test_null_momentum_trajectory_rejected_off_the_fast_path(D, orc):
     with pytest.raises(RuntimeError, match="register-resident"):
         D.titans_forward_dd(t["k"], t["v"], t["q"], t["alpha"], t["theta"], t["eta"], t["m0"],
                             t["s0"], store_s=False)
+
+
+def test_kernels_reproduce_the_committed_small_vectors(D):
+    """The committed known-answer file (tests/golden/oracle_small.npz, frozen oracle outputs on
+    the reference's rand_buf inputs) against the CUDA kernels: Titans exact pair at d=8, s=6."""
+    import os
+    import torch
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "oracle_small.npz"))
+    import oracle as orc
+    d, s = 8, 6
+    r = lambda n, seed: orc.rand_buf(n, seed, 0.1)
+    k, v, q, dy = (torch.from_numpy(r(s * d, 100 + i).reshape(1, s, d)).cuda() for i in range(4))
+    m0 = torch.from_numpy(r(d * d, 104).reshape(1, d * d)).cuda()
+    s0 = torch.from_numpy(r(d * d, 105).reshape(1, d * d)).cuda()
+    al = torch.full((1, s), 0.05, device="cuda")
+    th = torch.full((1, s), 0.01, device="cuda")
+    et = torch.full((1, s), 0.9, device="cuda")
+    ms, ss, y = D.titans_forward_dd(k, v, q, al, th, et, m0, s0)
+    assert max_abs(_np(y[0]), g["titans_y"]) < 1e-6
+    assert max_abs(_np(ms[0, -1]), g["titans_m_final"]) < 1e-6
+    got = D.titans_backward_dd(k, v, q, al, th, et, ms, ss, dy)
+    for key in ("d_k", "d_v", "d_q", "d_alpha", "d_theta", "d_eta"):
+        assert rel_err(_np(got[key][0]), g["titans_" + key]) <= REL, key

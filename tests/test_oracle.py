@@ -370,3 +370,22 @@ def test_embedding_gather_scatter_are_adjoint(orc):
     ref = np.zeros((vocab, d), np.float64)
     np.add.at(ref, ids, g.astype(np.float64))
     assert np.abs(dw - ref).max() < 1e-6
+
+
+def test_oracle_reproduces_the_committed_small_vectors():
+    """tests/golden/oracle_small.npz freezes the oracle's answers on seeded inputs (generated by
+    tests/golden/make_golden.py; not outputs of the reference, which cannot run here). The
+    oracle must reproduce them to 1e-5 relative (libm's exp/log may differ in the last bit
+    between host CPUs, everything else is plain fp32 arithmetic without FMA contraction)."""
+    import importlib.util
+    import os
+    here = os.path.dirname(os.path.abspath(__file__))
+    spec = importlib.util.spec_from_file_location("make_golden", os.path.join(here, "golden", "make_golden.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    want = np.load(os.path.join(here, "golden", "oracle_small.npz"))
+    got = mod.cases()
+    assert set(got) == set(want.files)
+    for key in want.files:
+        a, b = np.asarray(got[key], dtype=np.float64), want[key].astype(np.float64)
+        assert a.shape == b.shape and np.allclose(a, b, rtol=1e-5, atol=1e-7), key
