@@ -483,13 +483,12 @@ def test_null_momentum_trajectory_rejected_off_the_fast_path(D, orc):
                             t["s0"], store_s=False)
 
 
-def test_kernels_reproduce_the_committed_small_vectors(D):
+def test_kernels_reproduce_the_committed_small_vectors(D, orc):
     """The committed known-answer file (tests/golden/oracle_small.npz, frozen oracle outputs on
     the reference's rand_buf inputs) against the CUDA kernels: Titans exact pair at d=8, s=6."""
     import os
     import torch
     g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "oracle_small.npz"))
-    import oracle as orc
     d, s = 8, 6
     r = lambda n, seed: orc.rand_buf(n, seed, 0.1)
     k, v, q, dy = (torch.from_numpy(r(s * d, 100 + i).reshape(1, s, d)).cuda() for i in range(4))
