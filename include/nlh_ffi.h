@@ -398,6 +398,47 @@ int32_t nlh_cross_entropy_forward(const void* logits, int32_t logits_is_bf16, co
 int32_t nlh_cross_entropy_backward(const void* logits, int32_t logits_is_bf16, const int32_t* target_ids,
     const float* lse, const float* grad_scale, void* d_logits, int32_t n, int32_t vocab, float inv_count);
 
+/* ── Host-slice dispatch layer (compiled counterpart of core/src/dispatch.rs `*_dispatch`) ────
+ * Same argument order and meaning as the reference functions its kernel tests call
+ * (swa_forward_dispatch dispatch.rs:378, swa_backward_dispatch :408, delta :746/:775, titans
+ * :810/:842, hebbian :1083/:1110, dgd :1153/:1182): HOST pointers, one sequence, int64 sizes
+ * (usize), int32 status instead of a panic. Each call uploads, runs the drop-in entry,
+ * downloads and synchronises. SWA rounds q,k,v to bf16 on the device; its backward adds into
+ * d_q,d_k,d_v (caller pre-zeroes) and does not read attn_weights (may be NULL). */
+int32_t nlh_swa_forward_dispatch(const float* q, const float* k, const float* v, float* out,
+    float* attn_weights, int64_t seq_len, int64_t num_heads, int64_t head_dim, int64_t window_size);
+int32_t nlh_swa_backward_dispatch(const float* q, const float* k, const float* v, const float* attn_weights,
+    const float* d_attn_out, float* d_q, float* d_k, float* d_v, int64_t seq_len, int64_t num_heads,
+    int64_t head_dim, int64_t window_size);
+int32_t nlh_delta_forward_dispatch(const float* k_mem, const float* v_mem, const float* q_mem,
+    const float* alpha, const float* theta, const float* m_initial, float* m_states, float* y,
+    int64_t seq_len, int64_t d, float error_clip, float m_norm_max);
+int32_t nlh_delta_backward_dispatch(const float* k_mem, const float* v_mem, const float* q_mem,
+    const float* alpha, const float* theta, const float* m_states, const float* d_y, float* d_k_mem,
+    float* d_v_mem, float* d_q_mem, float* d_alpha, float* d_theta, float* d_m_initial, int64_t seq_len,
+    int64_t d, float error_clip);
+int32_t nlh_titans_forward_dispatch(const float* k_mem, const float* v_mem, const float* q_mem,
+    const float* alpha, const float* theta, const float* eta, const float* m_initial,
+    const float* s_initial, float* m_states, float* s_states, float* y, int64_t seq_len, int64_t d,
+    float error_clip, float m_norm_max);
+int32_t nlh_titans_backward_dispatch(const float* k_mem, const float* v_mem, const float* q_mem,
+    const float* alpha, const float* theta, const float* eta, const float* m_states,
+    const float* s_states, const float* d_y, float* d_k_mem, float* d_v_mem, float* d_q_mem,
+    float* d_alpha, float* d_theta, float* d_eta, float* d_m_initial, float* d_s_initial,
+    int64_t seq_len, int64_t d, float error_clip);
+int32_t nlh_hebbian_forward_dispatch(const float* k_mem, const float* v_mem, const float* q_mem,
+    const float* alpha, const float* m_initial, float* m_states, float* y, int64_t seq_len, int64_t d);
+int32_t nlh_hebbian_backward_dispatch(const float* k_mem, const float* v_mem, const float* q_mem,
+    const float* alpha, const float* m_states, const float* d_y, float* d_k_mem, float* d_v_mem,
+    float* d_q_mem, float* d_alpha, float* d_m_initial, int64_t seq_len, int64_t d);
+int32_t nlh_dgd_forward_dispatch(const float* k_mem, const float* v_mem, const float* q_mem,
+    const float* alpha, const float* theta, const float* m_initial, float* m_states, float* y,
+    int64_t seq_len, int64_t d, float error_clip);
+int32_t nlh_dgd_backward_dispatch(const float* k_mem, const float* v_mem, const float* q_mem,
+    const float* alpha, const float* theta, const float* m_states, const float* d_y, float* d_k_mem,
+    float* d_v_mem, float* d_q_mem, float* d_alpha, float* d_theta, float* d_m_initial, int64_t seq_len,
+    int64_t d, float error_clip);
+
 /* ── Opaque-VJP registry over the C ABI (boundary of core/src/tape.rs:98-182) ────────────────
  * Keys number the variants of the reference's OpaqueKey enum in declaration order
  * (core/src/tape.rs:100-134). nlh_opaque_backward is the C form of OpaqueBackwardFn

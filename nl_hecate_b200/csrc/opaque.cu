@@ -14,9 +14,7 @@
 // functions (core/src/dispatch.rs:330-1213).
 #include <cuda_bf16.h>
 
-#include <vector>
-
-#include "nlh_common.cuh"
+#include "host_staging.cuh"
 #include "../../include/nlh_ffi.h"
 
 namespace nlh {
@@ -40,42 +38,10 @@ __global__ void frozen_read_bwd_kernel(const float* __restrict__ m, const float*
     }
 }
 
-// Device staging of host slices; everything is released when the object dies.
-struct Staging {
-    std::vector<void*> bufs;
-    bool ok = true;
-    ~Staging() { for (void* p : bufs) cudaFree(p); }
-    void* alloc(size_t bytes)
-    {
-        void* p = nullptr;
-        if (bytes == 0) bytes = 4;
-        if (cudaMalloc(&p, bytes) != cudaSuccess) { ok = false; return nullptr; }
-        bufs.push_back(p);
-        return p;
-    }
-    float* upload(const float* host, long long n, cudaStream_t st)
-    {
-        float* p = (float*)alloc((size_t)n * sizeof(float));
-        if (p && n > 0 && cudaMemcpyAsync(p, host, (size_t)n * sizeof(float), cudaMemcpyHostToDevice, st) != cudaSuccess) ok = false;
-        return p;
-    }
-    float* zeros(long long n, cudaStream_t st)
-    {
-        float* p = (float*)alloc((size_t)n * sizeof(float));
-        if (p && cudaMemsetAsync(p, 0, (size_t)(n > 0 ? n : 1) * sizeof(float), st) != cudaSuccess) ok = false;
-        return p;
-    }
-};
-
 static int fail(int code, const char* detail)
 {
     record_status(code, "nlh_opaque_backward", detail);
     return code;
-}
-
-static bool download(float* host, const float* dev, long long n, cudaStream_t st)
-{
-    return n <= 0 || cudaMemcpyAsync(host, dev, (size_t)n * sizeof(float), cudaMemcpyDeviceToHost, st) == cudaSuccess;
 }
 
 }  // namespace nlh

@@ -394,3 +394,89 @@ def opaque_backward(key, d_outputs, saved, in_lens):
     call("nlh_opaque_backward", key=key, n_out=len(d_outputs), d_outputs=po, out_len=lo,
          n_saved=len(saved), saved=ps, saved_len=ls, n_in=len(d_inputs), d_inputs=pi, in_len=li)
     return d_inputs
+
+
+# ── compiled host-slice dispatch layer (core/src/dispatch.rs `*_dispatch` functions) ──
+def _h(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _hp(a):
+    return None if a is None else C.c_void_p(a.ctypes.data)
+
+
+def host_rule_forward(rule, k, v, q, alpha, theta=None, eta=None, m0=None, s0=None, error_clip=0.0,
+                      m_norm_max=0.0):
+    """Host arrays in, host arrays out through nlh_{delta,titans,hebbian,dgd}_forward_dispatch
+    (one sequence: k,v,q [s, d]). Returns dict(m_states, y[, s_states])."""
+    k, v, q, alpha, m0 = map(_h, (k, v, q, alpha, m0))
+    s, d = k.shape
+    ms, y = np.empty((s + 1, d * d), np.float32), np.empty((s, d), np.float32)
+    out = {"m_states": ms, "y": y}
+    if rule == "titans":
+        theta, eta, s0 = map(_h, (theta, eta, s0))
+        ss = np.empty((s + 1, d * d), np.float32)
+        out["s_states"] = ss
+        call("nlh_titans_forward_dispatch", k_mem=_hp(k), v_mem=_hp(v), q_mem=_hp(q), alpha=_hp(alpha),
+             theta=_hp(theta), eta=_hp(eta), m_initial=_hp(m0), s_initial=_hp(s0), m_states=_hp(ms),
+             s_states=_hp(ss), y=_hp(y), seq_len=s, d=d, error_clip=error_clip, m_norm_max=m_norm_max)
+    elif rule == "hebbian":
+        call("nlh_hebbian_forward_dispatch", k_mem=_hp(k), v_mem=_hp(v), q_mem=_hp(q), alpha=_hp(alpha),
+             m_initial=_hp(m0), m_states=_hp(ms), y=_hp(y), seq_len=s, d=d)
+    elif rule == "dgd":
+        theta = _h(theta)
+        call("nlh_dgd_forward_dispatch", k_mem=_hp(k), v_mem=_hp(v), q_mem=_hp(q), alpha=_hp(alpha),
+             theta=_hp(theta), m_initial=_hp(m0), m_states=_hp(ms), y=_hp(y), seq_len=s, d=d,
+             error_clip=error_clip)
+    else:
+        theta = _h(theta)
+        call("nlh_delta_forward_dispatch", k_mem=_hp(k), v_mem=_hp(v), q_mem=_hp(q), alpha=_hp(alpha),
+             theta=_hp(theta), m_initial=_hp(m0), m_states=_hp(ms), y=_hp(y), seq_len=s, d=d,
+             error_clip=error_clip, m_norm_max=m_norm_max)
+    return out
+
+
+def host_rule_backward(rule, k, v, q, alpha, m_states, d_y, theta=None, eta=None, s_states=None,
+                       error_clip=0.0):
+    k, v, q, alpha, m_states, d_y = map(_h, (k, v, q, alpha, m_states, d_y))
+    s, d = k.shape
+    z = lambda *sh: np.zeros(sh, np.float32)
+    g = {"d_k": z(s, d), "d_v": z(s, d), "d_q": z(s, d), "d_alpha": z(s), "d_m_initial": z(d * d)}
+    common = dict(k_mem=_hp(k), v_mem=_hp(v), q_mem=_hp(q), alpha=_hp(alpha), m_states=_hp(m_states),
+                  d_y=_hp(d_y), d_k_mem=_hp(g["d_k"]), d_v_mem=_hp(g["d_v"]), d_q_mem=_hp(g["d_q"]),
+                  d_alpha=_hp(g["d_alpha"]), d_m_initial=_hp(g["d_m_initial"]), seq_len=s, d=d)
+    if rule == "hebbian":
+        call("nlh_hebbian_backward_dispatch", **common)
+        return g
+    theta = _h(theta)
+    g["d_theta"] = z(s)
+    common.update(theta=_hp(theta), d_theta=_hp(g["d_theta"]), error_clip=error_clip)
+    if rule == "titans":
+        eta, s_states = _h(eta), _h(s_states)
+        g["d_eta"], g["d_s_initial"] = z(s), z(d * d)
+        call("nlh_titans_backward_dispatch", eta=_hp(eta), s_states=_hp(s_states), d_eta=_hp(g["d_eta"]),
+             d_s_initial=_hp(g["d_s_initial"]), **common)
+    else:
+        call("nlh_dgd_backward_dispatch" if rule == "dgd" else "nlh_delta_backward_dispatch", **common)
+    return g
+
+
+def host_swa_forward(q, k, v, num_heads, head_dim, window):
+    q, k, v = map(_h, (q, k, v))
+    s = q.shape[0]
+    out = np.empty_like(q)
+    aw = np.empty((num_heads, s, window), np.float32)
+    call("nlh_swa_forward_dispatch", q=_hp(q), k=_hp(k), v=_hp(v), out=_hp(out), attn_weights=_hp(aw),
+         seq_len=s, num_heads=num_heads, head_dim=head_dim, window_size=window)
+    return {"out": out, "attn_weights": aw}
+
+
+def host_swa_backward(q, k, v, attn_weights, d_out, num_heads, head_dim, window):
+    q, k, v, d_out = map(_h, (q, k, v, d_out))
+    s = q.shape[0]
+    g = {n: np.zeros_like(q) for n in ("d_q", "d_k", "d_v")}
+    call("nlh_swa_backward_dispatch", q=_hp(q), k=_hp(k), v=_hp(v),
+         attn_weights=None if attn_weights is None else _hp(_h(attn_weights)), d_attn_out=_hp(d_out),
+         d_q=_hp(g["d_q"]), d_k=_hp(g["d_k"]), d_v=_hp(g["d_v"]), seq_len=s, num_heads=num_heads,
+         head_dim=head_dim, window_size=window)
+    return g
