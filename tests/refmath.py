@@ -43,3 +43,47 @@ def fd_grad(fn, x, eps=1e-5):
         g[i] = (fn(xp) - fn(xm)) / (2 * eps)
         it.iternext()
     return g
+
+
+def swa_forward64(q, k, v, num_heads, head_dim, window):
+    """Causal sliding-window attention in float64 (core/src/swa.rs:33-92): query t sees keys
+    max(0, t+1-window) .. t."""
+    q, k, v = (np.asarray(a, dtype=np.float64) for a in (q, k, v))
+    s = q.shape[0]
+    out = np.zeros_like(q)
+    sc = 1.0 / np.sqrt(head_dim)
+    for h in range(num_heads):
+        sl = slice(h * head_dim, (h + 1) * head_dim)
+        for t in range(s):
+            lo = max(0, t + 1 - window)
+            z = (k[lo:t + 1, sl] @ q[t, sl]) * sc
+            w = np.exp(z - z.max())
+            out[t, sl] = (w / w.sum()) @ v[lo:t + 1, sl]
+    return out
+
+
+def mag_single_loss64(p, input_ids, target_ids, num_heads, window, rule="delta"):
+    """Loss of the single-block MAG model with one memory level in float64 (an independent
+    statement of core/src/mag.rs:74-187 with the rule wrapper of delta_rule.rs:278-400 /
+    titans_lmm.rs:1314-1530; no bf16 rounding of the memory projections)."""
+    P = {k_: np.asarray(v_, dtype=np.float64) for k_, v_ in p.items()}
+    ids, tgt = np.asarray(input_ids), np.asarray(target_ids)
+    vocab, d = P["w_embed"].shape
+    hd = d // num_heads
+    emb = P["w_embed"][ids]
+    attn = swa_forward64(emb @ P["w_q"].T, emb @ P["w_k"].T, emb @ P["w_v"].T, num_heads, hd, window)
+    km, vm, qm = emb @ P["w_k_mem"].T, emb @ P["w_v_mem"].T, emb @ P["w_q_mem"].T
+    km = km / np.maximum(np.linalg.norm(km, axis=1, keepdims=True), 1e-8)
+    qm = qm / np.maximum(np.linalg.norm(qm, axis=1, keepdims=True), 1e-8)
+    c = np.concatenate([km, vm], axis=1)
+    sig = lambda x: 1.0 / (1.0 + np.exp(-x))
+    alpha = sig(c @ P["w_alpha"] + P["b_alpha"][0])
+    theta = np.log1p(np.exp(c @ P["w_theta"] + P["b_theta"][0]))
+    eta = sig(c @ P["w_eta"] + P["b_eta"][0]) if rule == "titans" else None
+    z = np.zeros((d, d))
+    y = rule_forward64(rule, km, vm, qm, alpha, theta, eta, z, z if rule == "titans" else None)[0]
+    logits = ((attn * sig(y)) @ P["w_o"].T) @ P["w_unembed"]
+    m = logits.max(axis=1, keepdims=True)
+    lse = np.log(np.exp(logits - m).sum(axis=1)) + m[:, 0]
+    valid = [t for t in range(len(tgt)) if 0 <= tgt[t] < vocab]
+    return float(np.mean([lse[t] - logits[t, tgt[t]] for t in valid]))

@@ -389,3 +389,37 @@ def test_oracle_reproduces_the_committed_small_vectors():
     for key in want.files:
         a, b = np.asarray(got[key], dtype=np.float64), want[key].astype(np.float64)
         assert a.shape == b.shape and np.allclose(a, b, rtol=1e-5, atol=1e-7), key
+
+
+@pytest.mark.parametrize("rule", ["delta", "titans"])
+def test_mag_single_model_gradients_match_float64_finite_differences(orc, rule, monkeypatch):
+    """The model-level oracle (oracle/mag_single.py: core/src/mag.rs mag_forward/mag_backward with
+    the Delta / Titans rule wrapper) against an independent float64 statement of the loss,
+    finite-differenced along random directions, one parameter tensor at a time. The memory
+    projections' bf16 rounding is switched off for this test (it is a straight-through
+    projection of the weights, not part of the derivative)."""
+    from oracle import mag_single as M
+    from refmath import mag_single_loss64
+    monkeypatch.setattr(orc, "bf16_round", lambda a: np.ascontiguousarray(a, dtype=np.float32))
+    d, nh, s, vocab, w = 16, 2, 12, 24, 5
+    p = M.init_params(d, vocab, seed=7, rule=rule)
+    for n in ("w_k_mem", "w_v_mem", "w_q_mem", "w_o"):     # make the memory branch matter
+        p[n] = (p[n] * 3.0).astype(np.float32)
+    p["b_theta"][0], p["b_alpha"][0] = 0.3, -1.0
+    ids = orc.rng_tokens(11, vocab, s + 1)
+    x, t = ids[:-1], ids[1:]
+    loss, g = M.forward_backward(p, x, t, nh, w, rule)
+    l64 = mag_single_loss64(p, x, t, nh, w, rule)
+    assert abs(loss - l64) <= 1e-5 * abs(l64)
+    rng = np.random.default_rng(3)
+    for name in p:
+        u = rng.standard_normal(p[name].shape)
+        h = 1e-6
+        pp = {k: v.astype(np.float64) for k, v in p.items()}
+        pm = {k: v.astype(np.float64) for k, v in p.items()}
+        pp[name] = pp[name] + h * u
+        pm[name] = pm[name] - h * u
+        fd = (mag_single_loss64(pp, x, t, nh, w, rule) - mag_single_loss64(pm, x, t, nh, w, rule)) / (2 * h)
+        an = float((g[name].astype(np.float64) * u).sum())
+        scale = float(np.abs(g[name]).astype(np.float64).sum()) + 1e-12
+        assert abs(fd - an) <= 2e-3 * abs(fd) + 2e-5 * scale, (name, fd, an)
