@@ -556,7 +556,7 @@ def run_reference(args):
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": 1e3 * wl.tokens_per_step / value, "higher_is_better": True,
+        "ms_per_step": 1e3 * wl.tokens_per_step * max(1, args.gpus) / value, "higher_is_better": True,
         "scaling": "strong" if args.workload == "stacked_mag" else "weak", "vs_baseline": None,
         "dtype": wl.dtype, "data": "synthetic", "config": cfg,
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
