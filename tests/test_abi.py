@@ -116,3 +116,37 @@ def test_bench_reference_arm_prints_the_contract_line():
     assert rec["impl"] == "reference" and rec["value"] > 0
     assert rec["cpu_baseline"]["kind"] == "port" and rec["cpu_baseline"]["cores"] >= 1
     assert rec["e2e"]["h2d_bytes_per_step"] == 0 and rec["e2e"]["d2h_bytes_per_step"] == 0
+
+
+def test_drop_in_prototypes_match_the_reference_declarations():
+    """Every non-nlh_ prototype of include/nlh_ffi.h against the reference's Rust declaration of
+    the same name (tests/golden/ffi_signatures.json, extracted from core/src/cuda_ffi.rs by
+    tests/golden/make_ffi_signatures.py): same argument count, order, names and types, same
+    return type."""
+    import json
+    import os
+    import re
+    here = os.path.dirname(os.path.abspath(__file__))
+    sigs = json.load(open(os.path.join(here, "golden", "ffi_signatures.json")))
+    hdr = open(os.path.join(os.path.dirname(here), "include", "nlh_ffi.h")).read()
+    hdr = re.sub(r"/\*.*?\*/", "", hdr, flags=re.S)
+    tmap = {"*const f32": "const float*", "*mut f32": "float*", "*const u16": "const uint16_t*",
+            "*mut u16": "uint16_t*", "i32": "int32_t", "f32": "float", "*const i32": "const int32_t*",
+            "*mut i32": "int32_t*", "u32": "uint32_t", "i64": "int64_t"}
+    rmap = {None: "void", "u32": "uint32_t", "i32": "int32_t"}
+    checked = 0
+    for m in re.finditer(r"^(void|int32_t|uint32_t)\s+(\w+)\s*\((.*?)\)\s*;", hdr, flags=re.S | re.M):
+        ret, name, args = m.group(1), m.group(2), m.group(3)
+        if name.startswith("nlh_"):
+            continue
+        assert name in sigs, f"{name} is not declared by the reference"
+        want = sigs[name]
+        got = []
+        for a in args.split(","):
+            mm = re.match(r"(.*?)(\w+)$", " ".join(a.split()))
+            got.append((mm.group(2), mm.group(1).strip().replace(" *", "*").replace(" ", "")))
+        exp = [(n, tmap[t].replace(" ", "")) for n, t in want["args"]]
+        assert got == exp, (name, got, exp)
+        assert rmap[want["ret"]] == ret, name
+        checked += 1
+    assert checked >= 40
