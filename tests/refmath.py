@@ -87,3 +87,79 @@ def mag_single_loss64(p, input_ids, target_ids, num_heads, window, rule="delta")
     lse = np.log(np.exp(logits - m).sum(axis=1)) + m[:, 0]
     valid = [t for t in range(len(tgt)) if 0 <= tgt[t] < vocab]
     return float(np.mean([lse[t] - logits[t, tgt[t]] for t in valid]))
+
+
+def _bf16_round64(a):
+    """Round-to-nearest-even to bfloat16 precision, returned as float64."""
+    a32 = np.ascontiguousarray(a, dtype=np.float32)
+    u = a32.view(np.uint32).astype(np.uint64)
+    u = (u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000
+    return u.astype(np.uint32).view(np.float32).astype(np.float64)
+
+
+def _ln64(x, gamma, beta, eps=1e-5):
+    mu = x.mean(-1, keepdims=True)
+    var = ((x - mu) ** 2).mean(-1, keepdims=True)
+    return gamma * (x - mu) / np.sqrt(var + eps) + beta
+
+
+def stacked_mag_loss64(p, cfg, tokens, targets, context):
+    """Loss of the stacked MAG model (one call = one forward over [B, S] token ids) in float64
+    numpy, an independent statement of the block composition of
+    core/src/gpu_stacked_forward.rs:1656-1960 as the harness runs it in its fp32 mode:
+    LayerNorm -> q,k,v (rounded to bf16, as is the attention output) -> SWA -> W_o -> first
+    residual -> LayerNorm -> per level: mean pool by the chunk size, k|v|q projection, L2 norm of
+    k,q over d_model, three gates shared by the heads, per-head Titans memory (level 0 exact,
+    levels >= 1 frozen-M0 with chunk = min(chunk size, pooled length)), repeat-upsample ->
+    softmax(alpha_mem)-weighted sum -> out = x + attn_proj * sigmoid(y); final LayerNorm,
+    unembedding, mean cross-entropy. `context[b][l]` ([B*H, hd*hd] float64) is the carried memory:
+    read as M_0 and overwritten with the final M, like the harness does."""
+    P = {k_: np.asarray(v_, dtype=np.float64) for k_, v_ in p.items()}
+    d, nh, hd = cfg["d_model"], cfg["num_heads"], cfg["d_model"] // cfg["num_heads"]
+    tok, tgt = np.asarray(tokens), np.asarray(targets)
+    B, S = tok.shape
+    sig = lambda z: 1.0 / (1.0 + np.exp(-z))
+    x = P["w_embed"][tok]                                              # [B, S, d]
+    for b in range(cfg["n_blocks"]):
+        pre = f"b{b}."
+        h = _ln64(x, P[pre + "ln_attn_gamma"], P[pre + "ln_attn_beta"])
+        qkv = _bf16_round64(h @ P[pre + "w_qkv"].T)
+        q, k, v = qkv[..., :d], qkv[..., d:2 * d], qkv[..., 2 * d:]
+        attn = np.stack([swa_forward64(q[i], k[i], v[i], nh, hd, cfg["window"]) for i in range(B)])
+        attn = _bf16_round64(attn)
+        attn_proj = attn @ P[pre + "w_o"].T
+        m_in = _ln64(x + attn_proj, P[pre + "ln_mem_gamma"], P[pre + "ln_mem_beta"])
+        wts = np.exp(P[pre + "alpha_mem"] - P[pre + "alpha_mem"].max())
+        wts = wts / wts.sum()
+        y = np.zeros_like(x)
+        for l in range(cfg["k"]):
+            lp = pre + f"l{l}."
+            c = min(cfg["chunk_sizes"][l], S)
+            sf = S // c
+            xl = m_in.reshape(B, sf, c, d).mean(2) if c > 1 else m_in
+            kvq = xl @ P[lp + "w_kvq_mem"].T
+            km, vm, qm = kvq[..., :d], kvq[..., d:2 * d], kvq[..., 2 * d:]
+            km = km / np.maximum(np.linalg.norm(km, axis=-1, keepdims=True), 1e-8)
+            qm = qm / np.maximum(np.linalg.norm(qm, axis=-1, keepdims=True), 1e-8)
+            pg = np.concatenate([km, vm], axis=-1) @ P[lp + "w_gates"].T       # [B, sf, 3]
+            alpha = sig(pg[..., 0] + P[lp + "b_alpha"][0])
+            theta = np.log1p(np.exp(pg[..., 1] + P[lp + "b_theta"][0]))
+            eta = sig(pg[..., 2] + P[lp + "b_eta"][0])
+            chunk = 0 if l in cfg["exact_levels"] else min(cfg["chunk_sizes"][l], sf)
+            yl = np.zeros((B, sf, d))
+            for i in range(B):
+                for hh in range(nh):
+                    sl = slice(hh * hd, (hh + 1) * hd)
+                    m0 = context[b][l][i * nh + hh].reshape(hd, hd)
+                    yy, m_fin, _ = rule_forward64("titans", km[i][:, sl], vm[i][:, sl], qm[i][:, sl], alpha[i],
+                                                  theta[i], eta[i], m0, np.zeros((hd, hd)), chunk)
+                    yl[i][:, sl] = yy
+                    context[b][l][i * nh + hh] = m_fin.reshape(-1)
+            y = y + wts[l] * (np.repeat(yl, c, axis=1) if c > 1 else yl)
+        x = x + attn_proj * sig(y)
+    x = _ln64(x, P["ln_final_gamma"], P["ln_final_beta"])
+    logits = (x @ P["w_unembed"]).reshape(B * S, -1)
+    m = logits.max(axis=1, keepdims=True)
+    lse = np.log(np.exp(logits - m).sum(axis=1)) + m[:, 0]
+    flat = tgt.reshape(-1)
+    return float(np.mean(lse - logits[np.arange(B * S), flat]))

@@ -109,3 +109,40 @@ def test_sync_gradients_world1_is_a_no_op():
     before = m.opt.g.clone()
     m.sync_gradients(None, 1)
     assert torch.equal(before, m.opt.g)
+
+
+def test_harness_forward_matches_an_independent_float64_statement():
+    """The stacked harness (plain-PyTorch operators, fp32) against tests/refmath.py's float64
+    numpy statement of the same block composition, over two consecutive calls so that the
+    carried memories are non-zero in the second one."""
+    import numpy as np
+    from refmath import stacked_mag_loss64
+    m = _model(2, seed=11)
+    cfg = m.cfg
+    # make every branch matter: random LayerNorm affine terms, level weights and gate biases
+    g = torch.Generator().manual_seed(5)
+    with torch.no_grad():
+        for n, w in m.p.items():
+            base = n.split(".")[-1]
+            if base.endswith("gamma"):
+                w.add_(0.2 * torch.randn(w.shape, generator=g))
+            elif base.endswith("beta") or base == "alpha_mem":
+                w.add_(0.3 * torch.randn(w.shape, generator=g))
+            elif base == "b_theta":
+                w.fill_(-1.0)
+            elif base == "b_alpha":
+                w.fill_(-2.0)
+    params = {n: w.detach().numpy().astype(np.float64) for n, w in m.p.items()}
+    cfgd = dict(d_model=cfg.d_model, num_heads=cfg.num_heads, n_blocks=cfg.n_blocks, k=cfg.k,
+                chunk_sizes=cfg.chunk_sizes, window=cfg.window, exact_levels=cfg.exact_levels)
+    ctx = [[np.zeros((2 * cfg.num_heads, cfg.head_dim ** 2)) for _ in range(cfg.k)] for _ in range(cfg.n_blocks)]
+    for call in range(2):
+        tok, tgt = _data(2, seed=call)
+        with torch.no_grad():
+            got = float(m.forward(tok, tgt))
+        want = stacked_mag_loss64(params, cfgd, tok.numpy(), tgt.numpy(), ctx)
+        assert abs(got - want) <= 2e-4 * abs(want), (call, got, want)
+    for b in range(cfg.n_blocks):
+        for l in range(cfg.k):
+            a, r = m.context[b][l].numpy(), ctx[b][l]
+            assert np.abs(a - r).max() <= 1e-4 * max(np.abs(r).max(), 1e-9), (b, l)
