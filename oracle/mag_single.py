@@ -8,6 +8,8 @@ Restates, stage by stage and in fp32, on top of the C++ oracle primitives:
   DeltaRule::step / step_backward   core/src/delta_rule.rs:278-640 (identity feature map, L2 bias,
                                     no conv1d, default gate clamps = none)
   TitansLMM::step / step_backward   core/src/titans_lmm.rs:1314-1764 (same wrapper, plus eta)
+  HebbianRule::step / step_backward core/src/hebbian_rule.rs:91-300 (no L2 normalisation of k, q;
+                                    alpha gate only)
 Divergences followed as the CPU reference has them: the memory projections multiply by the
 bf16-rounded copy of W_{k,v,q}_mem (core/src/bf16.rs:54-115) while gradients go to the fp32
 master; the gate -> k/v gradient is included; M_0 = 0 (and S_0 = 0).
@@ -49,6 +51,8 @@ def init_params(d, vocab, seed=42, rule="delta"):
     if rule == "titans":
         p["w_eta"] = r(2 * d, 11, float(np.sqrt(1.0 / (2 * d))))
         p["b_eta"] = np.array([1.5], F32)
+    if rule == "hebbian":
+        del p["w_theta"], p["b_theta"]
     return p
 
 
@@ -69,13 +73,20 @@ def forward_backward(p, input_ids, target_ids, num_heads, window, rule="delta", 
 
     # memory branch: delta_rule.rs:286-304 / titans_lmm.rs:1333-1362
     wk16, wv16, wq16 = (orc.bf16_round(p[n]) for n in ("w_k_mem", "w_v_mem", "w_q_mem"))
-    k_mem, kn = orc.l2_normalize_rows(f(emb @ wk16.T))
+    hebbian = rule == "hebbian"
+    if hebbian:                                   # hebbian_rule.rs:111-118: raw projections
+        k_mem, q_mem, kn, qn = f(emb @ wk16.T), f(emb @ wq16.T), None, None
+    else:
+        k_mem, kn = orc.l2_normalize_rows(f(emb @ wk16.T))
+        q_mem, qn = orc.l2_normalize_rows(f(emb @ wq16.T))
     v_mem = f(emb @ wv16.T)
-    q_mem, qn = orc.l2_normalize_rows(f(emb @ wq16.T))
     alpha_pre, alpha = orc.gate(k_mem, v_mem, p["w_alpha"], float(p["b_alpha"][0]), 0)
-    theta_pre, theta = orc.gate(k_mem, v_mem, p["w_theta"], float(p["b_theta"][0]), 1)
+    if not hebbian:
+        theta_pre, theta = orc.gate(k_mem, v_mem, p["w_theta"], float(p["b_theta"][0]), 1)
     m0 = np.zeros(d * d, F32)
-    if rule == "titans":
+    if hebbian:
+        mem = orc.hebbian_forward(k_mem, v_mem, q_mem, alpha, m0)
+    elif rule == "titans":
         eta_pre, eta = orc.gate(k_mem, v_mem, p["w_eta"], float(p["b_eta"][0]), 0)
         mem = orc.titans_forward(k_mem, v_mem, q_mem, alpha, theta, eta, m0, m0)
     else:
@@ -103,15 +114,18 @@ def forward_backward(p, input_ids, target_ids, num_heads, window, rule="delta", 
     d_y = f(d_gated * attn_out * gate * (F32(1.0) - gate))
 
     # memory backward: delta_rule.rs:420-640 / titans_lmm.rs:1535-1764
-    if rule == "titans":
+    if hebbian:
+        b = orc.hebbian_backward(k_mem, v_mem, q_mem, alpha, mem["m_states"], d_y)
+    elif rule == "titans":
         b = orc.titans_backward(k_mem, v_mem, q_mem, alpha, theta, eta, mem["m_states"], mem["s_states"], d_y)
     else:
         b = orc.delta_backward(k_mem, v_mem, q_mem, alpha, theta, mem["m_states"], d_y)
     d_k, d_v, d_q = f(b["d_k"]), f(b["d_v"]), f(b["d_q"])
     concat = np.concatenate([k_mem, v_mem], axis=1)
     d_alpha_pre = f(b["d_alpha"] * alpha * (F32(1.0) - alpha))
-    d_theta_pre = f(b["d_theta"] * _sigmoid(theta_pre))           # softplus' = sigmoid; clamp mask = 1
-    gates = [("alpha", d_alpha_pre), ("theta", d_theta_pre)]
+    gates = [("alpha", d_alpha_pre)]
+    if not hebbian:
+        gates.append(("theta", f(b["d_theta"] * _sigmoid(theta_pre))))   # softplus' = sigmoid; clamp mask = 1
     if rule == "titans":
         gates.append(("eta", f(b["d_eta"] * eta * (F32(1.0) - eta))))
     for name, dpre in gates:
@@ -119,8 +133,8 @@ def forward_backward(p, input_ids, target_ids, num_heads, window, rule="delta", 
         g["b_" + name] = np.array([dpre.sum(dtype=F32)], F32)
         d_k += np.outer(dpre, p["w_" + name][:d]).astype(F32)       # gate -> k/v gradient
         d_v += np.outer(dpre, p["w_" + name][d:]).astype(F32)
-    d_k_raw = orc.l2_normalize_rows_backward(d_k, k_mem, kn)
-    d_q_raw = orc.l2_normalize_rows_backward(d_q, q_mem, qn)
+    d_k_raw = d_k if hebbian else orc.l2_normalize_rows_backward(d_k, k_mem, kn)
+    d_q_raw = d_q if hebbian else orc.l2_normalize_rows_backward(d_q, q_mem, qn)
     g["w_k_mem"], g["w_v_mem"], g["w_q_mem"] = f(d_k_raw.T @ emb), f(d_v.T @ emb), f(d_q_raw.T @ emb)
     d_emb = f(d_k_raw @ wk16 + d_v @ wv16 + d_q_raw @ wq16)
 

@@ -73,12 +73,13 @@ def mag_single_loss64(p, input_ids, target_ids, num_heads, window, rule="delta")
     emb = P["w_embed"][ids]
     attn = swa_forward64(emb @ P["w_q"].T, emb @ P["w_k"].T, emb @ P["w_v"].T, num_heads, hd, window)
     km, vm, qm = emb @ P["w_k_mem"].T, emb @ P["w_v_mem"].T, emb @ P["w_q_mem"].T
-    km = km / np.maximum(np.linalg.norm(km, axis=1, keepdims=True), 1e-8)
-    qm = qm / np.maximum(np.linalg.norm(qm, axis=1, keepdims=True), 1e-8)
+    if rule != "hebbian":                     # the Hebbian wrapper does not normalise k, q
+        km = km / np.maximum(np.linalg.norm(km, axis=1, keepdims=True), 1e-8)
+        qm = qm / np.maximum(np.linalg.norm(qm, axis=1, keepdims=True), 1e-8)
     c = np.concatenate([km, vm], axis=1)
     sig = lambda x: 1.0 / (1.0 + np.exp(-x))
     alpha = sig(c @ P["w_alpha"] + P["b_alpha"][0])
-    theta = np.log1p(np.exp(c @ P["w_theta"] + P["b_theta"][0]))
+    theta = np.log1p(np.exp(c @ P["w_theta"] + P["b_theta"][0])) if rule != "hebbian" else None
     eta = sig(c @ P["w_eta"] + P["b_eta"][0]) if rule == "titans" else None
     z = np.zeros((d, d))
     y = rule_forward64(rule, km, vm, qm, alpha, theta, eta, z, z if rule == "titans" else None)[0]

@@ -391,7 +391,7 @@ def test_oracle_reproduces_the_committed_small_vectors():
         assert a.shape == b.shape and np.allclose(a, b, rtol=1e-5, atol=1e-7), key
 
 
-@pytest.mark.parametrize("rule", ["delta", "titans"])
+@pytest.mark.parametrize("rule", ["delta", "titans", "hebbian"])
 def test_mag_single_model_gradients_match_float64_finite_differences(orc, rule, monkeypatch):
     """The model-level oracle (oracle/mag_single.py: core/src/mag.rs mag_forward/mag_backward with
     the Delta / Titans rule wrapper) against an independent float64 statement of the loss,
@@ -405,7 +405,9 @@ def test_mag_single_model_gradients_match_float64_finite_differences(orc, rule, 
     p = M.init_params(d, vocab, seed=7, rule=rule)
     for n in ("w_k_mem", "w_v_mem", "w_q_mem", "w_o"):     # make the memory branch matter
         p[n] = (p[n] * 3.0).astype(np.float32)
-    p["b_theta"][0], p["b_alpha"][0] = 0.3, -1.0
+    p["b_alpha"][0] = -1.0
+    if rule != "hebbian":
+        p["b_theta"][0] = 0.3
     ids = orc.rng_tokens(11, vocab, s + 1)
     x, t = ids[:-1], ids[1:]
     loss, g = M.forward_backward(p, x, t, nh, w, rule)
