@@ -38,6 +38,7 @@ const char* nlh_last_error(void);       /* text of the last recorded error ("" i
 void nlh_clear_status(void);
 int32_t nlh_workspace_reserve(int64_t bytes); /* pre-grow scratch (e.g. before graph capture) */
 void nlh_workspace_release(void);       /* free the scratch of the current device */
+int64_t nlh_workspace_bytes(void);      /* scratch bytes held on the current device, all slots */
 /* Scratch slot (0..7, default 0) used by the following calls. Launches that may overlap on the
  * GPU (different streams) must use different slots; each slot grows on its own. */
 int32_t nlh_set_workspace_slot(int32_t slot);
@@ -467,7 +468,8 @@ int32_t nlh_opaque_backward(int32_t key, int32_t n_out, const float* const* d_ou
  * so the call never reaches cudaMalloc/cudaFree or the workspace. Limit:
  * batch_size*d*d <= NLH_NOALLOC_MAX_STATE_FLOATS, otherwise NLH_ERR_INVALID_ARG. All calls
  * on a device share the array: calls that overlap on the GPU race; issue them in order on
- * one stream. The first call on each device resolves the array's device address and should
+ * one stream. Every pointer is required: unlike titans_backward_f32_cuda this entry has no
+ * M-only mode, s_states == NULL is rejected with NLH_ERR_INVALID_ARG. The first call on each device resolves the array's device address and should
  * be made while the stream is not being captured. */
 #define NLH_NOALLOC_MAX_STATE_FLOATS 262144
 #define NLH_NOALLOC_SCRATCH_BYTES (2 * NLH_NOALLOC_MAX_STATE_FLOATS * 4)

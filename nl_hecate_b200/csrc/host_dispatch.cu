@@ -44,6 +44,9 @@ static int rule_forward(const char* where, int rule, const float* k, const float
 {
     if (seq <= 0 || d <= 0 || !k || !v || !q || !alpha || !m_initial || !m_states || !y)
         return hd_fail(where, NLH_ERR_INVALID_ARG, "bad dimensions or NULL pointer");
+    // per-rule required inputs: every rule but Hebbian reads theta, Titans also eta and s_initial
+    if ((rule != 2 && !theta) || (rule == 1 && (!eta || !s_initial)))
+        return hd_fail(where, NLH_ERR_INVALID_ARG, "NULL gate or initial-state pointer for this rule");
     cudaStream_t st = current_stream();
     Staging sg;
     const long long sd = seq * d, dd = d * d, tr = (seq + 1) * dd;
@@ -78,6 +81,9 @@ static int rule_backward(const char* where, int rule, const float* k, const floa
     if (seq <= 0 || d <= 0 || !k || !v || !q || !alpha || !m_states || !d_y || !d_k || !d_v || !d_q ||
         !d_alpha || !d_m_initial)
         return hd_fail(where, NLH_ERR_INVALID_ARG, "bad dimensions or NULL pointer");
+    // per-rule required gates and gate gradients (Hebbian has neither theta nor eta)
+    if ((rule != 2 && (!theta || !d_theta)) || (rule == 1 && (!eta || !d_eta || !s_states || !d_s_initial)))
+        return hd_fail(where, NLH_ERR_INVALID_ARG, "NULL gate, gate-gradient or state pointer for this rule");
     cudaStream_t st = current_stream();
     Staging sg;
     const long long sd = seq * d, dd = d * d, tr = (seq + 1) * dd;

@@ -82,6 +82,14 @@ void nlh_workspace_release(void)
         s = nlh::WsSlot{};
     }
 }
+int64_t nlh_workspace_bytes(void)
+{
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= nlh::MAX_DEVICES) return -1;
+    int64_t total = 0;
+    for (int i = 0; i < nlh::WS_SLOTS; i++) total += (int64_t)nlh::g_ws[dev][i].bytes;
+    return total;
+}
 int32_t nlh_set_workspace_slot(int32_t slot)
 {
     if (slot < 0 || slot >= nlh::WS_SLOTS) return NLH_ERR_INVALID_ARG;

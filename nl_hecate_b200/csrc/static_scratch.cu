@@ -24,6 +24,8 @@
 //     independent. Two calls that overlap on the GPU (different streams, or
 //     different host threads with different streams) race on the array and
 //     give wrong results: serialise them.
+//   * s_states must be given: the M-only form of titans_backward_f32_cuda
+//     (s_states == NULL) is not available here and is rejected on the host;
 //   * the first call on each device looks up the device address of the array
 //     (cudaGetSymbolAddress). Make that first call while the stream is not
 //     being captured; later calls do no set-up work.
@@ -85,6 +87,17 @@ extern "C" int32_t nlh_titans_backward_noalloc(
         return NLH_ERR_INVALID_ARG;
     }
     if (batch_size == 0) return NLH_OK;
+    // Unlike titans_backward_f32_cuda this entry always reads the stored momentum trajectory:
+    // the kernel behind it has no M-only mode, so s_states must not be NULL. Every other pointer
+    // is dereferenced on the device as well; reject NULL here instead of faulting there.
+    if (!k_mem || !v_mem || !q_mem || !alpha || !theta || !eta || !m_states || !s_states || !d_y ||
+        !d_k_mem || !d_v_mem || !d_q_mem || !d_alpha || !d_theta || !d_eta || !d_m_initial ||
+        !d_s_initial) {
+        record_status(NLH_ERR_INVALID_ARG, "nlh_titans_backward_noalloc",
+                      "NULL pointer argument (this entry needs every buffer, including the stored "
+                      "s_states trajectory)");
+        return NLH_ERR_INVALID_ARG;
+    }
     const size_t need = (size_t)batch_size * (size_t)d * (size_t)d;
     if (need > kMaxStateFloats) {
         char msg[160];

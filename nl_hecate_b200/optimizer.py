@@ -56,6 +56,11 @@ class FlatAdamW:
         self._partial = torch.empty(148 * 8, dtype=torch.float32, device=dev)
         self.norm = torch.zeros(1, dtype=torch.float32, device=dev)
         self.scale = torch.ones(1, dtype=torch.float32, device=dev)
+        # recorded after the stream-ordered upload of the pinned table in launch(); prepare()
+        # waits on it before it rewrites the table, so a host that runs ahead of the GPU cannot
+        # replace step t's descriptors before step t's copy has read them
+        self._uploaded = torch.cuda.Event() if dev.type == "cuda" else None
+        self._upload_pending = False
 
     def view(self, arena: torch.Tensor, i: int) -> torch.Tensor:
         o, n = self.slices[i]
@@ -64,7 +69,11 @@ class FlatAdamW:
     def prepare(self, steps, active=None, lr_scale=1.0):
         """Host part of a step: fill the per-tensor descriptor table (bias corrections from each
         tensor's own 1-based step count, activity, clamp, learning-rate scale) in pinned memory.
-        The device reads it in launch(); do not call prepare() again before that copy has run."""
+        The device reads it in launch(); a second prepare() first waits until the previous
+        launch()'s upload of the table has completed."""
+        if self._upload_pending:
+            self._uploaded.synchronize()
+            self._upload_pending = False
         nt = len(self.sizes)
         active = [True] * nt if active is None else active
         for i in range(nt):
@@ -85,6 +94,9 @@ class FlatAdamW:
         global-norm clip scale, multi-tensor AdamW. Returns the device scalar with the pre-clip
         gradient norm (valid only when max_grad_norm > 0)."""
         self._desc_dev.copy_(self._desc_pinned, non_blocking=True)
+        if self._uploaded is not None and not torch.cuda.is_current_stream_capturing():
+            self._uploaded.record()
+            self._upload_pending = True
         scale_ptr = None
         if max_grad_norm > 0.0:
             call("nlh_arena_grad_norm_clip", g=self.g, n=self.arena_len,
