@@ -268,6 +268,9 @@ int32_t nlh_swa_backward_packed(const uint16_t* qkv, const uint16_t* out, const 
  * synchronously reads a device flag that the tcgen05 kernel sets if one of its bounded mbarrier
  * waits ran out (0 = never, 1 = a wait expired and results are invalid, -1 = read failed). */
 #define NLH_OPT_SWA_TCGEN05 1
+/* NLH_OPT_CHUNK_MATRIX (default 1): frozen-M0 chunkwise Titans / Delta entries at head_dim 64 and
+ * chunk sizes 16..64 run in chunk-parallel matrix form; 0 selects the per-token kernels. */
+#define NLH_OPT_CHUNK_MATRIX 2
 int32_t nlh_set_option(int32_t option, int32_t value);
 int32_t nlh_swa_tc_timeout_flag(void);
 

@@ -6,6 +6,7 @@
 // dimension and options allow it, the generic-d kernels otherwise.
 #include "memory_generic.cuh"
 #include "memory_exact_bwd.cuh"
+#include "chunk_mm.cuh"
 #include "../../include/nlh_ffi.h"
 
 namespace nlh {
@@ -66,6 +67,8 @@ static int run_forward(int rule, FwdArgs a, const char* where)
         return NLH_ERR_INVALID_ARG;
     }
     cudaStream_t st = current_stream();
+    if (option_value(NLH_OPT_CHUNK_MATRIX) && cmm::forward(rule, a, st))
+        return check_launch(where) ? NLH_OK : NLH_ERR_CUDA;
     if (fast_forward(rule, a, st)) return check_launch(where) ? NLH_OK : NLH_ERR_CUDA;
     if (rule == RULE_TITANS && a.s_out == nullptr) {
         record_status(NLH_ERR_UNSUPPORTED, where,
@@ -98,6 +101,8 @@ static int run_backward(int rule, BwdArgs a, const char* where)
         return NLH_ERR_INVALID_ARG;
     }
     cudaStream_t st = current_stream();
+    if (option_value(NLH_OPT_CHUNK_MATRIX) && cmm::backward(rule, a, st))
+        return check_launch(where) ? NLH_OK : NLH_ERR_CUDA;
     if (fast_backward(rule, a, st)) return check_launch(where) ? NLH_OK : NLH_ERR_CUDA;
     if (rule == RULE_TITANS && a.s_traj == nullptr) {
         record_status(NLH_ERR_UNSUPPORTED, where,

@@ -24,6 +24,9 @@ cudaStream_t current_stream();
 // process instead: core/kernels/titans_forward.cu:67-81).
 void record_status(int status, const char* where, const char* detail);
 
+// Value of a library option (nlh_set_option); unknown options read 0.
+int option_value(int option);
+
 // Grow-only per-device scratch. Returned pointer is 256-byte aligned and is
 // valid until the next call that asks for more bytes on the same device.
 // Returns nullptr (and records NLH_ERR_WORKSPACE) on failure.

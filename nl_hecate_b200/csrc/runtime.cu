@@ -27,6 +27,11 @@ static WsSlot g_ws[MAX_DEVICES][WS_SLOTS] = {};
 
 cudaStream_t current_stream() { return g_stream; }
 
+// Library options (nlh_set_option); index = option id, all default to 1 (enabled).
+constexpr int MAX_OPTIONS = 8;
+static int g_options[MAX_OPTIONS] = {1, 1, 1, 1, 1, 1, 1, 1};
+int option_value(int option) { return (option >= 0 && option < MAX_OPTIONS) ? g_options[option] : 0; }
+
 void record_status(int status, const char* where, const char* detail)
 {
     std::lock_guard<std::mutex> lk(g_mu);
@@ -94,6 +99,12 @@ int32_t nlh_set_workspace_slot(int32_t slot)
 {
     if (slot < 0 || slot >= nlh::WS_SLOTS) return NLH_ERR_INVALID_ARG;
     nlh::g_ws_slot = slot;
+    return NLH_OK;
+}
+int32_t nlh_set_option(int32_t option, int32_t value)
+{
+    if (option < 1 || option >= nlh::MAX_OPTIONS) return NLH_ERR_INVALID_ARG;
+    nlh::g_options[option] = value ? 1 : 0;
     return NLH_OK;
 }
 int32_t nlh_abi_version(void) { return 1; }

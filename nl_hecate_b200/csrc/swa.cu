@@ -583,7 +583,7 @@ __global__ void __launch_bounds__(SWA_THREADS) swa_bwd_dq_kernel(
 }
 
 // ───────────────────────────── host side ──────────────────────────────────
-static int g_swa_use_tcgen05 = 1;   // nlh_set_option(NLH_OPT_SWA_TCGEN05, 0) switches the head_dim-64 forward
+// nlh_set_option(NLH_OPT_SWA_TCGEN05, 0) switches the head_dim-64 forward
 template <int HD>
 static size_t swa_fwd_smem() { return (size_t)(SWA_BM + 4 * SWA_BN) * (HD + SWA_PAD) * sizeof(bf16); }
 template <int HD>
@@ -613,7 +613,7 @@ static int swa_forward_impl(const bf16* q, const bf16* k, const bf16* v, bf16* o
     if (rs_in == 0) rs_in = H * HD;     // dense [B, S, H*hd] rows unless the caller packs q|k|v
     if (rs_o == 0) rs_o = H * HD;
     const bool aligned = ((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15) == 0);
-    if (HD == 64 && g_swa_use_tcgen05 && aligned) {
+    if (HD == 64 && option_value(NLH_OPT_SWA_TCGEN05) && aligned) {
         // tcgen05 / TMEM kernel: 128 query rows per CTA
         cudaFuncSetAttribute(tc::swa_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM_BYTES);
         dim3 grid((S + tc::BM - 1) / tc::BM, B * H);
@@ -683,12 +683,6 @@ static int swa_backward_impl(const bf16* q, const bf16* k, const bf16* v, const 
 using namespace nlh;
 
 extern "C" {
-
-int32_t nlh_set_option(int32_t option, int32_t value)
-{
-    if (option == NLH_OPT_SWA_TCGEN05) { g_swa_use_tcgen05 = value ? 1 : 0; return NLH_OK; }
-    return NLH_ERR_INVALID_ARG;
-}
 
 int32_t nlh_swa_tc_timeout_flag(void)
 {

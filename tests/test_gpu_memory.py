@@ -110,7 +110,8 @@ def test_titans_clip_and_projection(D, orc, d):
 @pytest.mark.parametrize("rule", ["titans", "delta"])
 @pytest.mark.parametrize("d,s,chunk,n", [(8, 12, 4, 2), (16, 10, 3, 1), (32, 24, 8, 2),
                                          (64, 64, 64, 2), (64, 50, 16, 2), (64, 9, 1, 1),
-                                         (64, 130, 64, 1), (64, 8, 512, 1)])
+                                         (64, 130, 64, 1), (64, 8, 512, 1), (64, 100, 24, 3),
+                                         (64, 37, 33, 2), (64, 200, 48, 2), (64, 17, 17, 1)])
 def test_chunkwise(D, orc, rule, d, s, chunk, n):
     p = make_problem(orc, n, s, d, 900 + d + s + chunk, "rand")
     w = oracle_chunkwise(orc, rule, p, chunk)
@@ -131,6 +132,27 @@ def test_chunkwise(D, orc, rule, d, s, chunk, n):
     assert rel_err(_np(y), w["y"]) <= REL
     assert rel_err(_np(mc), w["m_chunk_states"]) <= REL
     _check_bwd(g, w, keys, tol_abs=1e-3)
+
+
+def test_chunk_matrix_form_matches_per_token_kernels(D, orc):
+    """Chunk sizes 16..64 at head_dim 64 run the chunk-parallel matrix form (contractions over the
+    chunk instead of a token loop); option NLH_OPT_CHUNK_MATRIX = 0 selects the per-token kernels.
+    Both must agree with each other (they are compared with the oracle in test_chunkwise)."""
+    p = make_problem(orc, 3, 150, 64, 4100, "rand")
+    t = to_dev(p)
+    res = []
+    for on in (1, 0):
+        D.call("nlh_set_option", option=2, value=on)
+        try:
+            mc, sc, y = D.titans_chunkwise_forward_dd(t["k"], t["v"], t["q"], t["alpha"], t["theta"],
+                                                      t["eta"], t["m0"], t["s0"], 40)
+            g = D.titans_chunkwise_backward_dd(t["k"], t["v"], t["q"], t["alpha"], t["theta"],
+                                               t["eta"], mc, sc, t["dy"], 40)
+        finally:
+            D.call("nlh_set_option", option=2, value=1)
+        res.append(dict(g, y=y, mc=mc, sc=sc))
+    for key in res[0]:
+        assert rel_err(_np(res[0][key]), _np(res[1][key])) <= REL, key
 
 
 def test_chunk1_matches_per_token_kernel(D, orc):
