@@ -189,7 +189,8 @@ class TitansPair:
             states = 2 * n * (s // self.chunk + 1) * d * d * 4
         else:
             states = 2 * n * (s + 1) * d * d * 4
-        return ("fast_bwd_kernel<64,TITANS," + ("frozen>" if self.chunk else "exact>"),
+        return ("cmm::chunk_mm_bwd_kernel<TITANS> (frozen-M0 backward, chunk-parallel matrix form)" if self.chunk
+                else "fast_bwd_kernel<64,TITANS,exact>",
                 lambda: self.bwd(self.dev), stream4 + out3 + gates + states, "hbm")
 
     def cpu_sample(self, oracle, threads, budget_s=12.0):

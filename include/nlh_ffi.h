@@ -448,11 +448,17 @@ int32_t nlh_dgd_backward_dispatch(const float* k_mem, const float* v_mem, const 
  * (core/src/tape.rs:100-134). nlh_opaque_backward is the C form of OpaqueBackwardFn
  * (tape.rs:141-145): HOST pointers, d_outputs[i] of out_len[i] floats, saved[i] of saved_len[i]
  * floats (saved[0] is the float-encoded meta buffer), d_inputs[i] of in_len[i] floats
- * caller-allocated and overwritten. GPU adapters exist for NLH_KEY_DGD
- * (opaque_adapters.rs:1680-1725), NLH_KEY_SWA (:952-997; q,k,v are rounded to bf16 on the device,
- * attn_weights is not read) and the frozen reads NLH_KEY_FROZEN_{DELTA_RULE,TITANS_LMM,
- * HEBBIAN_RULE} with the identity feature map (:999-1069); every other key returns
- * NLH_ERR_UNSUPPORTED. The call synchronises its stream before returning. */
+ * caller-allocated and overwritten. GPU adapters exist for
+ *   NLH_KEY_{DELTA_RULE,TITANS_LMM,HEBBIAN_RULE} — a whole rule block (opaque_adapters.rs:306-381,
+ *     :402-590, :593-628): saved = [meta, level_params_flat, embedded, cache fields in the order
+ *     record_on_tape stores them (:1180-1385)], d_inputs = [d_embedded, d_level_params_flat in the
+ *     order of level_params_to_flat (:93-113)]; identity feature map, L2 bias, EMA / no momentum,
+ *     linear memory, no conv1d (anything else: NLH_ERR_UNSUPPORTED);
+ *   NLH_KEY_DGD (opaque_adapters.rs:1680-1725);
+ *   NLH_KEY_SWA (:952-997; q,k,v are rounded to bf16 on the device, attn_weights is not read);
+ *   the frozen reads NLH_KEY_FROZEN_{DELTA_RULE,TITANS_LMM,HEBBIAN_RULE} with the identity feature
+ *     map (:999-1069).
+ * Every other key returns NLH_ERR_UNSUPPORTED. The call synchronises its stream before returning. */
 #define NLH_KEY_DELTA_RULE 0
 #define NLH_KEY_TITANS_LMM 1
 #define NLH_KEY_HEBBIAN_RULE 2

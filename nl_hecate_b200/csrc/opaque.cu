@@ -9,7 +9,8 @@
 //   Frozen{Delta,Titans,Hebbian} read
 //                       opaque_adapters.rs:999-1069   saved [meta(seq,d), M]           d_q[t] = M^T d_y[t]
 // The rule-level adapters (DeltaRule, TitansLMM, HebbianRule: projections, gates and the flat
-// parameter vector inside one block) and every key off the path return NLH_ERR_UNSUPPORTED.
+// parameter vector inside one block) live in opaque_rules.cu; every key off the path returns
+// NLH_ERR_UNSUPPORTED.
 // Staging buffers are allocated and freed per call, like the reference's host-slice dispatch
 // functions (core/src/dispatch.rs:330-1213).
 #include <cuda_bf16.h>
@@ -38,6 +39,11 @@ __global__ void frozen_read_bwd_kernel(const float* __restrict__ m, const float*
     }
 }
 
+// opaque_rules.cu
+int opaque_rule_backward(int rule, int n_out, const float* const* d_outputs, const int64_t* out_len,
+                         int n_saved, const float* const* saved, const int64_t* saved_len, int n_in,
+                         float* const* d_inputs, const int64_t* in_len);
+
 static int fail(int code, const char* detail)
 {
     record_status(code, "nlh_opaque_backward", detail);
@@ -59,6 +65,10 @@ extern "C" int32_t nlh_opaque_backward(int32_t key, int32_t n_out, const float* 
     const float* meta = saved[0];
     Staging sg;
 
+    if (key == NLH_KEY_DELTA_RULE || key == NLH_KEY_TITANS_LMM || key == NLH_KEY_HEBBIAN_RULE) {
+        const int rule = key == NLH_KEY_DELTA_RULE ? 0 : (key == NLH_KEY_TITANS_LMM ? 1 : 2);
+        return opaque_rule_backward(rule, n_out, d_outputs, out_len, n_saved, saved, saved_len, n_in, d_inputs, in_len);
+    }
     if (key == NLH_KEY_DGD) {
         const long long seq = (long long)meta[0], d = (long long)meta[1];
         const float clip = saved_len[0] > 2 ? meta[2] : 0.0f;
@@ -125,7 +135,7 @@ extern "C" int32_t nlh_opaque_backward(int32_t key, int32_t n_out, const float* 
         if (!check_launch("nlh_opaque_backward")) return NLH_ERR_CUDA;
         if (!download(d_inputs[0], dq, n, st)) return fail(NLH_ERR_CUDA, "frozen read: download failed");
     } else {
-        return fail(NLH_ERR_UNSUPPORTED, "no GPU adapter for this key (rule-level adapters and keys off the path)");
+        return fail(NLH_ERR_UNSUPPORTED, "no GPU adapter for this key (it is off the path)");
     }
     if (cudaStreamSynchronize(st) != cudaSuccess) return fail(NLH_ERR_CUDA, "stream synchronisation failed");
     return NLH_OK;

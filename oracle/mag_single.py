@@ -22,6 +22,7 @@ from __future__ import annotations
 import numpy as np
 
 import oracle as orc
+from oracle import rule_level
 
 F32 = np.float32
 
@@ -71,27 +72,13 @@ def forward_backward(p, input_ids, target_ids, num_heads, window, rule="delta", 
     swa = orc.swa_forward(q, k, v, num_heads, hd, window)
     attn_out = swa["out"]
 
-    # memory branch: delta_rule.rs:286-304 / titans_lmm.rs:1333-1362
-    wk16, wv16, wq16 = (orc.bf16_round(p[n]) for n in ("w_k_mem", "w_v_mem", "w_q_mem"))
-    hebbian = rule == "hebbian"
-    if hebbian:                                   # hebbian_rule.rs:111-118: raw projections
-        k_mem, q_mem, kn, qn = f(emb @ wk16.T), f(emb @ wq16.T), None, None
-    else:
-        k_mem, kn = orc.l2_normalize_rows(f(emb @ wk16.T))
-        q_mem, qn = orc.l2_normalize_rows(f(emb @ wq16.T))
-    v_mem = f(emb @ wv16.T)
-    alpha_pre, alpha = orc.gate(k_mem, v_mem, p["w_alpha"], float(p["b_alpha"][0]), 0)
-    if not hebbian:
-        theta_pre, theta = orc.gate(k_mem, v_mem, p["w_theta"], float(p["b_theta"][0]), 1)
-    m0 = np.zeros(d * d, F32)
-    if hebbian:
-        mem = orc.hebbian_forward(k_mem, v_mem, q_mem, alpha, m0)
-    elif rule == "titans":
-        eta_pre, eta = orc.gate(k_mem, v_mem, p["w_eta"], float(p["b_eta"][0]), 0)
-        mem = orc.titans_forward(k_mem, v_mem, q_mem, alpha, theta, eta, m0, m0)
-    else:
-        mem = orc.delta_forward(k_mem, v_mem, q_mem, alpha, theta, m0)
-    y = mem["y"]
+    # memory branch: the rule block as the tape records it (oracle/rule_level.py restates
+    # delta_rule.rs:286-304 / titans_lmm.rs:1333-1362 / hebbian_rule.rs:111-118)
+    z2, z1 = np.zeros(2 * d, F32), np.zeros(1, F32)
+    flat = np.concatenate([p["w_k_mem"].ravel(), p["w_v_mem"].ravel(), p["w_q_mem"].ravel(),
+                           p["w_alpha"], p["b_alpha"], p.get("w_theta", z2), p.get("b_theta", z1),
+                           p.get("w_eta", z2), p.get("b_eta", z1)]).astype(F32)
+    y, saved = rule_level.record(rule, flat, emb)
 
     # mag.rs:158-181 gating, output projection, unembedding, loss
     gate = _sigmoid(y)
@@ -113,30 +100,12 @@ def forward_backward(p, input_ids, target_ids, num_heads, window, rule="delta", 
     d_attn = f(d_gated * gate)
     d_y = f(d_gated * attn_out * gate * (F32(1.0) - gate))
 
-    # memory backward: delta_rule.rs:420-640 / titans_lmm.rs:1535-1764
-    if hebbian:
-        b = orc.hebbian_backward(k_mem, v_mem, q_mem, alpha, mem["m_states"], d_y)
-    elif rule == "titans":
-        b = orc.titans_backward(k_mem, v_mem, q_mem, alpha, theta, eta, mem["m_states"], mem["s_states"], d_y)
-    else:
-        b = orc.delta_backward(k_mem, v_mem, q_mem, alpha, theta, mem["m_states"], d_y)
-    d_k, d_v, d_q = f(b["d_k"]), f(b["d_v"]), f(b["d_q"])
-    concat = np.concatenate([k_mem, v_mem], axis=1)
-    d_alpha_pre = f(b["d_alpha"] * alpha * (F32(1.0) - alpha))
-    gates = [("alpha", d_alpha_pre)]
-    if not hebbian:
-        gates.append(("theta", f(b["d_theta"] * _sigmoid(theta_pre))))   # softplus' = sigmoid; clamp mask = 1
-    if rule == "titans":
-        gates.append(("eta", f(b["d_eta"] * eta * (F32(1.0) - eta))))
-    for name, dpre in gates:
-        g["w_" + name] = f(dpre @ concat)
-        g["b_" + name] = np.array([dpre.sum(dtype=F32)], F32)
-        d_k += np.outer(dpre, p["w_" + name][:d]).astype(F32)       # gate -> k/v gradient
-        d_v += np.outer(dpre, p["w_" + name][d:]).astype(F32)
-    d_k_raw = d_k if hebbian else orc.l2_normalize_rows_backward(d_k, k_mem, kn)
-    d_q_raw = d_q if hebbian else orc.l2_normalize_rows_backward(d_q, q_mem, qn)
-    g["w_k_mem"], g["w_v_mem"], g["w_q_mem"] = f(d_k_raw.T @ emb), f(d_v.T @ emb), f(d_q_raw.T @ emb)
-    d_emb = f(d_k_raw @ wk16 + d_v @ wv16 + d_q_raw @ wq16)
+    # memory backward: delta_rule.rs:420-640 / titans_lmm.rs:1535-1764 through the adapter
+    d_emb, gflat = rule_level.opaque_backward(rule, d_y, saved)
+    d_emb = f(d_emb.reshape(s, d))
+    for name, val in rule_level.split_flat(gflat, d).items():
+        if name in p:
+            g[name] = val.reshape(p[name].shape)
 
     # attention backward: mag.rs:341-372
     sb = orc.swa_backward(q, k, v, swa["attn_weights"], d_attn, num_heads, hd, window)

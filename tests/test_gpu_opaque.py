@@ -56,10 +56,51 @@ def test_frozen_read_adapter(D, orc, key):
     assert rel_err(got, want) <= 1e-5
 
 
+@pytest.mark.parametrize("rule,key", [("delta", "DeltaRule"), ("titans", "TitansLMM"), ("hebbian", "HebbianRule")])
+@pytest.mark.parametrize("d,s,pad", [(64, 40, 0), (32, 17, 0), (16, 9, 5), (128, 12, 0)])
+def test_rule_level_adapters(D, orc, rule, key, d, s, pad):
+    """A whole rule block (projections, L2 norm, gates, inner loop) behind one key: saved buffers in
+    the order record_on_tape stores them, d_embedded and the flat parameter gradient out
+    (core/src/opaque_adapters.rs:306-628), against the rule-level oracle."""
+    from oracle import rule_level as RL
+    flat = RL.make_flat(d, 7000 + d + s)
+    flat = np.concatenate([flat, np.zeros(pad, np.float32)])          # trailing optional fields
+    emb = orc.rand_buf(s * d, 7100 + d, 1.0).reshape(s, d)
+    d_y = orc.rand_buf(s * d, 7200 + d, 1.0).reshape(s, d)
+    y, saved = RL.record(rule, flat, emb)
+    want_emb, want_flat = RL.opaque_backward(rule, d_y, saved, flat.size)
+    got_emb, got_flat = D.opaque_backward(key, [d_y], saved, [s * d, flat.size])
+    assert rel_err(got_emb, want_emb) <= 1e-4, rel_err(got_emb, want_emb)
+    n = RL.flat_len(d)
+    parts = RL.split_flat(want_flat, d)
+    got_parts = RL.split_flat(got_flat, d)
+    for name in parts:
+        if np.abs(parts[name]).max() == 0.0:
+            assert np.abs(got_parts[name]).max() == 0.0, name          # fields the rule does not have
+        else:
+            assert rel_err(got_parts[name], parts[name]) <= 1e-4, (name, rel_err(got_parts[name], parts[name]))
+    assert np.all(got_flat[n:] == 0.0)
+
+
+def test_rule_level_adapter_rejects_what_is_off_the_path(D, orc):
+    from oracle import rule_level as RL
+    d, s = 16, 6
+    flat = RL.make_flat(d, 7300)
+    emb = orc.rand_buf(s * d, 7301, 1.0).reshape(s, d)
+    y, saved = RL.record("titans", flat, emb)
+    for idx, val in ((7, 1.0), (12, 2.0), (2, 1.0), (15, 4.0)):     # feature map, MLP memory, L1 bias, conv1d
+        bad = [a.copy() for a in saved]
+        bad[0][idx] = val
+        with pytest.raises(RuntimeError, match="on the path"):
+            D.opaque_backward("TitansLMM", [emb], bad, [s * d, flat.size])
+
+
 def test_unsupported_keys_and_bad_lengths_are_rejected(D):
     meta = np.array([4, 8], dtype=np.float32)
     z = np.zeros(32, dtype=np.float32)
-    with pytest.raises(RuntimeError):        # rule-level adapter: no GPU form
+    with pytest.raises(RuntimeError):        # a key off the path: no GPU form
+        D.opaque_backward(3, [z], [meta, z], [32])       # OpaqueKey::Moneta
+    with pytest.raises(RuntimeError):        # rule-level adapter with too few saved buffers
         D.opaque_backward("TitansLMM", [z], [meta, z], [32])
     with pytest.raises(RuntimeError):        # d_y length does not match meta
         D.opaque_backward("FrozenDeltaRule", [z[:5]], [meta, np.zeros(64, np.float32)], [32])
