@@ -11,7 +11,10 @@ workload over one batch of seeded synthetic input:
   titans_exact      same shapes, exact per-token rule (full-trajectory drop-in pair)
   swa               SWA forward+backward pair: bf16, batch 8 x 16 heads, head_dim 64,
                     seq 8192, causal window 512
+  titans_level0     exact Titans pair at the stacked model's level-0 shape (512 problems of 512
+                    tokens, M-only trajectory)
   adamw             flat-arena clip + AdamW step over 25.2 M fp32 parameters
+--small shrinks the kernel-pair workloads to a profiler-friendly problem count.
 
 `value` is device-timed (CUDA events on the launching stream, max over ranks) with
 inputs resident in HBM; `e2e` goes through the host-slice API: pinned host buffers,
@@ -518,11 +521,53 @@ class StackedModelStep:
                                f"4 CMS levels of Titans LMM, AdamW; 4 blocks), {dt:.1f} s incl. input generation")
 
 
-def make_workload(name, world=1):
+class TitansLevel0(TitansPair):
+    """Exact Titans pair as level 0 of the stacked model runs it: 512 problems (64 sequences x 8
+    heads) of 512 tokens, M-only trajectory (s_states = NULL), gates as the model's biases give."""
+    B, H, S, D = 64, 8, 512, 64
+
+    def __init__(self):
+        super().__init__(0)
+        self.name = "titans_level0"
+
+    def describe(self):
+        d = super().describe()
+        d["workload"] = (f"Titans LMM exact pair at the stacked model's level-0 shape: batch {self.B} x heads "
+                         f"{self.H}, head_dim {self.D}, seq {self.S}, fp32, M-only trajectory")
+        return d
+
+    def host_inputs(self, n=None, seed=1234):
+        h = super().host_inputs(n, seed)
+        g = np.random.Generator(np.random.Philox(seed + 7))
+        sig = lambda x: (1.0 / (1.0 + np.exp(-x))).astype(np.float32)
+        sh = h["alpha"].shape
+        h["alpha"] = sig(g.standard_normal(sh) + 3.0)
+        h["theta"] = np.log1p(np.exp(g.standard_normal(sh) - 4.6)).astype(np.float32)
+        h["eta"] = sig(g.standard_normal(sh) + 1.5)
+        return h
+
+    def setup(self, torch, dispatch):
+        super().setup(torch, dispatch)
+        self.sstate = None                      # s_states = NULL: M-only trajectory
+
+    def dominant(self):
+        n, s, d = self.N, self.S, self.D
+        streams = 7 * n * s * d * 4 + 6 * n * s * 4
+        return ("titans_exact_bwd_kernel<64> (exact Titans backward, M-only trajectory)",
+                lambda: self.bwd(self.dev), streams + n * (s + 1) * d * d * 4, "hbm")
+
+
+def make_workload(name, world=1, small=False):
+    """small: reduced problem counts of the same kernels, sized for profiler captures (inputs still
+    larger than L2, a few hundred MB on the device)."""
+    if small:
+        TitansPair.B, SwaPair.B, TitansLevel0.B = 4, 1, 37
     if name == "titans_chunkwise":
         return TitansPair(64)
     if name == "titans_exact":
         return TitansPair(0)
+    if name == "titans_level0":
+        return TitansLevel0()
     if name == "swa":
         return SwaPair()
     if name == "adamw":
@@ -574,6 +619,8 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--small", action="store_true",
+                    help="kernel-pair workloads at a reduced problem count (profiler captures)")
     ap.add_argument("--timed-only", action="store_true",
                     help="run only warm-up and the timed steps (for profiler launch lists)")
     args = ap.parse_args()
@@ -596,7 +643,7 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     warmup = max(args.warmup, 3)
 
-    wl = make_workload(args.workload, world)
+    wl = make_workload(args.workload, world, args.small)
     wl.setup(torch, dispatch)
 
     def barrier():

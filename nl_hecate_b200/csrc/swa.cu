@@ -17,7 +17,7 @@
 #include <cuda_bf16.h>
 
 #include "nlh_common.cuh"
-#include "swa_tc.cuh"
+#include "swa_tc_bwd.cuh"
 #include "../../include/nlh_ffi.h"
 
 namespace nlh {
@@ -363,7 +363,8 @@ __global__ void __launch_bounds__(256) swa_weights_kernel(
 template <int HD, typename TDO>
 __global__ void __launch_bounds__(256) swa_delta_kernel(const TDO* __restrict__ d_out,
                                                         const bf16* __restrict__ out,
-                                                        float* __restrict__ delta, int S, int H, int B, int rs_o)
+                                                        float* __restrict__ delta, int S, int H, int B, int rs_o,
+                                                        bf16* __restrict__ do16)
 {
     const int lane = threadIdx.x & 31;
     const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -373,7 +374,13 @@ __global__ void __launch_bounds__(256) swa_delta_kernel(const TDO* __restrict__ 
     const int b = (int)(row / ((long long)S * H));
     const size_t off = ((size_t)b * S + qp) * rs_o + (size_t)h * HD;
     float s = 0.f;
-    for (int i = lane; i < HD; i += 32) s += do_as_float(d_out[off + i]) * __bfloat162float(out[off + i]);
+    // do16 (optional): dense bf16 copy of the upstream gradient for the tensor-core kernels
+    const size_t off16 = ((size_t)b * S + qp) * ((size_t)H * HD) + (size_t)h * HD;
+    for (int i = lane; i < HD; i += 32) {
+        const float g = do_as_float(d_out[off + i]);
+        s += g * __bfloat162float(out[off + i]);
+        if (do16 != nullptr) do16[off16 + i] = __float2bfloat16(g);
+    }
     s = warp_sum(s);
     if (lane == 0) delta[row] = s;
 }
@@ -635,19 +642,47 @@ static int swa_forward_impl(const bf16* q, const bf16* k, const bf16* v, bf16* o
     return NLH_OK;
 }
 
+// do16_scratch: B*S*H*HD bf16 of scratch for the converted upstream gradient when TDO is float
+// (NULL: the tensor-core kernels are not used for an fp32 upstream gradient).
 template <int HD, typename TDO, typename TG>
 static int swa_backward_impl(const bf16* q, const bf16* k, const bf16* v, const bf16* out,
                              const float* lse, const TDO* d_out, float* delta, TG* d_q,
                              TG* d_k, TG* d_v, int S, int H, int W, int B, int n_p, bool accum,
-                             int rs_in = 0, int rs_o = 0)
+                             int rs_in = 0, int rs_o = 0, bf16* do16_scratch = nullptr)
 {
     cudaStream_t st = current_stream();
     const float scale = 1.0f / sqrtf((float)HD);
     if (rs_in == 0) rs_in = H * HD;
     if (rs_o == 0) rs_o = H * HD;
     const long long rows = (long long)B * H * S;
-    swa_delta_kernel<HD, TDO><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(d_out, out, delta, S, H, B, rs_o);
+    constexpr bool DO_IS_BF16 = sizeof(TDO) == 2;
+    const bool aligned = ((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)d_out | (uintptr_t)d_q |
+                            (uintptr_t)d_k | (uintptr_t)d_v | (uintptr_t)do16_scratch) & 15) == 0) &&
+                         (rs_in % 8 == 0) && (rs_o % 8 == 0);
+    const bool use_tc = HD == 64 && option_value(NLH_OPT_SWA_TCGEN05) && aligned && (DO_IS_BF16 || do16_scratch != nullptr);
+    bf16* do16 = (use_tc && !DO_IS_BF16) ? do16_scratch : nullptr;
+    swa_delta_kernel<HD, TDO><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(d_out, out, delta, S, H, B, rs_o, do16);
     if (!check_launch("swa_delta_kernel")) return NLH_ERR_CUDA;
+    if (use_tc) {
+        // tcgen05 / TMEM kernels: 128 key rows (dK, dV) and 128 query rows (dQ) per CTA
+        const bf16* g16 = DO_IS_BF16 ? reinterpret_cast<const bf16*>(d_out) : do16;
+        const int rs16 = DO_IS_BF16 ? rs_o : H * HD;
+        dim3 grid((S + tc::BM - 1) / tc::BM, B * H);
+        if (accum) {
+            cudaFuncSetAttribute(tc::swa_bwd_dkv_tc_kernel<TG, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::KV_SMEM_BYTES);
+            tc::swa_bwd_dkv_tc_kernel<TG, true><<<grid, tc::BTHREADS, tc::KV_SMEM_BYTES, st>>>(
+                q, k, v, g16, lse, delta, d_k, d_v, S, H, W, n_p, scale, rs_in, rs16);
+        } else {
+            cudaFuncSetAttribute(tc::swa_bwd_dkv_tc_kernel<TG, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::KV_SMEM_BYTES);
+            tc::swa_bwd_dkv_tc_kernel<TG, false><<<grid, tc::BTHREADS, tc::KV_SMEM_BYTES, st>>>(
+                q, k, v, g16, lse, delta, d_k, d_v, S, H, W, n_p, scale, rs_in, rs16);
+        }
+        if (!check_launch("swa_bwd_dkv_tc_kernel")) return NLH_ERR_CUDA;
+        cudaFuncSetAttribute(tc::swa_bwd_dq_tc_kernel<TG>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::DQ_SMEM_BYTES);
+        tc::swa_bwd_dq_tc_kernel<TG><<<grid, tc::BTHREADS, tc::DQ_SMEM_BYTES, st>>>(
+            q, k, v, g16, lse, delta, d_q, S, H, W, n_p, scale, rs_in, rs16);
+        return check_launch("swa_bwd_dq_tc_kernel") ? NLH_OK : NLH_ERR_CUDA;
+    }
     {
         const size_t smem = swa_dkv_smem<HD>();
         dim3 grid((S + SWA_BN - 1) / SWA_BN, B * H);
@@ -710,11 +745,14 @@ int32_t nlh_swa_backward(const uint16_t* q, const uint16_t* k, const uint16_t* v
     int rc = swa_check("nlh_swa_backward", seq_len, num_heads, head_dim, window_size, batch_size, n_persistent);
     if (rc != NLH_OK || batch_size == 0) return rc;
     const size_t rows = (size_t)batch_size * num_heads * seq_len;
-    float* delta = (float*)workspace(rows * sizeof(float));
-    if (!delta) return NLH_ERR_WORKSPACE;
+    const size_t row_bytes = (rows * sizeof(float) + 255) & ~(size_t)255;
+    char* ws = (char*)workspace(row_bytes + rows * head_dim * sizeof(bf16));
+    if (!ws) return NLH_ERR_WORKSPACE;
+    float* delta = (float*)ws;
+    bf16* do16 = (bf16*)(ws + row_bytes);       // bf16 copy of the fp32 upstream gradient
     SWA_DISPATCH_HD(head_dim, rc = swa_backward_impl<HD_, float, float>((const bf16*)q, (const bf16*)k, (const bf16*)v,
         (const bf16*)out, lse, d_attn_out, delta, d_q, d_k, d_v, seq_len, num_heads, window_size,
-        batch_size, n_persistent, false));
+        batch_size, n_persistent, false, 0, 0, do16));
     return rc;
 }
 
@@ -775,17 +813,18 @@ void swa_backward_f32_cuda(const uint16_t* q, const uint16_t* k, const uint16_t*
     const size_t rows = (size_t)batch_size * num_heads * seq_len;
     const size_t row_bytes = (rows * sizeof(float) + 255) & ~(size_t)255;
     const size_t out_bytes = ((size_t)batch_size * seq_len * num_heads * head_dim * sizeof(bf16) + 255) & ~(size_t)255;
-    char* ws = (char*)workspace(2 * row_bytes + out_bytes);
+    char* ws = (char*)workspace(2 * row_bytes + 2 * out_bytes);
     if (!ws) return;
     float* lse = (float*)ws;
     float* delta = (float*)(ws + row_bytes);
     bf16* out = (bf16*)(ws + 2 * row_bytes);
+    bf16* do16 = (bf16*)(ws + 2 * row_bytes + out_bytes);
     SWA_DISPATCH_HD(head_dim, rc = swa_forward_impl<HD_>((const bf16*)q, (const bf16*)k, (const bf16*)v,
         out, lse, nullptr, seq_len, num_heads, window_size, batch_size, n_persistent));
     if (rc != NLH_OK) return;
     SWA_DISPATCH_HD(head_dim, rc = swa_backward_impl<HD_, float, float>((const bf16*)q, (const bf16*)k, (const bf16*)v,
         out, lse, d_attn_out, delta, d_q, d_k, d_v, seq_len, num_heads, window_size, batch_size,
-        n_persistent, true));
+        n_persistent, true, 0, 0, do16));
 }
 
 }  // extern "C"

@@ -11,10 +11,12 @@
 //       S^T = K Q^T, dP^T = V dO^T         thread = key row
 //       dV += P^T dO,  dK += dS^T Q        B = dO / Q tile consumed MN-major
 // Operand tiles sit in shared memory in the canonical no-swizzle core-matrix layout (8 rows x 16
-// bytes), staged with 16-byte cp.async (fp32 upstream gradients are converted on the way); one
-// thread issues the MMAs, completion comes back through tcgen05.commit -> mbarrier, and every
-// mbarrier wait is bounded exactly as in the forward kernel. Two CTAs share an SM (256 TMEM
-// columns each), so one CTA's exponentials overlap the other's MMAs.
+// bytes), staged with 16-byte cp.async (the upstream gradient arrives as bf16: the delta pre-pass
+// converts an fp32 one once); one thread issues the MMAs, completion comes back through
+// tcgen05.commit -> mbarrier, and every mbarrier wait is bounded exactly as in the forward
+// kernel. A CTA has 256 threads: warps w and w+4 own the same 32 rows (TMEM lanes) and split the
+// 64 columns of the score tiles between them. Two CTAs share an SM (256 TMEM columns each), so
+// one CTA's exponentials overlap the other's MMAs.
 #pragma once
 
 #include "swa_tc.cuh"
@@ -23,6 +25,7 @@ namespace nlh {
 namespace tc {
 
 constexpr int BQ = 64;                       // query rows per step of the dK/dV kernel
+constexpr int BTHREADS = 256;                // two warpgroups: columns [0,32) and [32,64) of a row
 constexpr unsigned BWD_TMEM_COLS = 256;
 constexpr float LOG2E = 1.4426950408889634f;
 
@@ -53,30 +56,27 @@ __device__ __forceinline__ bool visible(int qp, int kp, int window, int n_p)
     return kp <= qp && (kp < n_p || kp >= qp + 1 - window);
 }
 
-// Rows of 64 upstream-gradient values into the core-matrix layout, as bf16. The bf16 form is an
-// async copy; the fp32 form converts (ABI of the drop-in entry: d_attn_out is fp32).
-__device__ __forceinline__ void stage_do(unsigned char* dst, const __nv_bfloat16* __restrict__ src, size_t rs,
-                                         int n_rows, int n_valid)
+// stage_rows of the forward kernel for a CTA of BTHREADS threads.
+__device__ __forceinline__ void stage_rows_b(unsigned char* dst, const __nv_bfloat16* __restrict__ src,
+                                             size_t rs, int n_rows, int n_valid)
 {
-    stage_rows(dst, src, rs, n_rows, n_valid);
-}
-__device__ __forceinline__ void stage_do(unsigned char* dst, const float* __restrict__ src, size_t rs,
-                                         int n_rows, int n_valid)
-{
-    for (int i = threadIdx.x; i < n_rows * 8; i += THREADS) {
+    for (int i = threadIdx.x; i < n_rows * 8; i += BTHREADS) {
         const int row = i >> 3, c = i & 7;
         unsigned char* d = dst + (row >> 3) * GROUP + c * CORE + (row & 7) * 16;
-        uint4 w = make_uint4(0u, 0u, 0u, 0u);
-        if (row < n_valid) {
-            const float4 a = *reinterpret_cast<const float4*>(src + (size_t)row * rs + c * 8);
-            const float4 b = *reinterpret_cast<const float4*>(src + (size_t)row * rs + c * 8 + 4);
-            __nv_bfloat162 t0 = __floats2bfloat162_rn(a.x, a.y), t1 = __floats2bfloat162_rn(a.z, a.w);
-            __nv_bfloat162 t2 = __floats2bfloat162_rn(b.x, b.y), t3 = __floats2bfloat162_rn(b.z, b.w);
-            w.x = *reinterpret_cast<unsigned*>(&t0); w.y = *reinterpret_cast<unsigned*>(&t1);
-            w.z = *reinterpret_cast<unsigned*>(&t2); w.w = *reinterpret_cast<unsigned*>(&t3);
-        }
-        *reinterpret_cast<uint4*>(d) = w;
+        if (row < n_valid) cp16_tc(d, src + (size_t)row * rs + c * 8);
+        else *reinterpret_cast<uint4*>(d) = make_uint4(0u, 0u, 0u, 0u);
     }
+}
+__device__ __forceinline__ void cp4_tc(void* smem_dst, const void* gsrc)
+{
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+// 32 TMEM lanes x 32 consecutive 32-bit columns -> 32 registers.
+__device__ __forceinline__ void tmem_ld_32x32b_x32(unsigned (&r)[32], unsigned taddr)
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr));
 }
 
 __device__ __forceinline__ void store_row8(float* dst, const float (&x)[8], bool accum)
@@ -126,15 +126,17 @@ __device__ __forceinline__ void tmem_free_cols(unsigned base, unsigned cols)
 }
 
 // ───────────────────────────────── dQ ─────────────────────────────────────
-// TMEM columns: S [0,64), dP [64,128), dQ [128,192).
-template <typename TDO, typename TG>
-__global__ void __launch_bounds__(THREADS, 2) swa_bwd_dq_tc_kernel(
+// TMEM columns: S [0,64), dP [64,128), dQ [128,192). Thread (row = (warp & 3) * 32 + lane,
+// half = warp >> 2) handles columns [32 half, 32 half + 32) of its row.
+template <typename TG>
+__global__ void __launch_bounds__(BTHREADS, 2) swa_bwd_dq_tc_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
-    const TDO* __restrict__ d_out, const float* __restrict__ lse, const float* __restrict__ delta,
+    const __nv_bfloat16* __restrict__ d_out, const float* __restrict__ lse, const float* __restrict__ delta,
     TG* __restrict__ d_q, int S, int H, int window, int n_p, float scale, int rs_in, int rs_o)
 {
     extern __shared__ __align__(128) unsigned char smem[];
-    const int tid = threadIdx.x, warp = tid >> 5;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int half = warp >> 2, row = (warp & 3) * 32 + lane;
     const int qt = (gridDim.x - 1) - blockIdx.x;
     const int bh = blockIdx.y, b = bh / H, h = bh - b * H;
     const size_t rs = (size_t)rs_in;
@@ -152,7 +154,7 @@ __global__ void __launch_bounds__(THREADS, 2) swa_bwd_dq_tc_kernel(
     __syncthreads();
     fence_after_sync();
     const unsigned tmem_base = *tmem_slot;
-    const unsigned tmem_row = tmem_base + ((unsigned)(warp * 32) << 16);
+    const unsigned tmem_row = tmem_base + ((unsigned)((warp & 3) * 32) << 16) + half * 32;
 
     const int kt_last = q_hi / BN;
     auto next_tile = [&](int cur) {
@@ -164,8 +166,8 @@ __global__ void __launch_bounds__(THREADS, 2) swa_bwd_dq_tc_kernel(
     };
     auto load_kv = [&](int tile, int bufi) {
         const int k0 = tile * BN;
-        stage_rows(smem + DQ_OFF_K + bufi * KV_BYTES, k + base + (size_t)k0 * rs, rs, BN, min(BN, S - k0));
-        stage_rows(smem + DQ_OFF_V + bufi * KV_BYTES, v + base + (size_t)k0 * rs, rs, BN, min(BN, S - k0));
+        stage_rows_b(smem + DQ_OFF_K + bufi * KV_BYTES, k + base + (size_t)k0 * rs, rs, BN, min(BN, S - k0));
+        stage_rows_b(smem + DQ_OFF_V + bufi * KV_BYTES, v + base + (size_t)k0 * rs, rs, BN, min(BN, S - k0));
     };
     const unsigned idesc_kk = make_idesc(false), idesc_mn = make_idesc(true);
     const unsigned q_addr = smem_u32(smem + DQ_OFF_Q), do_addr = smem_u32(smem + DQ_OFF_DO);
@@ -185,33 +187,33 @@ __global__ void __launch_bounds__(THREADS, 2) swa_bwd_dq_tc_kernel(
     };
 
     int kt = next_tile(-1);
-    stage_rows(smem + DQ_OFF_Q, q + base + (size_t)q0 * rs, rs, BM, min(BM, S - q0));
-    stage_do(smem + DQ_OFF_DO, d_out + base_o + (size_t)q0 * rs_o, (size_t)rs_o, BM, min(BM, S - q0));
+    stage_rows_b(smem + DQ_OFF_Q, q + base + (size_t)q0 * rs, rs, BM, min(BM, S - q0));
+    stage_rows_b(smem + DQ_OFF_DO, d_out + base_o + (size_t)q0 * rs_o, (size_t)rs_o, BM, min(BM, S - q0));
     if (kt >= 0) load_kv(kt, 0);
     cp_commit_tc();
+    const int qp = q0 + row;
+    const size_t rowi = ((size_t)b * H + h) * S + min(qp, S - 1);
+    const float lse2 = lse[rowi] * LOG2E;
+    const float del = delta[rowi];
     asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     fence_async_proxy();
     fence_before_sync();
     __syncthreads();
     if (tid == 0 && kt >= 0) { fence_after_sync(); issue_scores(0); }
 
-    const int qp = q0 + tid;
-    const size_t rowi = ((size_t)b * H + h) * S + min(qp, S - 1);
-    const float lse2 = lse[rowi] * LOG2E;
-    const float del = delta[rowi];
     unsigned par_s = 0, par_o = 0;
     bool dead = false;
     int it = 0;
 
     while (kt >= 0) {
         const int nxt = next_tile(kt);
-        // A: scores and dP of this tile
+        // A: this thread's 32 scores and 32 dP values of the tile
         if (!dead) dead = !mbar_wait(bar_s, par_s, WAIT_LIMIT);
         par_s ^= 1;
         fence_after_sync();
-        unsigned sr[64], dr[64];
-        tmem_ld_32x32b_x64(sr, tmem_row);
-        tmem_ld_32x32b_x64(dr, tmem_row + 64);
+        unsigned sr[32], dr[32];
+        tmem_ld_32x32b_x32(sr, tmem_row);
+        tmem_ld_32x32b_x32(dr, tmem_row + 64);
         tmem_wait_ld();
         fence_before_sync();
         // B: the previous dQ update has consumed dS and its K tile
@@ -227,16 +229,16 @@ __global__ void __launch_bounds__(THREADS, 2) swa_bwd_dq_tc_kernel(
         const int k0 = kt * BN;
         const bool interior = (k0 + BN - 1 <= q0) && (k0 + BN - 1 < S) &&
                               ((k0 >= q0 + BM - window) || (k0 + BN - 1 < n_p));
-        unsigned char* drow = smem + DQ_OFF_DS + (tid >> 3) * GROUP + (tid & 7) * 16;
+        unsigned char* drow = smem + DQ_OFF_DS + (row >> 3) * GROUP + (row & 7) * 16 + half * 4 * CORE;
 #pragma unroll
-        for (int c = 0; c < BN / 8; c++) {
+        for (int c = 0; c < 4; c++) {
             float ds[8];
 #pragma unroll
             for (int e = 0; e < 8; e++) {
                 const int j = c * 8 + e;
                 float p = ex2_approx(fmaf(__uint_as_float(sr[j]), sl2, -lse2));
                 if (!interior) {
-                    const int kp = k0 + j;
+                    const int kp = k0 + half * 32 + j;
                     if (!(qp < S && kp < S && visible(qp, kp, window, n_p))) p = 0.f;
                 }
                 ds[e] = p * (__uint_as_float(dr[j]) - del) * scale;
@@ -266,13 +268,13 @@ __global__ void __launch_bounds__(THREADS, 2) swa_bwd_dq_tc_kernel(
     if (it > 0) {
         if (!dead) dead = !mbar_wait(bar_o, par_o, WAIT_LIMIT);
         fence_after_sync();
-        unsigned orr[64];
-        tmem_ld_32x32b_x64(orr, tmem_row + 128);
+        unsigned orr[32];
+        tmem_ld_32x32b_x32(orr, tmem_row + 128);
         tmem_wait_ld();
         if (qp < S) {
-            TG* orow = d_q + base + (size_t)qp * rs;
+            TG* orow = d_q + base + (size_t)qp * rs + half * 32;
 #pragma unroll
-            for (int c = 0; c < HD / 8; c++) {
+            for (int c = 0; c < 4; c++) {
                 float x[8];
 #pragma unroll
                 for (int e = 0; e < 8; e++) x[e] = __uint_as_float(orr[c * 8 + e]);
@@ -280,28 +282,30 @@ __global__ void __launch_bounds__(THREADS, 2) swa_bwd_dq_tc_kernel(
             }
         }
     } else if (qp < S) {
-        TG* orow = d_q + base + (size_t)qp * rs;
+        TG* orow = d_q + base + (size_t)qp * rs + half * 32;
         const float z[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int c = 0; c < HD / 8; c++) store_row8(orow + c * 8, z, false);
+        for (int c = 0; c < 4; c++) store_row8(orow + c * 8, z, false);
     }
-    if (dead && (tid & 31) == 0) atomicExch(&g_swa_tc_timeout, 1);
+    if (dead && lane == 0) atomicExch(&g_swa_tc_timeout, 1);
     fence_before_sync();
     __syncthreads();
     if (warp == 0) tmem_free_cols(tmem_base, BWD_TMEM_COLS);
 }
 
 // ─────────────────────────────── dK, dV ───────────────────────────────────
-// TMEM columns: S^T [0,64), dP^T [64,128), dV [128,192), dK [192,256).
-template <typename TDO, typename TG, bool ACCUM>
-__global__ void __launch_bounds__(THREADS, 2) swa_bwd_dkv_tc_kernel(
+// TMEM columns: S^T [0,64), dP^T [64,128), dV [128,192), dK [192,256). Thread (row = key,
+// half) handles query columns [32 half, 32 half + 32) of its key row.
+template <typename TG, bool ACCUM>
+__global__ void __launch_bounds__(BTHREADS, 2) swa_bwd_dkv_tc_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
-    const TDO* __restrict__ d_out, const float* __restrict__ lse, const float* __restrict__ delta,
+    const __nv_bfloat16* __restrict__ d_out, const float* __restrict__ lse, const float* __restrict__ delta,
     TG* __restrict__ d_k, TG* __restrict__ d_v, int S, int H, int window, int n_p, float scale,
     int rs_in, int rs_o)
 {
     extern __shared__ __align__(128) unsigned char smem[];
-    const int tid = threadIdx.x, warp = tid >> 5;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int half = warp >> 2, row = (warp & 3) * 32 + lane;
     const int kt = blockIdx.x;
     const int bh = blockIdx.y, b = bh / H, h = bh - b * H;
     const size_t rs = (size_t)rs_in;
@@ -312,7 +316,7 @@ __global__ void __launch_bounds__(THREADS, 2) swa_bwd_dkv_tc_kernel(
     const float sl2 = scale * LOG2E;
     const unsigned bar_s = smem_u32(smem + KV_OFF_BAR), bar_o = bar_s + 8;
     volatile unsigned* tmem_slot = reinterpret_cast<volatile unsigned*>(smem + KV_OFF_TMEM);
-    float* rowv = reinterpret_cast<float*>(smem + KV_OFF_ROW);        // [buf][lse2 | delta][64]
+    float* rowv = reinterpret_cast<float*>(smem + KV_OFF_ROW);        // [buf][lse | delta][64]
 
     if (tid == 0) { mbar_init(bar_s, 1); mbar_init(bar_o, 1); }
     if (warp == 0) tmem_alloc_cols(smem + KV_OFF_TMEM, BWD_TMEM_COLS);
@@ -320,20 +324,21 @@ __global__ void __launch_bounds__(THREADS, 2) swa_bwd_dkv_tc_kernel(
     __syncthreads();
     fence_after_sync();
     const unsigned tmem_base = *tmem_slot;
-    const unsigned tmem_row = tmem_base + ((unsigned)(warp * 32) << 16);
+    const unsigned tmem_row = tmem_base + ((unsigned)((warp & 3) * 32) << 16) + half * 32;
 
     // query tiles of 64: from the one holding k0 up to the last query that sees k_hi
     const int q_last = (k0 < n_p) ? (S - 1) : min(S - 1, k_hi + window - 1);
     const int qt_first = k0 / BQ, qt_last = q_last / BQ;
+    const float* lse_bh = lse + ((size_t)b * H + h) * S;
+    const float* del_bh = delta + ((size_t)b * H + h) * S;
     auto load_q = [&](int qtile, int bufi) {
         const int q0 = qtile * BQ, nq = min(BQ, S - q0);
-        stage_rows(smem + KV_OFF_Q + bufi * KV_BYTES, q + base + (size_t)q0 * rs, rs, BQ, nq);
-        stage_do(smem + KV_OFF_DO + bufi * KV_BYTES, d_out + base_o + (size_t)q0 * rs_o, (size_t)rs_o, BQ, nq);
-        if (tid < BQ) {
-            const int qp = q0 + tid;
-            const size_t ri = ((size_t)b * H + h) * S + min(qp, S - 1);
-            rowv[(bufi * 2 + 0) * BQ + tid] = lse[ri] * LOG2E;
-            rowv[(bufi * 2 + 1) * BQ + tid] = delta[ri];
+        stage_rows_b(smem + KV_OFF_Q + bufi * KV_BYTES, q + base + (size_t)q0 * rs, rs, BQ, nq);
+        stage_rows_b(smem + KV_OFF_DO + bufi * KV_BYTES, d_out + base_o + (size_t)q0 * rs_o, (size_t)rs_o, BQ, nq);
+        if (tid < 2 * BQ) {                                   // lse and delta rows of the tile
+            const int j = tid & (BQ - 1), which = tid >> 6;
+            const int qp = min(q0 + j, S - 1);
+            cp4_tc(rowv + (bufi * 2 + which) * BQ + j, (which ? del_bh : lse_bh) + qp);
         }
     };
     const unsigned idesc_kk = make_idesc(false), idesc_mn = make_idesc(true);
@@ -353,8 +358,8 @@ __global__ void __launch_bounds__(THREADS, 2) swa_bwd_dkv_tc_kernel(
         mma_commit(bar_s);
     };
 
-    stage_rows(smem + KV_OFF_K, k + base + (size_t)k0 * rs, rs, BM, min(BM, S - k0));
-    stage_rows(smem + KV_OFF_V, v + base + (size_t)k0 * rs, rs, BM, min(BM, S - k0));
+    stage_rows_b(smem + KV_OFF_K, k + base + (size_t)k0 * rs, rs, BM, min(BM, S - k0));
+    stage_rows_b(smem + KV_OFF_V, v + base + (size_t)k0 * rs, rs, BM, min(BM, S - k0));
     load_q(qt_first, 0);
     cp_commit_tc();
     asm volatile("cp.async.wait_group 0;\n" ::: "memory");
@@ -363,20 +368,20 @@ __global__ void __launch_bounds__(THREADS, 2) swa_bwd_dkv_tc_kernel(
     __syncthreads();
     if (tid == 0) { fence_after_sync(); issue_scores(0); }
 
-    const int kp = k0 + tid;
+    const int kp = k0 + row;
     unsigned par_s = 0, par_o = 0;
     bool dead = false;
     int it = 0;
     for (int qtile = qt_first; qtile <= qt_last; qtile++, it++) {
         const bool has_next = qtile < qt_last;
         const int bufi = it & 1;
-        // A: S^T and dP^T of this query tile
+        // A: this thread's part of S^T and dP^T
         if (!dead) dead = !mbar_wait(bar_s, par_s, WAIT_LIMIT);
         par_s ^= 1;
         fence_after_sync();
-        unsigned sr[64], dr[64];
-        tmem_ld_32x32b_x64(sr, tmem_row);
-        tmem_ld_32x32b_x64(dr, tmem_row + 64);
+        unsigned sr[32], dr[32];
+        tmem_ld_32x32b_x32(sr, tmem_row);
+        tmem_ld_32x32b_x32(dr, tmem_row + 64);
         tmem_wait_ld();
         fence_before_sync();
         // B: the previous accumulation has consumed P, dS and its Q, dO tiles
@@ -388,25 +393,25 @@ __global__ void __launch_bounds__(THREADS, 2) swa_bwd_dkv_tc_kernel(
         // C: prefetch the next query tile into the buffer tile it-1 used
         if (has_next) load_q(qtile + 1, bufi ^ 1);
         cp_commit_tc();
-        // E: P^T and dS^T rows of this key
+        // E: P^T and dS^T of this key row for 32 queries
         const int q0 = qtile * BQ;
-        const float* l2 = rowv + (bufi * 2 + 0) * BQ;
-        const float* dl = rowv + (bufi * 2 + 1) * BQ;
+        const float* l2 = rowv + (bufi * 2 + 0) * BQ + half * 32;
+        const float* dl = rowv + (bufi * 2 + 1) * BQ + half * 32;
         // every (query, key) pair of the tile visible: all queries at or after the last key, inside
         // the sequence, and the first key inside the window of the last query (or in the prefix)
         const bool interior = (q0 >= k0 + BM - 1) && (q0 + BQ - 1 < S) && (k0 + BM - 1 < S) &&
                               ((k0 >= q0 + BQ - window) || (k0 + BM - 1 < n_p));
-        unsigned char* prow = smem + KV_OFF_P + (tid >> 3) * GROUP + (tid & 7) * 16;
-        unsigned char* drow = smem + KV_OFF_DS + (tid >> 3) * GROUP + (tid & 7) * 16;
+        unsigned char* prow = smem + KV_OFF_P + (row >> 3) * GROUP + (row & 7) * 16 + half * 4 * CORE;
+        unsigned char* drow = smem + KV_OFF_DS + (row >> 3) * GROUP + (row & 7) * 16 + half * 4 * CORE;
 #pragma unroll
-        for (int c = 0; c < BQ / 8; c++) {
+        for (int c = 0; c < 4; c++) {
             float pp[8], ds[8];
 #pragma unroll
             for (int e = 0; e < 8; e++) {
                 const int j = c * 8 + e;
-                float p = ex2_approx(fmaf(__uint_as_float(sr[j]), sl2, -l2[j]));
+                float p = ex2_approx(fmaf(__uint_as_float(sr[j]), sl2, -l2[j] * LOG2E));
                 if (!interior) {
-                    const int qp = q0 + j;
+                    const int qp = q0 + half * 32 + j;
                     if (!(qp < S && kp < S && visible(qp, kp, window, n_p))) p = 0.f;
                 }
                 pp[e] = p;
@@ -440,25 +445,25 @@ __global__ void __launch_bounds__(THREADS, 2) swa_bwd_dkv_tc_kernel(
     if (!dead) dead = !mbar_wait(bar_o, par_o, WAIT_LIMIT);
     fence_after_sync();
     {
-        unsigned orr[64];
-        tmem_ld_32x32b_x64(orr, tmem_row + 128);
+        unsigned orr[32];
+        tmem_ld_32x32b_x32(orr, tmem_row + 128);
         tmem_wait_ld();
         if (kp < S) {
-            TG* orow = d_v + base + (size_t)kp * rs;
+            TG* orow = d_v + base + (size_t)kp * rs + half * 32;
 #pragma unroll
-            for (int c = 0; c < HD / 8; c++) {
+            for (int c = 0; c < 4; c++) {
                 float x[8];
 #pragma unroll
                 for (int e = 0; e < 8; e++) x[e] = __uint_as_float(orr[c * 8 + e]);
                 store_row8(orow + c * 8, x, ACCUM);
             }
         }
-        tmem_ld_32x32b_x64(orr, tmem_row + 192);
+        tmem_ld_32x32b_x32(orr, tmem_row + 192);
         tmem_wait_ld();
         if (kp < S) {
-            TG* orow = d_k + base + (size_t)kp * rs;
+            TG* orow = d_k + base + (size_t)kp * rs + half * 32;
 #pragma unroll
-            for (int c = 0; c < HD / 8; c++) {
+            for (int c = 0; c < 4; c++) {
                 float x[8];
 #pragma unroll
                 for (int e = 0; e < 8; e++) x[e] = __uint_as_float(orr[c * 8 + e]);
@@ -466,7 +471,7 @@ __global__ void __launch_bounds__(THREADS, 2) swa_bwd_dkv_tc_kernel(
             }
         }
     }
-    if (dead && (tid & 31) == 0) atomicExch(&g_swa_tc_timeout, 1);
+    if (dead && lane == 0) atomicExch(&g_swa_tc_timeout, 1);
     fence_before_sync();
     __syncthreads();
     if (warp == 0) tmem_free_cols(tmem_base, BWD_TMEM_COLS);
