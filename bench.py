@@ -202,27 +202,23 @@ class TitansPair:
 
         def run(nprob):
             p = self.host_inputs(nprob, seed=99)
-            o = lambda *sh: np.empty(sh, np.float32)
+            z = lambda *sh: np.zeros(sh, np.float32)      # zeros: pages are touched before the clock starts
             L = oracle.lib()
             ptr = oracle._p
+            slots = (s // self.chunk + 1) if self.chunk else (s + 1)
+            out = [z(nprob, slots, d * d), z(nprob, slots, d * d)] + [z(nprob, s, d) for _ in range(4)] + \
+                  [z(nprob, s) for _ in range(3)] + [z(nprob, d * d), z(nprob, d * d)]
             t0 = time.perf_counter()
             if self.chunk:
-                nc = s // self.chunk
                 L.orc_chunkwise_fwd_bwd_batched_mt(
                     C.c_int(1), ptr(p["k"]), ptr(p["v"]), ptr(p["q"]), ptr(p["alpha"]), ptr(p["theta"]),
-                    ptr(p["eta"]), ptr(p["m0"]), ptr(p["s0"]), ptr(p["dy"]),
-                    ptr(o(nprob, nc + 1, d * d)), ptr(o(nprob, nc + 1, d * d)), ptr(o(nprob, s, d)),
-                    ptr(o(nprob, s, d)), ptr(o(nprob, s, d)), ptr(o(nprob, s, d)), ptr(o(nprob, s)),
-                    ptr(o(nprob, s)), ptr(o(nprob, s)), ptr(o(nprob, d * d)), ptr(o(nprob, d * d)),
+                    ptr(p["eta"]), ptr(p["m0"]), ptr(p["s0"]), ptr(p["dy"]), *[ptr(a) for a in out],
                     C.c_int(nprob), C.c_int(s), C.c_int(d), C.c_int(self.chunk), C.c_float(0.0),
                     C.c_float(0.0), C.c_int(threads))
             else:
                 L.orc_titans_fwd_bwd_batched_mt(
                     ptr(p["k"]), ptr(p["v"]), ptr(p["q"]), ptr(p["alpha"]), ptr(p["theta"]),
-                    ptr(p["eta"]), ptr(p["m0"]), ptr(p["s0"]), ptr(p["dy"]),
-                    ptr(o(nprob, s + 1, d * d)), ptr(o(nprob, s + 1, d * d)), ptr(o(nprob, s, d)),
-                    ptr(o(nprob, s, d)), ptr(o(nprob, s, d)), ptr(o(nprob, s, d)), ptr(o(nprob, s)),
-                    ptr(o(nprob, s)), ptr(o(nprob, s)), ptr(o(nprob, d * d)), ptr(o(nprob, d * d)),
+                    ptr(p["eta"]), ptr(p["m0"]), ptr(p["s0"]), ptr(p["dy"]), *[ptr(a) for a in out],
                     C.c_int(nprob), C.c_int(s), C.c_int(d), C.c_float(0.0), C.c_float(0.0),
                     C.c_int(threads))
             return time.perf_counter() - t0
@@ -232,7 +228,8 @@ class TitansPair:
         dt = run(nprob) if reps > 1 else t1
         head_tokens = nprob * s
         # tokens = sequence positions of the [B,S] batch = head-tokens / H
-        return head_tokens / self.H / dt, f"{nprob} of {self.N} (batch x head) problems, seq {s}, {dt:.1f} s"
+        return head_tokens / self.H / dt, (f"{nprob} of {self.N} (batch x head) problems, seq {s}, one problem at a time "
+                                           f"per host thread: {dt:.1f} s (inputs and outputs allocated before the clock)")
 
 
 class SwaPair:
@@ -309,11 +306,11 @@ class SwaPair:
         do = g.standard_normal(sh).astype(np.float32)
         o = lambda *shape: np.zeros(shape, np.float32)
         ptr = oracle._p
+        bufs = [o(*sh), o(threads, nh, s, w), o(*sh), o(*sh), o(*sh)]
         t0 = time.perf_counter()
         oracle.lib().orc_swa_fwd_bwd_batched_mt(
-            ptr(q), ptr(k), ptr(v), ptr(do), ptr(o(*sh)), ptr(o(threads, nh, s, w)), ptr(o(*sh)),
-            ptr(o(*sh)), ptr(o(*sh)), C.c_int(threads), C.c_int(s), C.c_int(nh), C.c_int(hd),
-            C.c_int(w), C.c_int(0), C.c_int(threads))
+            ptr(q), ptr(k), ptr(v), ptr(do), *[ptr(a) for a in bufs], C.c_int(threads), C.c_int(s),
+            C.c_int(nh), C.c_int(hd), C.c_int(w), C.c_int(0), C.c_int(threads))
         dt = time.perf_counter() - t0
         return threads * s / dt, f"{threads} sequences of seq {s} (window {w}, {nh} heads), {dt:.1f} s"
 
@@ -465,60 +462,72 @@ class StackedModelStep:
         # (296 problems x 128 tokens: 664.94 MB read + 28.05 MB written), scaled by problem-tokens
         # (the kernel reads each stored state once and streams the rest: traffic is proportional to them)
         self.dominant_traffic = (664_938_496 + 28_052_224) / (296 * 128) * n * s
+        self.dominant_traffic_source = ("literal: dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of "
+                                        "this kernel at 296 problems x 128 tokens (profiles/titans_exact_level0_"
+                                        "kernels.md), scaled by problem-tokens; not re-measured by this run")
         return ("titans_exact_bwd_kernel<64> (exact Titans backward, M-only trajectory) at level-0 shapes",
                 lambda: self.dd.titans_backward_dd(k, v, q, al, th, et, ms, None, dy), bytes_, "hbm")
 
     def cpu_sample(self, oracle, threads, budget_s=12.0):
-        """Hot-path operators of the step on the host: per sequence and block, SWA fwd+bwd and the
-        four CMS levels' Titans fwd+bwd (level 0 exact on 512 tokens, levels 1-3 frozen-M0 on
-        64/8/1 pooled tokens), 8 heads of 64; plus one AdamW step. Dense projections, LayerNorm
-        and cross-entropy glue are NOT included (they would only add CPU time)."""
+        """The SAME step on the host: the stacked-model oracle (oracle/stacked.py — embedding,
+        LayerNorms, projections, SWA, four CMS levels of per-head Titans LMM, MAG gating,
+        unembedding, cross-entropy, forward and backward) with the model's seeded initialisation on
+        the first min(64, threads) sequences of the same Zipf token ids, one sequence per host
+        thread and single-threaded inside a sequence (as the reference's Rust path runs), followed
+        by gradient averaging, global-norm clip and one AdamW step over all parameters. Parameters,
+        token ids and output buffers are prepared before the clock starts."""
         import ctypes as C
-        s, nh, hd, w, nb = self.S, 8, 64, 512, 4
-        nseq = threads
+        from concurrent.futures import ThreadPoolExecutor
+        from oracle import stacked as ST
+        try:
+            from threadpoolctl import threadpool_limits
+        except ImportError:                                  # pragma: no cover
+            threadpool_limits = None
+        nseq = max(1, min(self.GLOBAL_BATCH, threads))
+        cfg = ST.Cfg(d_model=512, num_heads=8, n_blocks=4, k=4, chunk_sizes=(1, 8, 64, 512), seq_len=self.S,
+                     window=512, vocab=self.VOCAB, exact_levels=(0,), mode="resident")
+        if getattr(self, "_cpu_params", None) is None:
+            self._cpu_params = ST.init_params(cfg, seed=42)
+            self._cpu_params["w_embed"] = np.ascontiguousarray(self._cpu_params["w_unembed"].T)   # tied
+        p = self._cpu_params
+        ids = self.zipf_tokens(self.GLOBAL_BATCH)[:nseq]
+        if getattr(self, "_cpu_state", None) is None or len(self._cpu_state[0]) != nseq:
+            # carried memories and trajectory buffers of the sampled sequence streams persist
+            # from one timed step to the next, like the GPU arm's
+            self._cpu_state = ([ST.new_context(cfg) for _ in range(nseq)], [dict() for _ in range(nseq)])
+        ctxs, pools = self._cpu_state
+        names = sorted(p)
+        npar = sum(p[n].size for n in names)
+        w_ = np.concatenate([p[n].ravel() for n in names]).astype(np.float32)
+        g_, m_, v_ = (np.zeros(npar, np.float32) for _ in range(3))
         L, ptr = oracle.lib(), oracle._p
-        g = np.random.Generator(np.random.Philox(3))
-        o = lambda *sh: np.zeros(sh, np.float32)
-        t0 = time.perf_counter()
-        for _ in range(nb):
-            sh = (nseq, s, nh * hd)
-            q, k, v = ((g.standard_normal(sh) / 8).astype(np.float32) for _ in range(3))
-            do = g.standard_normal(sh).astype(np.float32)
-            L.orc_swa_fwd_bwd_batched_mt(ptr(q), ptr(k), ptr(v), ptr(do), ptr(o(*sh)),
-                                         ptr(o(nseq, nh, s, w)), ptr(o(*sh)), ptr(o(*sh)), ptr(o(*sh)),
-                                         C.c_int(nseq), C.c_int(s), C.c_int(nh), C.c_int(hd),
-                                         C.c_int(w), C.c_int(0), C.c_int(threads))
-            for lvl, c in enumerate((1, 8, 64, 512)):
-                sf = s // c
-                n = nseq * nh
-                kk, vv, qq, dy = (g.standard_normal((n, sf, hd)).astype(np.float32) * 0.125 for _ in range(4))
-                ga = [np.full((n, sf), x, np.float32) for x in (0.05, 0.01, 0.9)]
-                z = o(n, hd * hd)
-                if lvl == 0:
-                    L.orc_titans_fwd_bwd_batched_mt(
-                        ptr(kk), ptr(vv), ptr(qq), ptr(ga[0]), ptr(ga[1]), ptr(ga[2]), ptr(z), ptr(z),
-                        ptr(dy), ptr(o(n, sf + 1, hd * hd)), ptr(o(n, sf + 1, hd * hd)), ptr(o(n, sf, hd)),
-                        ptr(o(n, sf, hd)), ptr(o(n, sf, hd)), ptr(o(n, sf, hd)), ptr(o(n, sf)), ptr(o(n, sf)),
-                        ptr(o(n, sf)), ptr(o(n, hd * hd)), ptr(o(n, hd * hd)), C.c_int(n), C.c_int(sf),
-                        C.c_int(hd), C.c_float(0.0), C.c_float(0.0), C.c_int(threads))
-                else:
-                    ch = min(c, sf)
-                    nc = (sf + ch - 1) // ch
-                    L.orc_chunkwise_fwd_bwd_batched_mt(
-                        C.c_int(1), ptr(kk), ptr(vv), ptr(qq), ptr(ga[0]), ptr(ga[1]), ptr(ga[2]), ptr(z),
-                        ptr(z), ptr(dy), ptr(o(n, nc + 1, hd * hd)), ptr(o(n, nc + 1, hd * hd)),
-                        ptr(o(n, sf, hd)), ptr(o(n, sf, hd)), ptr(o(n, sf, hd)), ptr(o(n, sf, hd)),
-                        ptr(o(n, sf)), ptr(o(n, sf)), ptr(o(n, sf)), ptr(o(n, hd * hd)), ptr(o(n, hd * hd)),
-                        C.c_int(n), C.c_int(sf), C.c_int(hd), C.c_int(ch), C.c_float(0.0),
-                        C.c_float(0.0), C.c_int(threads))
-        npar = 25_200_000
-        w_, g_, m_, v_ = (np.full(npar, x, np.float32) for x in (0.01, 0.001, 0.0, 0.0))
-        L.orc_adamw_step_mt(ptr(w_), ptr(g_), ptr(m_), ptr(v_), C.c_int64(npar), C.c_float(3e-4),
-                            C.c_float(0.9), C.c_float(0.999), C.c_float(1e-8), C.c_float(10.0),
-                            C.c_float(1000.0), C.c_float(0.1), C.c_int(threads))
-        dt = time.perf_counter() - t0
-        return nseq * s / dt, (f"{nseq} of {self.GLOBAL_BATCH} sequences, hot-path operators only (SWA, "
-                               f"4 CMS levels of Titans LMM, AdamW; 4 blocks), {dt:.1f} s incl. input generation")
+
+        def one(i):
+            return ST.forward_backward(p, ids[i, :-1], ids[i, 1:], ctxs[i], cfg, pool=pools[i])
+
+        import contextlib
+        with (threadpool_limits(limits=1) if threadpool_limits else contextlib.nullcontext()):
+            t0 = time.perf_counter()
+            with ThreadPoolExecutor(max_workers=nseq) as ex:
+                res = list(ex.map(one, range(nseq)))
+            o = 0
+            for n in names:                                  # average the per-sequence gradients
+                acc = res[0][1][n].astype(np.float32).ravel().copy()
+                for r in res[1:]:
+                    acc += r[1][n].ravel()
+                g_[o:o + acc.size] = acc / nseq
+                o += acc.size
+            scale = C.c_float(1.0)
+            L.orc_grad_norm_clip(ptr(g_), C.c_int64(npar), C.c_float(1.0), C.byref(scale))
+            L.orc_adamw_step_mt(ptr(w_), ptr(g_), ptr(m_), ptr(v_), C.c_int64(npar), C.c_float(3e-4),
+                                C.c_float(0.9), C.c_float(0.999), C.c_float(1e-8), C.c_float(10.0),
+                                C.c_float(1000.0), C.c_float(0.1), C.c_int(threads))
+            dt = time.perf_counter() - t0
+        loss = float(np.mean([r[0] for r in res]))
+        return nseq * self.S / dt, (f"one whole step (embedding to AdamW, forward + backward, same seeded init and "
+                                    f"token ids as the GPU arm) on {nseq} of {self.GLOBAL_BATCH} sequences, one per "
+                                    f"host thread: {dt:.1f} s, {self.S / dt:.0f} tokens/s per thread, loss {loss:.4f}; "
+                                    f"the {self.GLOBAL_BATCH}-sequence step time is extrapolated from it")
 
 
 class TitansLevel0(TitansPair):
@@ -582,6 +591,12 @@ METRIC = "fwd+bwd tokens/sec"
 UNIT = "tokens/s"
 
 
+def parallelism_label(workload, world):
+    if workload == "stacked_mag":
+        return f"dp{world} (batch shard, one fp32 all-reduce of the gradient arena per step)"
+    return f"dp{world} (independent problems per rank, no collective)"
+
+
 def run_reference(args):
     """CPU arm: the restated Rust reference path on all host threads, bounded sample."""
     rank = int(os.environ.get("RANK", "0"))
@@ -591,18 +606,26 @@ def run_reference(args):
     oracle.build()
     wl = make_workload(args.workload, max(1, args.gpus))
     threads = oracle.hardware_threads()
-    vals = []
+    vals, secs = [], []
     sample = ""
     for i in range(args.warmup + args.steps):
+        t0 = time.perf_counter()
         v, sample = wl.cpu_sample(oracle, threads, budget_s=max(2.0, 20.0 / max(1, args.steps)))
         if i >= args.warmup:
             vals.append(v)
+            secs.append(time.perf_counter() - t0)
     value = float(np.mean(vals))
     cfg = wl.describe()
+    cfg["parallelism"] = parallelism_label(args.workload, max(1, args.gpus))
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": 1e3 * wl.tokens_per_step * max(1, args.gpus) / value, "higher_is_better": True,
+        # a step of this arm is one bounded sample of the workload: ms_per_step is its measured wall
+        # time; the time a whole step of the configuration would take on these cores follows from
+        # the throughput (sequences / problems are independent)
+        "ms_per_step": 1e3 * float(np.mean(secs)),
+        "full_step_ms_extrapolated": 1e3 * wl.tokens_per_step * max(1, args.gpus) / value,
+        "higher_is_better": True,
         "scaling": "strong" if args.workload == "stacked_mag" else "weak", "vs_baseline": None,
         "dtype": wl.dtype, "data": "synthetic", "config": cfg,
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
@@ -705,6 +728,7 @@ def main():
         peak, runit = peaks["bf16_tflops"], "TFLOP/s"
     roofline = {"kernel": name, "bound": bound, "achieved": achieved, "peak": peak, "unit": runit,
                 "frac": achieved / peak, "traffic": getattr(wl, "dominant_traffic", None),
+                "traffic_source": getattr(wl, "dominant_traffic_source", None),
                 "ms_per_launch": ms_dom,
                 "algorithmic_work_per_launch": work, "peak_source": peaks["source"]}
 
@@ -719,8 +743,7 @@ def main():
     if rank == 0:
         cfg = wl.describe()
         model_step = args.workload == "stacked_mag"
-        cfg["parallelism"] = (f"dp{world} (batch shard, one fp32 all-reduce of the gradient arena per step)"
-                              if model_step else f"dp{world} (independent problems per rank, no collective)")
+        cfg["parallelism"] = parallelism_label(args.workload, world)
         print(json.dumps({
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
@@ -735,24 +758,29 @@ def main():
 
 
 def finish(world, barrier, wl):
-    """End of a run. With several ranks: wait for everyone, drop the captured step graph (it
-    holds the communicator's resources) and leave without running NCCL's teardown, which can
-    block forever once a captured collective has been replayed."""
+    """End of a multi-rank run, in the order the resources depend on each other: every rank has
+    printed / finished its work (barrier), the captured step graph — which holds the
+    communicator's captured all-reduce — is dropped, the device is idle, and only then the
+    process group is destroyed. A daemon timer ends the process if the teardown itself were to
+    block for more than 90 s (the result line is already out)."""
     sys.stdout.flush()
     sys.stderr.flush()
     if world <= 1:
         return
-    # the result line is out: whatever happens below, leave within a minute
-    watchdog = threading.Timer(60.0, lambda: os._exit(0))
+    import torch
+    import torch.distributed as dist
+    watchdog = threading.Timer(90.0, lambda: os._exit(0))
     watchdog.daemon = True
     watchdog.start()
     barrier()
     model = getattr(wl, "model", None)
     if model is not None and getattr(model, "_graph", None) is not None:
-        model._graph = None
-    import torch
+        model._graph = None          # releases the captured collective before the communicator goes
+    import gc
+    gc.collect()
     torch.cuda.synchronize()
-    os._exit(0)
+    dist.destroy_process_group()
+    watchdog.cancel()
 
 
 if __name__ == "__main__":

@@ -43,6 +43,11 @@ int64_t nlh_workspace_bytes(void);      /* scratch bytes held on the current dev
  * GPU (different streams) must use different slots; each slot grows on its own. */
 int32_t nlh_set_workspace_slot(int32_t slot);
 int32_t nlh_abi_version(void);
+/* The reference's parameter-init generator (SimpleRng, core/src/tensor.rs:380-408): xorshift64
+ * (<<13, >>7, <<17), uniform = (2 * (u64 / u64::MAX) - 1) * scale. HOST pointers; *state is
+ * advanced, so consecutive calls continue one stream (a zero state is replaced by 1 like a zero
+ * seed). Lets a host reproduce StackedMAGParams::init (core/src/stacked_model.rs:69-119,172-208). */
+void nlh_simple_rng_fill(uint64_t* state, float scale, float* out_host, int64_t n);
 
 /* ═════════════ Section 1: drop-in symbols (core/src/cuda_ffi.rs) ═════════════ */
 
@@ -263,6 +268,17 @@ int32_t nlh_swa_backward_packed(const uint16_t* qkv, const uint16_t* out, const 
     const uint16_t* d_attn_out, uint16_t* d_qkv, int32_t seq_len, int32_t num_heads, int32_t head_dim,
     int32_t window_size, int32_t batch_size, int32_t n_persistent);
 
+/* SWA pair in fp32 end to end (q, k, v, out, gradients all fp32; same visibility rule): the
+ * accuracy option for configurations stated in fp32, matching the reference's CPU path
+ * (core/src/swa.rs:33-92, :163-235) to rounding. CUDA-core kernels without tiling, meant for small
+ * shapes: head_dim <= 128, n_persistent + min(window, seq) <= 2048. d_q, d_k, d_v are overwritten. */
+int32_t nlh_swa_forward_f32(const float* q, const float* k, const float* v, float* out, float* lse,
+    int32_t seq_len, int32_t num_heads, int32_t head_dim, int32_t window_size, int32_t batch_size,
+    int32_t n_persistent);
+int32_t nlh_swa_backward_f32(const float* q, const float* k, const float* v, const float* out,
+    const float* lse, const float* d_attn_out, float* d_q, float* d_k, float* d_v, int32_t seq_len,
+    int32_t num_heads, int32_t head_dim, int32_t window_size, int32_t batch_size, int32_t n_persistent);
+
 /* Library options (no counterpart in the reference). NLH_OPT_SWA_TCGEN05 (default 1) runs the
  * head_dim-64 SWA forward on the tcgen05/TMEM kernel; 0 selects the mma.sync kernel instead. nlh_swa_tc_timeout_flag()
  * synchronously reads a device flag that the tcgen05 kernel sets if one of its bounded mbarrier
@@ -271,6 +287,11 @@ int32_t nlh_swa_backward_packed(const uint16_t* qkv, const uint16_t* out, const 
 /* NLH_OPT_CHUNK_MATRIX (default 1): frozen-M0 chunkwise Titans / Delta entries at head_dim 64 and
  * chunk sizes 16..64 run in chunk-parallel matrix form; 0 selects the per-token kernels. */
 #define NLH_OPT_CHUNK_MATRIX 2
+/* NLH_OPT_ROW_SPLIT (default 1): when a launch has no more problems than the GPU has SMs, the exact
+ * head_dim-64 forward and the M-only exact Titans backward divide every problem's rows over two
+ * CTAs (the rows of the memory evolve independently; the backward then zeroes d_q, d_k and the gate
+ * gradients itself and adds the two partial sums into them). 0 keeps one CTA per problem. */
+#define NLH_OPT_ROW_SPLIT 3
 int32_t nlh_set_option(int32_t option, int32_t value);
 int32_t nlh_swa_tc_timeout_flag(void);
 
@@ -297,9 +318,8 @@ int32_t nlh_adamw_multi_tensor(float* w, const float* g, float* m, float* v,
 int32_t nlh_arena_grad_norm_clip(const float* g, int64_t n, float max_grad_norm, float* partial,
     int32_t partial_capacity, float* out_norm, float* out_scale);
 
-/* Fused rule wrapper around the recurrence (row "next" of the scope: the ~15 small launches per
- * CMS level at core/src/gpu_forward.rs:1339-1382 and gpu_backward.rs:2047-2115 as one kernel each
- * way). kvq: [batch*seq, 3*d_model] rows (k | v | q) as produced by the projection GEMM, fp32 or
+/* Fused rule wrapper around the recurrence: the ~15 small launches per CMS level at
+ * core/src/gpu_forward.rs:1339-1382 and gpu_backward.rs:2047-2115 as one kernel each way. kvq: [batch*seq, 3*d_model] rows (k | v | q) as produced by the projection GEMM, fp32 or
  * bf16. Outputs in the per-head layout the memory kernels consume: k_ph,v_ph,q_ph
  * [batch*heads, seq, head_dim] (k,q L2-normalised over d_model), gates [batch*heads, seq]
  * (one value per token, repeated per head); k_norm,q_norm [batch*seq] for the backward.

@@ -19,7 +19,7 @@ INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 OBJ_DIR = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libnlh_b200.so")
 
-SOURCES = ["runtime.cu", "memory_ffi.cu", "swa.cu", "adamw.cu",
+SOURCES = ["runtime.cu", "memory_ffi.cu", "swa.cu", "swa_f32.cu", "adamw.cu",
            "static_scratch.cu", "wrapper.cu", "glue.cu", "opaque.cu", "opaque_rules.cu",
            "host_dispatch.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -19,36 +19,43 @@
 
 namespace nlh {
 
-template <int D>
+template <int D, int SPLIT = 1>
 constexpr size_t exact_bwd_smem_floats()
 {
-    using G = FastGeom<D>;
+    using G = FastGeom<D, SPLIT>;
     return (size_t)2 * FAST_TB * 4 * D        // k | v | q | dy rows, double buffered
          + 2 * FAST_TB * 4                    // gates (alpha, theta, eta, pad)
-         + (size_t)FAST_NST * D * D           // state ring (M only)
+         + (size_t)FAST_NST * G::ROWS * D     // state ring (M only, this CTA's rows)
          + (size_t)2 * G::NW * FAST_TB * D    // dq / dk warp partials
-         + (size_t)FAST_TB * D                // dv staging
-         + (size_t)3 * FAST_TB * D;           // per-row scalar partials
+         + (size_t)FAST_TB * G::ROWS          // dv staging
+         + (size_t)3 * FAST_TB * G::ROWS;     // per-row scalar partials
 }
 
-template <int D>
-__global__ void __launch_bounds__(FastGeom<D>::NT, D == 64 ? 2 : 8) titans_exact_bwd_kernel(BwdArgs a)
+// SPLIT = 2: the problem's rows are divided over two CTAs (see FastGeom). Each CTA then holds
+// partial column sums and partial gate gradients, which it ADDS into d_q, d_k, d_alpha, d_theta,
+// d_eta with atomicAdd (two addends per element: the result does not depend on their order); the
+// launcher zeroes those five outputs first.
+template <int D, int SPLIT = 1>
+__global__ void __launch_bounds__(FastGeom<D, SPLIT>::NT, D == 64 ? (SPLIT == 1 ? 2 : 3) : 8) titans_exact_bwd_kernel(BwdArgs a)
 {
-    using G = FastGeom<D>;
+    using G = FastGeom<D, SPLIT>;
     constexpr int NT = G::NT, TPR = G::TPR, NW = G::NW, TB = FAST_TB, NST = FAST_NST, DD = D * D;
+    constexpr int ROWS = G::ROWS, RD = ROWS * D;      // floats of one state slot held by this CTA
     constexpr int NOUT = ColReduce<TPR>::NOUT;
     constexpr int ROW = 4 * D;                        // staged floats per token: k | v | q | dy
     constexpr int VOFF = D, QOFF = 2 * D, DYOFF = 3 * D;
     extern __shared__ __align__(16) float sm[];
     float* tiles = sm;                                // [2][TB][ROW]
     float* gt = tiles + 2 * TB * ROW;                 // [2][TB][4]
-    float* ring = gt + 2 * TB * 4;                    // [NST][DD], thread-major pieces
-    float* pq = ring + (size_t)NST * DD;              // [NW][TB][D]
+    float* ring = gt + 2 * TB * 4;                    // [NST][RD], thread-major pieces
+    float* pq = ring + (size_t)NST * RD;              // [NW][TB][D]
     float* pk = pq + (size_t)NW * TB * D;             // [NW][TB][D]
-    float* dvs = pk + (size_t)NW * TB * D;            // [TB][D]
-    float* scp = dvs + TB * D;                        // [3][TB][D]
+    float* dvs = pk + (size_t)NW * TB * D;            // [TB][ROWS]
+    float* scp = dvs + TB * ROWS;                     // [3][TB][ROWS]
 
-    const int tid = threadIdx.x, r = tid / TPR, cg = tid % TPR;
+    const int tid = threadIdx.x, rl = tid / TPR, cg = tid % TPR;   // rl: row within this CTA
+    const int part = (SPLIT > 1) ? (int)(blockIdx.x % SPLIT) : 0;
+    const int r = part * ROWS + rl;                                // global row of the state
     const int lane = tid & 31, warp = tid >> 5;
     const int xc = chunk_perm(lane);
     int co[4];   // float offsets, within a row, of the four chunks this thread holds
@@ -58,7 +65,7 @@ __global__ void __launch_bounds__(FastGeom<D>::NT, D == 64 ? 2 : 8) titans_exact
     const int bi = ColReduce<TPR>::base_index(lane);
     const int wcol = warp * TB * D + col_of<D>(bi, cg);   // this lane's slot in a partial row
 
-    const int b = blockIdx.x;
+    const int b = blockIdx.x / SPLIT;
     const size_t so = (size_t)b * a.seq_len * D, go = (size_t)b * a.seq_len;
     const float* k = a.k + so; const float* v = a.v + so; const float* q = a.q + so;
     const float* dy = a.d_y + so;
@@ -100,7 +107,7 @@ __global__ void __launch_bounds__(FastGeom<D>::NT, D == 64 ? 2 : 8) titans_exact
     const float* gpre = mt_base + (size_t)max(len, 0) * DD + r * D;
     auto prefetch_state = [&]() {
         if (jp >= 0) {
-            float* dst = ring_t + pslot * DD;
+            float* dst = ring_t + pslot * RD;
 #pragma unroll
             for (int jj = 0; jj < 4; jj++) cp_async16(dst + jj * NT * 4, gpre + co[jj]);
         }
@@ -109,7 +116,7 @@ __global__ void __launch_bounds__(FastGeom<D>::NT, D == 64 ? 2 : 8) titans_exact
         pslot = (pslot == 0) ? NST - 1 : pslot - 1;
     };
     auto load_state = [&]() {     // consume the oldest state in flight into Mt
-        const float* ms = ring_t + cslot * DD;
+        const float* ms = ring_t + cslot * RD;
         cslot = (cslot == 0) ? NST - 1 : cslot - 1;
 #pragma unroll
         for (int jj = 0; jj < 4; jj++) {
@@ -197,11 +204,11 @@ __global__ void __launch_bounds__(FastGeom<D>::NT, D == 64 ? 2 : 8) titans_exact
             // <S_{t+1}, dS>_r = <M_{t+1}, dS>_r - (1-alpha) <M_t, dS>_r
             const float ps = row_allreduce<TPR>((pea.x + pea.y) - rr * (pb2.x + pb2.y));
             if (cg == 0) {
-                scp[(0 * TB + tl) * D + r] = pa;
-                scp[(1 * TB + tl) * D + r] = e * u;
+                scp[(0 * TB + tl) * ROWS + rl] = pa;
+                scp[(1 * TB + tl) * ROWS + rl] = e * u;
                 // d_eta_t = <S_t, dS> with S_t = (S_{t+1} + theta e k^T) / eta
-                scp[(2 * TB + tl) * D + r] = (et > 1e-30f) ? __fdividef(ps + th * e * u, et) : 0.f;
-                dvs[tl * D + r] = th * u;
+                scp[(2 * TB + tl) * ROWS + rl] = (et > 1e-30f) ? __fdividef(ps + th * e * u, et) : 0.f;
+                dvs[tl * ROWS + rl] = th * u;
             }
             {
                 float2 ck[8];
@@ -228,19 +235,27 @@ __global__ void __launch_bounds__(FastGeom<D>::NT, D == 64 ? 2 : 8) titans_exact
             float sq = 0.f, sk = 0.f;
 #pragma unroll
             for (int w = 0; w < NW; w++) { sq += pq[(size_t)w * TB * D + i]; sk += pk[(size_t)w * TB * D + i]; }
-            a.d_q[so + (size_t)tt0 * D + i] = sq;
-            a.d_k[so + (size_t)tt0 * D + i] = sk;
-            a.d_v[so + (size_t)tt0 * D + i] = dvs[i];
+            if (SPLIT > 1) {
+                atomicAdd(&a.d_q[so + (size_t)tt0 * D + i], sq);
+                atomicAdd(&a.d_k[so + (size_t)tt0 * D + i], sk);
+            } else {
+                a.d_q[so + (size_t)tt0 * D + i] = sq;
+                a.d_k[so + (size_t)tt0 * D + i] = sk;
+            }
+        }
+        for (int i = tid; i < ntok * ROWS; i += NT) {
+            const int tl = i / ROWS, rr = i - tl * ROWS;
+            a.d_v[so + (size_t)(tt0 + tl) * D + part * ROWS + rr] = dvs[i];
         }
         for (int job = warp; job < 3 * ntok; job += NW) {
             const int which = job / ntok, tl = job - which * ntok;
             float s = 0.f;
-            for (int i = lane; i < D; i += 32) s += scp[(which * TB + tl) * D + i];
+            for (int i = lane; i < ROWS; i += 32) s += scp[(which * TB + tl) * ROWS + i];
             s = warp_sum(s);
             if (lane == 0) {
-                if (which == 0) a.d_alpha[go + tt0 + tl] = -s;
-                else if (which == 1) a.d_theta[go + tt0 + tl] = -s;
-                else a.d_eta[go + tt0 + tl] = s;
+                float* dst = (which == 0 ? a.d_alpha : which == 1 ? a.d_theta : a.d_eta) + go + tt0 + tl;
+                const float val = (which == 2) ? s : -s;
+                if (SPLIT > 1) atomicAdd(dst, val); else *dst = val;
             }
         }
         __syncthreads();   // partial rows are rewritten by the next tile
@@ -265,6 +280,18 @@ __global__ void __launch_bounds__(FastGeom<D>::NT, D == 64 ? 2 : 8) titans_exact
 template <int D>
 static bool exact_bwd_launch(const BwdArgs& a, cudaStream_t st)
 {
+    if constexpr (D == 64) {
+        if (split_rows(a.d, a.batch)) {
+            // partial sums are added into these five outputs: start them from zero here
+            const size_t nd = (size_t)a.batch * a.seq_len * D * sizeof(float), ng = (size_t)a.batch * a.seq_len * sizeof(float);
+            cudaMemsetAsync(a.d_q, 0, nd, st); cudaMemsetAsync(a.d_k, 0, nd, st);
+            cudaMemsetAsync(a.d_alpha, 0, ng, st); cudaMemsetAsync(a.d_theta, 0, ng, st); cudaMemsetAsync(a.d_eta, 0, ng, st);
+            const size_t smem = exact_bwd_smem_floats<D, 2>() * sizeof(float);
+            cudaFuncSetAttribute(titans_exact_bwd_kernel<D, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            titans_exact_bwd_kernel<D, 2><<<a.batch * 2, FastGeom<D, 2>::NT, smem, st>>>(a);
+            return true;
+        }
+    }
     const size_t smem = exact_bwd_smem_floats<D>() * sizeof(float);
     cudaFuncSetAttribute(titans_exact_bwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     titans_exact_bwd_kernel<D><<<a.batch, FastGeom<D>::NT, smem, st>>>(a);

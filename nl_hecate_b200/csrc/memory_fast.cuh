@@ -17,6 +17,7 @@
 #pragma once
 
 #include "nlh_common.cuh"
+#include "../../include/nlh_ffi.h"
 
 namespace nlh {
 
@@ -115,10 +116,14 @@ struct ColReduce {
     }
 };
 
-template <int D>
+// SPLIT: CTAs per problem. The rows of M (and S) evolve independently of one another, so a problem's
+// rows can be divided over SPLIT CTAs that share nothing but the k/v/q/gate streams they read;
+// only the column sums (d_q, d_k) and the scalar gate gradients of the backward cross rows.
+template <int D, int SPLIT = 1>
 struct FastGeom {
     static constexpr int TPR = D / 16;          // threads per row
-    static constexpr int NT = D * TPR;          // threads per CTA
+    static constexpr int ROWS = D / SPLIT;      // rows of the state owned by one CTA
+    static constexpr int NT = ROWS * TPR;       // threads per CTA
     static constexpr int NW = NT / 32;          // warps
     static constexpr int RPW = 32 / TPR;        // rows per warp
 };
@@ -249,20 +254,22 @@ __device__ __forceinline__ float fast_readout(const float2 (&M)[8], const float*
 
 // D = 64, exact rules: capped at 64 registers so that four CTAs share an SM (the level-0 problem
 // count of the stacked model, batch x heads = 512, then fits in one wave of 148 x 4).
-template <int D, int RULE, bool FROZEN>
-__global__ void __launch_bounds__(FastGeom<D>::NT, (D == 64 && !FROZEN) ? 4 : 1) fast_fwd_kernel(FwdArgs a)
+template <int D, int RULE, bool FROZEN, int SPLIT = 1>
+__global__ void __launch_bounds__(FastGeom<D, SPLIT>::NT, (D == 64 && !FROZEN) ? 4 : 1) fast_fwd_kernel(FwdArgs a)
 {
-    using G = FastGeom<D>;
-    constexpr int NT = G::NT, TPR = G::TPR, TT = FAST_TT;
+    using G = FastGeom<D, SPLIT>;
+    constexpr int NT = G::NT, TPR = G::TPR, TT = FAST_TT, ROWS = G::ROWS;
     extern __shared__ __align__(16) float sm[];
     float* kt = sm;
     float* vt = kt + 2 * TT * D;
     float* qt = vt + 2 * TT * D;
     float* gt = qt + 2 * TT * D;   // [2][3][TT]
-    float* ys = gt + 2 * 3 * TT;   // [TT][D]
-    const int tid = threadIdx.x, r = tid / TPR, cg = tid % TPR;
+    float* ys = gt + 2 * 3 * TT;   // [TT][ROWS]
+    const int tid = threadIdx.x, cg = tid % TPR;
+    const int part = (SPLIT > 1) ? (int)(blockIdx.x % SPLIT) : 0;
+    const int r = part * ROWS + tid / TPR;       // global row of the state this thread holds
     const size_t dd = (size_t)D * D;
-    const int b = blockIdx.x;
+    const int b = blockIdx.x / SPLIT;
     const float* k = a.k + (size_t)b * a.in_stride_tok * D;
     const float* v = a.v + (size_t)b * a.in_stride_tok * D;
     const float* q = a.q + (size_t)b * a.in_stride_tok * D;
@@ -335,14 +342,17 @@ __global__ void __launch_bounds__(FastGeom<D>::NT, (D == 64 && !FROZEN) ? 4 : 1)
                 slot++;
             }
             const float yv = fast_readout<D>(M, qb + tl * D, cg);
-            if (cg == 0) ys[tl * D + r] = yv;
+            if (cg == 0) ys[tl * ROWS + (r - part * ROWS)] = yv;
         }
         __syncthreads();
         {
-            const int nvec = ntok * (D / 4);
-            float4* yd = reinterpret_cast<float4*>(y + (size_t)t0 * D);
+            // this CTA's ROWS entries of every output row
+            const int nvec = ntok * (ROWS / 4);
             const float4* ysv = reinterpret_cast<const float4*>(ys);
-            for (int i = tid; i < nvec; i += NT) yd[i] = ysv[i];
+            for (int i = tid; i < nvec; i += NT) {
+                const int tl = i / (ROWS / 4), c = i - tl * (ROWS / 4);
+                *reinterpret_cast<float4*>(y + (size_t)(t0 + tl) * D + part * ROWS + 4 * c) = ysv[i];
+            }
         }
     }
     if (mode == STORE_CHUNK) {
@@ -679,10 +689,34 @@ inline bool fast_common_ok(int d, float clip, float mmax)
     return (d == 64 || d == 32) && !(clip > 0.0f) && !m_norm_enabled(mmax);
 }
 
+// Number of SMs of the current device (queried once per process).
+inline int sm_count()
+{
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0, v = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess &&
+            cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0) n = v;
+        else n = 148;
+    }
+    return n;
+}
+// With no more problems than SMs, every problem's rows are divided over two CTAs (two SMs): the
+// run time of these kernels is then set by the per-token dependency chain of one CTA, not by
+// throughput, and half the rows per CTA shortens it.
+inline bool split_rows(int d, int batch) { return d == 64 && batch <= sm_count() && option_value(NLH_OPT_ROW_SPLIT) != 0; }
+
 template <int D, int RULE>
 static bool fast_fwd_launch(const FwdArgs& a, cudaStream_t st)
 {
     const size_t smem = fast_fwd_smem_floats<D>() * sizeof(float);
+    if constexpr (D == 64) {
+        if (!a.frozen && split_rows(a.d, a.batch)) {
+            if (smem > 48 * 1024) cudaFuncSetAttribute(fast_fwd_kernel<D, RULE, false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            fast_fwd_kernel<D, RULE, false, 2><<<a.batch * 2, FastGeom<D, 2>::NT, smem, st>>>(a);
+            return true;
+        }
+    }
     if (a.frozen) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(fast_fwd_kernel<D, RULE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         fast_fwd_kernel<D, RULE, true><<<a.batch, FastGeom<D>::NT, smem, st>>>(a);

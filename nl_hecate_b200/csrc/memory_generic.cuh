@@ -243,8 +243,8 @@ __global__ void __launch_bounds__(GEN_THREADS) gen_phase2_fwd_kernel(
     }
 }
 
-// One token of the reverse pass, executed by the whole CTA. See the oracle's
-// titans/delta/hebbian backward for the order of operations. d_M/d_S live in
+// One token of the reverse pass, executed by the whole CTA, in the order of operations of the
+// reference's rust_{titans,delta,hebbian}_backward (core/src/dispatch.rs:1300-1660). d_M/d_S live in
 // global work buffers owned (by row) by warps.
 template <int RULE, bool FROZEN>
 __device__ __forceinline__ void gen_bwd_token(

@@ -109,4 +109,19 @@ int32_t nlh_set_option(int32_t option, int32_t value)
 }
 int32_t nlh_abi_version(void) { return 1; }
 
+// SimpleRng of the reference (core/src/tensor.rs:380-408), host side.
+void nlh_simple_rng_fill(uint64_t* state, float scale, float* out_host, int64_t n)
+{
+    if (!state || !out_host || n <= 0) return;
+    uint64_t s = *state == 0 ? 1 : *state;
+    for (int64_t i = 0; i < n; i++) {
+        s ^= s << 13;
+        s ^= s >> 7;
+        s ^= s << 17;
+        const double u = (double)s / 18446744073709551615.0;
+        out_host[i] = (2.0f * (float)u - 1.0f) * scale;
+    }
+    *state = s;
+}
+
 }  // extern "C"

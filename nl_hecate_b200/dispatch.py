@@ -326,6 +326,25 @@ def swa_backward_lse(q, k, v, out, lse, d_out, num_heads, head_dim, window, n_pe
     return dq, dk, dv
 
 
+def swa_forward_f32(q, k, v, num_heads, head_dim, window, n_persistent=0):
+    """fp32 SWA (nlh_swa_forward_f32): q, k, v fp32 [B, S, H*hd]; returns (out fp32, lse)."""
+    b, s, _ = q.shape
+    out = torch.empty_like(q)
+    lse = _f32(b, num_heads, s, device=q.device)
+    call("nlh_swa_forward_f32", q=q, k=k, v=v, out=out, lse=lse, seq_len=s, num_heads=num_heads,
+         head_dim=head_dim, window_size=window, batch_size=b, n_persistent=n_persistent)
+    return out, lse
+
+
+def swa_backward_f32(q, k, v, out, lse, d_out, num_heads, head_dim, window, n_persistent=0):
+    b, s, td = q.shape
+    dq, dk, dv = (torch.empty(b, s, td, dtype=torch.float32, device=q.device) for _ in range(3))
+    call("nlh_swa_backward_f32", q=q, k=k, v=v, out=out, lse=lse, d_attn_out=d_out, d_q=dq, d_k=dk,
+         d_v=dv, seq_len=s, num_heads=num_heads, head_dim=head_dim, window_size=window,
+         batch_size=b, n_persistent=n_persistent)
+    return dq, dk, dv
+
+
 # ── AdamW ──────────────────────────────────────────────────────────────────
 def adamw_update_dd(w, g, m, v, lr, beta1, beta2, eps, bc1_inv, bc2_inv, weight_decay):
     call("adamw_update_cuda", w=w, g=g, m=m, v=v, n=w.numel(), lr=lr, beta1=beta1, beta2=beta2,

@@ -17,7 +17,8 @@ HEADER = os.path.join(os.path.dirname(HERE), "include", "nlh_ffi.h")
 NLH_OK = 0
 
 _SCALARS = {
-    "int32_t": C.c_int32, "int64_t": C.c_int64, "uint32_t": C.c_uint32, "float": C.c_float,
+    "int32_t": C.c_int32, "int64_t": C.c_int64, "uint32_t": C.c_uint32, "uint64_t": C.c_uint64,
+    "float": C.c_float,
     "int": C.c_int,
 }
 

@@ -8,8 +8,10 @@ tape through the C ABI; the dense projections are fp32 PyTorch matmuls.
 Follows the CPU reference where its CPU and GPU paths differ: ONE memory of size d_model
 (core/src/mag.rs:120-125), memory projections multiply by the bf16-rounded copy of
 W_{k,v,q}_mem while the gradient goes to the fp32 master (core/src/bf16.rs:54-115), gate -> k/v
-gradient included, M_0 = S_0 = 0 for every sequence. SWA runs on bf16-rounded q, k, v like the
-reference's GPU dispatch (core/src/dispatch.rs:478-560).
+gradient included, M_0 = S_0 = 0 for every sequence. With fp32_swa (default) the attention runs
+in fp32 like the reference's CPU path (core/src/swa.rs:33-235), so the whole configuration is
+fp32; fp32_swa = False rounds q, k, v to bf16 and runs the tensor-core pair like the reference's
+GPU dispatch (core/src/dispatch.rs:478-560).
 """
 from __future__ import annotations
 
@@ -41,9 +43,12 @@ def _bf16_weights(w):
 
 
 class MAGSingle:
-    """params: dict of fp32 tensors named as in oracle.mag_single.init_params."""
+    """params: dict of fp32 arrays keyed by the reference's MAGParams field names: w_embed [vocab, d],
+    w_unembed [d, vocab], w_q, w_k, w_v, w_o, w_k_mem, w_v_mem, w_q_mem [d, d], w_alpha, w_theta
+    (and w_eta for Titans) [2d], b_alpha, b_theta (b_eta) [1]."""
 
-    def __init__(self, params, num_heads, window, rule="delta", device="cuda"):
+    def __init__(self, params, num_heads, window, rule="delta", device="cuda", fp32_swa=True):
+        self.fp32_swa = fp32_swa
         self.p = {n: torch.as_tensor(a, dtype=torch.float32).to(device).clone().requires_grad_(True)
                   for n, a in params.items()}
         self.num_heads, self.window, self.rule = num_heads, window, rule
@@ -56,7 +61,8 @@ class MAGSingle:
         vocab, d = p["w_embed"].shape
         hd = d // self.num_heads
         emb = p["w_embed"][input_ids]                                       # [B, S, d]
-        q, k, v = (torch.nn.functional.linear(emb, p[n]).to(torch.bfloat16).contiguous()
+        sdt = torch.float32 if self.fp32_swa else torch.bfloat16
+        q, k, v = (torch.nn.functional.linear(emb, p[n]).to(sdt).contiguous()
                    for n in ("w_q", "w_k", "w_v"))
         attn = _SWA.apply(q, k, v, self.num_heads, hd, self.window).float()
         w_kvq = torch.cat([_bf16_weights(p[n]) for n in ("w_k_mem", "w_v_mem", "w_q_mem")], dim=0)

@@ -108,20 +108,25 @@ class _TitansMemory(torch.autograd.Function):
 
 
 class _SWA(torch.autograd.Function):
-    """Sliding-window attention over [B, S, H*hd] bf16 (nlh_swa_forward / nlh_swa_backward)."""
+    """Sliding-window attention over [B, S, H*hd]: bf16 inputs run the tensor-core pair
+    (nlh_swa_forward / nlh_swa_backward), fp32 inputs the fp32 pair (nlh_swa_forward_f32 /
+    nlh_swa_backward_f32)."""
 
     @staticmethod
     def forward(ctx, q, k, v, num_heads, head_dim, window):
-        out, lse = D.swa_forward_lse(q, k, v, num_heads, head_dim, window)
+        f32 = q.dtype == torch.float32
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        out, lse = (D.swa_forward_f32 if f32 else D.swa_forward_lse)(q, k, v, num_heads, head_dim, window)
         ctx.save_for_backward(q, k, v, out, lse)
-        ctx.cfg = (num_heads, head_dim, window)
+        ctx.cfg = (num_heads, head_dim, window, f32)
         return out
 
     @staticmethod
     def backward(ctx, d_out):
         q, k, v, out, lse = ctx.saved_tensors
-        nh, hd, w = ctx.cfg
-        dq, dk, dv = D.swa_backward_lse(q, k, v, out, lse, d_out.float().contiguous(), nh, hd, w)
+        nh, hd, w, f32 = ctx.cfg
+        bwd = D.swa_backward_f32 if f32 else D.swa_backward_lse
+        dq, dk, dv = bwd(q, k, v, out, lse, d_out.float().contiguous(), nh, hd, w)
         return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), None, None, None
 
 
@@ -381,6 +386,63 @@ class _CrossEntropy(torch.autograd.Function):
         return logits, None
 
 
+class _Linear(torch.autograd.Function):
+    """y = x W^T (or x W when transposed) on bf16 tensor cores, with the weight's bf16 copy taken
+    from the model's per-step shadow arena (one cast of the whole arena per forward instead of one
+    per weight) and the weight gradient added straight into the weight's slice of the fp32
+    gradient arena (no per-weight cast and accumulation kernels). w itself is an input only so
+    that the tape records the Function; no gradient is returned for it."""
+
+    @staticmethod
+    def forward(ctx, x, w, w16, grad_view, transposed):
+        x16 = x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
+        y = torch.matmul(x16, w16) if transposed else F.linear(x16, w16)
+        ctx.save_for_backward(x16, w16)
+        ctx.grad_view, ctx.transposed, ctx.x_dtype = grad_view, transposed, x.dtype
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x16, w16 = ctx.saved_tensors
+        dy16 = dy if dy.dtype == torch.bfloat16 else dy.to(torch.bfloat16)
+        dy2, x2 = dy16.reshape(-1, dy16.shape[-1]), x16.reshape(-1, x16.shape[-1])
+        if ctx.transposed:                       # y = x W, W [in, out]
+            dx = torch.matmul(dy16, w16.t())
+            ctx.grad_view.add_(torch.matmul(x2.t(), dy2))
+        else:                                    # y = x W^T, W [out, in]
+            dx = torch.matmul(dy16, w16)
+            ctx.grad_view.add_(torch.matmul(dy2.t(), x2))
+        return (dx if ctx.x_dtype == torch.bfloat16 else dx.to(ctx.x_dtype)), None, None, None, None
+
+
+class _Embedding(torch.autograd.Function):
+    """x[t] = w_embed[ids[t]] through embedding_gather_cuda; the backward scatter-adds the output
+    gradient straight into grad_out (the embedding's slice of the gradient arena,
+    embedding_scatter_add_cuda), so no dense [vocab, d] temporary and no accumulation pass exist.
+    Because of that side effect the Function returns no gradient for w_embed itself (w_embed is
+    an input only so that the tape records the Function)."""
+
+    @staticmethod
+    def forward(ctx, ids, w_embed, grad_out):
+        B, S = ids.shape
+        d = w_embed.shape[1]
+        ids32 = ids.reshape(-1).to(torch.int32).contiguous()
+        out = torch.empty(B * S, d, dtype=torch.float32, device=w_embed.device)
+        D.call("embedding_gather_cuda", w_embed=w_embed, input_ids=ids32, output=out, seq_len=B * S, d=d)
+        ctx.save_for_backward(ids32)
+        ctx.grad_out = grad_out
+        ctx.mark_non_differentiable(ids32)
+        return out.view(B, S, d)
+
+    @staticmethod
+    def backward(ctx, d_x):
+        (ids32,) = ctx.saved_tensors
+        d_x = d_x.contiguous().float()
+        D.call("embedding_scatter_add_cuda", d_embedded=d_x.view(-1, d_x.shape[-1]), input_ids=ids32,
+               d_embed=ctx.grad_out, seq_len=ids32.numel(), d=d_x.shape[-1])
+        return None, None, None
+
+
 def titans_memory(k, v, q, alpha, theta, eta, m0, chunk, slot=0):
     return _TitansMemory.apply(k, v, q, alpha, theta, eta, m0, chunk, slot)
 
@@ -430,6 +492,12 @@ class StackedMAG:
             w.grad = self.opt.view(self.opt.g, i).view(s)
             self.p[n], self.g[n] = w, w.grad
         self._init(seed)
+        # bf16 shadow of the parameter arena (GEMM operands), refreshed at the start of every forward
+        self._w16, self.p16 = None, {}
+        if cfg.bf16 and self.device.type == "cuda":
+            self._w16 = torch.empty_like(self.opt.w, dtype=torch.bfloat16)
+            for i, (n, sh) in enumerate(zip(names, shapes)):
+                self.p16[n] = self.opt.view(self._w16, i).view(sh)
         # carried memory: one slot per (block, level, local sequence, head)
         nh, hd = cfg.num_heads, cfg.head_dim
         self.context = [[torch.zeros(batch_per_rank * nh, hd * hd, device=self.device)
@@ -439,39 +507,78 @@ class StackedMAG:
 
     @torch.no_grad()
     def _init(self, seed):
+        """Seeded initialisation of the reference, draw for draw: StackedMAGParams::init and
+        BlockParams::init (core/src/stacked_model.rs:69-119,172-208) with
+        MemoryLevelParams::init_with_depth (core/src/model.rs:462-499). One xorshift64 stream
+        (SimpleRng) per scope: `seed` for the embedding and unembedding, seed + 10000 (b + 1) for
+        block b's attention projections, that + 1000 + 500 l for its level l."""
+        import ctypes as C
+        import numpy as np
+        from . import ffi
         cfg = self.cfg
-        d = cfg.d_model
-        g = torch.Generator(device=self.device).manual_seed(seed)
-        u = lambda t, sc: t.uniform_(-sc, sc, generator=g)
+        d, v, nb = cfg.d_model, cfg.vocab, cfg.n_blocks
+        lib = ffi.lib()
+
+        class Stream:
+            def __init__(self, sd):
+                self.state = C.c_uint64(max(int(sd) & 0xFFFFFFFFFFFFFFFF, 1))
+
+            def fill(self, dst, scale):
+                buf = np.empty(dst.numel(), dtype=np.float32)
+                lib.nlh_simple_rng_fill(C.byref(self.state), C.c_float(scale),
+                                        buf.ctypes.data_as(C.c_void_p), C.c_int64(buf.size))
+                dst.copy_(torch.from_numpy(buf).view(dst.shape))
+
+        p = self.p
         proj = math.sqrt(2.0 / (d + d))
-        depth = 1.0 / math.sqrt(2.0 * cfg.n_blocks)     # core/src/stacked_model.rs:75-79
+        depth = 1.0 / math.sqrt(2.0 * nb)              # GPT-2 depth scaling of output projections
         gate = math.sqrt(1.0 / (2 * d))
-        for n, w in self.p.items():
-            base = n.split(".")[-1]
-            if base in ("w_embed", "w_unembed"):
-                u(w, math.sqrt(2.0 / (d + cfg.vocab)))
-            elif base == "w_qkv":
-                u(w, proj)
-            elif base in ("w_o", "w_kvq_mem"):
-                u(w, proj * depth)
-            elif base == "w_gates":
-                u(w, gate)
-            elif base.endswith("gamma"):
-                w.fill_(1.0)
-            elif base in ("b_alpha", "b_theta", "b_eta"):
-                lvl = int(n.split(".")[1][1:])
-                w.fill_({"b_alpha": B_ALPHA, "b_theta": B_THETA, "b_eta": B_ETA}[base][lvl])
-            else:
-                w.zero_()
+        emb = math.sqrt(1.0 / d)
+        rng = Stream(seed)
+        rng.fill(p["w_embed"], emb)
+        rng.fill(p["w_unembed"], emb)
+        p["ln_final_gamma"].fill_(1.0); p["ln_final_beta"].zero_()
+        for b in range(nb):
+            pre = f"b{b}."
+            bseed = seed + 10_000 + b * 10_000
+            brng = Stream(bseed)
+            w_qkv = p[pre + "w_qkv"]
+            for i in range(3):                          # w_q, w_k, w_v in the packed [q; k; v] rows
+                brng.fill(w_qkv[i * d:(i + 1) * d], proj)
+            brng.fill(p[pre + "w_o"], proj * depth)
+            for n in ("ln_attn_", "ln_mem_"):
+                p[pre + n + "gamma"].fill_(1.0); p[pre + n + "beta"].zero_()
+            p[pre + "alpha_mem"].zero_()
+            for l in range(cfg.k):
+                q_ = pre + f"l{l}."
+                lrng = Stream(bseed + 1000 + l * 500)
+                w_kvq = p[q_ + "w_kvq_mem"]
+                for i in range(3):                      # w_k_mem, w_v_mem, w_q_mem
+                    lrng.fill(w_kvq[i * d:(i + 1) * d], proj * depth)
+                for i in range(3):                      # w_alpha, w_theta, w_eta
+                    lrng.fill(p[q_ + "w_gates"][i], gate)
+                p[q_ + "b_alpha"].fill_(B_ALPHA[l]); p[q_ + "b_theta"].fill_(B_THETA[l]); p[q_ + "b_eta"].fill_(B_ETA[l])
         if cfg.tie_embeddings:
             self.p["w_embed"].copy_(self.p["w_unembed"].t())
 
     # ── forward ────────────────────────────────────────────────────────────
-    def _mm(self, x, w):
-        """x [.., in] times w^T, w [out, in]; bf16 tensor-core GEMM when cfg.bf16."""
+    def _mm(self, x, name, transposed=False):
+        """x [.., in] times W^T (W = parameter `name`, [out, in]; transposed: x times W, W [in, out]).
+        bf16 tensor-core GEMM when cfg.bf16: on the GPU through _Linear (shadow bf16 weights, weight
+        gradient straight into the arena), else plain PyTorch operators."""
+        w = self.p[name]
+        if self.cfg.bf16 and x.is_cuda and self._w16 is not None:
+            return _Linear.apply(x, w, self.p16[name], self.g[name], transposed)
         if self.cfg.bf16:
-            return F.linear(x.to(torch.bfloat16), w.to(torch.bfloat16))
-        return F.linear(x.float(), w)
+            w16 = w.to(torch.bfloat16)
+            return torch.matmul(x.to(torch.bfloat16), w16) if transposed else F.linear(x.to(torch.bfloat16), w16)
+        return torch.matmul(x.float(), w) if transposed else F.linear(x.float(), w)
+
+    def _refresh_shadow(self):
+        """bf16 copy of the whole parameter arena for this forward (one kernel)."""
+        if self._w16 is not None:
+            with torch.no_grad():
+                self._w16.copy_(self.opt.w)
 
     def _level(self, b, l, m_in):
         cfg, p = self.cfg, self.p
@@ -482,7 +589,7 @@ class StackedMAG:
         sf = S // c
         x = m_in.view(B, sf, c, d).mean(2) if c > 1 else m_in
         pre = f"b{b}.l{l}."
-        kvq = self._mm(x, p[pre + "w_kvq_mem"]).float()
+        kvq = self._mm(x, pre + "w_kvq_mem").float()
         k, v, q = kvq.split(d, dim=-1)
         k = k / k.norm(dim=-1, keepdim=True).clamp_min(1e-8)
         q = q / q.norm(dim=-1, keepdim=True).clamp_min(1e-8)
@@ -506,7 +613,7 @@ class StackedMAG:
         cfg, p = self.cfg, self.p
         sf = x.shape[1]
         pre = f"b{b}.l{l}."
-        kvq = self._mm(x, p[pre + "w_kvq_mem"])
+        kvq = self._mm(x, pre + "w_kvq_mem")
         k, v, q, alpha, theta, eta = _LevelPrep.apply(kvq, p[pre + "w_gates"], p[pre + "b_alpha"],
                                                       p[pre + "b_theta"], p[pre + "b_eta"],
                                                       cfg.num_heads, slot)
@@ -553,17 +660,23 @@ class StackedMAG:
         d, nh, hd = cfg.d_model, cfg.num_heads, cfg.head_dim
         fused = (cfg.fused_glue and tokens.is_cuda and cfg.k <= 4 and d <= 1024 and hd % 4 == 0)
         lp = 1 if (fused and cfg.bf16) else 0           # LayerNorm output feeding only a GEMM
-        x = F.embedding(tokens, p["w_embed"])
+        self._refresh_shadow()
+        if fused:
+            x = _Embedding.apply(tokens, p["w_embed"], self.g["w_embed"])
+        else:
+            x = F.embedding(tokens, p["w_embed"])
         for b in range(cfg.n_blocks):
             pre = f"b{b}."
             h = self._ln(x, pre + "ln_attn_", lp, fused)
-            qkv = self._mm(h, p[pre + "w_qkv"]).to(torch.bfloat16)
-            if fused and self.swa_fn is swa:
+            qkv = self._mm(h, pre + "w_qkv")
+            if cfg.bf16 or not qkv.is_cuda:
+                qkv = qkv.to(torch.bfloat16)          # fp32 configurations keep fp32 attention on the GPU
+            if fused and self.swa_fn is swa and qkv.dtype == torch.bfloat16:
                 attn = _SWAPacked.apply(qkv, nh, hd, cfg.window)
             else:
                 q, k, v = (t.contiguous() for t in qkv.split(d, dim=-1))
                 attn = self.swa_fn(q, k, v, nh, hd, cfg.window)
-            attn_raw = self._mm(attn, p[pre + "w_o"])
+            attn_raw = self._mm(attn, pre + "w_o")
             res1 = x + attn_raw
             wts = torch.softmax(p[pre + "alpha_mem"], dim=0)
             if fused:
@@ -587,7 +700,7 @@ class StackedMAG:
                     y = yl if y is None else y + yl
                 x = x + attn_proj * torch.sigmoid(y)
         x = self._ln(x, "ln_final_", lp, fused)
-        logits = self._mm(x, p["w_unembed"].t())
+        logits = self._mm(x, "w_unembed", transposed=True)
         if fused:
             return _CrossEntropy.apply(logits.view(-1, cfg.vocab), targets.reshape(-1).to(torch.int32))
         return F.cross_entropy(logits.float().view(-1, cfg.vocab), targets.reshape(-1))

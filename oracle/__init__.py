@@ -169,11 +169,17 @@ def delta_backward(k, v, q, alpha, theta, m_states, d_y, error_clip=0.0, d_m_see
     return o
 
 
-def titans_forward(k, v, q, alpha, theta, eta, m0, s0, error_clip=0.0, m_norm_max=0.0):
+def titans_forward(k, v, q, alpha, theta, eta, m0, s0, error_clip=0.0, m_norm_max=0.0, out=None):
+    """out: optional (m_states, s_states) float32 arrays of shape [(s+1), d*d] to write into (a
+    caller that runs many steps reuses them instead of paying fresh page faults every call)."""
     k, v, q, alpha, theta, eta, m0, s0 = map(_f, (k, v, q, alpha, theta, eta, m0, s0))
     s, d = k.shape
-    ms = np.empty((s + 1, d * d), dtype=np.float32)
-    ss = np.empty((s + 1, d * d), dtype=np.float32)
+    if out is not None:
+        ms, ss = out
+        assert ms.shape == (s + 1, d * d) and ss.shape == (s + 1, d * d)
+    else:
+        ms = np.empty((s + 1, d * d), dtype=np.float32)
+        ss = np.empty((s + 1, d * d), dtype=np.float32)
     y = np.empty((s, d), dtype=np.float32)
     lib().orc_titans_forward(_p(k), _p(v), _p(q), _p(alpha), _p(theta), _p(eta), _p(m0), _p(s0),
                              _p(ms), _p(ss), _p(y), C.c_int(s), C.c_int(d), _cf(error_clip),

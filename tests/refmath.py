@@ -104,7 +104,7 @@ def _ln64(x, gamma, beta, eps=1e-5):
     return gamma * (x - mu) / np.sqrt(var + eps) + beta
 
 
-def stacked_mag_loss64(p, cfg, tokens, targets, context):
+def stacked_mag_loss64(p, cfg, tokens, targets, context, round_bf16=True):
     """Loss of the stacked MAG model (one call = one forward over [B, S] token ids) in float64
     numpy, an independent statement of the block composition of
     core/src/gpu_stacked_forward.rs:1656-1960 as the harness runs it in its fp32 mode:
@@ -114,7 +114,8 @@ def stacked_mag_loss64(p, cfg, tokens, targets, context):
     levels >= 1 frozen-M0 with chunk = min(chunk size, pooled length)), repeat-upsample ->
     softmax(alpha_mem)-weighted sum -> out = x + attn_proj * sigmoid(y); final LayerNorm,
     unembedding, mean cross-entropy. `context[b][l]` ([B*H, hd*hd] float64) is the carried memory:
-    read as M_0 and overwritten with the final M, like the harness does."""
+    read as M_0 and overwritten with the final M, like the harness does. round_bf16 = False keeps
+    q, k, v and the attention output in full precision (the fp32 configuration)."""
     P = {k_: np.asarray(v_, dtype=np.float64) for k_, v_ in p.items()}
     d, nh, hd = cfg["d_model"], cfg["num_heads"], cfg["d_model"] // cfg["num_heads"]
     tok, tgt = np.asarray(tokens), np.asarray(targets)
@@ -124,10 +125,13 @@ def stacked_mag_loss64(p, cfg, tokens, targets, context):
     for b in range(cfg["n_blocks"]):
         pre = f"b{b}."
         h = _ln64(x, P[pre + "ln_attn_gamma"], P[pre + "ln_attn_beta"])
-        qkv = _bf16_round64(h @ P[pre + "w_qkv"].T)
+        qkv = h @ P[pre + "w_qkv"].T
+        if round_bf16:
+            qkv = _bf16_round64(qkv)
         q, k, v = qkv[..., :d], qkv[..., d:2 * d], qkv[..., 2 * d:]
         attn = np.stack([swa_forward64(q[i], k[i], v[i], nh, hd, cfg["window"]) for i in range(B)])
-        attn = _bf16_round64(attn)
+        if round_bf16:
+            attn = _bf16_round64(attn)
         attn_proj = attn @ P[pre + "w_o"].T
         m_in = _ln64(x + attn_proj, P[pre + "ln_mem_gamma"], P[pre + "ln_mem_beta"])
         wts = np.exp(P[pre + "alpha_mem"] - P[pre + "alpha_mem"].max())

@@ -497,6 +497,42 @@ def test_titans_exact_without_momentum_trajectory(D, orc, d, s, n):
                       "d_s_initial"])
 
 
+@pytest.mark.parametrize("n,s", [(3, 40), (1, 9), (6, 130)])
+def test_row_split_exact_pair_matches_one_cta_per_problem(D, orc, n, s):
+    """With no more problems than SMs the exact head_dim-64 kernels divide every problem's rows over
+    two CTAs (option NLH_OPT_ROW_SPLIT, default on); the M-only backward then adds two partial sums
+    into d_q, d_k and the gate gradients, which it zeroes itself. Both modes against the oracle, with
+    the outputs pre-filled with garbage in split mode (nothing may depend on the caller's zeroing)."""
+    import torch
+    p = make_problem(orc, n, s, 64, 5200 + n + s, "rand")
+    w = oracle_exact(orc, "titans", p)
+    t = to_dev(p)
+    for on in (1, 0):
+        D.call("nlh_set_option", option=3, value=on)
+        try:
+            ms, ss, y = D.titans_forward_dd(t["k"], t["v"], t["q"], t["alpha"], t["theta"], t["eta"],
+                                            t["m0"], t["s0"], store_s=False)
+            assert rel_err(_np(y), w["y"]) <= REL and rel_err(_np(ms), w["m_states"]) <= REL
+            ms2, ss2, y2 = D.titans_forward_dd(t["k"], t["v"], t["q"], t["alpha"], t["theta"], t["eta"],
+                                               t["m0"], t["s0"])
+            assert rel_err(_np(ss2), w["s_states"]) <= REL and torch.equal(y, y2)
+            nan = lambda like: torch.full_like(like, float("nan"))
+            g = dict(d_k=nan(t["k"]), d_v=nan(t["k"]), d_q=nan(t["k"]), d_alpha=nan(t["alpha"]),
+                     d_theta=nan(t["alpha"]), d_eta=nan(t["alpha"]),
+                     d_m_initial=torch.zeros(64 * 64, device="cuda"), d_s_initial=torch.zeros(64 * 64, device="cuda"))
+            if not on:   # one CTA per problem follows the drop-in contract: d_k, d_v, d_q pre-zeroed
+                for key in ("d_k", "d_v", "d_q"):
+                    g[key].zero_()
+            D.call("titans_backward_f32_cuda", k_mem=t["k"], v_mem=t["v"], q_mem=t["q"], alpha=t["alpha"],
+                   theta=t["theta"], eta=t["eta"], m_states=ms, s_states=None, d_y=t["dy"], d_k_mem=g["d_k"],
+                   d_v_mem=g["d_v"], d_q_mem=g["d_q"], d_alpha=g["d_alpha"], d_theta=g["d_theta"],
+                   d_eta=g["d_eta"], d_m_initial=g["d_m_initial"], d_s_initial=g["d_s_initial"], seq_len=s,
+                   d=64, batch_size=n, error_clip=0.0)
+        finally:
+            D.call("nlh_set_option", option=3, value=1)
+        _check_bwd(g, w, ["d_k", "d_v", "d_q", "d_alpha", "d_theta", "d_eta", "d_m_initial", "d_s_initial"])
+
+
 def test_null_momentum_trajectory_rejected_off_the_fast_path(D, orc):
     p = make_problem(orc, 1, 6, 16, 2990, "rand")   # d = 16 runs the generic kernels
     t = to_dev(p)

@@ -425,3 +425,112 @@ def test_mag_single_model_gradients_match_float64_finite_differences(orc, rule, 
         an = float((g[name].astype(np.float64) * u).sum())
         scale = float(np.abs(g[name]).astype(np.float64).sum()) + 1e-12
         assert abs(fd - an) <= 2e-3 * abs(fd) + 2e-5 * scale, (name, fd, an)
+
+
+def _stacked_setup(orc, mode="resident", **kw):
+    from oracle import stacked as ST
+    cfg = ST.Cfg(d_model=16, num_heads=2, n_blocks=2, k=3, chunk_sizes=(1, 2, 8), seq_len=16, window=8,
+                 vocab=32, exact_levels=(0,), mode=mode)
+    for k_, v_ in kw.items():
+        setattr(cfg, k_, v_)
+    p = ST.init_params(cfg, seed=42)
+    rng = np.random.default_rng(3)
+    for n in p:                                   # make every branch matter
+        base = n.split(".")[-1]
+        if base.endswith("gamma"):
+            p[n] = (p[n] + 0.2 * rng.standard_normal(p[n].shape)).astype(np.float32)
+        elif base.endswith("beta") or base == "alpha_mem":
+            p[n] = (p[n] + 0.3 * rng.standard_normal(p[n].shape)).astype(np.float32)
+        elif base == "b_theta":
+            p[n] = np.array([-1.0], np.float32)
+        elif base == "b_alpha":
+            p[n] = np.array([-2.0], np.float32)
+        elif base == "w_kvq_mem":
+            p[n] = (p[n] * 3.0).astype(np.float32)
+    return ST, cfg, p
+
+
+def test_stacked_oracle_init_follows_the_reference_streams(orc):
+    """StackedMAGParams::init draw order (core/src/stacked_model.rs:69-119,172-208): one SimpleRng
+    stream per scope, seeds seed / seed + 10000 (b + 1) / that + 1000 + 500 l."""
+    from oracle import stacked as ST
+    cfg = ST.Cfg(d_model=8, num_heads=1, n_blocks=2, k=2, chunk_sizes=(1, 2), seq_len=4, window=4, vocab=16)
+    p = ST.init_params(cfg, seed=42)
+    d, v = 8, 16
+    top = orc.SimpleRng(42)
+    assert np.array_equal(p["w_embed"].ravel(), top.fill_uniform(v * d, float(np.sqrt(1.0 / d))))
+    assert np.array_equal(p["w_unembed"].ravel(), top.fill_uniform(d * v, float(np.sqrt(1.0 / d))))
+    blk = orc.SimpleRng(42 + 10_000 + 10_000)                       # block 1
+    proj, depth = float(np.sqrt(2.0 / (2 * d))), float(1.0 / np.sqrt(2.0 * 2))
+    for i in range(3):
+        assert np.array_equal(p["b1.w_qkv"][i * d:(i + 1) * d].ravel(), blk.fill_uniform(d * d, proj))
+    assert np.array_equal(p["b1.w_o"].ravel(), blk.fill_uniform(d * d, proj * depth))
+    lvl = orc.SimpleRng(42 + 20_000 + 1000 + 500)                   # block 1, level 1
+    for i in range(3):
+        assert np.array_equal(p["b1.l1.w_kvq_mem"][i * d:(i + 1) * d].ravel(), lvl.fill_uniform(d * d, proj * depth))
+    for i in range(3):
+        assert np.array_equal(p["b1.l1.w_gates"][i], lvl.fill_uniform(2 * d, float(np.sqrt(1.0 / (2 * d)))))
+    assert p["b1.l1.b_alpha"][0] == 4.0 and p["b1.l1.b_theta"][0] == np.float32(-5.6) and p["b1.l1.b_eta"][0] == 2.0
+
+
+def test_stacked_oracle_matches_float64_statement_and_finite_differences(orc):
+    """oracle/stacked.py (GPU-resident level semantics, fp32) against the independent float64
+    statement of the same composition: the loss over two consecutive calls (carried memories),
+    and the gradient of sampled entries of EVERY parameter tensor against central differences."""
+    from refmath import stacked_mag_loss64
+    ST, cfg, p = _stacked_setup(orc)
+    cfgd = dict(d_model=cfg.d_model, num_heads=cfg.num_heads, n_blocks=cfg.n_blocks, k=cfg.k,
+                chunk_sizes=cfg.chunk_sizes, window=cfg.window, exact_levels=cfg.exact_levels)
+    nh, hd = cfg.num_heads, cfg.d_model // cfg.num_heads
+    ids = orc.rng_tokens(9, cfg.vocab, 2 * (cfg.seq_len + 1)).reshape(2, -1)
+    ctx = ST.new_context(cfg)
+    ctx64 = [[np.zeros((nh, hd * hd)) for _ in range(cfg.k)] for _ in range(cfg.n_blocks)]
+    p64 = {n: a.astype(np.float64) for n, a in p.items()}
+    for call in range(2):
+        x, t = ids[call, :-1], ids[call, 1:]
+        ctx_before = [[c.copy() for c in row] for row in ctx64]
+        loss, g = ST.forward_backward(p, x, t, ctx, cfg)
+        want = stacked_mag_loss64(p64, cfgd, x[None], t[None], ctx64, round_bf16=False)
+        assert abs(loss - want) <= 1e-4 * abs(want), (call, loss, want)
+    # finite differences at the second call (non-zero carried memory)
+    rng = np.random.default_rng(0)
+
+    def loss_at(name, idx, delta):
+        q = dict(p64)
+        a = q[name].copy()
+        a[idx] += delta
+        q[name] = a
+        c = [[m.copy() for m in row] for row in ctx_before]
+        return stacked_mag_loss64(q, cfgd, x[None], t[None], c, round_bf16=False)
+
+    for name, grad in g.items():
+        flat_idx = rng.choice(grad.size, size=min(3, grad.size), replace=False)
+        scale = max(float(np.abs(grad).max()), 1e-8)
+        for fi in flat_idx:
+            idx = np.unravel_index(fi, grad.shape)
+            eps = 1e-5
+            fd = (loss_at(name, idx, eps) - loss_at(name, idx, -eps)) / (2 * eps)
+            assert abs(grad[idx] - fd) <= 3e-3 * scale + 1e-7, (name, idx, float(grad[idx]), fd)
+
+
+def test_stacked_oracle_traced_mode_equals_resident_mode_with_one_head(orc):
+    """What traced_stacked_forward records (one d_model x d_model memory per level, every level an
+    exact rule block on the full-resolution input, bf16-rounded projection weights) is the
+    resident composition with one head, pool factor 1 and all levels exact — when the memory
+    projection weights are bf16-representable, the two modes must agree."""
+    ST, cfg, p = _stacked_setup(orc, num_heads=1, chunk_sizes=(1, 1, 1), exact_levels=(0, 1, 2))
+    for n in p:
+        if n.endswith("w_kvq_mem"):
+            p[n] = orc.bf16_round(p[n].ravel()).reshape(p[n].shape)
+    ids = orc.rng_tokens(11, cfg.vocab, cfg.seq_len + 1)
+    x, t = ids[:-1], ids[1:]
+    out = {}
+    for mode in ("resident", "traced"):
+        cfg.mode = mode
+        ctx = ST.new_context(cfg)
+        ST.forward_backward(p, x, t, ctx, cfg)               # second call sees carried memories
+        out[mode] = ST.forward_backward(p, x, t, ctx, cfg)
+    assert abs(out["resident"][0] - out["traced"][0]) <= 1e-6 * abs(out["traced"][0])
+    for n, a in out["traced"][1].items():
+        b = out["resident"][1][n]
+        assert np.abs(a - b).max() <= 1e-5 * max(np.abs(a).max(), 1e-9), n
