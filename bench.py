@@ -762,14 +762,14 @@ def finish(world, barrier, wl):
     printed / finished its work (barrier), the captured step graph — which holds the
     communicator's captured all-reduce — is dropped, the device is idle, and only then the
     process group is destroyed. A daemon timer ends the process if the teardown itself were to
-    block for more than 90 s (the result line is already out)."""
+    block for more than 30 s (the result line is already out)."""
     sys.stdout.flush()
     sys.stderr.flush()
     if world <= 1:
         return
     import torch
     import torch.distributed as dist
-    watchdog = threading.Timer(90.0, lambda: os._exit(0))
+    watchdog = threading.Timer(30.0, lambda: os._exit(0))
     watchdog.daemon = True
     watchdog.start()
     barrier()

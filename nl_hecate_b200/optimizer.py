@@ -34,7 +34,7 @@ class FlatAdamW:
         off = 0
         for n in self.sizes:
             self.slices.append((off, n))
-            off += (n + 3) // 4 * 4          # keep every tensor 16-byte aligned
+            off += (n + 7) // 8 * 8          # 32-byte aligned in fp32, 16-byte aligned in a bf16 shadow of the arena
         self.arena_len = max(off, 4)
         dev = torch.device(device)
         z = lambda: torch.zeros(self.arena_len, dtype=torch.float32, device=dev)

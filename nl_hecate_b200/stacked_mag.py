@@ -394,11 +394,11 @@ class _Linear(torch.autograd.Function):
     that the tape records the Function; no gradient is returned for it."""
 
     @staticmethod
-    def forward(ctx, x, w, w16, grad_view, transposed):
+    def forward(ctx, x, w, w16, grad_view, transposed, fp32_acc=True):
         x16 = x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
         y = torch.matmul(x16, w16) if transposed else F.linear(x16, w16)
         ctx.save_for_backward(x16, w16)
-        ctx.grad_view, ctx.transposed, ctx.x_dtype = grad_view, transposed, x.dtype
+        ctx.grad_view, ctx.transposed, ctx.x_dtype, ctx.fp32_acc = grad_view, transposed, x.dtype, fp32_acc
         return y
 
     @staticmethod
@@ -406,13 +406,15 @@ class _Linear(torch.autograd.Function):
         x16, w16 = ctx.saved_tensors
         dy16 = dy if dy.dtype == torch.bfloat16 else dy.to(torch.bfloat16)
         dy2, x2 = dy16.reshape(-1, dy16.shape[-1]), x16.reshape(-1, x16.shape[-1])
-        if ctx.transposed:                       # y = x W, W [in, out]
-            dx = torch.matmul(dy16, w16.t())
-            ctx.grad_view.add_(torch.matmul(x2.t(), dy2))
-        else:                                    # y = x W^T, W [out, in]
-            dx = torch.matmul(dy16, w16)
-            ctx.grad_view.add_(torch.matmul(dy2.t(), x2))
-        return (dx if ctx.x_dtype == torch.bfloat16 else dx.to(ctx.x_dtype)), None, None, None, None
+        gv = ctx.grad_view
+        # bf16 operands, fp32 accumulation and output, beta = 1 epilogue: grad += dW in one GEMM
+        a, b = (x2.t(), dy2) if ctx.transposed else (dy2.t(), x2)
+        dx = torch.matmul(dy16, w16.t() if ctx.transposed else w16)
+        if ctx.fp32_acc:
+            torch.addmm(gv, a, b, out_dtype=torch.float32, out=gv)
+        else:
+            gv.add_(torch.matmul(a, b))
+        return (dx if ctx.x_dtype == torch.bfloat16 else dx.to(ctx.x_dtype)), None, None, None, None, None
 
 
 class _Embedding(torch.autograd.Function):
@@ -493,8 +495,12 @@ class StackedMAG:
             self.p[n], self.g[n] = w, w.grad
         self._init(seed)
         # bf16 shadow of the parameter arena (GEMM operands), refreshed at the start of every forward
+        import os
+        self._use_linear = os.environ.get("NLH_MODEL_LINEAR", "1") == "1"
+        self._use_embed = os.environ.get("NLH_MODEL_EMBED", "1") == "1"
+        self._linear_fp32_acc = os.environ.get("NLH_MODEL_LINEAR_FP32", "1") == "1"
         self._w16, self.p16 = None, {}
-        if cfg.bf16 and self.device.type == "cuda":
+        if cfg.bf16 and self.device.type == "cuda" and self._use_linear:
             self._w16 = torch.empty_like(self.opt.w, dtype=torch.bfloat16)
             for i, (n, sh) in enumerate(zip(names, shapes)):
                 self.p16[n] = self.opt.view(self._w16, i).view(sh)
@@ -567,8 +573,8 @@ class StackedMAG:
         bf16 tensor-core GEMM when cfg.bf16: on the GPU through _Linear (shadow bf16 weights, weight
         gradient straight into the arena), else plain PyTorch operators."""
         w = self.p[name]
-        if self.cfg.bf16 and x.is_cuda and self._w16 is not None:
-            return _Linear.apply(x, w, self.p16[name], self.g[name], transposed)
+        if self.cfg.bf16 and x.is_cuda and self._w16 is not None and self._use_linear:
+            return _Linear.apply(x, w, self.p16[name], self.g[name], transposed, self._linear_fp32_acc)
         if self.cfg.bf16:
             w16 = w.to(torch.bfloat16)
             return torch.matmul(x.to(torch.bfloat16), w16) if transposed else F.linear(x.to(torch.bfloat16), w16)
@@ -661,7 +667,7 @@ class StackedMAG:
         fused = (cfg.fused_glue and tokens.is_cuda and cfg.k <= 4 and d <= 1024 and hd % 4 == 0)
         lp = 1 if (fused and cfg.bf16) else 0           # LayerNorm output feeding only a GEMM
         self._refresh_shadow()
-        if fused:
+        if fused and self._use_embed:
             x = _Embedding.apply(tokens, p["w_embed"], self.g["w_embed"])
         else:
             x = F.embedding(tokens, p["w_embed"])
