@@ -381,11 +381,13 @@ class StackedModelStep:
     forward + backward + gradient all-reduce + clip + AdamW."""
     GLOBAL_BATCH, S, VOCAB = 64, 512, 8192
 
-    def __init__(self, world):
+    def __init__(self, world, local_batch=0):
         self.name = "stacked_mag"
         self.world = world
         assert self.GLOBAL_BATCH % world == 0
-        self.local_batch = self.GLOBAL_BATCH // world
+        # local_batch > 0 (--local-batch): run the per-rank shard of a larger job on this GPU alone,
+        # e.g. 8 sequences = one rank of the 8-GPU run, to profile that shape without 8 GPUs
+        self.local_batch = local_batch if local_batch > 0 else self.GLOBAL_BATCH // world
         self.tokens_per_step = self.local_batch * self.S
         self.dtype = "bf16"
 
@@ -566,7 +568,7 @@ class TitansLevel0(TitansPair):
                 lambda: self.bwd(self.dev), streams + n * (s + 1) * d * d * 4, "hbm")
 
 
-def make_workload(name, world=1, small=False):
+def make_workload(name, world=1, small=False, local_batch=0):
     """small: reduced problem counts of the same kernels, sized for profiler captures (inputs still
     larger than L2, a few hundred MB on the device)."""
     if small:
@@ -582,7 +584,7 @@ def make_workload(name, world=1, small=False):
     if name == "adamw":
         return AdamWStep()
     if name == "stacked_mag":
-        return StackedModelStep(world)
+        return StackedModelStep(world, local_batch)
     raise SystemExit(f"unknown workload {name}")
 
 
@@ -644,6 +646,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--small", action="store_true",
                     help="kernel-pair workloads at a reduced problem count (profiler captures)")
+    ap.add_argument("--local-batch", type=int, default=0,
+                    help="stacked_mag only: sequences on this GPU instead of global batch / ranks "
+                         "(profiles the per-rank shape of a multi-GPU run on one GPU)")
     ap.add_argument("--timed-only", action="store_true",
                     help="run only warm-up and the timed steps (for profiler launch lists)")
     args = ap.parse_args()
@@ -666,7 +671,7 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     warmup = max(args.warmup, 3)
 
-    wl = make_workload(args.workload, world, args.small)
+    wl = make_workload(args.workload, world, args.small, args.local_batch)
     wl.setup(torch, dispatch)
 
     def barrier():

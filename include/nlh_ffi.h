@@ -287,7 +287,7 @@ int32_t nlh_swa_backward_f32(const float* q, const float* k, const float* v, con
 /* NLH_OPT_CHUNK_MATRIX (default 1): frozen-M0 chunkwise Titans / Delta entries at head_dim 64 and
  * chunk sizes 16..64 run in chunk-parallel matrix form; 0 selects the per-token kernels. */
 #define NLH_OPT_CHUNK_MATRIX 2
-/* NLH_OPT_ROW_SPLIT (default 1): when a launch has no more problems than the GPU has SMs, the exact
+/* NLH_OPT_ROW_SPLIT (default 1): when a launch has at most half as many problems as the GPU has SMs, the exact
  * head_dim-64 forward and the M-only exact Titans backward divide every problem's rows over two
  * CTAs (the rows of the memory evolve independently; the backward then zeroes d_q, d_k and the gate
  * gradients itself and adds the two partial sums into them). 0 keeps one CTA per problem. */
