@@ -461,12 +461,13 @@ class StackedModelStep:
         bytes_ = (4 + 3) * n * s * d * 4 + 6 * n * s * 4 + n * (s + 1) * d * d * 4
         self._dom = (k, v, q, al, th, et, ms, dy)
         # DRAM bytes of one launch from the profiler capture of this kernel on a smaller case
-        # (296 problems x 128 tokens: 664.94 MB read + 28.05 MB written), scaled by problem-tokens
+        # (296 problems x 512 tokens: 2645.1 MB read + 113.5 MB written), scaled by problem-tokens
         # (the kernel reads each stored state once and streams the rest: traffic is proportional to them)
-        self.dominant_traffic = (664_938_496 + 28_052_224) / (296 * 128) * n * s
+        self.dominant_traffic = (2_645_135_872 + 113_477_632) / (296 * 512) * n * s
         self.dominant_traffic_source = ("literal: dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of "
-                                        "this kernel at 296 problems x 128 tokens (profiles/titans_exact_level0_"
-                                        "kernels.md), scaled by problem-tokens; not re-measured by this run")
+                                        "this kernel at 296 problems x 512 tokens (bench.py --workload titans_level0 "
+                                        "--small; profiles/titans_exact_level0_kernels.md), scaled by problem-tokens; "
+                                        "not re-measured by this run")
         return ("titans_exact_bwd_kernel<64> (exact Titans backward, M-only trajectory) at level-0 shapes",
                 lambda: self.dd.titans_backward_dd(k, v, q, al, th, et, ms, None, dy), bytes_, "hbm")
 

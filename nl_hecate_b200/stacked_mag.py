@@ -73,9 +73,16 @@ class _TitansMemory(torch.autograd.Function):
     chunk == 0: exact rule (titans_forward/backward_f32_cuda, full trajectory);
     chunk > 0 : frozen-M0 chunkwise rule (titans_chunkwise_*_f32_cuda)."""
 
+    _ZEROS = {}
+
     @staticmethod
     def forward(ctx, k, v, q, alpha, theta, eta, m0, chunk, slot=0):
-        s0 = torch.zeros_like(m0)     # momentum restarts every call (gpu_forward.rs:1516-1517)
+        # momentum restarts every call (gpu_forward.rs:1516-1517): S_0 = 0, a read-only buffer that
+        # is created once per shape instead of being filled every call
+        key = (tuple(m0.shape), m0.device)
+        s0 = _TitansMemory._ZEROS.get(key)
+        if s0 is None:
+            s0 = _TitansMemory._ZEROS[key] = torch.zeros_like(m0)
         ctx.slot = slot
         with D.workspace_slot(slot):
             return _TitansMemory._forward(ctx, k, v, q, alpha, theta, eta, m0, s0, chunk)
