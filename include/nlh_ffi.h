@@ -72,7 +72,8 @@ void delta_backward_f32_cuda(const float* k_mem, const float* v_mem, const float
     float* d_k_mem, float* d_v_mem, float* d_q_mem, float* d_alpha, float* d_theta,
     float* d_m_initial, int32_t seq_len, int32_t d, int32_t batch_size, float error_clip);
 /* cuda_ffi.rs:134 / :156 — Titans LMM. d_m_initial/d_s_initial [d*d] are summed
- * over the batch (caller zeroes). Additive: s_states may be NULL in both calls (head_dim 32/64,
+ * over the batch (caller zeroes); additive: both may be NULL, they are then not computed (the
+ * same holds for every backward entry of this header). Additive: s_states may be NULL in both calls (head_dim 32/64,
  * no clip/projection): the forward then writes only the M trajectory and the backward derives
  * S_t = M_t - (1-alpha_{t-1}) M_{t-1} from it (needs eta_t > 0), halving the state traffic. */
 void titans_forward_f32_cuda(const float* k_mem, const float* v_mem, const float* q_mem,
@@ -354,6 +355,17 @@ int32_t nlh_mag_combine_backward(const float* d_out, const void* attn_proj, int3
     int32_t c0, int32_t c1, int32_t c2, int32_t c3, int32_t k, void* d_attn_proj, float* d_ycomb,
     float* dw_partial, int32_t n_partial_rows, float* dy0, float* dy1, float* dy2, float* dy3,
     int32_t batch, int32_t seq, int32_t d_model, int32_t num_heads);
+/* Finishers of the per-CTA partial rows the two backward entries above leave: rows are summed
+ * in a fixed order and ADDED into the caller's gradient buffers (no reduction or accumulation
+ * pass on the caller's side). nlh_gate_grad_finish: dw_partial [rows, 3, 2*d_model] into
+ * g_w_gates [3, 2*d_model], db_partial [rows, 3] into the three bias gradients (each [1]; a NULL
+ * one is skipped). nlh_level_weight_grad_finish: dw_partial [rows, 4] of nlh_mag_combine_backward
+ * through the softmax adjoint d_logit_i = w_i (dw_i - sum_j w_j dw_j), w = level_weights =
+ * softmax(logits) (core/src/mag.rs aggregation weights), into g_logits [k]. */
+int32_t nlh_gate_grad_finish(const float* dw_partial, const float* db_partial, int32_t rows,
+    int32_t d_model, float* g_w_gates, float* g_b_alpha, float* g_b_theta, float* g_b_eta);
+int32_t nlh_level_weight_grad_finish(const float* dw_partial, int32_t rows, int32_t k,
+    const float* level_weights, float* g_logits);
 /* dy_ph[(b*H+h), t', :] = level_weights[level] * sum_{i<pool} d_ycomb[b, t'*pool+i, h*hd:(h+1)*hd]
  * (adjoint of repeat_upsample_1d + head transpose, pool_ops.cu / elementwise.cu). */
 int32_t nlh_pool_to_heads(const float* d_ycomb, const float* level_weights, int32_t level,

@@ -690,7 +690,9 @@ __global__ void __launch_bounds__(NT, 1) chunk_mm_bwd_kernel(BwdArgs a)
         }
     }
     __syncthreads();
-    // d_m_initial / d_s_initial: summed over the batch (drop-in entries) or per problem
+    // d_m_initial / d_s_initial: summed over the batch (drop-in entries) or per problem; not
+    // written at all when the caller passed NULL
+    if (a.d_m_out == nullptr) return;
     for (int p = tid; p < D * D; p += NT) {
         const int row = p >> 6, col = p & 63;
         const float gm = GMb[row * LD + col];

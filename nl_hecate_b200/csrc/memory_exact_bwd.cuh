@@ -263,6 +263,7 @@ __global__ void __launch_bounds__(FastGeom<D, SPLIT>::NT, D == 64 ? (SPLIT == 1 
 
     cp_async_wait<0>();
     if (a.atomic_out) {
+        if (a.d_m_out == nullptr) return;   // batch-summed initial-state gradients not requested
 #pragma unroll
         for (int i = 0; i < 8; i++) {
             const size_t o = (size_t)r * D + col_of<D>((2 * i) ^ (xc << 2), cg);

@@ -667,6 +667,7 @@ __global__ void __launch_bounds__(FastGeom<D>::NT, (D == 64 && !FROZEN) ? 2 : 1)
     }
 
     if (a.atomic_out) {
+        if (a.d_m_out == nullptr) return;   // batch-summed initial-state gradients not requested
 #pragma unroll
         for (int i = 0; i < 8; i++) {
             // physical pair i holds logical elements 2i ^ (xc << 2) and the next one

@@ -500,6 +500,7 @@ __global__ void __launch_bounds__(GEN_THREADS) gen_bwd_kernel(BwdArgs a)
         }
     }
 
+    if (a.d_m_out == nullptr) return;   // initial-state gradients not requested
     for (size_t idx = threadIdx.x; idx < dd; idx += blockDim.x) {
         if (a.atomic_out) {
             atomicAdd(&a.d_m_out[idx], dM[idx]);

@@ -698,6 +698,60 @@ static int wr_grid(long long items, int per_cta)
     return (int)(need < cap ? need : cap);
 }
 
+
+// ───────────────────────── partial-row finishers ──────────────────────────
+// The backward kernels above leave parameter gradients as per-CTA partial rows. These kernels sum
+// the rows in a fixed order (deterministic) and ADD the result into the caller's gradient
+// buffers, so that a training step needs no reduction and no accumulation pass of its own.
+// Gate weights: thread per column of dw_partial [rows, cols]; the last CTA also sums the three
+// bias columns of db_partial [rows, 3].
+__global__ void __launch_bounds__(256) gate_grad_finish_kernel(
+    const float* __restrict__ dw_partial, const float* __restrict__ db_partial, int rows, int cols,
+    float* __restrict__ g_w, float* g_b0, float* g_b1, float* g_b2)
+{
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c < cols) {
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+        int r = 0;
+        for (; r + 4 <= rows; r += 4) {
+            a0 += dw_partial[(size_t)r * cols + c];
+            a1 += dw_partial[(size_t)(r + 1) * cols + c];
+            a2 += dw_partial[(size_t)(r + 2) * cols + c];
+            a3 += dw_partial[(size_t)(r + 3) * cols + c];
+        }
+        for (; r < rows; r++) a0 += dw_partial[(size_t)r * cols + c];
+        g_w[c] += (a0 + a1) + (a2 + a3);
+    }
+    if (blockIdx.x == gridDim.x - 1 && threadIdx.x < 96) {
+        const int g = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        float s = 0.f;
+        for (int r = lane; r < rows; r += 32) s += db_partial[(size_t)r * 3 + g];
+        s = warp_sum(s);
+        float* dst = g == 0 ? g_b0 : g == 1 ? g_b1 : g_b2;
+        if (lane == 0 && dst) dst[0] += s;
+    }
+}
+
+// Level weights w = softmax(logits): sums dw_partial [rows, WR_MAX_LEVELS] over rows (warp per
+// level) and adds the softmax adjoint d_logit_i = w_i (dw_i - sum_j w_j dw_j) into g_logits [k].
+__global__ void __launch_bounds__(32 * WR_MAX_LEVELS) level_weight_grad_finish_kernel(
+    const float* __restrict__ dw_partial, int rows, int k, const float* __restrict__ weights,
+    float* g_logits)
+{
+    __shared__ float dw[WR_MAX_LEVELS];
+    const int g = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float s = 0.f;
+    if (g < k)
+        for (int r = lane; r < rows; r += 32) s += dw_partial[(size_t)r * WR_MAX_LEVELS + g];
+    s = warp_sum(s);
+    if (lane == 0) dw[g] = (g < k) ? s : 0.f;
+    __syncthreads();
+    if (threadIdx.x < k) {
+        float dot = 0.f;
+        for (int j = 0; j < k; j++) dot += weights[j] * dw[j];
+        g_logits[threadIdx.x] += weights[threadIdx.x] * (dw[threadIdx.x] - dot);
+    }
+}
 }  // namespace nlh
 
 using namespace nlh;
@@ -893,6 +947,31 @@ int32_t nlh_mag_combine_backward(const float* d_out, const void* attn_proj, int3
             d_out, (const float*)attn_proj, level_weights, L, (float*)d_attn_proj, d_ycomb,
             dw_partial, G, batch, seq, d_model, num_heads);
     return check_launch("nlh_mag_combine_backward") ? NLH_OK : NLH_ERR_CUDA;
+}
+
+int32_t nlh_gate_grad_finish(const float* dw_partial, const float* db_partial, int32_t rows,
+    int32_t d_model, float* g_w_gates, float* g_b_alpha, float* g_b_theta, float* g_b_eta)
+{
+    if (rows <= 0 || d_model <= 0 || !dw_partial || !db_partial || !g_w_gates) {
+        record_status(NLH_ERR_INVALID_ARG, "nlh_gate_grad_finish", "bad dimensions or NULL buffer");
+        return NLH_ERR_INVALID_ARG;
+    }
+    const int cols = 3 * 2 * d_model;
+    gate_grad_finish_kernel<<<(cols + 255) / 256, 256, 0, current_stream()>>>(
+        dw_partial, db_partial, rows, cols, g_w_gates, g_b_alpha, g_b_theta, g_b_eta);
+    return check_launch("nlh_gate_grad_finish") ? NLH_OK : NLH_ERR_CUDA;
+}
+
+int32_t nlh_level_weight_grad_finish(const float* dw_partial, int32_t rows, int32_t k,
+    const float* level_weights, float* g_logits)
+{
+    if (rows <= 0 || k <= 0 || k > WR_MAX_LEVELS || !dw_partial || !level_weights || !g_logits) {
+        record_status(NLH_ERR_INVALID_ARG, "nlh_level_weight_grad_finish", "bad dimensions or NULL buffer");
+        return NLH_ERR_INVALID_ARG;
+    }
+    level_weight_grad_finish_kernel<<<1, 32 * WR_MAX_LEVELS, 0, current_stream()>>>(
+        dw_partial, rows, k, level_weights, g_logits);
+    return check_launch("nlh_level_weight_grad_finish") ? NLH_OK : NLH_ERR_CUDA;
 }
 
 int32_t nlh_pool_to_heads(const float* d_ycomb, const float* level_weights, int32_t level,

@@ -109,20 +109,17 @@ def checkpoint_count(seq_len: int, c: int) -> int:
 # ── memory rules, device tensors ───────────────────────────────────────────
 # Shapes: k,v,q,d_y [N,S,d]; gates [N,S]; m0,s0 [N,d*d]; states [N,(S+1),d*d].
 
-def _zero_grads(k, alpha, d):
-    """Pre-zeroed backward outputs of a Titans entry carved out of ONE buffer (one fill instead
-    of eight): d_k, d_v, d_q like k; d_alpha, d_theta, d_eta like alpha; d_m_initial,
-    d_s_initial [d*d]. Sizes are multiples of 4 floats for the shapes the kernels accept, so
-    every view stays 16-byte aligned."""
-    nk, na, dd = k.numel(), alpha.numel(), d * d
-    pad = lambda x: (x + 3) // 4 * 4
-    sizes = [pad(nk)] * 3 + [pad(na)] * 3 + [pad(dd)] * 2
-    flat = torch.zeros(sum(sizes), dtype=torch.float32, device=k.device)
-    out, o = [], 0
-    for sz, (cnt, shape) in zip(sizes, [(nk, k.shape)] * 3 + [(na, alpha.shape)] * 3 + [(dd, (dd,))] * 2):
-        out.append(flat[o:o + cnt].view(shape))
-        o += sz
-    return out
+def _zero_grads(k, alpha, d, want_initial=True):
+    """Backward outputs of a Titans entry: d_k, d_v, d_q like k and d_alpha, d_theta, d_eta like
+    alpha are overwritten by every kernel path, so they are left uninitialised; d_m_initial and
+    d_s_initial [d*d] are summed over the batch with atomics and start from zero (one small
+    fill). want_initial=False passes NULL for those two: the entries then skip them."""
+    dk, dv, dq = (torch.empty_like(k) for _ in range(3))
+    da, dt, de = (torch.empty_like(alpha) for _ in range(3))
+    if not want_initial:
+        return dk, dv, dq, da, dt, de, None, None
+    init = torch.zeros(2, d * d, dtype=torch.float32, device=k.device)
+    return dk, dv, dq, da, dt, de, init[0], init[1]
 
 
 def titans_forward_dd(k, v, q, alpha, theta, eta, m0, s0, error_clip=0.0, m_norm_max=0.0,
@@ -139,9 +136,9 @@ def titans_forward_dd(k, v, q, alpha, theta, eta, m0, s0, error_clip=0.0, m_norm
     return ms, ss, y
 
 
-def titans_backward_dd(k, v, q, alpha, theta, eta, ms, ss, d_y, error_clip=0.0):
+def titans_backward_dd(k, v, q, alpha, theta, eta, ms, ss, d_y, error_clip=0.0, want_initial=True):
     n, s, d = k.shape
-    dk, dv, dq, da, dt, de, dm0, ds0 = _zero_grads(k, alpha, d)
+    dk, dv, dq, da, dt, de, dm0, ds0 = _zero_grads(k, alpha, d, want_initial)
     call("titans_backward_f32_cuda", k_mem=k, v_mem=v, q_mem=q, alpha=alpha, theta=theta, eta=eta,
          m_states=ms, s_states=ss, d_y=d_y, d_k_mem=dk, d_v_mem=dv, d_q_mem=dq, d_alpha=da,
          d_theta=dt, d_eta=de, d_m_initial=dm0, d_s_initial=ds0, seq_len=s, d=d, batch_size=n,
@@ -217,9 +214,9 @@ def titans_chunkwise_forward_dd(k, v, q, alpha, theta, eta, m0, s0, chunk, error
 
 
 def titans_chunkwise_backward_dd(k, v, q, alpha, theta, eta, mc, sc, d_y, chunk, error_clip=0.0,
-                                 m_norm_max=0.0):
+                                 m_norm_max=0.0, want_initial=True):
     n, s, d = k.shape
-    dk, dv, dq, da, dt, de, dm0, ds0 = _zero_grads(k, alpha, d)
+    dk, dv, dq, da, dt, de, dm0, ds0 = _zero_grads(k, alpha, d, want_initial)
     call("titans_chunkwise_backward_f32_cuda", k_mem=k, v_mem=v, q_mem=q, alpha=alpha, theta=theta,
          eta=eta, m_chunk_states=mc, s_chunk_states=sc, d_y=d_y, d_k_mem=dk, d_v_mem=dv,
          d_q_mem=dq, d_alpha=da, d_theta=dt, d_eta=de, d_m_initial=dm0, d_s_initial=ds0,

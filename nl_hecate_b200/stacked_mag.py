@@ -76,7 +76,7 @@ class _TitansMemory(torch.autograd.Function):
     _ZEROS = {}
 
     @staticmethod
-    def forward(ctx, k, v, q, alpha, theta, eta, m0, chunk, slot=0):
+    def forward(ctx, k, v, q, alpha, theta, eta, m0, chunk, slot=0, carry=None):
         # momentum restarts every call (gpu_forward.rs:1516-1517): S_0 = 0, a read-only buffer that
         # is created once per shape instead of being filled every call
         key = (tuple(m0.shape), m0.device)
@@ -85,10 +85,10 @@ class _TitansMemory(torch.autograd.Function):
             s0 = _TitansMemory._ZEROS[key] = torch.zeros_like(m0)
         ctx.slot = slot
         with D.workspace_slot(slot):
-            return _TitansMemory._forward(ctx, k, v, q, alpha, theta, eta, m0, s0, chunk)
+            return _TitansMemory._forward(ctx, k, v, q, alpha, theta, eta, m0, s0, chunk, carry)
 
     @staticmethod
-    def _forward(ctx, k, v, q, alpha, theta, eta, m0, s0, chunk):
+    def _forward(ctx, k, v, q, alpha, theta, eta, m0, s0, chunk, carry=None):
         if chunk == 0:
             # M trajectory only: the backward derives S_t = M_t - (1-alpha_{t-1}) M_{t-1}
             ms, ss, y = D.titans_forward_dd(k, v, q, alpha, theta, eta, m0, s0, store_s=False)
@@ -97,6 +97,11 @@ class _TitansMemory(torch.autograd.Function):
             ms, ss, y = D.titans_chunkwise_forward_dd(k, v, q, alpha, theta, eta, m0, s0, chunk)
             ctx.save_for_backward(k, v, q, alpha, theta, eta, ms, ss)
         ctx.chunk = chunk
+        if carry is not None:
+            # the carried memory is updated in place from the last stored state (one strided copy;
+            # the kernels have read m0 by then, stream order), no separate m_final tensor
+            carry.copy_(ms[:, -1])
+            return y, None
         m_final = ms[:, -1].clone()
         ctx.mark_non_differentiable(m_final)
         return y, m_final
@@ -107,11 +112,12 @@ class _TitansMemory(torch.autograd.Function):
         with D.workspace_slot(ctx.slot):
             if ctx.chunk == 0:
                 k, v, q, alpha, theta, eta, ms = ctx.saved_tensors
-                g = D.titans_backward_dd(k, v, q, alpha, theta, eta, ms, None, dy)
+                g = D.titans_backward_dd(k, v, q, alpha, theta, eta, ms, None, dy, want_initial=False)
             else:
                 k, v, q, alpha, theta, eta, ms, ss = ctx.saved_tensors
-                g = D.titans_chunkwise_backward_dd(k, v, q, alpha, theta, eta, ms, ss, dy, ctx.chunk)
-        return g["d_k"], g["d_v"], g["d_q"], g["d_alpha"], g["d_theta"], g["d_eta"], None, None, None
+                g = D.titans_chunkwise_backward_dd(k, v, q, alpha, theta, eta, ms, ss, dy, ctx.chunk,
+                                                   want_initial=False)
+        return g["d_k"], g["d_v"], g["d_q"], g["d_alpha"], g["d_theta"], g["d_eta"], None, None, None, None
 
 
 class _SWA(torch.autograd.Function):
@@ -172,9 +178,12 @@ class _LevelPrep(torch.autograd.Function):
     split, and in backward the gate/L2-norm/transposes adjoints plus gate weight gradients."""
 
     @staticmethod
-    def forward(ctx, kvq, w_gates, b_alpha, b_theta, b_eta, num_heads, slot=0):
+    def forward(ctx, kvq, w_gates, b_alpha, b_theta, b_eta, num_heads, slot=0, grads=None):
+        """grads = (g_w_gates, g_b_alpha, g_b_theta, g_b_eta): gradient buffers the backward adds
+        the four parameter gradients into (nlh_gate_grad_finish); it then returns none for them."""
         kvq = kvq.contiguous()
         ctx.slot = slot
+        ctx.grads = grads
         B, sf, d3 = kvq.shape
         d, H = d3 // 3, num_heads
         hd, dev = d // H, kvq.device
@@ -208,9 +217,14 @@ class _LevelPrep(torch.autograd.Function):
                    eta_ph=et, k_norm=kn, q_norm=qn, dk_ph=dk, dv_ph=dv, dq_ph=dq, dalpha_ph=da,
                    dtheta_ph=dt, deta_ph=de, w_gates=w_gates, d_kvq=d_kvq, kvq_is_bf16=is_bf16,
                    dw_partial=dwp, db_partial=dbp, batch=B, seq=sf, d_model=d, num_heads=H)
+            if ctx.grads is not None:
+                gw, ga, gt, ge = ctx.grads
+                D.call("nlh_gate_grad_finish", dw_partial=dwp, db_partial=dbp, rows=rows, d_model=d,
+                       g_w_gates=gw, g_b_alpha=ga, g_b_theta=gt, g_b_eta=ge)
+                return d_kvq, None, None, None, None, None, None, None
         dw = dwp.sum(0)
         db = dbp.sum(0)
-        return d_kvq, dw, db[0:1], db[1:2], db[2:3], None, None
+        return d_kvq, dw, db[0:1], db[1:2], db[2:3], None, None, None
 
 
 class _MagCombine(torch.autograd.Function):
@@ -219,7 +233,11 @@ class _MagCombine(torch.autograd.Function):
     ROWS = 148 * 8
 
     @staticmethod
-    def forward(ctx, x, attn_proj, wts, pools, num_heads, *ys):
+    def forward(ctx, x, attn_proj, wts, pools, num_heads, g_logits, *ys):
+        """wts = softmax(alpha_mem). g_logits None: wts is a tensor of the graph and receives its
+        gradient. g_logits = gradient buffer of alpha_mem: wts was computed outside the graph, the
+        backward adds the softmax adjoint into g_logits (nlh_level_weight_grad_finish)."""
+        ctx.g_logits = g_logits
         x, attn_proj, wts = x.contiguous(), attn_proj.contiguous(), wts.contiguous().float()
         B, S, d = x.shape
         k = len(ys)
@@ -253,7 +271,12 @@ class _MagCombine(torch.autograd.Function):
                c2=cp[2], c3=cp[3], k=k, d_attn_proj=d_ap, d_ycomb=d_yc, dw_partial=dwp,
                n_partial_rows=rows, dy0=direct[0], dy1=direct[1], dy2=direct[2], dy3=direct[3],
                batch=B, seq=S, d_model=d, num_heads=H)
-        d_wts = dwp.sum(0)[:k]
+        if ctx.g_logits is not None:
+            D.call("nlh_level_weight_grad_finish", dw_partial=dwp, rows=rows, k=k, level_weights=wts,
+                   g_logits=ctx.g_logits)
+            d_wts = None
+        else:
+            d_wts = dwp.sum(0)[:k]
         # pooled levels, finest first; a level whose pool factor is a multiple of the previous
         # pooled level's is reduced from that level's unscaled sums instead of from d_ycomb
         order = sorted((l for l in range(k) if cp[l] != 1), key=lambda l: cp[l])
@@ -270,7 +293,7 @@ class _MagCombine(torch.autograd.Function):
                        dy_ph=dys[l], sum_out=sums, batch=B, seq=S, d_model=d, num_heads=H)
             if sums is not None:
                 prev = (cp[l], sums)
-        return (d_out, d_ap, d_wts, None, None, *dys)
+        return (d_out, d_ap, d_wts, None, None, None, *dys)
 
 
 class _PoolLevels(torch.autograd.Function):
@@ -326,7 +349,10 @@ class _LayerNorm(torch.autograd.Function):
     output, 2: both (fp32 for the pooled levels, bf16 for the GEMM that follows)."""
 
     @staticmethod
-    def forward(ctx, x, gamma, beta, eps, mode):
+    def forward(ctx, x, gamma, beta, eps, mode, grads=None):
+        """grads = (g_gamma, g_beta): buffers the backward accumulates the two parameter gradients
+        into (the kernel adds with atomics); it then returns none for them."""
+        ctx.grads = grads
         x = x.contiguous()
         d = x.shape[-1]
         n = x.numel() // d
@@ -355,12 +381,19 @@ class _LayerNorm(torch.autograd.Function):
             else:
                 g32 = g.contiguous()
         d_x = torch.empty_like(x)
+        if ctx.grads is not None:
+            if g32 is None and g16 is None:
+                return d_x.zero_(), None, None, None, None, None
+            D.call("nlh_layer_norm_backward", d_out_f32=g32, d_out_bf16=g16, x=x, gamma=gamma.contiguous(),
+                   mean_cache=mean, rstd_cache=rstd, d_x=d_x, d_gamma=ctx.grads[0], d_beta=ctx.grads[1],
+                   n=n, d=d)
+            return d_x, None, None, None, None, None
         d_gb = torch.zeros(2, d, dtype=torch.float32, device=x.device)
         if g32 is None and g16 is None:
-            return d_x.zero_(), d_gb[0], d_gb[1], None, None
+            return d_x.zero_(), d_gb[0], d_gb[1], None, None, None
         D.call("nlh_layer_norm_backward", d_out_f32=g32, d_out_bf16=g16, x=x, gamma=gamma.contiguous(),
                mean_cache=mean, rstd_cache=rstd, d_x=d_x, d_gamma=d_gb[0], d_beta=d_gb[1], n=n, d=d)
-        return d_x, d_gb[0], d_gb[1], None, None
+        return d_x, d_gb[0], d_gb[1], None, None, None
 
 
 class _CrossEntropy(torch.autograd.Function):
@@ -452,8 +485,8 @@ class _Embedding(torch.autograd.Function):
         return None, None, None
 
 
-def titans_memory(k, v, q, alpha, theta, eta, m0, chunk, slot=0):
-    return _TitansMemory.apply(k, v, q, alpha, theta, eta, m0, chunk, slot)
+def titans_memory(k, v, q, alpha, theta, eta, m0, chunk, slot=0, carry=None):
+    return _TitansMemory.apply(k, v, q, alpha, theta, eta, m0, chunk, slot, carry)
 
 
 def swa(q, k, v, num_heads, head_dim, window):
@@ -627,15 +660,18 @@ class StackedMAG:
         sf = x.shape[1]
         pre = f"b{b}.l{l}."
         kvq = self._mm(x, pre + "w_kvq_mem")
-        k, v, q, alpha, theta, eta = _LevelPrep.apply(kvq, p[pre + "w_gates"], p[pre + "b_alpha"],
-                                                      p[pre + "b_theta"], p[pre + "b_eta"],
-                                                      cfg.num_heads, slot)
+        g = self.g
+        k, v, q, alpha, theta, eta = _LevelPrep.apply(
+            kvq, p[pre + "w_gates"], p[pre + "b_alpha"], p[pre + "b_theta"], p[pre + "b_eta"],
+            cfg.num_heads, slot,
+            (g[pre + "w_gates"], g[pre + "b_alpha"], g[pre + "b_theta"], g[pre + "b_eta"]))
         chunk = 0 if l in cfg.exact_levels else min(cfg.chunk_sizes[l], sf)
-        if self.memory_fn is titans_memory:
-            y, m_final = titans_memory(k, v, q, alpha, theta, eta, self.context[b][l], chunk, slot)
+        if self.memory_fn is titans_memory:   # carried memory updated in place by the Function
+            y, _ = titans_memory(k, v, q, alpha, theta, eta, self.context[b][l], chunk, slot,
+                                 self.context[b][l])
         else:
             y, m_final = self.memory_fn(k, v, q, alpha, theta, eta, self.context[b][l], chunk)
-        self.context[b][l].copy_(m_final.detach())   # in place: addresses stay fixed for graph replay
+            self.context[b][l].copy_(m_final.detach())   # in place: addresses stay fixed for graph replay
         return y
 
     def _levels(self, b, inputs):
@@ -664,7 +700,8 @@ class StackedMAG:
     def _ln(self, x, name, mode, fused):
         p = self.p
         if fused:
-            return _LayerNorm.apply(x, p[name + "gamma"], p[name + "beta"], 1e-5, mode)
+            return _LayerNorm.apply(x, p[name + "gamma"], p[name + "beta"], 1e-5, mode,
+                                    (self.g[name + "gamma"], self.g[name + "beta"]))
         out = F.layer_norm(x, (x.shape[-1],), p[name + "gamma"], p[name + "beta"], 1e-5)
         return (out, out) if mode == 2 else out
 
@@ -691,7 +728,11 @@ class StackedMAG:
                 attn = self.swa_fn(q, k, v, nh, hd, cfg.window)
             attn_raw = self._mm(attn, pre + "w_o")
             res1 = x + attn_raw
-            wts = torch.softmax(p[pre + "alpha_mem"], dim=0)
+            if fused:
+                with torch.no_grad():
+                    wts = torch.softmax(p[pre + "alpha_mem"], dim=0)
+            else:
+                wts = torch.softmax(p[pre + "alpha_mem"], dim=0)
             if fused:
                 m32, m16 = self._ln(res1, pre + "ln_mem_", 2, True) if cfg.bf16 else \
                     (self._ln(res1, pre + "ln_mem_", 0, True),) * 2
@@ -703,7 +744,7 @@ class StackedMAG:
                     assert S % c == 0, "seq_len must be a multiple of every chunk size"
                 ys = self._levels(b, [pooled.get(cs[l], m16) for l in range(cfg.k)])
                 pools = cs
-                x = _MagCombine.apply(x, attn_raw, wts, tuple(pools), nh, *ys)
+                x = _MagCombine.apply(x, attn_raw, wts, tuple(pools), nh, self.g[pre + "alpha_mem"], *ys)
             else:
                 m_in = self._ln(res1, pre + "ln_mem_", 0, False)
                 attn_proj = attn_raw.float()
