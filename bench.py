@@ -596,7 +596,7 @@ UNIT = "tokens/s"
 
 def parallelism_label(workload, world):
     if workload == "stacked_mag":
-        return f"dp{world} (batch shard, one fp32 all-reduce of the gradient arena per step)"
+        return f"dp{world} (batch shard, fp32 gradient all-reduce in per-block buckets under the backward)"
     return f"dp{world} (independent problems per rank, no collective)"
 
 

@@ -62,6 +62,7 @@ class StackedMAGConfig:
     tie_embeddings: bool = True
     fused_glue: bool = True           # fused CUDA rule wrapper / MAG combine (CUDA only)
     level_streams: bool = True        # run CMS levels >= 1 on side streams next to level 0
+    overlap_grad_sync: bool = True    # data-parallel: all-reduce each block's gradients under the rest of the backward
 
     @property
     def head_dim(self):
@@ -717,6 +718,7 @@ class StackedMAG:
             x = F.embedding(tokens, p["w_embed"])
         for b in range(cfg.n_blocks):
             pre = f"b{b}."
+            self._mark_bucket(x, f"b{b}")            # fires once block b's backward has run
             h = self._ln(x, pre + "ln_attn_", lp, fused)
             qkv = self._mm(h, pre + "w_qkv")
             if cfg.bf16 or not qkv.is_cuda:
@@ -753,6 +755,7 @@ class StackedMAG:
                     yl = self._level(b, l, m_in) * wts[l]
                     y = yl if y is None else y + yl
                 x = x + attn_proj * torch.sigmoid(y)
+        self._mark_bucket(x, "tail")                 # unembedding and final LayerNorm
         x = self._ln(x, "ln_final_", lp, fused)
         logits = self._mm(x, "w_unembed", transposed=True)
         if fused:
@@ -765,16 +768,68 @@ class StackedMAG:
         cfg = self.cfg
         return [self.global_step % cs == 0 or cfg.seq_len >= cs for cs in cfg.chunk_sizes]
 
-    def forward_backward(self, tokens, targets):
-        """Loss (mean over the local batch) and its gradients, accumulated into the arena."""
+    def forward_backward(self, tokens, targets, process_group=None, world=1):
+        """Loss (mean over the local batch) and its gradients, accumulated into the arena.
+        With world > 1 on the GPU (and cfg.overlap_grad_sync) the gradients are also averaged
+        over the ranks here: the arena is laid out in the order the backward completes it
+        backwards (embedding | unembedding + final LayerNorm | block 0 | block 1 | ...), so each
+        block's slice is all-reduced (NCCL, average) as soon as that block's backward has been
+        issued and the exchange runs under the backward of the blocks below it; the embedding's
+        slice goes last. sync_gradients() is then a no-op for this step."""
+        overlap = (world > 1 and tokens.is_cuda and self.cfg.overlap_grad_sync)
+        self._sync_state = dict(pg=process_group, works=[], seen=set()) if overlap else None
         loss = self.forward(tokens, targets)
         loss.backward()
+        if overlap:
+            st = self._sync_state
+            for name in self._bucket_order():         # whatever no hook has covered (the embedding)
+                if name not in st["seen"]:
+                    self._reduce_bucket(name)
+            for w in st["works"]:
+                w.wait()                               # the compute stream waits, the host does not
+            self._sync_state = None
+            self._grads_synced = True
         return loss.detach()
 
+    # ── bucketed gradient exchange ─────────────────────────────────────────
+    def _bucket_order(self):
+        return ["tail"] + [f"b{b}" for b in reversed(range(self.cfg.n_blocks))] + ["embed"]
+
+    def _bucket_range(self, name):
+        """[start, end) of a bucket in the flat arenas."""
+        off = {n: self.opt.slices[i][0] for i, n in enumerate(self.names)}
+        nb = self.cfg.n_blocks
+        if name == "embed":
+            return 0, off["w_unembed"]
+        if name == "tail":
+            return off["w_unembed"], off["b0.w_qkv"]
+        b = int(name[1:])
+        return off[f"b{b}.w_qkv"], (off[f"b{b + 1}.w_qkv"] if b + 1 < nb else self.opt.arena_len)
+
+    def _reduce_bucket(self, name):
+        st = self._sync_state
+        st["seen"].add(name)
+        o0, o1 = self._bucket_range(name)
+        st["works"].append(torch.distributed.all_reduce(
+            self.opt.g[o0:o1], op=torch.distributed.ReduceOp.AVG, group=st["pg"], async_op=True))
+
+    def _mark_bucket(self, x, name):
+        """Tensor hook on the activation that enters a block (or the final LayerNorm): autograd
+        calls it when that activation's gradient is complete, i.e. after every backward node of
+        the block has been issued — side-stream levels included, their results are joined into
+        the compute stream before the block's first LayerNorm backward runs."""
+        if getattr(self, "_sync_state", None) is None or not x.requires_grad:
+            return
+        x.register_hook(lambda g, name=name: self._reduce_bucket(name))
+
     def sync_gradients(self, process_group=None, world=1):
-        """Data-parallel gradient exchange: ONE all-reduce(SUM) over the flat gradient arena,
-        then divide by the world size (core/src/distributed.rs:121-150 does the same per
-        tensor). Inner-loop state (carried memories) is rank-local and never communicated."""
+        """Data-parallel gradient exchange when forward_backward() has not already done it:
+        ONE all-reduce(SUM) over the flat gradient arena, then divide by the world size
+        (core/src/distributed.rs:121-150 does the same per tensor). Inner-loop state (carried
+        memories) is rank-local and never communicated."""
+        if getattr(self, "_grads_synced", False):
+            self._grads_synced = False
+            return
         if world > 1:
             torch.distributed.all_reduce(self.opt.g, group=process_group)
             self.opt.g.mul_(1.0 / world)
@@ -807,7 +862,7 @@ class StackedMAG:
 
     def step(self, tokens, targets, process_group=None, world=1):
         """forward + backward + gradient all-reduce + clip + AdamW. Returns the local loss."""
-        loss = self.forward_backward(tokens, targets)
+        loss = self.forward_backward(tokens, targets, process_group, world)
         self.sync_gradients(process_group, world)
         self.apply_update()
         return loss
@@ -832,7 +887,8 @@ class StackedMAG:
             self._host_schedule()
             self._graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(self._graph):
-                self._static_loss = self.forward_backward(self._static_tok, self._static_tgt)
+                self._static_loss = self.forward_backward(self._static_tok, self._static_tgt,
+                                                          process_group, world)
                 self.sync_gradients(process_group, world)
                 self._device_update()
             self._graph.replay()            # capture records only: run the scheduled step now

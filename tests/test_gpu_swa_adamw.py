@@ -224,6 +224,37 @@ def test_multi_tensor_adamw_matches_per_tensor(D, orc):
     assert total <= opt.arena_len
 
 
+def test_eager_steps_without_host_sync_use_their_own_descriptors(D, orc):
+    """A host that runs several optimizer steps ahead of the GPU must not replace step t's
+    descriptor table (bias corrections, activity flags) before step t's stream-ordered upload
+    has read it: FlatAdamW.prepare() waits for the previous launch()'s upload. The GPU is kept
+    busy with queued work first, so without that wait every step would see the LAST table."""
+    import torch
+    from nl_hecate_b200.optimizer import FlatAdamW
+    sizes = [4096, 8, 1030]
+
+    def run(sync_each_step):
+        opt = FlatAdamW(sizes, device="cuda", beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.1)
+        for i, (o, n) in enumerate(opt.slices):
+            opt.w[o:o + n].copy_(torch.from_numpy(orc.rand_buf(n, 5200 + i, 2.0)))
+            opt.g[o:o + n].copy_(torch.from_numpy(orc.rand_buf(n, 5250 + i, 0.5)))
+        torch.cuda.synchronize()
+        if not sync_each_step:                      # queue ~100 ms of GPU work ahead of the steps
+            a = torch.randn(4096, 4096, device="cuda")
+            for _ in range(60):
+                a = (a @ a) * 1e-4
+        for t in range(1, 7):
+            opt.step(lr=1e-2, steps=[t, t, t], active=[True, t % 2 == 1, True], max_grad_norm=0.0)
+            if sync_each_step:
+                torch.cuda.synchronize()
+        torch.cuda.synchronize()
+        return opt.w.detach().cpu().numpy().copy()
+
+    want = run(True)
+    got = run(False)
+    assert np.array_equal(got, want)
+
+
 @pytest.mark.parametrize("b,s,nh,hd,w", [(2, 300, 2, 64, 128), (1, 513, 4, 64, 512), (2, 100, 2, 32, 40)])
 def test_swa_packed_entries_match_split_entries(D, b, s, nh, hd, w):
     """q|k|v packed as one [B, S, 3*H*hd] tensor: the forward is bit-identical to the split
