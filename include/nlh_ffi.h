@@ -424,6 +424,16 @@ int32_t nlh_layer_norm_forward(const float* x, const float* gamma, const float* 
 int32_t nlh_layer_norm_backward(const float* d_out_f32, const uint16_t* d_out_bf16, const float* x,
     const float* gamma, const float* mean_cache, const float* rstd_cache, float* d_x, float* d_gamma,
     float* d_beta, int32_t n, int32_t d);
+/* The same backward with up to three more gradient sources: gradients of mean-pooled copies of
+ * the LayerNorm output, g_l [n / c_l, d] fp32 or bf16, each adding g_l[b, t / c_l, :] / c_l to
+ * the output gradient of row (b, t) (seq rows per sequence, seq % c_l == 0) — the adjoint of
+ * nlh_mean_pool folded into this kernel, so the upsampled sum is never written to memory.
+ * d_out_f32 and d_out_bf16 may both be NULL when n_src > 0. Needs d % 8 == 0, d <= 1024. */
+int32_t nlh_layer_norm_backward_pooled(const float* d_out_f32, const uint16_t* d_out_bf16,
+    const void* g0, int32_t c0, int32_t g0_is_bf16, const void* g1, int32_t c1, int32_t g1_is_bf16,
+    const void* g2, int32_t c2, int32_t g2_is_bf16, int32_t n_src, int32_t seq, const float* x,
+    const float* gamma, const float* mean_cache, const float* rstd_cache, float* d_x, float* d_gamma,
+    float* d_beta, int32_t n, int32_t d);
 /* Cross-entropy on fp32 or bf16 logits [n, vocab]. Forward ACCUMULATES the loss sum into
  * loss_sum[0] and the number of valid targets into valid_count[0] (optional) and stores the
  * per-row log-sum-exp in lse [n] (optional). Backward writes

@@ -118,11 +118,47 @@ __global__ void __launch_bounds__(256) ln_fwd_generic_kernel(
     }
 }
 
-// Backward, fast path. d_out = (fp32 part, may be NULL) + (bf16 part, may be NULL).
+// Upsampled gradient sources of the backward: gradients of mean-pooled copies of the LayerNorm
+// output, g_l [rows / c_l, d] (fp32 or bf16), each contributing g_l[b, t / c_l, :] / c_l to row
+// (b, t) (adjoint of core/kernels/pool_ops.cu mean pooling). seq = rows per sequence.
+struct LnPooled {
+    const void* g[3];
+    int c[3];
+    FastDiv cdiv[3];
+    FastDiv sdiv;        // division by seq
+    int is_bf16[3];
+    int n;
+    int seq;
+};
+
+// Backward, fast path. d_out = (fp32 part, may be NULL) + (bf16 part, may be NULL) + pooled parts.
 // d_x = rstd/d * (d*dg - sum(dg) - x_hat*sum(dg*x_hat)), dg = d_out*gamma (core/src/mag.rs:421-449).
+// Warp per row; the row's x_hat and output gradient stay in registers across the two warp sums.
 template <int NV>
-__global__ void __launch_bounds__(LN_WARPS * 32) ln_bwd_kernel(
-    const float* __restrict__ d_out, const __nv_bfloat16* __restrict__ d_out_bf16,
+__device__ __forceinline__ float4 ln_bwd_dy(const float* __restrict__ d_out, const __nv_bfloat16* __restrict__ d_out_bf16,
+                                            const LnPooled& P, const size_t ro, const size_t (&po)[3],
+                                            const float (&pinv)[3], int c)
+{
+    float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (d_out) t = ld4f(d_out + ro + 4 * c);
+    if (d_out_bf16) {
+        const float4 w = ld4f(d_out_bf16 + ro + 4 * c);
+        t.x += w.x; t.y += w.y; t.z += w.z; t.w += w.w;
+    }
+#pragma unroll
+    for (int l = 0; l < 3; l++) {
+        if (l < P.n) {
+            const float4 w = P.is_bf16[l] ? ld4f((const __nv_bfloat16*)P.g[l] + po[l] + 4 * c)
+                                          : ld4f((const float*)P.g[l] + po[l] + 4 * c);
+            t.x += w.x * pinv[l]; t.y += w.y * pinv[l]; t.z += w.z * pinv[l]; t.w += w.w * pinv[l];
+        }
+    }
+    return t;
+}
+
+template <int NV>
+__global__ void __launch_bounds__(LN_WARPS * 32, 2) ln_bwd_kernel(
+    const float* __restrict__ d_out, const __nv_bfloat16* __restrict__ d_out_bf16, LnPooled P,
     const float* __restrict__ x, const float* __restrict__ gamma,
     const float* __restrict__ mean_cache, const float* __restrict__ rstd_cache,
     float* __restrict__ d_x, float* __restrict__ d_gamma, float* __restrict__ d_beta, int n, int d)
@@ -131,11 +167,9 @@ __global__ void __launch_bounds__(LN_WARPS * 32) ln_bwd_kernel(
     __shared__ float4 sred[LN_WARPS][32 * HV];   // [warp][chunk] for half of the chunks at a time
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int nv = d >> 2;
-    float4 g[NV], ag[NV], ab[NV];
+    float4 ag[NV], ab[NV];
 #pragma unroll
     for (int i = 0; i < NV; i++) {
-        const int c = lane + 32 * i;
-        g[i] = (c < nv) ? ld4f(gamma + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
         ag[i] = make_float4(0.f, 0.f, 0.f, 0.f);
         ab[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
@@ -143,6 +177,17 @@ __global__ void __launch_bounds__(LN_WARPS * 32) ln_bwd_kernel(
     for (int row = blockIdx.x * LN_WARPS + warp; row < n; row += gridDim.x * LN_WARPS) {
         const float mean = mean_cache[row], rstd = rstd_cache[row];
         const size_t ro = (size_t)row * d;
+        size_t po[3] = {0, 0, 0};
+        float pinv[3] = {0.f, 0.f, 0.f};
+        if (P.n > 0) {
+            const int b = fd_div(row, P.sdiv), tt = row - b * P.seq;
+#pragma unroll
+            for (int l = 0; l < 3; l++)
+                if (l < P.n) {
+                    po[l] = ((size_t)b * fd_div(P.seq, P.cdiv[l]) + fd_div(tt, P.cdiv[l])) * d;
+                    pinv[l] = 1.0f / (float)P.c[l];
+                }
+        }
         float4 xh[NV], dy[NV];
         float s1 = 0.f, s2 = 0.f;
 #pragma unroll
@@ -150,19 +195,15 @@ __global__ void __launch_bounds__(LN_WARPS * 32) ln_bwd_kernel(
             const int c = lane + 32 * i;
             if (c < nv) {
                 const float4 xv = ld4f(x + ro + 4 * c);
-                float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (d_out) t = ld4f(d_out + ro + 4 * c);
-                if (d_out_bf16) {
-                    const float4 u = ld4f(d_out_bf16 + ro + 4 * c);
-                    t.x += u.x; t.y += u.y; t.z += u.z; t.w += u.w;
-                }
-                dy[i] = t;
-                xh[i] = make_float4((xv.x - mean) * rstd, (xv.y - mean) * rstd, (xv.z - mean) * rstd, (xv.w - mean) * rstd);
-                ag[i].x += t.x * xh[i].x; ag[i].y += t.y * xh[i].y; ag[i].z += t.z * xh[i].z; ag[i].w += t.w * xh[i].w;
+                const float4 t = ln_bwd_dy<NV>(d_out, d_out_bf16, P, ro, po, pinv, c);
+                const float4 g = ld4f(gamma + 4 * c);
+                const float4 h = make_float4((xv.x - mean) * rstd, (xv.y - mean) * rstd, (xv.z - mean) * rstd, (xv.w - mean) * rstd);
+                xh[i] = h; dy[i] = t;
+                ag[i].x += t.x * h.x; ag[i].y += t.y * h.y; ag[i].z += t.z * h.z; ag[i].w += t.w * h.w;
                 ab[i].x += t.x; ab[i].y += t.y; ab[i].z += t.z; ab[i].w += t.w;
-                const float a = t.x * g[i].x, b = t.y * g[i].y, e = t.z * g[i].z, f = t.w * g[i].w;
+                const float a = t.x * g.x, b = t.y * g.y, e = t.z * g.z, f = t.w * g.w;
                 s1 += (a + b) + (e + f);
-                s2 += (a * xh[i].x + b * xh[i].y) + (e * xh[i].z + f * xh[i].w);
+                s2 += (a * h.x + b * h.y) + (e * h.z + f * h.w);
             }
         }
         s1 = warp_sum(s1);
@@ -172,11 +213,12 @@ __global__ void __launch_bounds__(LN_WARPS * 32) ln_bwd_kernel(
         for (int i = 0; i < NV; i++) {
             const int c = lane + 32 * i;
             if (c < nv) {
+                const float4 g = ld4f(gamma + 4 * c);
                 float4 o;
-                o.x = k * ((float)d * dy[i].x * g[i].x - s1 - xh[i].x * s2);
-                o.y = k * ((float)d * dy[i].y * g[i].y - s1 - xh[i].y * s2);
-                o.z = k * ((float)d * dy[i].z * g[i].z - s1 - xh[i].z * s2);
-                o.w = k * ((float)d * dy[i].w * g[i].w - s1 - xh[i].w * s2);
+                o.x = k * ((float)d * dy[i].x * g.x - s1 - xh[i].x * s2);
+                o.y = k * ((float)d * dy[i].y * g.y - s1 - xh[i].y * s2);
+                o.z = k * ((float)d * dy[i].z * g.z - s1 - xh[i].z * s2);
+                o.w = k * ((float)d * dy[i].w * g.w - s1 - xh[i].w * s2);
                 *reinterpret_cast<float4*>(d_x + ro + 4 * c) = o;
             }
         }
@@ -247,6 +289,15 @@ __device__ __forceinline__ float ce_ld(const float* p) { return *p; }
 __device__ __forceinline__ float ce_ld(const __nv_bfloat16* p) { return __bfloat162float(*p); }
 
 // (max, sum of exp(x - max)) pairs merge associatively.
+// 2^x with the hardware approximation, flushing denormals: one instruction.
+__device__ __forceinline__ float ex2_ftz(float x)
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+constexpr float CE_LOG2E = 1.4426950408889634f;
+
 __device__ __forceinline__ void lse_merge(float& m, float& s, float m2, float s2)
 {
     const float mm = fmaxf(m, m2);
@@ -261,24 +312,36 @@ __device__ __forceinline__ float row_lse(const T* __restrict__ row, int vocab, f
 {
     float m = -CUDART_INF_F, s = 0.f;
     if (sizeof(T) == 2 && (vocab & 7) == 0 && ((uintptr_t)row & 15) == 0) {
+        // four 16-byte loads per thread in flight, one running-maximum update per 32 values
         const uint4* r4 = reinterpret_cast<const uint4*>(row);
-        for (int j = threadIdx.x; j < (vocab >> 3); j += blockDim.x) {
-            const uint4 u = r4[j];
-            const unsigned w[4] = {u.x, u.y, u.z, u.w};
-            float f[8];
+        const int nvec = vocab >> 3;
+        for (int j0 = threadIdx.x; j0 < nvec; j0 += 4 * blockDim.x) {
+            uint4 u[4];
 #pragma unroll
             for (int q = 0; q < 4; q++) {
-                const float2 t = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[q]));
-                f[2 * q] = t.x; f[2 * q + 1] = t.y;
+                const int jj = j0 + q * blockDim.x;
+                u[q] = jj < nvec ? r4[jj] : make_uint4(0xff80ff80u, 0xff80ff80u, 0xff80ff80u, 0xff80ff80u);   // -inf pairs
+            }
+            float f[32];
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const unsigned w[4] = {u[q].x, u[q].y, u[q].z, u[q].w};
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const float2 t = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[e]));
+                    f[8 * q + 2 * e] = t.x; f[8 * q + 2 * e + 1] = t.y;
+                }
             }
             float lm = f[0];
 #pragma unroll
-            for (int q = 1; q < 8; q++) lm = fmaxf(lm, f[q]);
+            for (int q = 1; q < 32; q++) lm = fmaxf(lm, f[q]);
             const float mm = fmaxf(m, lm);
+            if (mm == -CUDART_INF_F) continue;
+            const float nb = -mm * CE_LOG2E;             // e^(f - mm) = 2^(f log2e - mm log2e): one FMA + ex2
             float ls = 0.f;
 #pragma unroll
-            for (int q = 0; q < 8; q++) ls += __expf(f[q] - mm);
-            s = s * __expf(m - mm) + ls;
+            for (int q = 0; q < 32; q++) ls += ex2_ftz(fmaf(f[q], CE_LOG2E, nb));
+            s = s * ex2_ftz(fmaf(m, CE_LOG2E, nb)) + ls;
             m = mm;
         }
     } else {
@@ -297,8 +360,11 @@ __device__ __forceinline__ float row_lse(const T* __restrict__ row, int vocab, f
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
     if (lane == 0) { red_m[warp] = m; red_s[warp] = s; }
     __syncthreads();
-    m = red_m[0]; s = red_s[0];
-    for (int w = 1; w < nw; w++) lse_merge(m, s, red_m[w], red_s[w]);
+    m = red_m[0];
+    for (int w = 1; w < nw; w++) m = fmaxf(m, red_m[w]);
+    if (m == -CUDART_INF_F) { __syncthreads(); return m; }
+    s = 0.f;
+    for (int w = 0; w < nw; w++) s += red_s[w] * ex2_ftz((red_m[w] - m) * CE_LOG2E);
     __syncthreads();
     return m + logf(s);
 }
@@ -430,22 +496,32 @@ static int ln_forward(const char* where, const float* x, const float* gamma, con
 
 static int ln_backward(const char* where, const float* d_out, const __nv_bfloat16* d_out_bf16,
                        const float* x, const float* gamma, const float* mean_cache,
-                       const float* rstd_cache, float* d_x, float* d_gamma, float* d_beta, int n, int d)
+                       const float* rstd_cache, float* d_x, float* d_gamma, float* d_beta, int n, int d,
+                       const LnPooled* pooled = nullptr)
 {
-    if (n < 0 || d <= 0 || (!d_out && !d_out_bf16) || !x || !gamma || !mean_cache || !rstd_cache ||
+    LnPooled P;
+    P.n = 0; P.seq = 1; P.sdiv = make_fastdiv(1);
+    for (int l = 0; l < 3; l++) { P.g[l] = nullptr; P.c[l] = 1; P.is_bf16[l] = 0; P.cdiv[l] = make_fastdiv(1); }
+    if (pooled) P = *pooled;
+    if (n < 0 || d <= 0 || (!d_out && !d_out_bf16 && P.n == 0) || !x || !gamma || !mean_cache || !rstd_cache ||
         !d_x || !d_gamma || !d_beta) {
         record_status(NLH_ERR_INVALID_ARG, where, "bad dimensions or NULL pointer");
         return NLH_ERR_INVALID_ARG;
     }
     if (n == 0) return NLH_OK;
     cudaStream_t st = current_stream();
-    if (ln_fast_ok(x, gamma, d_out, d_out_bf16, d_x, nullptr, d) && (!d_out_bf16 || (d & 7) == 0)) {
+    const bool fast = ln_fast_ok(x, gamma, d_out, d_out_bf16, d_x, nullptr, d) && (!d_out_bf16 || (d & 7) == 0);
+    if (P.n > 0 && !(fast && (d & 7) == 0)) {
+        record_status(NLH_ERR_UNSUPPORTED, where, "pooled gradient sources need d % 8 == 0, d <= 1024 and 16-byte aligned buffers");
+        return NLH_ERR_UNSUPPORTED;
+    }
+    if (fast) {
         const int need = (n + LN_WARPS - 1) / LN_WARPS;
         const int nv = (d / 4 + 31) / 32;
         // persistent: a few CTAs per SM, each warp walks rows so that the parameter gradients
         // are reduced once per CTA
         const int grid = need < 148 * 2 ? need : 148 * 2;
-#define NLH_LN_BWD(NV) ln_bwd_kernel<NV><<<grid, LN_WARPS * 32, 0, st>>>(d_out, d_out_bf16, x, gamma, mean_cache, rstd_cache, d_x, d_gamma, d_beta, n, d)
+#define NLH_LN_BWD(NV) ln_bwd_kernel<NV><<<grid, LN_WARPS * 32, 0, st>>>(d_out, d_out_bf16, P, x, gamma, mean_cache, rstd_cache, d_x, d_gamma, d_beta, n, d)
         if (nv <= 1) NLH_LN_BWD(1); else if (nv <= 2) NLH_LN_BWD(2); else if (nv <= 4) NLH_LN_BWD(4); else NLH_LN_BWD(8);
 #undef NLH_LN_BWD
     } else {
@@ -482,6 +558,32 @@ int32_t nlh_layer_norm_backward(const float* d_out_f32, const uint16_t* d_out_bf
 {
     return ln_backward("nlh_layer_norm_backward", d_out_f32, (const __nv_bfloat16*)d_out_bf16, x, gamma,
                        mean_cache, rstd_cache, d_x, d_gamma, d_beta, n, d);
+}
+
+int32_t nlh_layer_norm_backward_pooled(const float* d_out_f32, const uint16_t* d_out_bf16,
+    const void* g0, int32_t c0, int32_t g0_is_bf16, const void* g1, int32_t c1, int32_t g1_is_bf16,
+    const void* g2, int32_t c2, int32_t g2_is_bf16, int32_t n_src, int32_t seq, const float* x,
+    const float* gamma, const float* mean_cache, const float* rstd_cache, float* d_x, float* d_gamma,
+    float* d_beta, int32_t n, int32_t d)
+{
+    LnPooled P;
+    const void* gs[3] = {g0, g1, g2};
+    const int cs[3] = {c0, c1, c2}, bs[3] = {g0_is_bf16, g1_is_bf16, g2_is_bf16};
+    bool ok = n_src >= 0 && n_src <= 3 && seq > 0 && n % seq == 0;
+    for (int l = 0; l < 3; l++) {
+        P.g[l] = l < n_src ? gs[l] : nullptr;
+        P.c[l] = l < n_src ? cs[l] : 1;
+        P.is_bf16[l] = bs[l];
+        if (l < n_src && (gs[l] == nullptr || cs[l] <= 0 || seq % cs[l] != 0 || ((uintptr_t)gs[l] & 15) != 0)) ok = false;
+        P.cdiv[l] = make_fastdiv(P.c[l]);
+    }
+    P.n = n_src; P.seq = seq; P.sdiv = make_fastdiv(seq > 0 ? seq : 1);
+    if (!ok) {
+        record_status(NLH_ERR_INVALID_ARG, "nlh_layer_norm_backward_pooled", "bad pooled sources, pool factors or alignment");
+        return NLH_ERR_INVALID_ARG;
+    }
+    return ln_backward("nlh_layer_norm_backward_pooled", d_out_f32, (const __nv_bfloat16*)d_out_bf16, x, gamma,
+                       mean_cache, rstd_cache, d_x, d_gamma, d_beta, n, d, &P);
 }
 
 void embedding_gather_cuda(const float* w_embed, const int32_t* input_ids, float* output,

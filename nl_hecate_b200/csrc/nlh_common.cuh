@@ -102,6 +102,31 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
     return t;
 }
 
+// Division of a non-negative 31-bit integer by a divisor fixed at launch: a shift for powers of
+// two, otherwise one multiply-high and a shift (mul = ceil(2^(32+shr) / d), shr = floor(log2 d),
+// exact for every n < 2^31). Replaces the ~20-instruction integer division in index arithmetic.
+struct FastDiv {
+    unsigned mul;
+    int shr;
+    int d;
+};
+inline FastDiv make_fastdiv(int d)
+{
+    FastDiv f;
+    f.d = d < 1 ? 1 : d;
+    int lg = 0;
+    while ((1LL << (lg + 1)) <= f.d) lg++;
+    f.shr = lg;
+    if ((1LL << lg) == f.d) { f.mul = 0; return f; }
+    const unsigned long long num = 1ULL << (32 + lg);
+    f.mul = (unsigned)((num + (unsigned long long)f.d - 1) / (unsigned long long)f.d);
+    return f;
+}
+__device__ __forceinline__ int fd_div(int n, const FastDiv& f)
+{
+    return f.mul ? (int)(__umulhi((unsigned)n, f.mul) >> f.shr) : (n >> f.shr);
+}
+
 __host__ __device__ __forceinline__ bool m_norm_enabled(float m_norm_max) {
     // core/kernels/m_norm_project.cuh: disabled when <= 0 or >= 1e30.
     return m_norm_max > 0.0f && m_norm_max < 1e30f;

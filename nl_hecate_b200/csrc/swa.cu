@@ -385,6 +385,56 @@ __global__ void __launch_bounds__(256) swa_delta_kernel(const TDO* __restrict__ 
     if (lane == 0) delta[row] = s;
 }
 
+// Same pre-pass with 16-byte accesses: HD/8 lanes per (b,h,q) row, 8 elements per lane. Needs
+// 16-byte aligned bases and row strides that are multiples of 8 elements.
+__device__ __forceinline__ void ld8_do(const bf16* p, float (&x)[8])
+{
+    const uint4 r = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+    for (int i = 0; i < 4; i++) { x[2 * i] = __low2float(h[i]); x[2 * i + 1] = __high2float(h[i]); }
+}
+__device__ __forceinline__ void ld8_do(const float* p, float (&x)[8])
+{
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+}
+template <int HD, typename TDO>
+__global__ void __launch_bounds__(256) swa_delta_vec_kernel(const TDO* __restrict__ d_out,
+                                                            const bf16* __restrict__ out,
+                                                            float* __restrict__ delta, int S, int H, int B, int rs_o,
+                                                            bf16* __restrict__ do16)
+{
+    constexpr int LPR = HD / 8;                      // lanes per row: 4, 8 or 16
+    static_assert(LPR >= 1 && LPR <= 32 && (LPR & (LPR - 1)) == 0, "head_dim / 8 must be a power of two <= 32");
+    const long long gt = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long row = gt / LPR;
+    const int c = (int)(gt - row * LPR) * 8;
+    const bool live = row < (long long)B * H * S;
+    float s = 0.f;
+    if (live) {
+        const int qp = (int)(row % S);
+        const int h = (int)((row / S) % H);
+        const int b = (int)(row / ((long long)S * H));
+        const size_t off = ((size_t)b * S + qp) * rs_o + (size_t)h * HD + c;
+        float g[8], o[8];
+        ld8_do(d_out + off, g);
+        ld8_do(out + off, o);
+#pragma unroll
+        for (int i = 0; i < 8; i++) s += g[i] * o[i];
+        if (do16 != nullptr) {
+            uint4 u;
+            __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+            for (int i = 0; i < 4; i++) h2[i] = __floats2bfloat162_rn(g[2 * i], g[2 * i + 1]);
+            *reinterpret_cast<uint4*>(do16 + ((size_t)b * S + qp) * ((size_t)H * HD) + (size_t)h * HD + c) = u;
+        }
+    }
+#pragma unroll
+    for (int o = LPR / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (live && c == 0) delta[row] = s;
+}
+
 // ───────────────────────────── backward: dK, dV ───────────────────────────
 // CTA = one tile of 64 keys; warp = 16 keys (rows of S^T). Loops over the
 // query tiles that can see the key tile.
@@ -661,7 +711,14 @@ static int swa_backward_impl(const bf16* q, const bf16* k, const bf16* v, const 
                          (rs_in % 8 == 0) && (rs_o % 8 == 0);
     const bool use_tc = HD == 64 && option_value(NLH_OPT_SWA_TCGEN05) && aligned && (DO_IS_BF16 || do16_scratch != nullptr);
     bf16* do16 = (use_tc && !DO_IS_BF16) ? do16_scratch : nullptr;
-    swa_delta_kernel<HD, TDO><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(d_out, out, delta, S, H, B, rs_o, do16);
+    const bool delta_vec = HD % 8 == 0 && (rs_o % 8 == 0) && ((H * HD) % 8 == 0) &&
+                           ((((uintptr_t)d_out | (uintptr_t)out | (uintptr_t)do16) & 15) == 0);
+    if (delta_vec) {
+        const long long lanes = rows * (HD / 8);
+        swa_delta_vec_kernel<HD, TDO><<<(unsigned)((lanes + 255) / 256), 256, 0, st>>>(d_out, out, delta, S, H, B, rs_o, do16);
+    } else {
+        swa_delta_kernel<HD, TDO><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(d_out, out, delta, S, H, B, rs_o, do16);
+    }
     if (!check_launch("swa_delta_kernel")) return NLH_ERR_CUDA;
     if (use_tc) {
         // tcgen05 / TMEM kernels: 128 key rows (dK, dV) and 128 query rows (dQ) per CTA

@@ -442,23 +442,18 @@ __global__ void __launch_bounds__(WG_THREADS) gate_wgrad_kernel(
 struct CombineLevels {
     const float* y[WR_MAX_LEVELS];   // per-head level outputs [B*H, S/c, hd]
     int c[WR_MAX_LEVELS];            // pooling factor of the level (tokens per level token)
+    FastDiv cdiv[WR_MAX_LEVELS];     // division by c[l]
+    FastDiv sdiv;                    // division by the sequence length
     int k;
 };
 
-// y_comb for 4 consecutive channels j..j+3 of token (b,t)
-__device__ __forceinline__ float4 combine_y(const CombineLevels& L, const float* __restrict__ wts,
-                                            int b, int t, int j, int S, int H, int hd)
+// Gate of the MAG combine: sigmoid with the fast exponential and reciprocal (relative error about
+// 1e-6 over the unsaturated range; saturates like wr_sigmoid).
+__device__ __forceinline__ float combine_sigmoid(float x)
 {
-    const int h = j / hd, w = j - h * hd;
-    float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int l = 0; l < L.k; l++) {
-        const int sfl = S / L.c[l];
-        const float4 v = *reinterpret_cast<const float4*>(
-            L.y[l] + (((size_t)b * H + h) * sfl + t / L.c[l]) * hd + w);
-        const float wl = wts[l];
-        y.x += wl * v.x; y.y += wl * v.y; y.z += wl * v.z; y.w += wl * v.w;
-    }
-    return y;
+    if (x >= 15.0f) return 1.0f;
+    if (x <= -15.0f) return 0.0f;
+    return __fdividef(1.0f, 1.0f + __expf(-x));
 }
 
 template <typename TIN>
@@ -501,25 +496,66 @@ __device__ __forceinline__ RowWalk row_walk(int d4)
     return w;
 }
 
+// Warp per row of [B*S, d]: lane owns the float4 chunks c = lane + 32 i (i < NV) of the row, so the
+// row -> (sequence, token, level token) index arithmetic is done once per row instead of once per
+// element, the per-chunk head offsets are fixed for the whole kernel, and a lane has NV
+// independent load groups in flight.
+constexpr int CMB_WARPS = 8;
+
+struct CombineRow {
+    size_t base[WR_MAX_LEVELS];     // element offset of (sequence b, level token of t, head 0, 0) in y_l
+};
+__device__ __forceinline__ CombineRow combine_row(const CombineLevels& L, int row, int S, int H, int hd)
+{
+    CombineRow r;
+    const int b = fd_div(row, L.sdiv), t = row - b * S;
+#pragma unroll
+    for (int l = 0; l < WR_MAX_LEVELS; l++) {
+        const int sfl = fd_div(S, L.cdiv[l]);
+        r.base[l] = ((size_t)b * H * sfl + fd_div(t, L.cdiv[l])) * hd;
+    }
+    return r;
+}
+
 // out = x + attn_proj * sigmoid(y_comb)
-template <typename TIN>
-__global__ void __launch_bounds__(256) mag_combine_fwd_kernel(
+template <typename TIN, int NV>
+__global__ void __launch_bounds__(CMB_WARPS * 32) mag_combine_fwd_kernel(
     const float* __restrict__ x, const TIN* __restrict__ attn_proj, const float* __restrict__ wts,
     CombineLevels L, float* __restrict__ out, int B, int S, int d, int H)
 {
-    const int hd = d / H, d4 = d / 4;
-    const int n_rows = B * S;
-    const RowWalk rw = row_walk(d4);
-    const int j = rw.c4 * 4;
-    for (int row = rw.row; row < n_rows; row += rw.step) {
-        const int b = row / S, t = row - b * S;
-        const size_t i = (size_t)row * d4 + rw.c4;
-        const float4 y = combine_y(L, wts, b, t, j, S, H, hd);
-        const float4 xa = ld4<float>(x + i * 4), ap = ld4<TIN>(attn_proj + i * 4);
-        float4 o;
-        o.x = xa.x + ap.x * wr_sigmoid(y.x); o.y = xa.y + ap.y * wr_sigmoid(y.y);
-        o.z = xa.z + ap.z * wr_sigmoid(y.z); o.w = xa.w + ap.w * wr_sigmoid(y.w);
-        st4(out + i * 4, o);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int hd = d / H, nv = d >> 2, n_rows = B * S;
+    float wl[WR_MAX_LEVELS];
+    int hstride[WR_MAX_LEVELS];                 // elements between heads in y_l
+#pragma unroll
+    for (int l = 0; l < WR_MAX_LEVELS; l++) {
+        wl[l] = l < L.k ? wts[l] : 0.f;
+        hstride[l] = fd_div(S, L.cdiv[l]) * hd;
+    }
+    int hh[NV], ww[NV];
+#pragma unroll
+    for (int i = 0; i < NV; i++) { const int j = 4 * (lane + 32 * i); hh[i] = j / hd; ww[i] = j - hh[i] * hd; }
+    for (int row = blockIdx.x * CMB_WARPS + warp; row < n_rows; row += gridDim.x * CMB_WARPS) {
+        const CombineRow R = combine_row(L, row, S, H, hd);
+        const size_t ro = (size_t)row * d;
+#pragma unroll
+        for (int i = 0; i < NV; i++) {
+            const int c = lane + 32 * i;
+            if (c < nv) {
+                float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int l = 0; l < WR_MAX_LEVELS; l++)
+                    if (l < L.k) {
+                        const float4 v = *reinterpret_cast<const float4*>(L.y[l] + R.base[l] + (size_t)hh[i] * hstride[l] + ww[i]);
+                        y.x += wl[l] * v.x; y.y += wl[l] * v.y; y.z += wl[l] * v.z; y.w += wl[l] * v.w;
+                    }
+                const float4 xa = ld4<float>(x + ro + 4 * c), ap = ld4<TIN>(attn_proj + ro + 4 * c);
+                float4 o;
+                o.x = xa.x + ap.x * combine_sigmoid(y.x); o.y = xa.y + ap.y * combine_sigmoid(y.y);
+                o.z = xa.z + ap.z * combine_sigmoid(y.z); o.w = xa.w + ap.w * combine_sigmoid(y.w);
+                st4(out + ro + 4 * c, o);
+            }
+        }
     }
 }
 
@@ -531,50 +567,57 @@ struct CombineGrads {
 
 // d_attn_proj = d_out * gate ; d_ycomb = d_out * attn_proj * gate * (1 - gate) ;
 // dw_partial[cta][l] = sum d_ycomb * upsample(y_l)   (gradient of the level weights)
-template <typename TIN>
-__global__ void __launch_bounds__(256) mag_combine_bwd_kernel(
+template <typename TIN, int NV>
+__global__ void __launch_bounds__(CMB_WARPS * 32) mag_combine_bwd_kernel(
     const float* __restrict__ d_out, const TIN* __restrict__ attn_proj, const float* __restrict__ wts,
     CombineLevels L, TIN* __restrict__ d_attn_proj, float* __restrict__ d_ycomb,
     float* __restrict__ dw_partial, CombineGrads G, int B, int S, int d, int H)
 {
     __shared__ float red[WR_MAX_LEVELS * 32];
-    const int hd = d / H, d4 = d / 4;
-    const int n_rows = B * S;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int hd = d / H, nv = d >> 2, n_rows = B * S;
     float dw[WR_MAX_LEVELS] = {0.f, 0.f, 0.f, 0.f};
-    const RowWalk rw = row_walk(d4);
-    const int j = rw.c4 * 4;
-    const int h = j / hd, w = j - h * hd;
-    for (int row = rw.row; row < n_rows; row += rw.step) {
-        const int b = row / S, t = row - b * S;
-        const size_t i = (size_t)row * d4 + rw.c4;
-        float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
-        float4 yl[WR_MAX_LEVELS];
+    float wl[WR_MAX_LEVELS];
+    int hstride[WR_MAX_LEVELS];
 #pragma unroll
-        for (int l = 0; l < WR_MAX_LEVELS; l++) {
-            if (l < L.k) {
-                const int sfl = S / L.c[l];
-                yl[l] = *reinterpret_cast<const float4*>(
-                    L.y[l] + (((size_t)b * H + h) * sfl + t / L.c[l]) * hd + w);
-                const float wl = wts[l];
-                y.x += wl * yl[l].x; y.y += wl * yl[l].y; y.z += wl * yl[l].z; y.w += wl * yl[l].w;
-            }
-        }
-        const float4 go = ld4<float>(d_out + i * 4), ap = ld4<TIN>(attn_proj + i * 4);
-        float4 g, dap, dy;
-        g.x = wr_sigmoid(y.x); g.y = wr_sigmoid(y.y); g.z = wr_sigmoid(y.z); g.w = wr_sigmoid(y.w);
-        dap.x = go.x * g.x; dap.y = go.y * g.y; dap.z = go.z * g.z; dap.w = go.w * g.w;
-        dy.x = go.x * ap.x * g.x * (1.f - g.x); dy.y = go.y * ap.y * g.y * (1.f - g.y);
-        dy.z = go.z * ap.z * g.z * (1.f - g.z); dy.w = go.w * ap.w * g.w * (1.f - g.w);
-        st4(d_attn_proj + i * 4, dap);
-        st4(d_ycomb + i * 4, dy);
+    for (int l = 0; l < WR_MAX_LEVELS; l++) {
+        wl[l] = l < L.k ? wts[l] : 0.f;
+        hstride[l] = fd_div(S, L.cdiv[l]) * hd;
+    }
+    int hh[NV], ww[NV];
 #pragma unroll
-        for (int l = 0; l < WR_MAX_LEVELS; l++) {
-            if (l < L.k) {
-                dw[l] += dy.x * yl[l].x + dy.y * yl[l].y + dy.z * yl[l].z + dy.w * yl[l].w;
-                if (G.dy[l] != nullptr) {   // unpooled level: its gradient needs no pooling pass
-                    const float wl = wts[l];
-                    *reinterpret_cast<float4*>(G.dy[l] + (((size_t)b * H + h) * S + t) * hd + w) =
-                        make_float4(wl * dy.x, wl * dy.y, wl * dy.z, wl * dy.w);
+    for (int i = 0; i < NV; i++) { const int j = 4 * (lane + 32 * i); hh[i] = j / hd; ww[i] = j - hh[i] * hd; }
+    for (int row = blockIdx.x * CMB_WARPS + warp; row < n_rows; row += gridDim.x * CMB_WARPS) {
+        const CombineRow R = combine_row(L, row, S, H, hd);
+        const size_t ro = (size_t)row * d;
+#pragma unroll
+        for (int i = 0; i < NV; i++) {
+            const int c = lane + 32 * i;
+            if (c < nv) {
+                float4 yl[WR_MAX_LEVELS];
+                float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int l = 0; l < WR_MAX_LEVELS; l++)
+                    if (l < L.k) {
+                        yl[l] = *reinterpret_cast<const float4*>(L.y[l] + R.base[l] + (size_t)hh[i] * hstride[l] + ww[i]);
+                        y.x += wl[l] * yl[l].x; y.y += wl[l] * yl[l].y; y.z += wl[l] * yl[l].z; y.w += wl[l] * yl[l].w;
+                    }
+                const float4 go = ld4<float>(d_out + ro + 4 * c), ap = ld4<TIN>(attn_proj + ro + 4 * c);
+                float4 g, dap, dy;
+                g.x = combine_sigmoid(y.x); g.y = combine_sigmoid(y.y); g.z = combine_sigmoid(y.z); g.w = combine_sigmoid(y.w);
+                dap.x = go.x * g.x; dap.y = go.y * g.y; dap.z = go.z * g.z; dap.w = go.w * g.w;
+                dy.x = go.x * ap.x * g.x * (1.f - g.x); dy.y = go.y * ap.y * g.y * (1.f - g.y);
+                dy.z = go.z * ap.z * g.z * (1.f - g.z); dy.w = go.w * ap.w * g.w * (1.f - g.w);
+                st4(d_attn_proj + ro + 4 * c, dap);
+                st4(d_ycomb + ro + 4 * c, dy);
+#pragma unroll
+                for (int l = 0; l < WR_MAX_LEVELS; l++) {
+                    if (l < L.k) {
+                        dw[l] += dy.x * yl[l].x + dy.y * yl[l].y + dy.z * yl[l].z + dy.w * yl[l].w;
+                        if (G.dy[l] != nullptr)     // unpooled level (c_l = 1): same layout as y_l, no pooling pass
+                            *reinterpret_cast<float4*>(G.dy[l] + R.base[l] + (size_t)hh[i] * hstride[l] + ww[i]) =
+                                make_float4(wl[l] * dy.x, wl[l] * dy.y, wl[l] * dy.z, wl[l] * dy.w);
+                    }
                 }
             }
         }
@@ -662,6 +705,8 @@ __global__ void __launch_bounds__(256) mean_pool_kernel(const float* __restrict_
 struct UnpoolSrc {
     const void* g[3];
     int c[3];
+    FastDiv cdiv[3];
+    FastDiv sdiv;        // division by the sequence length
     int is_bf16[3];
     int n;
 };
@@ -672,13 +717,13 @@ __global__ void __launch_bounds__(256) unpool_sum_kernel(UnpoolSrc P, float* __r
     const RowWalk rw = row_walk(d4);
     const int c4 = rw.c4;
     for (int r = rw.row; r < n_rows; r += rw.step) {
-        const int b = r / S, t = r - b * S;
+        const int b = fd_div(r, P.sdiv), t = r - b * S;
         const size_t i = (size_t)r * d4 + c4;
         float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
         for (int l = 0; l < 3; l++) {
             if (l < P.n) {
-                const long long row = (long long)b * (S / P.c[l]) + t / P.c[l];
+                const long long row = (long long)b * fd_div(S, P.cdiv[l]) + fd_div(t, P.cdiv[l]);
                 const size_t o = ((size_t)row * d4 + c4) * 4;
                 const float4 v = P.is_bf16[l] ? ld4<__nv_bfloat16>((const __nv_bfloat16*)P.g[l] + o)
                                               : ld4<float>((const float*)P.g[l] + o);
@@ -886,7 +931,9 @@ static int fill_levels(CombineLevels& L, const float* y0, const float* y1, const
         L.y[l] = l < k ? ys[l] : nullptr;
         L.c[l] = l < k ? cs[l] : 1;
         if (l < k && (ys[l] == nullptr || cs[l] <= 0 || S % cs[l] != 0)) return NLH_ERR_INVALID_ARG;
+        L.cdiv[l] = make_fastdiv(L.c[l]);
     }
+    L.sdiv = make_fastdiv(S);
     L.k = k;
     return NLH_OK;
 }
@@ -903,15 +950,22 @@ int32_t nlh_mag_combine_forward(const float* x, const void* attn_proj, int32_t a
         record_status(NLH_ERR_INVALID_ARG, "nlh_mag_combine_forward", "bad level list");
         return NLH_ERR_INVALID_ARG;
     }
-    const long long n4 = (long long)batch * seq * (d_model / 4);
-    const int grid = wr_grid(n4, 256 * 4);
+    const int n_rows = batch * seq;
+    const int need = (n_rows + CMB_WARPS - 1) / CMB_WARPS;
+    const int grid = need < 148 * 8 ? need : 148 * 8;
+    const int ncl = (d_model / 4 + 31) / 32;      // float4 chunks per lane, <= 8 because d_model <= 1024
     cudaStream_t st = current_stream();
-    if (attn_is_bf16)
-        mag_combine_fwd_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
-            x, (const __nv_bfloat16*)attn_proj, level_weights, L, out, batch, seq, d_model, num_heads);
-    else
-        mag_combine_fwd_kernel<float><<<grid, 256, 0, st>>>(
-            x, (const float*)attn_proj, level_weights, L, out, batch, seq, d_model, num_heads);
+#define NLH_CMB_FWD(T, NV)                                                                       \
+    mag_combine_fwd_kernel<T, NV><<<grid, CMB_WARPS * 32, 0, st>>>(                                \
+        x, (const T*)attn_proj, level_weights, L, out, batch, seq, d_model, num_heads)
+    if (attn_is_bf16) {
+        if (ncl <= 1) NLH_CMB_FWD(__nv_bfloat16, 1); else if (ncl <= 2) NLH_CMB_FWD(__nv_bfloat16, 2);
+        else if (ncl <= 4) NLH_CMB_FWD(__nv_bfloat16, 4); else NLH_CMB_FWD(__nv_bfloat16, 8);
+    } else {
+        if (ncl <= 1) NLH_CMB_FWD(float, 1); else if (ncl <= 2) NLH_CMB_FWD(float, 2);
+        else if (ncl <= 4) NLH_CMB_FWD(float, 4); else NLH_CMB_FWD(float, 8);
+    }
+#undef NLH_CMB_FWD
     return check_launch("nlh_mag_combine_forward") ? NLH_OK : NLH_ERR_CUDA;
 }
 
@@ -938,14 +992,19 @@ int32_t nlh_mag_combine_backward(const float* d_out, const void* attn_proj, int3
             return NLH_ERR_INVALID_ARG;
         }
     }
-    if (attn_is_bf16)
-        mag_combine_bwd_kernel<__nv_bfloat16><<<n_partial_rows, 256, 0, st>>>(
-            d_out, (const __nv_bfloat16*)attn_proj, level_weights, L, (__nv_bfloat16*)d_attn_proj,
-            d_ycomb, dw_partial, G, batch, seq, d_model, num_heads);
-    else
-        mag_combine_bwd_kernel<float><<<n_partial_rows, 256, 0, st>>>(
-            d_out, (const float*)attn_proj, level_weights, L, (float*)d_attn_proj, d_ycomb,
-            dw_partial, G, batch, seq, d_model, num_heads);
+    const int ncl = (d_model / 4 + 31) / 32;
+#define NLH_CMB_BWD(T, NV)                                                                       \
+    mag_combine_bwd_kernel<T, NV><<<n_partial_rows, CMB_WARPS * 32, 0, st>>>(                      \
+        d_out, (const T*)attn_proj, level_weights, L, (T*)d_attn_proj, d_ycomb, dw_partial, G,  \
+        batch, seq, d_model, num_heads)
+    if (attn_is_bf16) {
+        if (ncl <= 1) NLH_CMB_BWD(__nv_bfloat16, 1); else if (ncl <= 2) NLH_CMB_BWD(__nv_bfloat16, 2);
+        else if (ncl <= 4) NLH_CMB_BWD(__nv_bfloat16, 4); else NLH_CMB_BWD(__nv_bfloat16, 8);
+    } else {
+        if (ncl <= 1) NLH_CMB_BWD(float, 1); else if (ncl <= 2) NLH_CMB_BWD(float, 2);
+        else if (ncl <= 4) NLH_CMB_BWD(float, 4); else NLH_CMB_BWD(float, 8);
+    }
+#undef NLH_CMB_BWD
     return check_launch("nlh_mag_combine_backward") ? NLH_OK : NLH_ERR_CUDA;
 }
 
@@ -1037,7 +1096,9 @@ int32_t nlh_unpool_sum(const void* g0, int32_t c0, int32_t g0_is_bf16, const voi
         P.c[l] = l < n_src ? cs[l] : 1;
         P.is_bf16[l] = bs[l];
         if (l < n_src && (gs[l] == nullptr || cs[l] <= 0 || seq % cs[l] != 0 || ((uintptr_t)gs[l] & 15) != 0)) ok = false;
+        P.cdiv[l] = make_fastdiv(P.c[l]);
     }
+    P.sdiv = make_fastdiv(seq > 0 ? seq : 1);
     P.n = n_src;
     if (!ok) {
         record_status(NLH_ERR_INVALID_ARG, "nlh_unpool_sum", "bad dimensions, pool factors or alignment");

@@ -397,6 +397,67 @@ class _LayerNorm(torch.autograd.Function):
         return d_x, d_gb[0], d_gb[1], None, None, None
 
 
+class _LayerNormPools(torch.autograd.Function):
+    """LayerNorm of x [B, S, d] followed by the mean pools that feed the coarser CMS levels: returns
+    the LayerNorm output (bf16 when out_bf16, the GEMM operand of level 0) and one mean-pooled copy
+    per pool factor (ascending; coarser ones reduced from the finer one's sums when divisible).
+    The backward is ONE kernel (nlh_layer_norm_backward_pooled): the pooled levels' gradients are
+    upsampled and summed inside the LayerNorm backward instead of being written out first.
+    grads = (g_gamma, g_beta): buffers the parameter gradients are accumulated into."""
+
+    @staticmethod
+    def forward(ctx, x, gamma, beta, eps, pools, out_bf16, grads):
+        x = x.contiguous()
+        B, S, d = x.shape
+        n, dev = B * S, x.device
+        o32 = torch.empty_like(x)
+        o16 = torch.empty(x.shape, dtype=torch.bfloat16, device=dev) if out_bf16 else None
+        mean = torch.empty(n, dtype=torch.float32, device=dev)
+        rstd = torch.empty(n, dtype=torch.float32, device=dev)
+        D.call("nlh_layer_norm_forward", x=x, gamma=gamma.contiguous(), beta=beta.contiguous(),
+               out_f32=o32, out_bf16=o16, mean_cache=mean, rstd_cache=rstd, n=n, d=d, eps=eps)
+        dt = torch.bfloat16 if out_bf16 else torch.float32
+        outs, prev = [], None                       # prev = (pool factor, unscaled sums)
+        for i, c in enumerate(pools):
+            later = any(c2 % c == 0 for c2 in pools[i + 1:])
+            out = torch.empty(B, S // c, d, dtype=dt, device=dev)
+            sums = torch.empty(B, S // c, d, dtype=torch.float32, device=dev) if later else None
+            src, f = (prev[1], c // prev[0]) if prev is not None and c % prev[0] == 0 else (o32, c)
+            D.call("nlh_mean_pool", src=src, factor=f, scale=1.0 / c, out=out, out_is_bf16=int(out_bf16),
+                   sum_out=sums, rows_out=B * (S // c), d_model=d)
+            if sums is not None:
+                prev = (c, sums)
+            outs.append(out)
+        ctx.save_for_backward(x, gamma, mean, rstd)
+        ctx.meta = (B, S, d, tuple(pools))
+        ctx.grads = grads
+        return (o16 if out_bf16 else o32, *outs)
+
+    @staticmethod
+    def backward(ctx, g_main, *gp):
+        x, gamma, mean, rstd = ctx.saved_tensors
+        B, S, d, pools = ctx.meta
+        src = [(g.contiguous(), c) for g, c in zip(gp, pools) if g is not None]
+        assert len(src) <= 3, "at most three pooled levels"
+        d_x = torch.empty_like(x)
+        if g_main is None and not src:
+            return d_x.zero_(), None, None, None, None, None, None
+        g32 = g16 = None
+        if g_main is not None:
+            g_main = g_main.contiguous()
+            g16, g32 = (g_main, None) if g_main.dtype == torch.bfloat16 else (None, g_main)
+        src = src + [(None, 1)] * (3 - len(src))
+        isb = lambda t: int(t is not None and t.dtype == torch.bfloat16)
+        D.call("nlh_layer_norm_backward_pooled", d_out_f32=g32, d_out_bf16=g16,
+               g0=src[0][0], c0=src[0][1], g0_is_bf16=isb(src[0][0]),
+               g1=src[1][0], c1=src[1][1], g1_is_bf16=isb(src[1][0]),
+               g2=src[2][0], c2=src[2][1], g2_is_bf16=isb(src[2][0]),
+               n_src=sum(1 for g, _ in src if g is not None), seq=S, x=x, gamma=gamma.contiguous(),
+               mean_cache=mean, rstd_cache=rstd, d_x=d_x, d_gamma=ctx.grads[0], d_beta=ctx.grads[1],
+               n=B * S, d=d)
+        return d_x, None, None, None, None, None, None
+
+
 class _CrossEntropy(torch.autograd.Function):
     """Mean cross-entropy over valid targets on fp32 or bf16 logits [n, vocab]
     (nlh_cross_entropy_forward / _backward). The backward overwrites the logits with their
@@ -736,14 +797,20 @@ class StackedMAG:
             else:
                 wts = torch.softmax(p[pre + "alpha_mem"], dim=0)
             if fused:
-                m32, m16 = self._ln(res1, pre + "ln_mem_", 2, True) if cfg.bf16 else \
-                    (self._ln(res1, pre + "ln_mem_", 0, True),) * 2
                 S = res1.shape[1]
                 cs = [min(c, S) for c in cfg.chunk_sizes[:cfg.k]]
-                uniq = sorted({c for c in cs if c > 1})
-                pooled = dict(zip(uniq, _PoolLevels.apply(m32, tuple(uniq), cfg.bf16))) if uniq else {}
                 for c in cs:
                     assert S % c == 0, "seq_len must be a multiple of every chunk size"
+                uniq = sorted({c for c in cs if c > 1})
+                if d % 8 == 0 and len(uniq) <= 3:       # LayerNorm + pools, one backward kernel
+                    m16, *pl = _LayerNormPools.apply(
+                        res1, p[pre + "ln_mem_gamma"], p[pre + "ln_mem_beta"], 1e-5, tuple(uniq), cfg.bf16,
+                        (self.g[pre + "ln_mem_gamma"], self.g[pre + "ln_mem_beta"]))
+                    pooled = dict(zip(uniq, pl))
+                else:
+                    m32, m16 = self._ln(res1, pre + "ln_mem_", 2, True) if cfg.bf16 else \
+                        (self._ln(res1, pre + "ln_mem_", 0, True),) * 2
+                    pooled = dict(zip(uniq, _PoolLevels.apply(m32, tuple(uniq), cfg.bf16))) if uniq else {}
                 ys = self._levels(b, [pooled.get(cs[l], m16) for l in range(cfg.k)])
                 pools = cs
                 x = _MagCombine.apply(x, attn_raw, wts, tuple(pools), nh, self.g[pre + "alpha_mem"], *ys)
@@ -770,14 +837,16 @@ class StackedMAG:
 
     def forward_backward(self, tokens, targets, process_group=None, world=1):
         """Loss (mean over the local batch) and its gradients, accumulated into the arena.
-        With world > 1 on the GPU (and cfg.overlap_grad_sync) the gradients are also averaged
-        over the ranks here: the arena is laid out in the order the backward completes it
+        With world > 1 (and cfg.overlap_grad_sync) the gradients are also averaged over the
+        ranks here: the arena is laid out in the order the backward completes it
         backwards (embedding | unembedding + final LayerNorm | block 0 | block 1 | ...), so each
-        block's slice is all-reduced (NCCL, average) as soon as that block's backward has been
+        block's slice is all-reduced (average) as soon as that block's backward has been
         issued and the exchange runs under the backward of the blocks below it; the embedding's
         slice goes last. sync_gradients() is then a no-op for this step."""
-        overlap = (world > 1 and tokens.is_cuda and self.cfg.overlap_grad_sync)
-        self._sync_state = dict(pg=process_group, works=[], seen=set()) if overlap else None
+        overlap = (world > 1 and self.cfg.overlap_grad_sync and torch.distributed.is_available()
+                   and torch.distributed.is_initialized())
+        self._sync_state = dict(pg=process_group, works=[], seen=set(), world=world,
+                                avg=tokens.is_cuda) if overlap else None
         loss = self.forward(tokens, targets)
         loss.backward()
         if overlap:
@@ -786,7 +855,10 @@ class StackedMAG:
                 if name not in st["seen"]:
                     self._reduce_bucket(name)
             for w in st["works"]:
-                w.wait()                               # the compute stream waits, the host does not
+                w.wait()                               # on the GPU the compute stream waits, not the host
+            if not st["avg"]:                          # backends without an averaging reduction
+                self.opt.g.mul_(1.0 / world)
+            self._last_buckets = sorted(st["seen"])
             self._sync_state = None
             self._grads_synced = True
         return loss.detach()
@@ -810,8 +882,9 @@ class StackedMAG:
         st = self._sync_state
         st["seen"].add(name)
         o0, o1 = self._bucket_range(name)
-        st["works"].append(torch.distributed.all_reduce(
-            self.opt.g[o0:o1], op=torch.distributed.ReduceOp.AVG, group=st["pg"], async_op=True))
+        op = torch.distributed.ReduceOp.AVG if st["avg"] else torch.distributed.ReduceOp.SUM
+        st["works"].append(torch.distributed.all_reduce(self.opt.g[o0:o1], op=op, group=st["pg"],
+                                                        async_op=True))
 
     def _mark_bucket(self, x, name):
         """Tensor hook on the activation that enters a block (or the final LayerNorm): autograd

@@ -74,6 +74,61 @@ def test_layer_norm_bf16_outputs_and_split_gradient(orc):
     assert rel_err(_np(dgb[0]), dg_r) <= 1e-4 and rel_err(_np(dgb[1]), db_r) <= 1e-4
 
 
+@pytest.mark.parametrize("B,S,d,pools,bf16", [(2, 64, 512, (8, 64), True), (3, 48, 128, (2, 8, 24), False),
+                                             (1, 512, 512, (8, 64, 512), True), (5, 6, 64, (3,), False)])
+def test_layer_norm_backward_with_pooled_sources(orc, B, S, d, pools, bf16):
+    """nlh_layer_norm_backward_pooled == oracle LayerNorm backward of (direct gradient + the
+    upsampled, 1/c-scaled gradients of the mean-pooled copies); odd row counts exercise the
+    two-rows-per-pass tail."""
+    import torch
+    from nl_hecate_b200 import dispatch as D
+    n = B * S
+    x = orc.rand_buf(n * d, 721, 2.0).reshape(n, d)
+    gamma = 1.0 + orc.rand_buf(d, 722, 0.3)
+    beta = orc.rand_buf(d, 723, 0.2)
+    g_main = orc.rand_buf(n * d, 724, 1.0).reshape(n, d)
+    if bf16:
+        g_main = orc.bf16_round(g_main)
+    gp = []
+    for i, c in enumerate(pools):
+        g = orc.rand_buf(B * (S // c) * d, 730 + i, 1.0).reshape(B, S // c, d)
+        gp.append(orc.bf16_round(g) if bf16 else g)
+    total = g_main.reshape(B, S, d).copy()
+    for g, c in zip(gp, pools):
+        total += np.repeat(g, c, axis=1) / np.float32(c)
+    out_r, mean_r, rstd_r = orc.layer_norm_forward(x, gamma, beta, 1e-5)
+    dx_r, dg_r, db_r = orc.layer_norm_backward(total.reshape(n, d), x, gamma, mean_r, rstd_r)
+    dt = torch.bfloat16 if bf16 else None
+    xd, gd = _dev(x), _dev(gamma)
+    mean, rstd = _dev(mean_r), _dev(rstd_r)
+    gm = _dev(g_main, dt)
+    gpd = [_dev(g, dt) for g in gp] + [None] * (3 - len(gp))
+    cs = list(pools) + [1] * (3 - len(pools))
+    dx = torch.empty_like(xd)
+    dgb = torch.zeros(2, d, device="cuda")
+    D.call("nlh_layer_norm_backward_pooled", d_out_f32=None if bf16 else gm, d_out_bf16=gm if bf16 else None,
+           g0=gpd[0], c0=cs[0], g0_is_bf16=int(bf16), g1=gpd[1], c1=cs[1], g1_is_bf16=int(bf16),
+           g2=gpd[2], c2=cs[2], g2_is_bf16=int(bf16), n_src=len(pools), seq=S, x=xd, gamma=gd,
+           mean_cache=mean, rstd_cache=rstd, d_x=dx, d_gamma=dgb[0], d_beta=dgb[1], n=n, d=d)
+    assert rel_err(_np(dx), dx_r) <= 1e-4
+    assert rel_err(_np(dgb[0]), dg_r) <= 1e-4 and rel_err(_np(dgb[1]), db_r) <= 1e-4
+    # pooled sources alone (no direct gradient)
+    dx2 = torch.empty_like(xd)
+    dgb2 = torch.zeros(2, d, device="cuda")
+    D.call("nlh_layer_norm_backward_pooled", d_out_f32=None, d_out_bf16=None,
+           g0=gpd[0], c0=cs[0], g0_is_bf16=int(bf16), g1=gpd[1], c1=cs[1], g1_is_bf16=int(bf16),
+           g2=gpd[2], c2=cs[2], g2_is_bf16=int(bf16), n_src=len(pools), seq=S, x=xd, gamma=gd,
+           mean_cache=mean, rstd_cache=rstd, d_x=dx2, d_gamma=dgb2[0], d_beta=dgb2[1], n=n, d=d)
+    dx_r2, _, _ = orc.layer_norm_backward((total - g_main.reshape(B, S, d)).reshape(n, d), x, gamma, mean_r, rstd_r)
+    assert rel_err(_np(dx2), dx_r2) <= 1e-4
+    # a pool factor that does not divide the sequence is rejected on the host
+    with pytest.raises(Exception):
+        D.call("nlh_layer_norm_backward_pooled", d_out_f32=None, d_out_bf16=None,
+               g0=gpd[0], c0=S + 1, g0_is_bf16=int(bf16), g1=None, c1=1, g1_is_bf16=0, g2=None, c2=1,
+               g2_is_bf16=0, n_src=1, seq=S, x=xd, gamma=gd, mean_cache=mean, rstd_cache=rstd, d_x=dx2,
+               d_gamma=dgb2[0], d_beta=dgb2[1], n=n, d=d)
+
+
 @pytest.mark.parametrize("n,v", [(5, 37), (64, 8192), (3, 1000), (1, 1)])
 def test_cross_entropy_drop_in_matches_oracle(orc, n, v):
     import torch

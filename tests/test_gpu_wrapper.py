@@ -99,6 +99,35 @@ def test_mag_combine_forward_backward(B, S, d, H, pools, dtype):
         assert _rel(a, b) <= tol, (name, _rel(a, b))
 
 
+def test_partial_row_finishers_accumulate_into_gradient_buffers():
+    """nlh_gate_grad_finish and nlh_level_weight_grad_finish: column sums of the partial rows,
+    added to what the gradient buffers already hold; the level weights go through the softmax
+    adjoint."""
+    from nl_hecate_b200 import dispatch as D
+    g = torch.Generator().manual_seed(3)
+    for rows, d in [(1, 64), (37, 512), (300, 128)]:
+        dwp = torch.randn(rows, 3, 2 * d, generator=g).cuda()
+        dbp = torch.randn(rows, 3, generator=g).cuda()
+        gw = torch.randn(3, 2 * d, generator=g).cuda()
+        gb = [torch.randn(1, generator=g).cuda() for _ in range(3)]
+        want_w = gw.double() + dwp.double().sum(0)
+        want_b = [gb[i].double() + dbp.double().sum(0)[i] for i in range(3)]
+        D.call("nlh_gate_grad_finish", dw_partial=dwp, db_partial=dbp, rows=rows, d_model=d,
+               g_w_gates=gw, g_b_alpha=gb[0], g_b_theta=gb[1], g_b_eta=gb[2])
+        assert float((gw.double() - want_w).abs().max()) <= 1e-4 * float(want_w.abs().max())
+        for i in range(3):
+            assert abs(float(gb[i]) - float(want_b[i])) <= 1e-4 * max(1.0, abs(float(want_b[i])))
+    for rows, k in [(1, 1), (1184, 4), (50, 3)]:
+        dwp = torch.randn(rows, 4, generator=g).cuda()
+        logits = torch.randn(k, generator=g).cuda().requires_grad_(True)
+        w = torch.softmax(logits, 0)
+        (w * dwp[:, :k].sum(0)).sum().backward()
+        gl = torch.full((k,), 0.25, device="cuda")
+        D.call("nlh_level_weight_grad_finish", dw_partial=dwp, rows=rows, k=k, level_weights=w.detach().contiguous(),
+               g_logits=gl)
+        assert float((gl - 0.25 - logits.grad).abs().max()) <= 1e-4 * max(1.0, float(logits.grad.abs().max()))
+
+
 def test_wrapper_rejects_unsupported_shapes():
     if not torch.cuda.is_available():
         pytest.skip("needs a CUDA device")

@@ -77,7 +77,15 @@ def _dp_worker(rank, world, port, q):
     lo = rank * 2
     m.forward_backward(tok[lo:lo + 2], tgt[lo:lo + 2])
     m.sync_gradients(None, world)
-    q.put((rank, m.opt.g.clone()))
+    one = m.opt.g.clone()
+    # the same exchange in per-block buckets issued from autograd hooks during the backward
+    m2 = _model(2)
+    m2.forward_backward(tok[lo:lo + 2], tgt[lo:lo + 2], None, world)
+    assert m2._grads_synced
+    m2.sync_gradients(None, world)          # no second exchange
+    assert torch.allclose(m2.opt.g, one, atol=1e-9, rtol=1e-6)
+    assert sorted(m2._last_buckets) == sorted(m2._bucket_order())
+    q.put((rank, one))
     dist.barrier()
     dist.destroy_process_group()
 
