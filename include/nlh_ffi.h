@@ -356,7 +356,7 @@ int32_t nlh_mag_combine_backward(const float* d_out, const void* attn_proj, int3
     float* dw_partial, int32_t n_partial_rows, float* dy0, float* dy1, float* dy2, float* dy3,
     int32_t batch, int32_t seq, int32_t d_model, int32_t num_heads);
 /* Finishers of the per-CTA partial rows the two backward entries above leave: rows are summed
- * in a fixed order and ADDED into the caller's gradient buffers (no reduction or accumulation
+ * and ADDED into the caller's gradient buffers (no reduction or accumulation
  * pass on the caller's side). nlh_gate_grad_finish: dw_partial [rows, 3, 2*d_model] into
  * g_w_gates [3, 2*d_model], db_partial [rows, 3] into the three bias gradients (each [1]; a NULL
  * one is skipped). nlh_level_weight_grad_finish: dw_partial [rows, 4] of nlh_mag_combine_backward

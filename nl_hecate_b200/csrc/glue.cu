@@ -306,9 +306,11 @@ __device__ __forceinline__ void lse_merge(float& m, float& s, float m2, float s2
     m = mm;
 }
 
-// One CTA per row: log-sum-exp in one pass over the row.
+// One CTA per row: log-sum-exp in one pass over the row. Not inlined: the cross-entropy backward
+// calls it only when no stored log-sum-exp is given, and its 32-value register block must not
+// raise the register count of that kernel's main path.
 template <typename T>
-__device__ __forceinline__ float row_lse(const T* __restrict__ row, int vocab, float* red_m, float* red_s)
+__device__ __noinline__ float row_lse(const T* __restrict__ row, int vocab, float* red_m, float* red_s)
 {
     float m = -CUDART_INF_F, s = 0.f;
     if (sizeof(T) == 2 && (vocab & 7) == 0 && ((uintptr_t)row & 15) == 0) {

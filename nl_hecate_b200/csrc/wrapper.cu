@@ -746,18 +746,22 @@ static int wr_grid(long long items, int per_cta)
 
 // ───────────────────────── partial-row finishers ──────────────────────────
 // The backward kernels above leave parameter gradients as per-CTA partial rows. These kernels sum
-// the rows in a fixed order (deterministic) and ADD the result into the caller's gradient
-// buffers, so that a training step needs no reduction and no accumulation pass of its own.
-// Gate weights: thread per column of dw_partial [rows, cols]; the last CTA also sums the three
-// bias columns of db_partial [rows, 3].
+// the rows and ADD the result into the caller's gradient buffers, so that a training step needs no
+// reduction and no accumulation pass of its own.
+// Gate weights: thread per column of dw_partial [rows, cols], the rows divided over gridDim.y
+// slices (one atomicAdd per column and slice: up to 16 addends per element, in any order); the
+// last CTA of slice 0 also sums the three bias columns of db_partial [rows, 3].
 __global__ void __launch_bounds__(256) gate_grad_finish_kernel(
-    const float* __restrict__ dw_partial, const float* __restrict__ db_partial, int rows, int cols,
+    const float* __restrict__ dw_partial, const float* __restrict__ db_partial, int rows_total, int cols,
     float* __restrict__ g_w, float* g_b0, float* g_b1, float* g_b2)
 {
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c < cols) {
+    const int per = (rows_total + gridDim.y - 1) / gridDim.y;
+    const int r_lo = blockIdx.y * per;
+    const int rows = min(rows_total, r_lo + per);
+    if (c < cols && r_lo < rows) {
         float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-        int r = 0;
+        int r = r_lo;
         for (; r + 4 <= rows; r += 4) {
             a0 += dw_partial[(size_t)r * cols + c];
             a1 += dw_partial[(size_t)(r + 1) * cols + c];
@@ -765,12 +769,13 @@ __global__ void __launch_bounds__(256) gate_grad_finish_kernel(
             a3 += dw_partial[(size_t)(r + 3) * cols + c];
         }
         for (; r < rows; r++) a0 += dw_partial[(size_t)r * cols + c];
-        g_w[c] += (a0 + a1) + (a2 + a3);
+        const float t = (a0 + a1) + (a2 + a3);
+        if (gridDim.y == 1) g_w[c] += t; else atomicAdd(g_w + c, t);
     }
-    if (blockIdx.x == gridDim.x - 1 && threadIdx.x < 96) {
+    if (blockIdx.x == gridDim.x - 1 && blockIdx.y == 0 && threadIdx.x < 96) {
         const int g = threadIdx.x >> 5, lane = threadIdx.x & 31;
         float s = 0.f;
-        for (int r = lane; r < rows; r += 32) s += db_partial[(size_t)r * 3 + g];
+        for (int r = lane; r < rows_total; r += 32) s += db_partial[(size_t)r * 3 + g];
         s = warp_sum(s);
         float* dst = g == 0 ? g_b0 : g == 1 ? g_b1 : g_b2;
         if (lane == 0 && dst) dst[0] += s;
@@ -1016,7 +1021,9 @@ int32_t nlh_gate_grad_finish(const float* dw_partial, const float* db_partial, i
         return NLH_ERR_INVALID_ARG;
     }
     const int cols = 3 * 2 * d_model;
-    gate_grad_finish_kernel<<<(cols + 255) / 256, 256, 0, current_stream()>>>(
+    int slices = rows / 48;                       // about 48 rows per CTA, at most 16 slices
+    slices = slices < 1 ? 1 : (slices > 16 ? 16 : slices);
+    gate_grad_finish_kernel<<<dim3((cols + 255) / 256, slices), 256, 0, current_stream()>>>(
         dw_partial, db_partial, rows, cols, g_w_gates, g_b_alpha, g_b_theta, g_b_eta);
     return check_launch("nlh_gate_grad_finish") ? NLH_OK : NLH_ERR_CUDA;
 }
