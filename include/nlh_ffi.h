@@ -229,7 +229,11 @@ void titans_fused_forward_f32_cuda(float* k_mem, const float* v_mem, float* q_me
  *   m_ckpt/s_ckpt [B, ceil(S/interval)+1, d*d] (slot j = state before token
  *   j*interval; last slot = final state);
  * frozen-M0 rule (chunk_size > 0): interval must equal chunk_size and the
- *   buffers are the reference's *_chunk_states.
+ *   buffers are the reference's *_chunk_states; or interval = 1 with chunk_size > 1 (Titans,
+ *   head_dim 32/64): EVERY state is stored, m_ckpt [B, S+1, d*d], s_ckpt may be NULL, and the
+ *   backward streams the stored states instead of recomputing chunk windows (the momentum is
+ *   derived from consecutive M states, which needs eta_t > 0) — the faster pair for short
+ *   chunks, at (S+1) d*d floats per problem.
  * Replaces the trajectory-materialising pairs core/kernels/titans_forward.cu:83
  * + titans_backward.cu:66 (and the Delta/Hebbian twins) at the call sites
  * core/src/gpu_forward.rs:1521 and gpu_backward.rs:459. */
@@ -239,7 +243,8 @@ int32_t nlh_rule_forward(int32_t rule, const float* k_mem, const float* v_mem, c
     int32_t batch_size, int32_t interval, int32_t chunk_size, float error_clip,
     float m_norm_max);
 /* Matching backward. d_m_initial/d_s_initial are PER PROBLEM [B,d*d] (the
- * reference sums them over the batch with atomicAdd: titans_backward.cu:337). */
+ * reference sums them over the batch with atomicAdd: titans_backward.cu:337); in the
+ * full-trajectory frozen mode both may be NULL. */
 int32_t nlh_rule_backward(int32_t rule, const float* k_mem, const float* v_mem,
     const float* q_mem, const float* alpha, const float* theta, const float* eta,
     const float* m_ckpt, const float* s_ckpt, const float* d_y, float* d_k_mem, float* d_v_mem,

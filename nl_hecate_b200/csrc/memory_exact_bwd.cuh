@@ -19,11 +19,12 @@
 
 namespace nlh {
 
-template <int D, int SPLIT = 1>
+template <int D, int SPLIT = 1, bool FROZEN = false>
 constexpr size_t exact_bwd_smem_floats()
 {
     using G = FastGeom<D, SPLIT>;
-    return (size_t)2 * FAST_TB * 4 * D        // k | v | q | dy rows, double buffered
+    return (FROZEN ? (size_t)G::ROWS * D : 0)  // chunk-start state (frozen rule)
+         + (size_t)2 * FAST_TB * 4 * D        // k | v | q | dy rows, double buffered
          + 2 * FAST_TB * 4                    // gates (alpha, theta, eta, pad)
          + (size_t)FAST_NST * G::ROWS * D     // state ring (M only, this CTA's rows)
          + (size_t)2 * G::NW * FAST_TB * D    // dq / dk warp partials
@@ -35,9 +36,18 @@ constexpr size_t exact_bwd_smem_floats()
 // partial column sums and partial gate gradients, which it ADDS into d_q, d_k, d_alpha, d_theta,
 // d_eta with atomicAdd (two addends per element: the result does not depend on their order); the
 // launcher zeroes those five outputs first.
-template <int D, int SPLIT = 1>
-__global__ void __launch_bounds__(FastGeom<D, SPLIT>::NT, D == 64 ? (SPLIT == 1 ? 2 : 3) : 8) titans_exact_bwd_kernel(BwdArgs a)
+// FROZEN: the frozen-M0 chunkwise rule on a FULL stored M trajectory (every token's state, as the
+// exact rule stores it) instead of a recomputed chunk window: inside a chunk of a.chunk tokens the
+// error reads the chunk-start state M_c (e_t = M_c k_t - v_t), so d_k takes M_c^T de, the de k^T
+// terms collect in dM0 and join dM when the walk reaches the chunk's first token
+// (core/kernels/titans_chunkwise_backward.cu:196-351). Everything else — the S derivation from
+// consecutive M states included — is the exact rule's. M_c (16 registers) and dM0 (16) leave room
+// for one CTA per SM; the chunk-start state of the NEXT chunk is fetched with cp.async into a
+// thread-private buffer while the current chunk is processed.
+template <int D, int SPLIT = 1, bool FROZEN = false>
+__global__ void __launch_bounds__(FastGeom<D, SPLIT>::NT, FROZEN ? 1 : (D == 64 ? (SPLIT == 1 ? 2 : 3) : 8)) titans_exact_bwd_kernel(BwdArgs a)
 {
+    static_assert(!FROZEN || SPLIT == 1, "the frozen variant is not row-split");
     using G = FastGeom<D, SPLIT>;
     constexpr int NT = G::NT, TPR = G::TPR, NW = G::NW, TB = FAST_TB, NST = FAST_NST, DD = D * D;
     constexpr int ROWS = G::ROWS, RD = ROWS * D;      // floats of one state slot held by this CTA
@@ -52,6 +62,7 @@ __global__ void __launch_bounds__(FastGeom<D, SPLIT>::NT, D == 64 ? (SPLIT == 1 
     float* pk = pq + (size_t)NW * TB * D;             // [NW][TB][D]
     float* dvs = pk + (size_t)NW * TB * D;            // [TB][ROWS]
     float* scp = dvs + TB * ROWS;                     // [3][TB][ROWS]
+    float* mcb = scp + 3 * TB * ROWS;                 // [RD] chunk-start state, thread-major (FROZEN)
 
     const int tid = threadIdx.x, rl = tid / TPR, cg = tid % TPR;   // rl: row within this CTA
     const int part = (SPLIT > 1) ? (int)(blockIdx.x % SPLIT) : 0;
@@ -73,6 +84,25 @@ __global__ void __launch_bounds__(FastGeom<D, SPLIT>::NT, D == 64 ? (SPLIT == 1 
     const float* mt_base = a.m_traj + (size_t)b * a.traj_stride;   // slot j = state before token t0+j
 
     float2 dM[8], dS[8], Mt[8];
+    float2 Mc[8], dM0[8];                             // FROZEN only: chunk-start state, its gradient terms
+    float* const mcb_t = mcb + tid * 4;
+    const int C = FROZEN ? a.chunk : 1;
+    int cs_next = -1;                                 // chunk start whose state is to be fetched next
+    int cs_age = NST;                                 // commit groups since the last fetch was issued
+    auto prefetch_chunk_state = [&](int cs) {         // state before token cs (trajectory slot cs)
+        const float* src = mt_base + (size_t)(cs - t0) * DD + r * D;
+#pragma unroll
+        for (int jj = 0; jj < 4; jj++) cp_async16(mcb_t + jj * NT * 4, src + co[jj]);
+        cs_age = 0;
+    };
+    auto load_chunk_state = [&]() {
+#pragma unroll
+        for (int jj = 0; jj < 4; jj++) {
+            const float4 t4 = *reinterpret_cast<const float4*>(mcb_t + jj * NT * 4);
+            Mc[2 * jj] = make_float2(t4.x, t4.y); Mc[2 * jj + 1] = make_float2(t4.z, t4.w);
+        }
+    };
+    if (FROZEN) zero8(dM0);
     if (a.d_m_seed) load_state8<D>(dM, a.d_m_seed + (size_t)b * DD, r, cg, xc);
     else zero8(dM);
     if (a.d_s_seed) load_state8<D>(dS, a.d_s_seed + (size_t)b * DD, r, cg, xc);
@@ -151,6 +181,7 @@ __global__ void __launch_bounds__(FastGeom<D, SPLIT>::NT, D == 64 ? (SPLIT == 1 
 
     if (len > 0) {
         prefetch_tile(ntl - 1);
+        if (FROZEN) prefetch_chunk_state(((t1 - 1) / C) * C);   // the last chunk's start, first group
         prefetch_state();            // state len, same group as the last tile
         cp_async_commit();
         prefetch_state();            // state len-1
@@ -159,6 +190,7 @@ __global__ void __launch_bounds__(FastGeom<D, SPLIT>::NT, D == 64 ? (SPLIT == 1 
         cp_async_commit();
         cp_async_wait<NST - 1>();    // first group landed
         __syncthreads();             // ... for every thread: the tile is visible
+        cs_age = NST;                // ... and so has the last chunk's start state
         load_state();                // Mt = M_len
     }
     for (int tile = ntl - 1; tile >= 0; tile--) {
@@ -172,9 +204,20 @@ __global__ void __launch_bounds__(FastGeom<D, SPLIT>::NT, D == 64 ? (SPLIT == 1 
             // keep NST-1 state groups in flight; the next tile's streams ride in the first group
             prefetch_state();
             if (tl == ntok - 1 && tile > 0) prefetch_tile(tile - 1);
+            if (FROZEN && cs_next >= 0) { prefetch_chunk_state(cs_next); cs_next = -1; }
             cp_async_commit();
             cp_async_wait<NST - 1>();
             load_state();            // Mt = M_t
+            if (FROZEN) {
+                const int t = tt0 + tl;
+                cs_age++;
+                if (t == t1 - 1 || (t + 1) % C == 0) {       // first token processed of its chunk
+                    if (cs_age < NST) cp_async_wait<0>();    // a short chunk: the fetch may still be in flight
+                    load_chunk_state();
+                    const int cs = (t / C) * C;
+                    cs_next = (cs - C >= t0) ? cs - C : -1;  // fetched from the next iteration on
+                }
+            }
             const float* row = tb + tl * ROW;
             float2 kk[8];
 #pragma unroll
@@ -192,7 +235,7 @@ __global__ void __launch_bounds__(FastGeom<D, SPLIT>::NT, D == 64 ? (SPLIT == 1 
 #pragma unroll
             for (int i = 0; i < 8; i++) {
                 if (i & 1) ub = fma2(dS[i], kk[i], ub); else ua = fma2(dS[i], kk[i], ua);
-                p2 = fma2(Mt[i], kk[i], p2);
+                p2 = fma2(FROZEN ? Mc[i] : Mt[i], kk[i], p2);
                 pa2 = fma2(Mt[i], dM[i], pa2);
                 pb2 = fma2(Mt[i], dS[i], pb2);
             }
@@ -215,9 +258,14 @@ __global__ void __launch_bounds__(FastGeom<D, SPLIT>::NT, D == 64 ? (SPLIT == 1 
                 const float2 de2 = bc2(de), nthe2 = bc2(-th * e), et2 = bc2(et), rr2 = bc2(rr);
 #pragma unroll
                 for (int i = 0; i < 8; i++) {
-                    ck[i] = fma2(dS[i], nthe2, mul2(Mt[i], de2));     // d_k = -theta dS^T e + M_t^T de
+                    ck[i] = fma2(dS[i], nthe2, mul2(FROZEN ? Mc[i] : Mt[i], de2));   // d_k = -theta dS^T e + M^T de
                     dS[i] = mul2(dS[i], et2);
-                    dM[i] = fma2(kk[i], de2, mul2(dM[i], rr2));
+                    if (FROZEN) { dM0[i] = fma2(kk[i], de2, dM0[i]); dM[i] = mul2(dM[i], rr2); }
+                    else dM[i] = fma2(kk[i], de2, mul2(dM[i], rr2));
+                }
+                if (FROZEN && (tt0 + tl) % C == 0) {          // the chunk's first token: dM += dM0
+#pragma unroll
+                    for (int i = 0; i < 8; i++) { dM[i] = add2(dM[i], dM0[i]); dM0[i] = make_float2(0.f, 0.f); }
                 }
                 float ok[NOUT];
                 ColReduce<TPR>::run(ck, lane, ok);
@@ -272,7 +320,7 @@ __global__ void __launch_bounds__(FastGeom<D, SPLIT>::NT, D == 64 ? (SPLIT == 1 
             atomicAdd(&a.d_s_out[o], dS[i].x);
             atomicAdd(&a.d_s_out[o + 1], dS[i].y);
         }
-    } else {
+    } else if (a.d_m_out != nullptr) {
         store_state8<D>(dM, a.d_m_out + (size_t)b * DD, r, cg, xc);
         store_state8<D>(dS, a.d_s_out + (size_t)b * DD, r, cg, xc);
     }
@@ -296,6 +344,17 @@ static bool exact_bwd_launch(const BwdArgs& a, cudaStream_t st)
     const size_t smem = exact_bwd_smem_floats<D>() * sizeof(float);
     cudaFuncSetAttribute(titans_exact_bwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     titans_exact_bwd_kernel<D><<<a.batch, FastGeom<D>::NT, smem, st>>>(a);
+    return true;
+}
+
+// Frozen-M0 chunkwise Titans backward on a full M trajectory (a.m_traj [batch, seq_len + 1, d*d],
+// a.chunk tokens per chunk, whole sequence).
+template <int D>
+static bool frozen_stream_bwd_launch(const BwdArgs& a, cudaStream_t st)
+{
+    const size_t smem = exact_bwd_smem_floats<D, 1, true>() * sizeof(float);
+    cudaFuncSetAttribute(titans_exact_bwd_kernel<D, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    titans_exact_bwd_kernel<D, 1, true><<<a.batch, FastGeom<D>::NT, smem, st>>>(a);
     return true;
 }
 

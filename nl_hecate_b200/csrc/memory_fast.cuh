@@ -327,6 +327,8 @@ __global__ void __launch_bounds__(FastGeom<D, SPLIT>::NT, (D == 64 && !FROZEN) ?
                 store_state8<D>(M, m_out + off, r, cg);
                 if (RULE == RULE_TITANS && s_out != nullptr) store_state8<D>(S, s_out + off, r, cg);
                 if (FROZEN) copy8(M0, M);
+            } else if (FROZEN && mode == STORE_ALL && (t % a.interval) == 0) {
+                copy8(M0, M);        // frozen rule with every state stored: interval = chunk size
             }
             const float al = gb[tl];
             const float th = (RULE != RULE_HEBBIAN) ? gb[TT + tl] : 0.f;

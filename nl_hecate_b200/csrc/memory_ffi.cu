@@ -600,10 +600,22 @@ int32_t nlh_rule_forward(int32_t rule, const float* k_mem, const float* v_mem, c
     int32_t batch_size, int32_t interval, int32_t chunk_size, float error_clip,
     float m_norm_max)
 {
-    if (interval <= 0 || (chunk_size > 0 && chunk_size != interval) || chunk_size < 0)
+    if (interval <= 0 || chunk_size < 0 || (chunk_size > 0 && chunk_size != interval && interval != 1))
         return NLH_ERR_INVALID_ARG;
     if (rule == RULE_HEBBIAN && chunk_size > 0) return NLH_ERR_INVALID_ARG;
     const int frozen = chunk_size > 0 ? 1 : 0;
+    if (frozen && interval == 1 && chunk_size > 1) {
+        // frozen rule, every state stored: m_ckpt [B, S+1, d*d]; s_ckpt may be NULL (Titans)
+        if (rule != RULE_TITANS || !fast_common_ok(d, error_clip, m_norm_max)) {
+            record_status(NLH_ERR_UNSUPPORTED, "nlh_rule_forward",
+                          "full-trajectory frozen mode: Titans, head_dim 32/64, no clip/projection");
+            return NLH_ERR_UNSUPPORTED;
+        }
+        return run_forward(rule, fwd_args(k_mem, v_mem, q_mem, alpha, theta, eta, m_initial, s_initial,
+            m_ckpt, s_ckpt, y, seq_len, d, batch_size, seq_len, (long long)d * d,
+            (long long)(seq_len + 1) * d * d, STORE_ALL, chunk_size, 1, error_clip, m_norm_max),
+            "nlh_rule_forward");
+    }
     return run_forward(rule, fwd_args(k_mem, v_mem, q_mem, alpha, theta, eta, m_initial, s_initial,
         m_ckpt, s_ckpt, y, seq_len, d, batch_size, seq_len, (long long)d * d,
         ckpt_slots(seq_len, interval) * d * d, frozen ? STORE_CHUNK : STORE_CKPT, interval, frozen,
@@ -617,10 +629,30 @@ int32_t nlh_rule_backward(int32_t rule, const float* k_mem, const float* v_mem,
     float* d_s_initial, int32_t seq_len, int32_t d, int32_t batch_size, int32_t interval,
     int32_t chunk_size, float error_clip, float m_norm_max)
 {
-    if (interval <= 0 || (chunk_size > 0 && chunk_size != interval) || chunk_size < 0)
+    if (interval <= 0 || chunk_size < 0 || (chunk_size > 0 && chunk_size != interval && interval != 1))
         return NLH_ERR_INVALID_ARG;
     if (rule == RULE_HEBBIAN && chunk_size > 0) return NLH_ERR_INVALID_ARG;
     const int frozen = chunk_size > 0 ? 1 : 0;
+    if (frozen && interval == 1 && chunk_size > 1) {
+        // frozen rule on a full M trajectory: streamed, nothing recomputed (s_ckpt is not read)
+        const char* where = "nlh_rule_backward";
+        if (!valid_dims(where, seq_len, d, batch_size)) return NLH_ERR_INVALID_ARG;
+        if (batch_size == 0) return NLH_OK;
+        BwdArgs a = bwd_args(k_mem, v_mem, q_mem, alpha, theta, eta, m_ckpt, nullptr, d_y, nullptr, nullptr,
+            d_k_mem, d_v_mem, d_q_mem, d_alpha, d_theta, d_eta, d_m_initial, d_s_initial, seq_len, d,
+            batch_size, 0, seq_len, (long long)(seq_len + 1) * d * d, 1, chunk_size, 0, error_clip, m_norm_max);
+        const bool al = aligned16(a.k) && aligned16(a.v) && aligned16(a.q) && aligned16(a.d_y) && aligned16(a.d_k) &&
+                        aligned16(a.d_v) && aligned16(a.d_q) && aligned16(a.m_traj) &&
+                        aligned16(a.d_m_out) && aligned16(a.d_s_out);
+        if (rule != RULE_TITANS || !fast_common_ok(d, error_clip, m_norm_max) || !al || ((d_m_initial == nullptr) != (d_s_initial == nullptr))) {
+            record_status(NLH_ERR_UNSUPPORTED, where,
+                          "full-trajectory frozen mode: Titans, head_dim 32/64, no clip/projection, 16-byte aligned buffers");
+            return NLH_ERR_UNSUPPORTED;
+        }
+        cudaStream_t st = current_stream();
+        if (d == 64) frozen_stream_bwd_launch<64>(a, st); else frozen_stream_bwd_launch<32>(a, st);
+        return check_launch(where) ? NLH_OK : NLH_ERR_CUDA;
+    }
     return run_backward(rule, bwd_args(k_mem, v_mem, q_mem, alpha, theta, eta, m_ckpt, s_ckpt, d_y,
         nullptr, nullptr, d_k_mem, d_v_mem, d_q_mem, d_alpha, d_theta, d_eta, d_m_initial,
         d_s_initial, seq_len, d, batch_size, 0, seq_len, ckpt_slots(seq_len, interval) * d * d,

@@ -282,6 +282,35 @@ def rule_backward(rule, k, v, q, alpha, theta, eta, mc, sc, d_y, interval, chunk
                 d_s_initial=ds0)
 
 
+def titans_frozen_stream_forward(k, v, q, alpha, theta, eta, m0, s0, chunk):
+    """Frozen-M0 chunkwise Titans forward that stores EVERY state (nlh_rule_forward with
+    interval = 1): ms [N, S+1, d*d], no momentum trajectory. For short chunks, where the
+    backward then streams the states instead of recomputing chunk windows."""
+    n, s, d = k.shape
+    ms = _f32(n, s + 1, d * d, device=k.device)
+    y = _f32(n, s, d, device=k.device)
+    call("nlh_rule_forward", rule=RULE_TITANS, k_mem=k, v_mem=v, q_mem=q, alpha=alpha, theta=theta,
+         eta=eta, m_initial=m0, s_initial=s0, m_ckpt=ms, s_ckpt=None, y=y, seq_len=s, d=d,
+         batch_size=n, interval=1, chunk_size=chunk, error_clip=0.0, m_norm_max=0.0)
+    return ms, y
+
+
+def titans_frozen_stream_backward(k, v, q, alpha, theta, eta, ms, d_y, chunk, want_initial=True):
+    """Backward twin (nlh_rule_backward with interval = 1). d_m_initial / d_s_initial are per
+    problem [N, d*d]; want_initial=False passes NULL for both."""
+    n, s, d = k.shape
+    dk, dv, dq = (torch.empty_like(k) for _ in range(3))
+    da, dt, de = (torch.empty_like(alpha) for _ in range(3))
+    dm0 = _f32(n, d * d, device=k.device) if want_initial else None
+    ds0 = _f32(n, d * d, device=k.device) if want_initial else None
+    call("nlh_rule_backward", rule=RULE_TITANS, k_mem=k, v_mem=v, q_mem=q, alpha=alpha, theta=theta,
+         eta=eta, m_ckpt=ms, s_ckpt=None, d_y=d_y, d_k_mem=dk, d_v_mem=dv, d_q_mem=dq, d_alpha=da,
+         d_theta=dt, d_eta=de, d_m_initial=dm0, d_s_initial=ds0, seq_len=s, d=d, batch_size=n,
+         interval=1, chunk_size=chunk, error_clip=0.0, m_norm_max=0.0)
+    return dict(d_k=dk, d_v=dv, d_q=dq, d_alpha=da, d_theta=dt, d_eta=de, d_m_initial=dm0,
+                d_s_initial=ds0)
+
+
 # ── SWA ────────────────────────────────────────────────────────────────────
 # q,k,v,out: [B,S,H*hd] bf16; attn_weights [B,H,S,n_p+W] bf16; grads f32.
 

@@ -71,8 +71,28 @@ class StackedMAGConfig:
 
 class _TitansMemory(torch.autograd.Function):
     """Per-head Titans LMM over [N, S, hd] (N = batch*heads) through the C ABI.
-    chunk == 0: exact rule (titans_forward/backward_f32_cuda, full trajectory);
-    chunk > 0 : frozen-M0 chunkwise rule (titans_chunkwise_*_f32_cuda)."""
+    chunk == 0: exact rule (titans_forward/backward_f32_cuda, M trajectory only);
+    chunk > 0 : frozen-M0 chunkwise rule — chunk-boundary states and the chunk-parallel kernels
+    (titans_chunkwise_*_f32_cuda) for chunks of 16 tokens and more; for shorter chunks (the pooled
+    CMS levels see 64, 8 and 1 tokens) every state is stored and the backward streams them
+    (nlh_rule_forward / nlh_rule_backward with interval = 1). One-token chunks stay on the
+    chunk-boundary entries: their stored S_0 = 0 gives the exactly-zero d_eta of a level that sees
+    a single token per call, which the M-difference form only reaches to rounding."""
+
+    STREAM_BELOW = 16        # chunks shorter than this take the full-trajectory frozen pair ...
+    # ... unless the problems (batch x heads) number at most half the SMs: level 0 is then split over
+    # two CTAs per problem and fills the GPU, and the lighter chunk-boundary kernels disturb it less
+    # next to it (measured at 64 problems: 4.89 ms per step against 5.26 ms)
+    STREAM_MIN_PROBLEMS = None
+
+    @staticmethod
+    def _stream_ok(k, chunk):
+        if not (1 < chunk < _TitansMemory.STREAM_BELOW and k.shape[-1] in (32, 64)):
+            return False
+        lo = _TitansMemory.STREAM_MIN_PROBLEMS
+        if lo is None:
+            lo = torch.cuda.get_device_properties(k.device).multi_processor_count // 2 + 1
+        return k.shape[0] >= lo
 
     _ZEROS = {}
 
@@ -90,9 +110,13 @@ class _TitansMemory(torch.autograd.Function):
 
     @staticmethod
     def _forward(ctx, k, v, q, alpha, theta, eta, m0, s0, chunk, carry=None):
+        ctx.stream = _TitansMemory._stream_ok(k, chunk)
         if chunk == 0:
             # M trajectory only: the backward derives S_t = M_t - (1-alpha_{t-1}) M_{t-1}
             ms, ss, y = D.titans_forward_dd(k, v, q, alpha, theta, eta, m0, s0, store_s=False)
+            ctx.save_for_backward(k, v, q, alpha, theta, eta, ms)
+        elif ctx.stream:
+            ms, y = D.titans_frozen_stream_forward(k, v, q, alpha, theta, eta, m0, s0, chunk)
             ctx.save_for_backward(k, v, q, alpha, theta, eta, ms)
         else:
             ms, ss, y = D.titans_chunkwise_forward_dd(k, v, q, alpha, theta, eta, m0, s0, chunk)
@@ -114,6 +138,10 @@ class _TitansMemory(torch.autograd.Function):
             if ctx.chunk == 0:
                 k, v, q, alpha, theta, eta, ms = ctx.saved_tensors
                 g = D.titans_backward_dd(k, v, q, alpha, theta, eta, ms, None, dy, want_initial=False)
+            elif ctx.stream:
+                k, v, q, alpha, theta, eta, ms = ctx.saved_tensors
+                g = D.titans_frozen_stream_backward(k, v, q, alpha, theta, eta, ms, dy, ctx.chunk,
+                                                    want_initial=False)
             else:
                 k, v, q, alpha, theta, eta, ms, ss = ctx.saved_tensors
                 g = D.titans_chunkwise_backward_dd(k, v, q, alpha, theta, eta, ms, ss, dy, ctx.chunk,

@@ -306,6 +306,33 @@ def test_recompute_training_pair_frozen(D, orc, d, s, chunk, n):
         assert rel_err(_np(g[key]), w[key]) <= REL, key
 
 
+@pytest.mark.parametrize("d,s,chunk,n", [(64, 64, 8, 3), (64, 8, 8, 2), (64, 37, 8, 2), (64, 50, 4, 1),
+                                         (64, 21, 2, 2), (32, 40, 8, 2), (64, 130, 16, 1), (64, 9, 3, 2)])
+def test_frozen_pair_on_a_full_trajectory(D, orc, d, s, chunk, n):
+    """Frozen-M0 chunkwise Titans with every state stored (nlh_rule_forward / _backward with
+    interval = 1): outputs, stored states at the chunk boundaries and every gradient against the
+    oracle's chunkwise rule; ragged last chunks, chunks shorter than the prefetch pipeline and a
+    single-chunk sequence included."""
+    p = make_problem(orc, n, s, d, 2100 + d + s + chunk, "rand")
+    w = oracle_chunkwise(orc, "titans", p, chunk)
+    t = to_dev(p)
+    ms, y = D.titans_frozen_stream_forward(t["k"], t["v"], t["q"], t["alpha"], t["theta"], t["eta"],
+                                           t["m0"], t["s0"], chunk)
+    assert rel_err(_np(y), w["y"]) <= REL
+    nc = (s + chunk - 1) // chunk
+    bounds = [min(c * chunk, s) for c in range(nc + 1)]
+    assert rel_err(_np(ms[:, bounds]), w["m_chunk_states"].reshape(n, nc + 1, d * d)) <= REL
+    g = D.titans_frozen_stream_backward(t["k"], t["v"], t["q"], t["alpha"], t["theta"], t["eta"], ms,
+                                        t["dy"], chunk)
+    for key in ["d_k", "d_v", "d_q", "d_alpha", "d_theta", "d_eta"]:
+        assert rel_err(_np(g[key]), w[key]) <= REL, key
+    for key in ["d_m_initial", "d_s_initial"]:            # per problem, like the oracle's
+        assert rel_err(_np(g[key]), w[key].reshape(n, d * d)) <= REL, key
+    g2 = D.titans_frozen_stream_backward(t["k"], t["v"], t["q"], t["alpha"], t["theta"], t["eta"], ms,
+                                         t["dy"], chunk, want_initial=False)
+    assert g2["d_m_initial"] is None and rel_err(_np(g2["d_k"]), w["d_k"]) <= REL
+
+
 def test_input_stride_and_m_stride(D, orc):
     """Forward entries address batch element b at b*input_stride tokens and b*m_stride floats
     (core/kernels/titans_forward.cu:102-113): run on a sub-range of a longer padded buffer."""

@@ -38,13 +38,18 @@ def test_seeded_init_is_the_reference_init_bit_for_bit(orc):
         assert np.array_equal(m.p[n].detach().cpu().numpy(), a.reshape(m.p[n].shape)), n
 
 
+@pytest.mark.parametrize("stream", [False, True])
 @pytest.mark.parametrize("kw", [dict(), dict(d_model=64, num_heads=1, k=2, chunk_sizes=(1, 1), exact_levels=(0, 1))])
-def test_stacked_model_matches_the_stacked_oracle(orc, kw):
+def test_stacked_model_matches_the_stacked_oracle(orc, kw, stream, monkeypatch):
+    """stream: the pooled levels with short chunks run the full-trajectory frozen pair (what the
+    model picks at large problem counts) or the chunk-boundary pair (small problem counts)."""
     import torch
     if not torch.cuda.is_available():
         pytest.skip("needs a CUDA device")
+    from nl_hecate_b200 import stacked_mag
     from nl_hecate_b200.stacked_mag import StackedMAG
     from oracle import stacked as ST
+    monkeypatch.setattr(stacked_mag._TitansMemory, "STREAM_MIN_PROBLEMS", 0 if stream else 10 ** 9)
     gcfg, ocfg = _cfgs(**kw)
     B, S = 2, gcfg.seq_len
     m = StackedMAG(gcfg, batch_per_rank=B, seed=42)
