@@ -412,7 +412,8 @@ class StackedModelStep:
         from nl_hecate_b200.stacked_mag import StackedMAG, StackedMAGConfig
         self.torch, self.dd = torch, dispatch
         rank = int(os.environ.get("RANK", "0"))
-        self.cfg = StackedMAGConfig(level_streams=os.environ.get("NLH_BENCH_LEVEL_STREAMS", "1") == "1")
+        self.cfg = StackedMAGConfig(level_streams=os.environ.get("NLH_BENCH_LEVEL_STREAMS", "1") == "1",
+                                    overlap_grad_sync=os.environ.get("NLH_BENCH_OVERLAP", "1") == "1")
         self.model = StackedMAG(self.cfg, self.local_batch, device="cuda", seed=42)
         ids = self.zipf_tokens(self.GLOBAL_BATCH)[rank * self.local_batch:(rank + 1) * self.local_batch]
         self.host_tok = torch.from_numpy(np.ascontiguousarray(ids[:, :-1])).pin_memory()
@@ -420,13 +421,13 @@ class StackedModelStep:
         self.tok, self.tgt = self.host_tok.cuda(), self.host_tgt.cuda()
         self.host_loss = torch.empty(1, dtype=torch.float32).pin_memory()
         # this library's launches per step (the profiler's launch list shows the same kernels).
-        # Per block: SWA fwd (1) + bwd (3); MAG combine fwd + bwd (2); two LayerNorms fwd + bwd (4);
-        # pooled-level inputs: one mean pool per pooled level + their fused adjoint (p + 1);
-        # pooled-level output gradients (p); per level: prep fwd (1) + bwd (2: d_kvq, gate
-        # weights), memory fwd + bwd (2). Once: final LayerNorm (2), cross-entropy (2), gradient
-        # norm (1), AdamW (1).
+        # Per block: SWA fwd (1) + bwd (3); MAG combine fwd + bwd + level-weight finisher (3); two
+        # LayerNorms fwd + bwd (4; the second backward also upsamples the pooled levels' gradients);
+        # one mean pool per pooled level (p); pooled-level output gradients (p); per level: prep
+        # fwd (1) + bwd (3: d_kvq, gate weights, finisher), memory fwd + bwd (2). Once: final
+        # LayerNorm (2), cross-entropy (2), embedding (2), gradient norm (2), AdamW (1).
         p = sum(1 for c in self.cfg.chunk_sizes[:self.cfg.k] if min(c, self.S) > 1)
-        self.launches_per_step = self.cfg.n_blocks * (4 + 2 + 4 + (p + 1) + p + 5 * self.cfg.k) + 6
+        self.launches_per_step = self.cfg.n_blocks * (4 + 3 + 4 + p + p + 6 * self.cfg.k) + 9
         self.h2d = self.host_tok.numel() * 8 * 2
         self.d2h = 4
         self.pg = None
