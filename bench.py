@@ -413,7 +413,8 @@ class StackedModelStep:
         self.torch, self.dd = torch, dispatch
         rank = int(os.environ.get("RANK", "0"))
         self.cfg = StackedMAGConfig(level_streams=os.environ.get("NLH_BENCH_LEVEL_STREAMS", "1") == "1",
-                                    overlap_grad_sync=os.environ.get("NLH_BENCH_OVERLAP", "1") == "1")
+                                    overlap_grad_sync=os.environ.get("NLH_BENCH_OVERLAP", "1") == "1",
+                                    exact_checkpoint=int(os.environ.get("NLH_BENCH_EXACT_CKPT", "0")))
         self.model = StackedMAG(self.cfg, self.local_batch, device="cuda", seed=42)
         ids = self.zipf_tokens(self.GLOBAL_BATCH)[rank * self.local_batch:(rank + 1) * self.local_batch]
         self.host_tok = torch.from_numpy(np.ascontiguousarray(ids[:, :-1])).pin_memory()

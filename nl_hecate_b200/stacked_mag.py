@@ -53,6 +53,8 @@ class StackedMAGConfig:
     vocab: int = 8192
     bf16: bool = True                 # bf16 activations for SWA and the dense projections
     exact_levels: tuple = (0,)        # tape strategy: level 0 exact, others frozen-M0 (proxy)
+    exact_checkpoint: int = 0         # > 0: exact levels keep a checkpoint every this many tokens and
+                                      # recompute the windows in the backward (less memory, more time)
     lr: float = 3e-4
     beta1: float = 0.9
     beta2: float = 0.999
@@ -97,7 +99,7 @@ class _TitansMemory(torch.autograd.Function):
     _ZEROS = {}
 
     @staticmethod
-    def forward(ctx, k, v, q, alpha, theta, eta, m0, chunk, slot=0, carry=None):
+    def forward(ctx, k, v, q, alpha, theta, eta, m0, chunk, slot=0, carry=None, ckpt=0):
         # momentum restarts every call (gpu_forward.rs:1516-1517): S_0 = 0, a read-only buffer that
         # is created once per shape instead of being filled every call
         key = (tuple(m0.shape), m0.device)
@@ -106,12 +108,18 @@ class _TitansMemory(torch.autograd.Function):
             s0 = _TitansMemory._ZEROS[key] = torch.zeros_like(m0)
         ctx.slot = slot
         with D.workspace_slot(slot):
-            return _TitansMemory._forward(ctx, k, v, q, alpha, theta, eta, m0, s0, chunk, carry)
+            return _TitansMemory._forward(ctx, k, v, q, alpha, theta, eta, m0, s0, chunk, carry, ckpt)
 
     @staticmethod
-    def _forward(ctx, k, v, q, alpha, theta, eta, m0, s0, chunk, carry=None):
+    def _forward(ctx, k, v, q, alpha, theta, eta, m0, s0, chunk, carry=None, ckpt=0):
         ctx.stream = _TitansMemory._stream_ok(k, chunk)
-        if chunk == 0:
+        ctx.ckpt = ckpt if chunk == 0 else 0
+        if chunk == 0 and ckpt > 0:
+            # exact rule, checkpoints only (reference semantics core/src/cuda_ffi.rs:230,262): the
+            # trajectory shrinks by the interval, the backward recomputes each window
+            ms, ss, y = D.rule_forward(1, k, v, q, alpha, theta, eta, m0, s0, ckpt, 0)
+            ctx.save_for_backward(k, v, q, alpha, theta, eta, ms, ss)
+        elif chunk == 0:
             # M trajectory only: the backward derives S_t = M_t - (1-alpha_{t-1}) M_{t-1}
             ms, ss, y = D.titans_forward_dd(k, v, q, alpha, theta, eta, m0, s0, store_s=False)
             ctx.save_for_backward(k, v, q, alpha, theta, eta, ms)
@@ -135,7 +143,10 @@ class _TitansMemory(torch.autograd.Function):
     def backward(ctx, dy, _dm):
         dy = dy.contiguous()
         with D.workspace_slot(ctx.slot):
-            if ctx.chunk == 0:
+            if ctx.ckpt > 0:
+                k, v, q, alpha, theta, eta, ms, ss = ctx.saved_tensors
+                g = D.rule_backward(1, k, v, q, alpha, theta, eta, ms, ss, dy, ctx.ckpt, 0)
+            elif ctx.chunk == 0:
                 k, v, q, alpha, theta, eta, ms = ctx.saved_tensors
                 g = D.titans_backward_dd(k, v, q, alpha, theta, eta, ms, None, dy, want_initial=False)
             elif ctx.stream:
@@ -146,7 +157,8 @@ class _TitansMemory(torch.autograd.Function):
                 k, v, q, alpha, theta, eta, ms, ss = ctx.saved_tensors
                 g = D.titans_chunkwise_backward_dd(k, v, q, alpha, theta, eta, ms, ss, dy, ctx.chunk,
                                                    want_initial=False)
-        return g["d_k"], g["d_v"], g["d_q"], g["d_alpha"], g["d_theta"], g["d_eta"], None, None, None, None
+        return (g["d_k"], g["d_v"], g["d_q"], g["d_alpha"], g["d_theta"], g["d_eta"], None, None, None,
+                None, None)
 
 
 class _SWA(torch.autograd.Function):
@@ -575,8 +587,8 @@ class _Embedding(torch.autograd.Function):
         return None, None, None
 
 
-def titans_memory(k, v, q, alpha, theta, eta, m0, chunk, slot=0, carry=None):
-    return _TitansMemory.apply(k, v, q, alpha, theta, eta, m0, chunk, slot, carry)
+def titans_memory(k, v, q, alpha, theta, eta, m0, chunk, slot=0, carry=None, ckpt=0):
+    return _TitansMemory.apply(k, v, q, alpha, theta, eta, m0, chunk, slot, carry, ckpt)
 
 
 def swa(q, k, v, num_heads, head_dim, window):
@@ -758,7 +770,7 @@ class StackedMAG:
         chunk = 0 if l in cfg.exact_levels else min(cfg.chunk_sizes[l], sf)
         if self.memory_fn is titans_memory:   # carried memory updated in place by the Function
             y, _ = titans_memory(k, v, q, alpha, theta, eta, self.context[b][l], chunk, slot,
-                                 self.context[b][l])
+                                 self.context[b][l], cfg.exact_checkpoint if chunk == 0 else 0)
         else:
             y, m_final = self.memory_fn(k, v, q, alpha, theta, eta, self.context[b][l], chunk)
             self.context[b][l].copy_(m_final.detach())   # in place: addresses stay fixed for graph replay

@@ -145,6 +145,28 @@ def test_graph_replayed_step_matches_eager_steps():
             assert float((a - r).abs().max()) <= 1e-3 * max(float(r.abs().max()), 1e-6)
 
 
+def test_checkpointed_exact_level_matches_the_stored_trajectory():
+    """cfg.exact_checkpoint: level 0 keeps a checkpoint every 8 tokens and recomputes the windows in
+    the backward: same loss and gradients as the stored-trajectory pair (both fp32 state; the
+    stored-M pair derives S from M differences, so agreement is to fp32 rounding)."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    import dataclasses
+    from nl_hecate_b200.stacked_mag import StackedMAG
+    tok, tgt = _data(3, seed=4)
+    full = StackedMAG(_cfg(True), 3, device="cuda", seed=5)
+    ckpt = StackedMAG(dataclasses.replace(_cfg(True), exact_checkpoint=8), 3, device="cuda", seed=5)
+    for _ in range(2):
+        full.opt.g.zero_(); ckpt.opt.g.zero_()
+        lf = full.forward_backward(tok, tgt)
+        lc = ckpt.forward_backward(tok, tgt)
+    assert abs(float(lf) - float(lc)) <= 1e-6 * abs(float(lf))
+    for i, n in enumerate(full.names):
+        a, b = ckpt.opt.view(ckpt.opt.g, i), full.opt.view(full.opt.g, i)
+        denom = max(float(b.abs().max()), 1e-7)
+        assert float((a - b).abs().max()) <= 2e-4 * denom, n
+
+
 def test_level_streams_match_single_stream_eager_and_graphed():
     """cfg.level_streams issues CMS levels >= 1 on side streams (own scratch slots): the same
     kernels run, so gradients agree with the single-stream model to rounding (only the order of
