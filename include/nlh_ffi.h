@@ -439,6 +439,24 @@ int32_t nlh_layer_norm_backward_pooled(const float* d_out_f32, const uint16_t* d
     const void* g2, int32_t c2, int32_t g2_is_bf16, int32_t n_src, int32_t seq, const float* x,
     const float* gamma, const float* mean_cache, const float* rstd_cache, float* d_x, float* d_gamma,
     float* d_beta, int32_t n, int32_t d);
+/* LayerNorm of x + res with the neighbouring element-wise passes of a residual block folded in
+ * (res fp32 or bf16 [n, d], may be NULL; the sum is never written). Backward twin: the general
+ * form of the two backwards above. The kernel normalises x + res again, adds the pooled sources
+ * (n_src may be 0) to the output gradient, and writes
+ *   d_x      = input gradient + add_in            (add_in fp32 [n, d] or NULL: a gradient of x that
+ *                                                  arrives from another consumer, summed here),
+ *   d_x_bf16 = bf16(input gradient + add_in_bf16) (optional: the gradient of a bf16 res operand with
+ *                                                  its own fan-in).
+ * Needs d % 8 == 0, d <= 1024, 16-byte aligned buffers when any of these operands is given. */
+int32_t nlh_layer_norm_residual_forward(const float* x, const void* res, int32_t res_is_bf16,
+    const float* gamma, const float* beta, float* out_f32, uint16_t* out_bf16, float* mean_cache,
+    float* rstd_cache, int32_t n, int32_t d, float eps);
+int32_t nlh_layer_norm_backward_fused(const float* d_out_f32, const uint16_t* d_out_bf16,
+    const void* g0, int32_t c0, int32_t g0_is_bf16, const void* g1, int32_t c1, int32_t g1_is_bf16,
+    const void* g2, int32_t c2, int32_t g2_is_bf16, int32_t n_src, int32_t seq, const float* x,
+    const void* res, int32_t res_is_bf16, const float* add_in, const float* gamma,
+    const float* mean_cache, const float* rstd_cache, float* d_x, uint16_t* d_x_bf16,
+    const uint16_t* add_in_bf16, float* d_gamma, float* d_beta, int32_t n, int32_t d);
 /* Cross-entropy on fp32 or bf16 logits [n, vocab]. Forward ACCUMULATES the loss sum into
  * loss_sum[0] and the number of valid targets into valid_count[0] (optional) and stores the
  * per-row log-sum-exp in lse [n] (optional). Backward writes

@@ -42,10 +42,33 @@ __device__ __forceinline__ void st4bf(__nv_bfloat16* p, float4 v)
 }
 
 // ───────────────────────────── LayerNorm ─────────────────────────────────
+// Optional operands that fold a residual block's neighbouring element-wise passes into the
+// LayerNorm kernels (fast path only; every member may be NULL):
+//   res_*      : second addend of the LayerNorm input, the kernels normalise x + res (forward and
+//                backward; the sum is never written to memory);
+//   add_in     : backward, fp32 [n, d] added to d_x (a gradient of x that arrives from another
+//                consumer: the fan-in sum happens here instead of in a pass of its own);
+//   d_x_bf16   : backward, bf16 copy of the INPUT gradient (without add_in) plus add_in_bf16 —
+//                the gradient of a bf16 residual operand and its own fan-in.
+struct LnExtra {
+    const float* res_f32;
+    const __nv_bfloat16* res_bf16;
+    const float* add_in;
+    __nv_bfloat16* d_x_bf16;
+    const __nv_bfloat16* add_in_bf16;
+};
+__device__ __forceinline__ float4 ln_input(const float* __restrict__ x, const LnExtra& E, size_t off)
+{
+    float4 v = ld4f(x + off);
+    if (E.res_f32) { const float4 r = ld4f(E.res_f32 + off); v.x += r.x; v.y += r.y; v.z += r.z; v.w += r.w; }
+    if (E.res_bf16) { const float4 r = ld4f(E.res_bf16 + off); v.x += r.x; v.y += r.y; v.z += r.z; v.w += r.w; }
+    return v;
+}
+
 // Fast path: d % 4 == 0, d <= 1024. Lane owns float4 chunks c = lane + 32*i, i < NV.
 template <int NV>
 __global__ void __launch_bounds__(LN_WARPS * 32) ln_fwd_kernel(
-    const float* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
+    const float* __restrict__ x, LnExtra E, const float* __restrict__ gamma, const float* __restrict__ beta,
     float* __restrict__ out, __nv_bfloat16* __restrict__ out_bf16, float* __restrict__ mean_cache,
     float* __restrict__ rstd_cache, int n, int d, float eps)
 {
@@ -53,13 +76,12 @@ __global__ void __launch_bounds__(LN_WARPS * 32) ln_fwd_kernel(
     const int row = blockIdx.x * LN_WARPS + (threadIdx.x >> 5);
     if (row >= n) return;
     const int nv = d >> 2;
-    const float* xr = x + (size_t)row * d;
     float4 v[NV];
     float s = 0.f;
 #pragma unroll
     for (int i = 0; i < NV; i++) {
         const int c = lane + 32 * i;
-        if (c < nv) { v[i] = ld4f(xr + 4 * c); s += (v[i].x + v[i].y) + (v[i].z + v[i].w); }
+        if (c < nv) { v[i] = ln_input(x, E, (size_t)row * d + 4 * c); s += (v[i].x + v[i].y) + (v[i].z + v[i].w); }
     }
     const float mean = warp_sum(s) / (float)d;
     float q = 0.f;
@@ -159,7 +181,7 @@ __device__ __forceinline__ float4 ln_bwd_dy(const float* __restrict__ d_out, con
 template <int NV>
 __global__ void __launch_bounds__(LN_WARPS * 32, 2) ln_bwd_kernel(
     const float* __restrict__ d_out, const __nv_bfloat16* __restrict__ d_out_bf16, LnPooled P,
-    const float* __restrict__ x, const float* __restrict__ gamma,
+    const float* __restrict__ x, LnExtra E, const float* __restrict__ gamma,
     const float* __restrict__ mean_cache, const float* __restrict__ rstd_cache,
     float* __restrict__ d_x, float* __restrict__ d_gamma, float* __restrict__ d_beta, int n, int d)
 {
@@ -194,7 +216,7 @@ __global__ void __launch_bounds__(LN_WARPS * 32, 2) ln_bwd_kernel(
         for (int i = 0; i < NV; i++) {
             const int c = lane + 32 * i;
             if (c < nv) {
-                const float4 xv = ld4f(x + ro + 4 * c);
+                const float4 xv = ln_input(x, E, ro + 4 * c);
                 const float4 t = ln_bwd_dy<NV>(d_out, d_out_bf16, P, ro, po, pinv, c);
                 const float4 g = ld4f(gamma + 4 * c);
                 const float4 h = make_float4((xv.x - mean) * rstd, (xv.y - mean) * rstd, (xv.z - mean) * rstd, (xv.w - mean) * rstd);
@@ -219,6 +241,18 @@ __global__ void __launch_bounds__(LN_WARPS * 32, 2) ln_bwd_kernel(
                 o.y = k * ((float)d * dy[i].y * g.y - s1 - xh[i].y * s2);
                 o.z = k * ((float)d * dy[i].z * g.z - s1 - xh[i].z * s2);
                 o.w = k * ((float)d * dy[i].w * g.w - s1 - xh[i].w * s2);
+                if (E.d_x_bf16) {
+                    float4 ob = o;
+                    if (E.add_in_bf16) {
+                        const float4 r = ld4f(E.add_in_bf16 + ro + 4 * c);
+                        ob.x += r.x; ob.y += r.y; ob.z += r.z; ob.w += r.w;
+                    }
+                    st4bf(E.d_x_bf16 + ro + 4 * c, ob);
+                }
+                if (E.add_in) {
+                    const float4 r = ld4f(E.add_in + ro + 4 * c);
+                    o.x += r.x; o.y += r.y; o.z += r.z; o.w += r.w;
+                }
                 *reinterpret_cast<float4*>(d_x + ro + 4 * c) = o;
             }
         }
@@ -474,20 +508,38 @@ static bool ln_fast_ok(const void* a, const void* b, const void* c, const void* 
     return (d & 3) == 0 && d <= 128 * LN_MAXV && (u & 15) == 0;
 }
 
+static bool ln_extra_any(const LnExtra& E)
+{
+    return E.res_f32 || E.res_bf16 || E.add_in || E.d_x_bf16 || E.add_in_bf16;
+}
+static bool ln_extra_aligned(const LnExtra& E, int d)
+{
+    const uintptr_t u = (uintptr_t)E.res_f32 | (uintptr_t)E.res_bf16 | (uintptr_t)E.add_in |
+                        (uintptr_t)E.d_x_bf16 | (uintptr_t)E.add_in_bf16;
+    return (u & 15) == 0 && (d & 7) == 0;
+}
+
 static int ln_forward(const char* where, const float* x, const float* gamma, const float* beta,
                       float* out, __nv_bfloat16* out_bf16, float* mean_cache, float* rstd_cache,
-                      int n, int d, float eps)
+                      int n, int d, float eps, const LnExtra* extra = nullptr)
 {
+    LnExtra E = {nullptr, nullptr, nullptr, nullptr, nullptr};
+    if (extra) E = *extra;
     if (n < 0 || d <= 0 || !x || !gamma || !beta || (!out && !out_bf16)) {
         record_status(NLH_ERR_INVALID_ARG, where, "bad dimensions or NULL pointer");
         return NLH_ERR_INVALID_ARG;
     }
     if (n == 0) return NLH_OK;
     cudaStream_t st = current_stream();
-    if (ln_fast_ok(x, gamma, beta, out, out_bf16, nullptr, d) && (!out_bf16 || (d & 7) == 0)) {
+    const bool fast = ln_fast_ok(x, gamma, beta, out, out_bf16, nullptr, d) && (!out_bf16 || (d & 7) == 0);
+    if (ln_extra_any(E) && !(fast && ln_extra_aligned(E, d))) {
+        record_status(NLH_ERR_UNSUPPORTED, where, "fused operands need d % 8 == 0, d <= 1024 and 16-byte aligned buffers");
+        return NLH_ERR_UNSUPPORTED;
+    }
+    if (fast) {
         const int grid = (n + LN_WARPS - 1) / LN_WARPS;
         const int nv = (d / 4 + 31) / 32;
-#define NLH_LN_FWD(NV) ln_fwd_kernel<NV><<<grid, LN_WARPS * 32, 0, st>>>(x, gamma, beta, out, out_bf16, mean_cache, rstd_cache, n, d, eps)
+#define NLH_LN_FWD(NV) ln_fwd_kernel<NV><<<grid, LN_WARPS * 32, 0, st>>>(x, E, gamma, beta, out, out_bf16, mean_cache, rstd_cache, n, d, eps)
         if (nv <= 1) NLH_LN_FWD(1); else if (nv <= 2) NLH_LN_FWD(2); else if (nv <= 4) NLH_LN_FWD(4); else NLH_LN_FWD(8);
 #undef NLH_LN_FWD
     } else {
@@ -499,8 +551,10 @@ static int ln_forward(const char* where, const float* x, const float* gamma, con
 static int ln_backward(const char* where, const float* d_out, const __nv_bfloat16* d_out_bf16,
                        const float* x, const float* gamma, const float* mean_cache,
                        const float* rstd_cache, float* d_x, float* d_gamma, float* d_beta, int n, int d,
-                       const LnPooled* pooled = nullptr)
+                       const LnPooled* pooled = nullptr, const LnExtra* extra = nullptr)
 {
+    LnExtra E = {nullptr, nullptr, nullptr, nullptr, nullptr};
+    if (extra) E = *extra;
     LnPooled P;
     P.n = 0; P.seq = 1; P.sdiv = make_fastdiv(1);
     for (int l = 0; l < 3; l++) { P.g[l] = nullptr; P.c[l] = 1; P.is_bf16[l] = 0; P.cdiv[l] = make_fastdiv(1); }
@@ -513,8 +567,8 @@ static int ln_backward(const char* where, const float* d_out, const __nv_bfloat1
     if (n == 0) return NLH_OK;
     cudaStream_t st = current_stream();
     const bool fast = ln_fast_ok(x, gamma, d_out, d_out_bf16, d_x, nullptr, d) && (!d_out_bf16 || (d & 7) == 0);
-    if (P.n > 0 && !(fast && (d & 7) == 0)) {
-        record_status(NLH_ERR_UNSUPPORTED, where, "pooled gradient sources need d % 8 == 0, d <= 1024 and 16-byte aligned buffers");
+    if ((P.n > 0 && !(fast && (d & 7) == 0)) || (ln_extra_any(E) && !(fast && ln_extra_aligned(E, d)))) {
+        record_status(NLH_ERR_UNSUPPORTED, where, "pooled gradient sources and fused operands need d % 8 == 0, d <= 1024 and 16-byte aligned buffers");
         return NLH_ERR_UNSUPPORTED;
     }
     if (fast) {
@@ -523,7 +577,7 @@ static int ln_backward(const char* where, const float* d_out, const __nv_bfloat1
         // persistent: a few CTAs per SM, each warp walks rows so that the parameter gradients
         // are reduced once per CTA
         const int grid = need < 148 * 2 ? need : 148 * 2;
-#define NLH_LN_BWD(NV) ln_bwd_kernel<NV><<<grid, LN_WARPS * 32, 0, st>>>(d_out, d_out_bf16, P, x, gamma, mean_cache, rstd_cache, d_x, d_gamma, d_beta, n, d)
+#define NLH_LN_BWD(NV) ln_bwd_kernel<NV><<<grid, LN_WARPS * 32, 0, st>>>(d_out, d_out_bf16, P, x, E, gamma, mean_cache, rstd_cache, d_x, d_gamma, d_beta, n, d)
         if (nv <= 1) NLH_LN_BWD(1); else if (nv <= 2) NLH_LN_BWD(2); else if (nv <= 4) NLH_LN_BWD(4); else NLH_LN_BWD(8);
 #undef NLH_LN_BWD
     } else {
@@ -586,6 +640,45 @@ int32_t nlh_layer_norm_backward_pooled(const float* d_out_f32, const uint16_t* d
     }
     return ln_backward("nlh_layer_norm_backward_pooled", d_out_f32, (const __nv_bfloat16*)d_out_bf16, x, gamma,
                        mean_cache, rstd_cache, d_x, d_gamma, d_beta, n, d, &P);
+}
+
+int32_t nlh_layer_norm_residual_forward(const float* x, const void* res, int32_t res_is_bf16,
+    const float* gamma, const float* beta, float* out_f32, uint16_t* out_bf16, float* mean_cache,
+    float* rstd_cache, int32_t n, int32_t d, float eps)
+{
+    LnExtra E = {nullptr, nullptr, nullptr, nullptr, nullptr};
+    if (res) { if (res_is_bf16) E.res_bf16 = (const __nv_bfloat16*)res; else E.res_f32 = (const float*)res; }
+    return ln_forward("nlh_layer_norm_residual_forward", x, gamma, beta, out_f32, (__nv_bfloat16*)out_bf16,
+                      mean_cache, rstd_cache, n, d, eps, &E);
+}
+
+int32_t nlh_layer_norm_backward_fused(const float* d_out_f32, const uint16_t* d_out_bf16,
+    const void* g0, int32_t c0, int32_t g0_is_bf16, const void* g1, int32_t c1, int32_t g1_is_bf16,
+    const void* g2, int32_t c2, int32_t g2_is_bf16, int32_t n_src, int32_t seq, const float* x,
+    const void* res, int32_t res_is_bf16, const float* add_in, const float* gamma,
+    const float* mean_cache, const float* rstd_cache, float* d_x, uint16_t* d_x_bf16,
+    const uint16_t* add_in_bf16, float* d_gamma, float* d_beta, int32_t n, int32_t d)
+{
+    LnPooled P;
+    const void* gs[3] = {g0, g1, g2};
+    const int cs[3] = {c0, c1, c2}, bs[3] = {g0_is_bf16, g1_is_bf16, g2_is_bf16};
+    bool ok = n_src >= 0 && n_src <= 3 && seq > 0 && n % seq == 0 && (d_x_bf16 || !add_in_bf16);
+    for (int l = 0; l < 3; l++) {
+        P.g[l] = l < n_src ? gs[l] : nullptr;
+        P.c[l] = l < n_src ? cs[l] : 1;
+        P.is_bf16[l] = bs[l];
+        if (l < n_src && (gs[l] == nullptr || cs[l] <= 0 || seq % cs[l] != 0 || ((uintptr_t)gs[l] & 15) != 0)) ok = false;
+        P.cdiv[l] = make_fastdiv(P.c[l]);
+    }
+    P.n = n_src; P.seq = seq; P.sdiv = make_fastdiv(seq > 0 ? seq : 1);
+    if (!ok) {
+        record_status(NLH_ERR_INVALID_ARG, "nlh_layer_norm_backward_fused", "bad pooled sources, pool factors, alignment or operands");
+        return NLH_ERR_INVALID_ARG;
+    }
+    LnExtra E = {nullptr, nullptr, add_in, (__nv_bfloat16*)d_x_bf16, (const __nv_bfloat16*)add_in_bf16};
+    if (res) { if (res_is_bf16) E.res_bf16 = (const __nv_bfloat16*)res; else E.res_f32 = (const float*)res; }
+    return ln_backward("nlh_layer_norm_backward_fused", d_out_f32, (const __nv_bfloat16*)d_out_bf16, x, gamma,
+                       mean_cache, rstd_cache, d_x, d_gamma, d_beta, n, d, &P, &E);
 }
 
 void embedding_gather_cuda(const float* w_embed, const int32_t* input_ids, float* output,

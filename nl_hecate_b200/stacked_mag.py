@@ -274,11 +274,16 @@ class _MagCombine(torch.autograd.Function):
     ROWS = 148 * 8
 
     @staticmethod
-    def forward(ctx, x, attn_proj, wts, pools, num_heads, g_logits, *ys):
+    def forward(ctx, x, attn_proj, wts, pools, num_heads, g_logits, fan, *ys):
         """wts = softmax(alpha_mem). g_logits None: wts is a tensor of the graph and receives its
         gradient. g_logits = gradient buffer of alpha_mem: wts was computed outside the graph, the
-        backward adds the softmax adjoint into g_logits (nlh_level_weight_grad_finish)."""
+        backward adds the softmax adjoint into g_logits (nlh_level_weight_grad_finish).
+        fan (dict or None): the block's gradient fan-in. When given, the backward does NOT return
+        the gradients of x and attn_proj; it leaves them in fan["c_dx"], fan["c_dap"] for the
+        block's memory LayerNorm backward, whose kernel adds them to its own (those two tensors have
+        other consumers in the block, and the sums would otherwise be separate passes)."""
         ctx.g_logits = g_logits
+        ctx.fan = fan
         x, attn_proj, wts = x.contiguous(), attn_proj.contiguous(), wts.contiguous().float()
         B, S, d = x.shape
         k = len(ys)
@@ -334,7 +339,10 @@ class _MagCombine(torch.autograd.Function):
                        dy_ph=dys[l], sum_out=sums, batch=B, seq=S, d_model=d, num_heads=H)
             if sums is not None:
                 prev = (cp[l], sums)
-        return (d_out, d_ap, d_wts, None, None, None, *dys)
+        if ctx.fan is not None:
+            ctx.fan["c_dx"], ctx.fan["c_dap"] = d_out, d_ap
+            return (None, None, d_wts, None, None, None, None, *dys)
+        return (d_out, d_ap, d_wts, None, None, None, None, *dys)
 
 
 class _PoolLevels(torch.autograd.Function):
@@ -390,10 +398,13 @@ class _LayerNorm(torch.autograd.Function):
     output, 2: both (fp32 for the pooled levels, bf16 for the GEMM that follows)."""
 
     @staticmethod
-    def forward(ctx, x, gamma, beta, eps, mode, grads=None):
+    def forward(ctx, x, gamma, beta, eps, mode, grads=None, fan=None):
         """grads = (g_gamma, g_beta): buffers the backward accumulates the two parameter gradients
-        into (the kernel adds with atomics); it then returns none for them."""
+        into (the kernel adds with atomics); it then returns none for them. fan (dict or None):
+        the block's gradient fan-in; the backward adds fan["r_dx"] (the gradient of x collected by
+        the block's other consumers) to d_x inside the kernel."""
         ctx.grads = grads
+        ctx.fan = fan
         x = x.contiguous()
         d = x.shape[-1]
         n = x.numel() // d
@@ -422,19 +433,28 @@ class _LayerNorm(torch.autograd.Function):
             else:
                 g32 = g.contiguous()
         d_x = torch.empty_like(x)
+        add_in = ctx.fan.pop("r_dx", None) if ctx.fan is not None else None
+        if add_in is not None:
+            assert ctx.grads is not None and (g32 is not None or g16 is not None)
+            D.call("nlh_layer_norm_backward_fused", d_out_f32=g32, d_out_bf16=g16, g0=None, c0=1,
+                   g0_is_bf16=0, g1=None, c1=1, g1_is_bf16=0, g2=None, c2=1, g2_is_bf16=0, n_src=0, seq=1,
+                   x=x, res=None, res_is_bf16=0, add_in=add_in, gamma=gamma.contiguous(), mean_cache=mean,
+                   rstd_cache=rstd, d_x=d_x, d_x_bf16=None, add_in_bf16=None, d_gamma=ctx.grads[0],
+                   d_beta=ctx.grads[1], n=n, d=d)
+            return d_x, None, None, None, None, None, None
         if ctx.grads is not None:
             if g32 is None and g16 is None:
-                return d_x.zero_(), None, None, None, None, None
+                return d_x.zero_(), None, None, None, None, None, None
             D.call("nlh_layer_norm_backward", d_out_f32=g32, d_out_bf16=g16, x=x, gamma=gamma.contiguous(),
                    mean_cache=mean, rstd_cache=rstd, d_x=d_x, d_gamma=ctx.grads[0], d_beta=ctx.grads[1],
                    n=n, d=d)
-            return d_x, None, None, None, None, None
+            return d_x, None, None, None, None, None, None
         d_gb = torch.zeros(2, d, dtype=torch.float32, device=x.device)
         if g32 is None and g16 is None:
-            return d_x.zero_(), d_gb[0], d_gb[1], None, None, None
+            return d_x.zero_(), d_gb[0], d_gb[1], None, None, None, None
         D.call("nlh_layer_norm_backward", d_out_f32=g32, d_out_bf16=g16, x=x, gamma=gamma.contiguous(),
                mean_cache=mean, rstd_cache=rstd, d_x=d_x, d_gamma=d_gb[0], d_beta=d_gb[1], n=n, d=d)
-        return d_x, d_gb[0], d_gb[1], None, None, None
+        return d_x, d_gb[0], d_gb[1], None, None, None, None
 
 
 class _LayerNormPools(torch.autograd.Function):
@@ -446,7 +466,13 @@ class _LayerNormPools(torch.autograd.Function):
     grads = (g_gamma, g_beta): buffers the parameter gradients are accumulated into."""
 
     @staticmethod
-    def forward(ctx, x, gamma, beta, eps, pools, out_bf16, grads):
+    def forward(ctx, x, res, gamma, beta, eps, pools, out_bf16, grads, fan=None):
+        """res (bf16 [B, S, d] or None): second addend of the LayerNorm input — the block's
+        residual add x + attn_proj happens inside the LayerNorm kernels (forward and backward), the
+        sum is never written. fan (dict or None, needs res): the block's gradient fan-in; the
+        backward adds fan["c_dx"] / fan["c_dap"] (left by the MAG combine's backward) to the
+        gradients of x / res inside the kernel, leaves the gradient of x in fan["r_dx"] for the
+        attention LayerNorm's backward and returns none for x."""
         x = x.contiguous()
         B, S, d = x.shape
         n, dev = B * S, x.device
@@ -454,8 +480,15 @@ class _LayerNormPools(torch.autograd.Function):
         o16 = torch.empty(x.shape, dtype=torch.bfloat16, device=dev) if out_bf16 else None
         mean = torch.empty(n, dtype=torch.float32, device=dev)
         rstd = torch.empty(n, dtype=torch.float32, device=dev)
-        D.call("nlh_layer_norm_forward", x=x, gamma=gamma.contiguous(), beta=beta.contiguous(),
-               out_f32=o32, out_bf16=o16, mean_cache=mean, rstd_cache=rstd, n=n, d=d, eps=eps)
+        if res is not None:
+            res = res.contiguous()
+            assert res.dtype == torch.bfloat16
+            D.call("nlh_layer_norm_residual_forward", x=x, res=res, res_is_bf16=1, gamma=gamma.contiguous(),
+                   beta=beta.contiguous(), out_f32=o32, out_bf16=o16, mean_cache=mean, rstd_cache=rstd,
+                   n=n, d=d, eps=eps)
+        else:
+            D.call("nlh_layer_norm_forward", x=x, gamma=gamma.contiguous(), beta=beta.contiguous(),
+                   out_f32=o32, out_bf16=o16, mean_cache=mean, rstd_cache=rstd, n=n, d=d, eps=eps)
         dt = torch.bfloat16 if out_bf16 else torch.float32
         outs, prev = [], None                       # prev = (pool factor, unscaled sums)
         for i, c in enumerate(pools):
@@ -468,20 +501,47 @@ class _LayerNormPools(torch.autograd.Function):
             if sums is not None:
                 prev = (c, sums)
             outs.append(out)
-        ctx.save_for_backward(x, gamma, mean, rstd)
+        ctx.has_res = res is not None
+        ctx.save_for_backward(x, gamma, mean, rstd, *([res] if res is not None else []))
         ctx.meta = (B, S, d, tuple(pools))
         ctx.grads = grads
+        ctx.fan = fan if res is not None else None
         return (o16 if out_bf16 else o32, *outs)
 
     @staticmethod
     def backward(ctx, g_main, *gp):
-        x, gamma, mean, rstd = ctx.saved_tensors
+        x, gamma, mean, rstd, *rest = ctx.saved_tensors
+        res = rest[0] if ctx.has_res else None
         B, S, d, pools = ctx.meta
         src = [(g.contiguous(), c) for g, c in zip(gp, pools) if g is not None]
         assert len(src) <= 3, "at most three pooled levels"
         d_x = torch.empty_like(x)
+        if res is not None:
+            assert g_main is not None or src
+            g32 = g16 = None
+            if g_main is not None:
+                g_main = g_main.contiguous()
+                g16, g32 = (g_main, None) if g_main.dtype == torch.bfloat16 else (None, g_main)
+            src = src + [(None, 1)] * (3 - len(src))
+            isb = lambda t: int(t is not None and t.dtype == torch.bfloat16)
+            fan = ctx.fan
+            add_in = fan.pop("c_dx", None) if fan is not None else None
+            add_bf = fan.pop("c_dap", None) if fan is not None else None
+            d_res = torch.empty_like(res)
+            D.call("nlh_layer_norm_backward_fused", d_out_f32=g32, d_out_bf16=g16,
+                   g0=src[0][0], c0=src[0][1], g0_is_bf16=isb(src[0][0]),
+                   g1=src[1][0], c1=src[1][1], g1_is_bf16=isb(src[1][0]),
+                   g2=src[2][0], c2=src[2][1], g2_is_bf16=isb(src[2][0]),
+                   n_src=sum(1 for g, _ in src if g is not None), seq=S, x=x, res=res, res_is_bf16=1,
+                   add_in=add_in, gamma=gamma.contiguous(), mean_cache=mean, rstd_cache=rstd, d_x=d_x,
+                   d_x_bf16=d_res, add_in_bf16=add_bf, d_gamma=ctx.grads[0], d_beta=ctx.grads[1],
+                   n=B * S, d=d)
+            if fan is not None:
+                fan["r_dx"] = d_x
+                return None, d_res, None, None, None, None, None, None, None
+            return d_x, d_res, None, None, None, None, None, None, None
         if g_main is None and not src:
-            return d_x.zero_(), None, None, None, None, None, None
+            return d_x.zero_(), None, None, None, None, None, None, None, None
         g32 = g16 = None
         if g_main is not None:
             g_main = g_main.contiguous()
@@ -495,7 +555,7 @@ class _LayerNormPools(torch.autograd.Function):
                n_src=sum(1 for g, _ in src if g is not None), seq=S, x=x, gamma=gamma.contiguous(),
                mean_cache=mean, rstd_cache=rstd, d_x=d_x, d_gamma=ctx.grads[0], d_beta=ctx.grads[1],
                n=B * S, d=d)
-        return d_x, None, None, None, None, None, None
+        return d_x, None, None, None, None, None, None, None, None
 
 
 class _CrossEntropy(torch.autograd.Function):
@@ -799,11 +859,11 @@ class StackedMAG:
             ys[l].record_stream(main)
         return ys
 
-    def _ln(self, x, name, mode, fused):
+    def _ln(self, x, name, mode, fused, fan=None):
         p = self.p
         if fused:
             return _LayerNorm.apply(x, p[name + "gamma"], p[name + "beta"], 1e-5, mode,
-                                    (self.g[name + "gamma"], self.g[name + "beta"]))
+                                    (self.g[name + "gamma"], self.g[name + "beta"]), fan)
         out = F.layer_norm(x, (x.shape[-1],), p[name + "gamma"], p[name + "beta"], 1e-5)
         return (out, out) if mode == 2 else out
 
@@ -820,7 +880,15 @@ class StackedMAG:
         for b in range(cfg.n_blocks):
             pre = f"b{b}."
             self._mark_bucket(x, f"b{b}")            # fires once block b's backward has run
-            h = self._ln(x, pre + "ln_attn_", lp, fused)
+            S = x.shape[1]
+            cs = [min(c, S) for c in cfg.chunk_sizes[:cfg.k]]
+            uniq = sorted({c for c in cs if c > 1})
+            # fan: the block's gradient fan-in. x and attn_proj both have three / two consumers in
+            # the block; instead of autograd's sums (separate passes) the combine's backward hands
+            # its contributions to the memory LayerNorm's backward, which hands the gradient of x to
+            # the attention LayerNorm's backward; the kernels add them while they write.
+            fan = {} if (fused and cfg.bf16 and d % 8 == 0 and len(uniq) <= 3) else None
+            h = self._ln(x, pre + "ln_attn_", lp, fused, fan)
             qkv = self._mm(h, pre + "w_qkv")
             if cfg.bf16 or not qkv.is_cuda:
                 qkv = qkv.to(torch.bfloat16)          # fp32 configurations keep fp32 attention on the GPU
@@ -830,21 +898,23 @@ class StackedMAG:
                 q, k, v = (t.contiguous() for t in qkv.split(d, dim=-1))
                 attn = self.swa_fn(q, k, v, nh, hd, cfg.window)
             attn_raw = self._mm(attn, pre + "w_o")
-            res1 = x + attn_raw
+            res1 = x + attn_raw if fan is None else None
             if fused:
                 with torch.no_grad():
                     wts = torch.softmax(p[pre + "alpha_mem"], dim=0)
             else:
                 wts = torch.softmax(p[pre + "alpha_mem"], dim=0)
             if fused:
-                S = res1.shape[1]
-                cs = [min(c, S) for c in cfg.chunk_sizes[:cfg.k]]
                 for c in cs:
                     assert S % c == 0, "seq_len must be a multiple of every chunk size"
-                uniq = sorted({c for c in cs if c > 1})
-                if d % 8 == 0 and len(uniq) <= 3:       # LayerNorm + pools, one backward kernel
+                if fan is not None:                     # residual add, LayerNorm, pools and fan-in
                     m16, *pl = _LayerNormPools.apply(
-                        res1, p[pre + "ln_mem_gamma"], p[pre + "ln_mem_beta"], 1e-5, tuple(uniq), cfg.bf16,
+                        x, attn_raw, p[pre + "ln_mem_gamma"], p[pre + "ln_mem_beta"], 1e-5, tuple(uniq), True,
+                        (self.g[pre + "ln_mem_gamma"], self.g[pre + "ln_mem_beta"]), fan)
+                    pooled = dict(zip(uniq, pl))
+                elif d % 8 == 0 and len(uniq) <= 3:     # LayerNorm + pools, one backward kernel
+                    m16, *pl = _LayerNormPools.apply(
+                        res1, None, p[pre + "ln_mem_gamma"], p[pre + "ln_mem_beta"], 1e-5, tuple(uniq), cfg.bf16,
                         (self.g[pre + "ln_mem_gamma"], self.g[pre + "ln_mem_beta"]))
                     pooled = dict(zip(uniq, pl))
                 else:
@@ -853,7 +923,7 @@ class StackedMAG:
                     pooled = dict(zip(uniq, _PoolLevels.apply(m32, tuple(uniq), cfg.bf16))) if uniq else {}
                 ys = self._levels(b, [pooled.get(cs[l], m16) for l in range(cfg.k)])
                 pools = cs
-                x = _MagCombine.apply(x, attn_raw, wts, tuple(pools), nh, self.g[pre + "alpha_mem"], *ys)
+                x = _MagCombine.apply(x, attn_raw, wts, tuple(pools), nh, self.g[pre + "alpha_mem"], fan, *ys)
             else:
                 m_in = self._ln(res1, pre + "ln_mem_", 0, False)
                 attn_proj = attn_raw.float()

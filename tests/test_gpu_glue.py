@@ -129,6 +129,50 @@ def test_layer_norm_backward_with_pooled_sources(orc, B, S, d, pools, bf16):
                d_gamma=dgb2[0], d_beta=dgb2[1], n=n, d=d)
 
 
+@pytest.mark.parametrize("B,S,d,pools", [(2, 64, 512, (8, 64)), (3, 7, 128, ()), (1, 33, 1024, (3,))])
+def test_layer_norm_with_residual_operand_and_gradient_fan_in(orc, B, S, d, pools):
+    """nlh_layer_norm_residual_forward / nlh_layer_norm_backward_fused: LayerNorm of x + res (bf16
+    res), pooled sources, add_in into d_x and the bf16 copy of the input gradient with its own
+    addend — against the oracle's LayerNorm on the explicit sum."""
+    import torch
+    from nl_hecate_b200 import dispatch as D
+    n = B * S
+    x = orc.rand_buf(n * d, 741, 2.0).reshape(n, d)
+    res = orc.bf16_round(orc.rand_buf(n * d, 742, 1.0).reshape(n, d))
+    gamma = 1.0 + orc.rand_buf(d, 743, 0.3)
+    beta = orc.rand_buf(d, 744, 0.2)
+    g16 = orc.bf16_round(orc.rand_buf(n * d, 745, 1.0).reshape(n, d))
+    add_in = orc.rand_buf(n * d, 746, 1.0).reshape(n, d)
+    add_bf = orc.bf16_round(orc.rand_buf(n * d, 747, 1.0).reshape(n, d))
+    gp = [orc.bf16_round(orc.rand_buf(B * (S // c) * d, 750 + i, 1.0).reshape(B, S // c, d)) for i, c in enumerate(pools)]
+    total = g16.reshape(B, S, d).copy()
+    for g, c in zip(gp, pools):
+        total += np.repeat(g, c, axis=1) / np.float32(c)
+    xs = (x + res).astype(np.float32)
+    out_r, mean_r, rstd_r = orc.layer_norm_forward(xs, gamma, beta, 1e-5)
+    dx_r, dg_r, db_r = orc.layer_norm_backward(total.reshape(n, d), xs, gamma, mean_r, rstd_r)
+    bf = torch.bfloat16
+    xd, rd, gd, bd = _dev(x), _dev(res, bf), _dev(gamma), _dev(beta)
+    o32 = torch.empty_like(xd); o16 = torch.empty(n, d, dtype=bf, device="cuda")
+    mean = torch.empty(n, device="cuda"); rstd = torch.empty(n, device="cuda")
+    D.call("nlh_layer_norm_residual_forward", x=xd, res=rd, res_is_bf16=1, gamma=gd, beta=bd, out_f32=o32,
+           out_bf16=o16, mean_cache=mean, rstd_cache=rstd, n=n, d=d, eps=1e-5)
+    assert max_abs(_np(o32), out_r) <= 2e-5
+    assert rel_err(_np(o16), out_r) <= 1e-2
+    gpd = [_dev(g, bf) for g in gp] + [None] * (3 - len(gp))
+    cs = list(pools) + [1] * (3 - len(pools))
+    dx = torch.empty_like(xd); dxb = torch.empty(n, d, dtype=bf, device="cuda")
+    dgb = torch.zeros(2, d, device="cuda")
+    D.call("nlh_layer_norm_backward_fused", d_out_f32=None, d_out_bf16=_dev(g16, bf),
+           g0=gpd[0], c0=cs[0], g0_is_bf16=1, g1=gpd[1], c1=cs[1], g1_is_bf16=1, g2=gpd[2], c2=cs[2],
+           g2_is_bf16=1, n_src=len(pools), seq=S, x=xd, res=rd, res_is_bf16=1, add_in=_dev(add_in), gamma=gd,
+           mean_cache=mean, rstd_cache=rstd, d_x=dx, d_x_bf16=dxb, add_in_bf16=_dev(add_bf, bf),
+           d_gamma=dgb[0], d_beta=dgb[1], n=n, d=d)
+    assert rel_err(_np(dx), dx_r + add_in) <= 1e-4
+    assert rel_err(_np(dxb), dx_r + add_bf) <= 1e-2
+    assert rel_err(_np(dgb[0]), dg_r) <= 1e-4 and rel_err(_np(dgb[1]), db_r) <= 1e-4
+
+
 @pytest.mark.parametrize("n,v", [(5, 37), (64, 8192), (3, 1000), (1, 1)])
 def test_cross_entropy_drop_in_matches_oracle(orc, n, v):
     import torch

@@ -90,7 +90,7 @@ def test_mag_combine_forward_backward(B, S, d, H, pools, dtype):
         (out * up).sum().backward()
         return out.detach(), [t.grad for t in leaves]
 
-    o1, g1 = run(lambda x_, ap_, w_, ys_: _MagCombine.apply(x_, ap_, w_, pools, H, None, *ys_))
+    o1, g1 = run(lambda x_, ap_, w_, ys_: _MagCombine.apply(x_, ap_, w_, pools, H, None, None, *ys_))
     o2, g2 = run(lambda x_, ap_, w_, ys_: _torch_combine(x_, ap_, w_, pools, H, ys_))
     assert _rel(o1, o2) <= 1e-5
     names = ["d_x", "d_attn_proj", "d_alpha_mem"] + [f"d_y{l}" for l in range(len(pools))]
