@@ -13,6 +13,8 @@ workload over one batch of seeded synthetic input:
                     seq 8192, causal window 512
   titans_level0     exact Titans pair at the stacked model's level-0 shape (512 problems of 512
                     tokens, M-only trajectory)
+  titans_level1     frozen-M0 Titans pair at the stacked model's level-1 shape (512 problems of 64
+                    pooled tokens, chunk 8, every state stored, streaming backward)
   adamw             flat-arena clip + AdamW step over 25.2 M fp32 parameters
 --small shrinks the kernel-pair workloads to a profiler-friendly problem count.
 
@@ -223,7 +225,7 @@ class TitansPair:
                     C.c_int(threads))
             return time.perf_counter() - t0
         t1 = run(threads)                              # one problem per thread
-        reps = max(1, min(8, int(budget_s / max(t1, 1e-3)) - 1))
+        reps = max(1, min(64 if s < 256 else 8, int(budget_s / max(t1, 1e-3)) - 1))
         nprob = threads * reps
         dt = run(nprob) if reps > 1 else t1
         head_tokens = nprob * s
@@ -571,17 +573,66 @@ class TitansLevel0(TitansPair):
                 lambda: self.bwd(self.dev), streams + n * (s + 1) * d * d * 4, "hbm")
 
 
+class TitansLevel1(TitansLevel0):
+    """Frozen-M0 Titans pair as level 1 of the stacked model runs it: 512 problems of 64 pooled
+    tokens, chunk 8, every state stored and the backward streaming them (nlh_rule_forward /
+    nlh_rule_backward with interval = 1)."""
+    B, H, S, D = 64, 8, 64, 64
+    CHUNK = 8
+
+    def __init__(self):
+        super().__init__()
+        self.name = "titans_level1"
+
+    def describe(self):
+        d = super().describe()
+        d["workload"] = (f"Titans LMM frozen-M0 pair (chunk {self.CHUNK}, full trajectory) at the stacked model's "
+                         f"level-1 shape: batch {self.B} x heads {self.H}, head_dim {self.D}, seq {self.S}, fp32")
+        d["l2_policy"] = "L2 flushed by the harness between steps is not needed: 0.55 GB of trajectory per step > L2"
+        return d
+
+    def fwd(self, t):
+        self.dd.call("nlh_rule_forward", rule=1, k_mem=t["k"], v_mem=t["v"], q_mem=t["q"], alpha=t["alpha"],
+                     theta=t["theta"], eta=t["eta"], m_initial=t["m0"], s_initial=t["s0"], m_ckpt=self.mstate,
+                     s_ckpt=None, y=self.y, seq_len=self.S, d=self.D, batch_size=self.N, interval=1,
+                     chunk_size=self.CHUNK, error_clip=0.0, m_norm_max=0.0)
+
+    def bwd(self, t):
+        o = self.out
+        self.dd.call("nlh_rule_backward", rule=1, k_mem=t["k"], v_mem=t["v"], q_mem=t["q"], alpha=t["alpha"],
+                     theta=t["theta"], eta=t["eta"], m_ckpt=self.mstate, s_ckpt=None, d_y=t["dy"],
+                     d_k_mem=o["d_k"], d_v_mem=o["d_v"], d_q_mem=o["d_q"], d_alpha=o["d_alpha"],
+                     d_theta=o["d_theta"], d_eta=o["d_eta"], d_m_initial=None, d_s_initial=None,
+                     seq_len=self.S, d=self.D, batch_size=self.N, interval=1, chunk_size=self.CHUNK,
+                     error_clip=0.0, m_norm_max=0.0)
+
+    def dominant(self):
+        n, s, d = self.N, self.S, self.D
+        streams = 7 * n * s * d * 4 + 6 * n * s * 4
+        return ("titans_exact_bwd_kernel<64,1,FROZEN> (frozen-M0 backward on the full M trajectory)",
+                lambda: self.bwd(self.dev), streams + n * (s + 1) * d * d * 4, "hbm")
+
+    def cpu_sample(self, oracle, threads, budget_s=12.0):
+        self.chunk = self.CHUNK                      # the CPU arm runs the oracle's chunkwise rule
+        try:
+            return super().cpu_sample(oracle, threads, budget_s)
+        finally:
+            self.chunk = 0
+
+
 def make_workload(name, world=1, small=False, local_batch=0):
     """small: reduced problem counts of the same kernels, sized for profiler captures (inputs still
     larger than L2, a few hundred MB on the device)."""
     if small:
-        TitansPair.B, SwaPair.B, TitansLevel0.B = 4, 1, 37
+        TitansPair.B, SwaPair.B, TitansLevel0.B, TitansLevel1.B = 4, 1, 37, 64
     if name == "titans_chunkwise":
         return TitansPair(64)
     if name == "titans_exact":
         return TitansPair(0)
     if name == "titans_level0":
         return TitansLevel0()
+    if name == "titans_level1":
+        return TitansLevel1()
     if name == "swa":
         return SwaPair()
     if name == "adamw":
