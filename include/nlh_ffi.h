@@ -298,7 +298,15 @@ int32_t nlh_swa_backward_f32(const float* q, const float* k, const float* v, con
  * CTAs (the rows of the memory evolve independently; the backward then zeroes d_q, d_k and the gate
  * gradients itself and adds the two partial sums into them). 0 keeps one CTA per problem. */
 #define NLH_OPT_ROW_SPLIT 3
+/* NLH_OPT_SWA_TMA (default 1): the tcgen05 SWA forward stages its Q, K and V tiles with tiled TMA
+ * copies (cp.async.bulk.tensor, one issuing thread, completion on an mbarrier; plain single-CTA
+ * loads) instead of per-thread cp.async; 0 selects the cp.async staging. Results are identical. */
+#define NLH_OPT_SWA_TMA 4
 int32_t nlh_set_option(int32_t option, int32_t value);
+/* How the last tcgen05 SWA forward of this process staged its operand tiles: 1 = tiled TMA copies,
+ * 0 = cp.async (NLH_OPT_SWA_TMA off, or the driver's tensor-map encoder was not available or
+ * rejected the shape), -1 = no such launch yet. */
+int32_t nlh_swa_forward_staging(void);
 int32_t nlh_swa_tc_timeout_flag(void);
 
 /* Multi-tensor AdamW over one flat arena (w,g,m,v share the layout). The

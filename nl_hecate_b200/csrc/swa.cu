@@ -661,6 +661,41 @@ static int swa_check(const char* where, int S, int H, int hd, int W, int B, int 
     return NLH_OK;
 }
 
+// Tiled TMA descriptor of one of q, k, v as the tcgen05 forward stages it: a 3-D bf16 tensor
+// {H*64 head-dim elements, S positions (stride rs elements), B batch elements (stride S*rs)}, box
+// {8 elements, rows, 1}. The driver's encoder is reached through cudaGetDriverEntryPoint (no link
+// against libcuda). Returns false when the encoder is not available or rejects the shape; the
+// caller then stages with cp.async.
+static int g_swa_fwd_staging = -1;     // staging of the last tcgen05 forward launch: 1 TMA, 0 cp.async
+typedef CUresult (*TmaEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static TmaEncodeFn tma_encode_fn()
+{
+    static TmaEncodeFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) != cudaSuccess ||
+            qr != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        (void)cudaGetLastError();
+        return (TmaEncodeFn)p;
+    }();
+    return fn;
+}
+static bool swa_tile_map(CUtensorMap* m, const bf16* base, int S, int H, int B, int rs, int rows)
+{
+    TmaEncodeFn enc = tma_encode_fn();
+    if (enc == nullptr || (rs % 8) != 0 || (((uintptr_t)base) & 15) != 0) return false;
+    const cuuint64_t dims[3] = {(cuuint64_t)H * 64, (cuuint64_t)S, (cuuint64_t)B};
+    const cuuint64_t strides[2] = {(cuuint64_t)rs * 2, (cuuint64_t)S * rs * 2};     // bytes, dims 1 and 2
+    const cuuint32_t box[3] = {8, (cuuint32_t)rows, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    return enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<bf16*>(base), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int HD>
 static int swa_forward_impl(const bf16* q, const bf16* k, const bf16* v, bf16* out, float* lse,
                             bf16* aw, int S, int H, int W, int B, int n_p, int rs_in = 0, int rs_o = 0)
@@ -671,10 +706,21 @@ static int swa_forward_impl(const bf16* q, const bf16* k, const bf16* v, bf16* o
     if (rs_o == 0) rs_o = H * HD;
     const bool aligned = ((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15) == 0);
     if (HD == 64 && option_value(NLH_OPT_SWA_TCGEN05) && aligned) {
-        // tcgen05 / TMEM kernel: 128 query rows per CTA
-        cudaFuncSetAttribute(tc::swa_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM_BYTES);
+        // tcgen05 / TMEM kernel: 128 query rows per CTA; operand tiles staged by TMA when the
+        // descriptors can be made, else by cp.async
         dim3 grid((S + tc::BM - 1) / tc::BM, B * H);
-        tc::swa_fwd_tc_kernel<<<grid, tc::THREADS, tc::SMEM_BYTES, st>>>(q, k, v, out, lse, S, H, W, n_p, scale, rs_in, rs_o);
+        CUtensorMap mq, mk, mv;
+        memset(&mq, 0, sizeof(mq)); memset(&mk, 0, sizeof(mk)); memset(&mv, 0, sizeof(mv));
+        const bool tma = option_value(NLH_OPT_SWA_TMA) && swa_tile_map(&mq, q, S, H, B, rs_in, tc::BM) &&
+                         swa_tile_map(&mk, k, S, H, B, rs_in, tc::BN) && swa_tile_map(&mv, v, S, H, B, rs_in, tc::BN);
+        g_swa_fwd_staging = tma ? 1 : 0;
+        if (tma) {
+            cudaFuncSetAttribute(tc::swa_fwd_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM_BYTES);
+            tc::swa_fwd_tc_kernel<true><<<grid, tc::THREADS, tc::SMEM_BYTES, st>>>(q, k, v, out, lse, S, H, W, n_p, scale, rs_in, rs_o, mq, mk, mv);
+        } else {
+            cudaFuncSetAttribute(tc::swa_fwd_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM_BYTES);
+            tc::swa_fwd_tc_kernel<false><<<grid, tc::THREADS, tc::SMEM_BYTES, st>>>(q, k, v, out, lse, S, H, W, n_p, scale, rs_in, rs_o, mq, mk, mv);
+        }
         if (!check_launch("swa_fwd_tc_kernel")) return NLH_ERR_CUDA;
     } else {
         const size_t smem = swa_fwd_smem<HD>();
@@ -782,6 +828,8 @@ int32_t nlh_swa_tc_timeout_flag(void)
     if (cudaMemcpyFromSymbol(&v, tc::g_swa_tc_timeout, sizeof(int)) != cudaSuccess) return -1;
     return v;
 }
+
+int32_t nlh_swa_forward_staging(void) { return g_swa_fwd_staging; }
 
 int32_t nlh_swa_forward(const uint16_t* q, const uint16_t* k, const uint16_t* v, uint16_t* out,
     float* lse, int32_t seq_len, int32_t num_heads, int32_t head_dim, int32_t window_size,

@@ -8,14 +8,17 @@
 //   PV = P V     : tcgen05.mma M=128 N=64 K=64, V consumed MN-major straight from its tile,
 //                  accumulated across key tiles in TMEM cols [64,128); when a row's running
 //                  maximum moves, its warp rescales the accumulator in place (tcgen05.ld / st)
-// Operands are staged with 16-byte cp.async into the canonical no-swizzle core-matrix layouts
-// (8 rows x 16 bytes contiguous), so no tensor map is needed; K and V tiles are double buffered
-// and the score MMA of tile i+1 is issued before the softmax of tile i so the two overlap.
+// Operands are staged into canonical no-swizzle core-matrix layouts (8 rows x 16 bytes contiguous)
+// either by tiled TMA copies issued by one thread (TMA variant: one cp.async.bulk.tensor per
+// 8-element chunk column of a tile, completion counted on an mbarrier) or by 16-byte cp.async of
+// every thread; K and V tiles are double buffered and the score MMA of tile i+1 is issued before
+// the softmax of tile i so the two overlap.
 // A single thread issues the MMAs; completion is tracked with tcgen05.commit -> mbarrier. Every
 // mbarrier wait is bounded: on expiry the CTA sets a global error flag, stops waiting, frees its
 // TMEM and returns.
 #pragma once
 
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <stdint.h>
 
@@ -37,8 +40,8 @@ constexpr int OFF_Q = 0;
 constexpr int OFF_K = OFF_Q + Q_BYTES;              // 2 buffers
 constexpr int OFF_V = OFF_K + 2 * KV_BYTES;         // 2 buffers
 constexpr int OFF_P = OFF_V + 2 * KV_BYTES;
-constexpr int OFF_BAR = OFF_P + P_BYTES;            // two 8-byte mbarriers (S ready, O updated)
-constexpr int OFF_TMEM = OFF_BAR + 16;              // 4-byte TMEM base address
+constexpr int OFF_BAR = OFF_P + P_BYTES;            // four 8-byte mbarriers (S ready, O updated, two tile-load stages)
+constexpr int OFF_TMEM = OFF_BAR + 32;              // 4-byte TMEM base address
 constexpr int SMEM_BYTES = OFF_TMEM + 16;
 
 // Canonical no-swizzle core-matrix layouts (core matrix = 8 rows x 16 bytes, contiguous):
@@ -151,6 +154,37 @@ __device__ __forceinline__ void cp16_tc(void* smem_dst, const void* gsrc)
 }
 __device__ __forceinline__ void cp_commit_tc() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 
+// ── TMA staging (TMA = true variant of the forward kernel) ──
+// The operand tiles are then laid out chunk-major: 16-byte chunk c of row r at c * (rows * 16) +
+// r * 16, i.e. one contiguous column of `rows` x 16 bytes per chunk of 8 head-dim elements. That is
+// still a canonical no-swizzle core-matrix layout (8 rows x 16 bytes contiguous), only with the
+// two descriptor strides exchanged (K-chunk stride rows * 16, 8-row-group stride 128), and it is
+// what a tiled TMA copy with a box of {8 elements, rows} writes: one cp.async.bulk.tensor per
+// chunk, issued by one thread, completion counted in bytes on an mbarrier. The tensor maps are
+// 3-D {head-dim elements of all heads, sequence positions, batch}: rows past the end of the
+// sequence are out of bounds of the map and arrive as zeros. Every copy is a plain single-CTA load.
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar_addr, unsigned bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar_addr), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(unsigned smem_dst, const CUtensorMap* map, int c0, int c1, int c2,
+                                            unsigned bar_addr)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n"
+        ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(bar_addr)
+        : "memory");
+}
+// One tile of `rows` rows x 64 head-dim elements of head h, starting at sequence position row0 of
+// batch element b: 8 copies of {8 elements, rows}. c0 = h*64 + 8*c is a multiple of 8 bf16 = 16 bytes.
+__device__ __forceinline__ void tma_tile(unsigned smem_dst, const CUtensorMap* map, int h, int row0, int b,
+                                         int rows, unsigned bar_addr)
+{
+#pragma unroll
+    for (int c = 0; c < HD / 8; c++)
+        tma_load_3d(smem_dst + c * rows * 16, map, h * HD + 8 * c, row0, b, bar_addr);
+}
+
 // Stage n_rows rows of 64 bf16 (row stride rs elements) into the core-matrix layout:
 // 16-byte chunk c of row r goes to (r/8)*GROUP + c*CORE + (r%8)*16. Rows >= n_valid are zeroed.
 __device__ __forceinline__ void stage_rows(unsigned char* dst, const __nv_bfloat16* __restrict__ src,
@@ -175,10 +209,16 @@ __device__ int g_swa_tc_timeout = 0;   // set when a bounded mbarrier wait ran o
 //   E  softmax of tile i in registers (masks only on boundary tiles), P -> shared memory;
 //      O is rescaled in TMEM only by warps whose running maximum moved (tcgen05.ld/st)
 //   F  barrier; one thread issues O += P V(i)
+// TMA = true: Q, K and V tiles are staged by thread 0 with tiled TMA copies (see above) instead of
+// every thread's cp.async; only that thread waits for them (it is the one that issues the MMAs
+// that read them), on two alternating mbarriers with bounded waits.
+template <bool TMA>
 __global__ void __launch_bounds__(THREADS) swa_fwd_tc_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
     const __nv_bfloat16* __restrict__ v, __nv_bfloat16* __restrict__ out, float* __restrict__ lse,
-    int S, int H, int window, int n_p, float scale, int rs_in, int rs_o)
+    int S, int H, int window, int n_p, float scale, int rs_in, int rs_o,
+    const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+    const __grid_constant__ CUtensorMap map_v)
 {
     extern __shared__ __align__(128) unsigned char smem[];
     const int tid = threadIdx.x, warp = tid >> 5;
@@ -190,10 +230,13 @@ __global__ void __launch_bounds__(THREADS) swa_fwd_tc_kernel(
     const int q0 = qt * BM;
     const int q_hi = min(q0 + BM - 1, S - 1);
     const float sl2 = scale * 1.4426950408889634f;
-    const unsigned bar_s = smem_u32(smem + OFF_BAR), bar_o = bar_s + 8;
+    const unsigned bar_s = smem_u32(smem + OFF_BAR), bar_o = bar_s + 8, bar_ld = bar_s + 16;   // bar_ld, bar_ld + 8
     volatile unsigned* tmem_slot = reinterpret_cast<volatile unsigned*>(smem + OFF_TMEM);
 
-    if (tid == 0) { mbar_init(bar_s, 1); mbar_init(bar_o, 1); }
+    if (tid == 0) {
+        mbar_init(bar_s, 1); mbar_init(bar_o, 1);
+        if (TMA) { mbar_init(bar_ld, 1); mbar_init(bar_ld + 8, 1); }
+    }
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
                      ::"r"(smem_u32(smem + OFF_TMEM)), "r"(TMEM_COLS) : "memory");
@@ -213,41 +256,66 @@ __global__ void __launch_bounds__(THREADS) swa_fwd_tc_kernel(
         }
         return -1;
     };
-    auto load_k = [&](int tile, int bufi) {
+    // cp.async variant: every thread stages its part; TMA variant: thread 0 issues the copies onto
+    // the mbarrier ld_bar given by the caller
+    auto load_k = [&](int tile, int bufi, unsigned ld_bar) {
         const int k0 = tile * BN;
-        stage_rows(smem + OFF_K + bufi * KV_BYTES, k + base + (size_t)k0 * rs, rs, BN, min(BN, S - k0));
+        if (TMA) { if (tid == 0) tma_tile(smem_u32(smem + OFF_K + bufi * KV_BYTES), &map_k, h, k0, b, BN, ld_bar); }
+        else stage_rows(smem + OFF_K + bufi * KV_BYTES, k + base + (size_t)k0 * rs, rs, BN, min(BN, S - k0));
     };
-    auto load_v = [&](int tile, int bufi) {
+    auto load_v = [&](int tile, int bufi, unsigned ld_bar) {
         const int k0 = tile * BN;
-        stage_rows(smem + OFF_V + bufi * KV_BYTES, v + base + (size_t)k0 * rs, rs, BN, min(BN, S - k0));
+        if (TMA) { if (tid == 0) tma_tile(smem_u32(smem + OFF_V + bufi * KV_BYTES), &map_v, h, k0, b, BN, ld_bar); }
+        else stage_rows(smem + OFF_V + bufi * KV_BYTES, v + base + (size_t)k0 * rs, rs, BN, min(BN, S - k0));
     };
     const unsigned idesc_qk = make_idesc(false), idesc_pv = make_idesc(true);
     const unsigned q_addr = smem_u32(smem + OFF_Q), p_addr = smem_u32(smem + OFF_P);
+    // descriptor strides of the staged operands: (stride between K chunks, stride between 8-row groups)
+    constexpr unsigned Q_LBO = TMA ? BM * 16 : CORE, Q_SBO = TMA ? CORE : GROUP;
+    constexpr unsigned K_LBO = TMA ? BN * 16 : CORE, K_SBO = TMA ? CORE : GROUP;
+    // V is consumed MN-major: (stride between 8-key groups, stride between head-dim chunks)
+    constexpr unsigned V_KG = TMA ? CORE : GROUP, V_NC = TMA ? BN * 16 : CORE;
     auto issue_qk = [&](int bufi) {     // S = Q K^T, both operands K-major, 2 chunks per K=16 step
         const unsigned k_addr = smem_u32(smem + OFF_K + bufi * KV_BYTES);
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ks++)
-            mma_bf16(tmem_base, make_desc(q_addr + ks * 2 * CORE, CORE, GROUP),
-                     make_desc(k_addr + ks * 2 * CORE, CORE, GROUP), idesc_qk, ks > 0 ? 1u : 0u);
+            mma_bf16(tmem_base, make_desc(q_addr + ks * 2 * Q_LBO, Q_LBO, Q_SBO),
+                     make_desc(k_addr + ks * 2 * K_LBO, K_LBO, K_SBO), idesc_qk, ks > 0 ? 1u : 0u);
         mma_commit(bar_s);
     };
 
     int kt = next_tile(-1);
     int nxt = (kt >= 0) ? next_tile(kt) : -1;
-    stage_rows(smem + OFF_Q, q + base + (size_t)q0 * rs, rs, BM, min(BM, S - q0));
-    if (kt >= 0) { load_k(kt, 0); load_v(kt, 0); }
-    if (nxt >= 0) load_k(nxt, 1);
-    cp_commit_tc();
-    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
-    fence_async_proxy();
-    fence_before_sync();
-    __syncthreads();
-    if (tid == 0 && kt >= 0) { fence_after_sync(); issue_qk(0); }
+    bool dead = false;
+    if (TMA) {
+        // load group 0 on bar_ld: Q, K(0), V(0), K(1); group it+1 (issued in iteration it) goes to
+        // bar_ld + 8 * ((it + 1) & 1) and is waited for by thread 0 in iteration it+1
+        if (tid == 0) {
+            const unsigned bytes = Q_BYTES + (kt >= 0 ? 2 * KV_BYTES : 0) + (nxt >= 0 ? KV_BYTES : 0);
+            mbar_expect_tx(bar_ld, bytes);
+            tma_tile(q_addr, &map_q, h, q0, b, BM, bar_ld);
+        }
+        if (kt >= 0) { load_k(kt, 0, bar_ld); load_v(kt, 0, bar_ld); }
+        if (nxt >= 0) load_k(nxt, 1, bar_ld);
+        if (tid == 0) {
+            dead = !mbar_wait(bar_ld, 0, WAIT_LIMIT);
+            if (kt >= 0) { fence_after_sync(); issue_qk(0); }
+        }
+    } else {
+        stage_rows(smem + OFF_Q, q + base + (size_t)q0 * rs, rs, BM, min(BM, S - q0));
+        if (kt >= 0) { load_k(kt, 0, 0); load_v(kt, 0, 0); }
+        if (nxt >= 0) load_k(nxt, 1, 0);
+        cp_commit_tc();
+        asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        fence_async_proxy();
+        fence_before_sync();
+        __syncthreads();
+        if (tid == 0 && kt >= 0) { fence_after_sync(); issue_qk(0); }
+    }
 
     float m_run = -INFINITY, l_run = 0.f;
     const int qp = q0 + tid;
     unsigned par_s = 0, par_o = 0;
-    bool dead = false;
     int it = 0;
 
     while (kt >= 0) {
@@ -267,12 +335,22 @@ __global__ void __launch_bounds__(THREADS) swa_fwd_tc_kernel(
             fence_after_sync();
         }
         // C: prefetch
-        if (nxt2 >= 0) load_k(nxt2, it & 1);            // K(it+2) over K(it)
-        if (nxt >= 0) load_v(nxt, (it + 1) & 1);        // V(it+1) over V(it-1)
-        cp_commit_tc();
-        // D: K(it+1) (committed one tile ago) has landed; start the next score tile
-        asm volatile("cp.async.wait_group 1;\n" ::: "memory");
-        fence_async_proxy();
+        if (TMA) {
+            const unsigned ld_next = bar_ld + 8 * ((it + 1) & 1);
+            if (tid == 0 && nxt >= 0) mbar_expect_tx(ld_next, (nxt2 >= 0 ? KV_BYTES : 0) + KV_BYTES);
+            if (nxt2 >= 0) load_k(nxt2, it & 1, ld_next);       // K(it+2) over K(it)
+            if (nxt >= 0) load_v(nxt, (it + 1) & 1, ld_next);   // V(it+1) over V(it-1)
+            // D: thread 0 waits for load group `it` (K(it+1), V(it)); the barrier is for the S
+            // columns, which every thread has read by now
+            if (tid == 0 && it > 0 && !dead) dead = !mbar_wait(bar_ld + 8 * (it & 1), (unsigned)(it >> 1) & 1u, WAIT_LIMIT);
+        } else {
+            if (nxt2 >= 0) load_k(nxt2, it & 1, 0);            // K(it+2) over K(it)
+            if (nxt >= 0) load_v(nxt, (it + 1) & 1, 0);        // V(it+1) over V(it-1)
+            cp_commit_tc();
+            // D: K(it+1) (committed one tile ago) has landed; start the next score tile
+            asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+            fence_async_proxy();
+        }
         fence_before_sync();
         __syncthreads();
         if (tid == 0 && nxt >= 0) { fence_after_sync(); issue_qk((it + 1) & 1); }
@@ -339,7 +417,7 @@ __global__ void __launch_bounds__(THREADS) swa_fwd_tc_kernel(
 #pragma unroll
             for (int ks = 0; ks < BN / 16; ks++)      // A = P (K-major over keys), B = V (MN-major)
                 mma_bf16(tmem_base + 64, make_desc(p_addr + ks * 2 * CORE, CORE, GROUP),
-                         make_desc(v_addr + ks * 2 * GROUP, GROUP, CORE), idesc_pv,
+                         make_desc(v_addr + ks * 2 * V_KG, V_KG, V_NC), idesc_pv,
                          (it > 0 || ks > 0) ? 1u : 0u);
             mma_commit(bar_o);
         }
