@@ -302,6 +302,13 @@ int32_t nlh_swa_backward_f32(const float* q, const float* k, const float* v, con
  * copies (cp.async.bulk.tensor, one issuing thread, completion on an mbarrier; plain single-CTA
  * loads) instead of per-thread cp.async; 0 selects the cp.async staging. Results are identical. */
 #define NLH_OPT_SWA_TMA 4
+/* NLH_OPT_BULK_STAGING (default 1): the register-resident memory-rule forward kernels (head_dim
+ * 32/64) stage their k, v, q tiles with one bulk asynchronous copy per stream and tile
+ * (cp.async.bulk from one thread, completion counted on an mbarrier) instead of per-thread
+ * cp.async; 0 selects the cp.async staging. Results are identical. nlh_bulk_timeout_flag() is
+ * nonzero if a bounded mbarrier wait of these kernels ever ran out. */
+#define NLH_OPT_BULK_STAGING 5
+int32_t nlh_bulk_timeout_flag(void);
 int32_t nlh_set_option(int32_t option, int32_t value);
 /* How the last tcgen05 SWA forward of this process staged its operand tiles: 1 = tiled TMA copies,
  * 0 = cp.async (NLH_OPT_SWA_TMA off, or the driver's tensor-map encoder was not available or

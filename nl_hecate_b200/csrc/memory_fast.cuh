@@ -199,6 +199,46 @@ __device__ __forceinline__ void tile_async(float* dst, const float* __restrict__
     for (int i = threadIdx.x; i < nvec; i += NT) cp_async16(dst + 4 * i, src + 4 * i);
 }
 
+// ── bulk (TMA engine) staging of the stream tiles ──
+// A tile of TT tokens of one stream is TT*D contiguous floats in global memory and in shared
+// memory, so one thread can stage it with ONE bulk asynchronous copy whose completion is counted
+// in bytes on an mbarrier (cp.async.bulk, the untiled form: both addresses 16-byte aligned, size a
+// multiple of 16 bytes; plain single-CTA copies of this GPU's memory). Every thread then waits on
+// the mbarrier phase instead of on its own cp.async group. Waits are bounded: when the limit runs
+// out the CTA sets g_bulk_timeout and carries on (wrong results, no hang).
+__device__ int g_bulk_timeout = 0;
+constexpr unsigned BULK_WAIT_LIMIT = 1u << 22;
+__device__ __forceinline__ unsigned smem_addr_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void bulk_bar_init(unsigned bar, unsigned count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+}
+__device__ __forceinline__ void bulk_bar_expect(unsigned bar, unsigned bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_copy_g2s(unsigned dst, const void* src, unsigned bytes, unsigned bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ bool bulk_bar_wait(unsigned bar, unsigned parity)
+{
+    for (unsigned i = 0; i < BULK_WAIT_LIMIT; i++) {
+        unsigned ok;
+        asm volatile(
+            "{\n\t"
+            ".reg .pred P;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, P;\n\t"
+            "}\n"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
 // One forward token on register state. Msrc is the matrix the error is taken
 // against (M itself, or the frozen chunk-start copy). Returns e (error or v for Hebbian).
 template <int D, int RULE>
@@ -254,12 +294,15 @@ __device__ __forceinline__ float fast_readout(const float2 (&M)[8], const float*
 
 // D = 64, exact rules: capped at 64 registers so that four CTAs share an SM (the level-0 problem
 // count of the stacked model, batch x heads = 512, then fits in one wave of 148 x 4).
-template <int D, int RULE, bool FROZEN, int SPLIT = 1>
+// BULK: the k, v, q tiles are staged by thread 0 with bulk asynchronous copies (see above) instead
+// of every thread's cp.async; the gates (4 bytes per token and stream) stay on cp.async.
+template <int D, int RULE, bool FROZEN, int SPLIT = 1, bool BULK = false>
 __global__ void __launch_bounds__(FastGeom<D, SPLIT>::NT, (D == 64 && !FROZEN) ? 4 : 1) fast_fwd_kernel(FwdArgs a)
 {
     using G = FastGeom<D, SPLIT>;
     constexpr int NT = G::NT, TPR = G::TPR, TT = FAST_TT, ROWS = G::ROWS;
     extern __shared__ __align__(16) float sm[];
+    __shared__ __align__(8) unsigned long long tile_bar[2];     // one mbarrier per tile buffer (BULK)
     float* kt = sm;
     float* vt = kt + 2 * TT * D;
     float* qt = vt + 2 * TT * D;
@@ -293,13 +336,29 @@ __global__ void __launch_bounds__(FastGeom<D, SPLIT>::NT, (D == 64 && !FROZEN) ?
     }
 
     const int ntiles = (a.seq_len + TT - 1) / TT;
+    if (BULK) {
+        if (tid == 0) { bulk_bar_init(smem_addr_u32(&tile_bar[0]), 1); bulk_bar_init(smem_addr_u32(&tile_bar[1]), 1); }
+        __syncthreads();
+    }
+    bool bulk_dead = false;
     auto prefetch = [&](int tile) {
         const int t0 = tile * TT;
         const int ntok = min(TT, a.seq_len - t0);
         const int buf = tile & 1;
-        tile_async<D, NT>(kt + buf * TT * D, k + (size_t)t0 * D, ntok);
-        tile_async<D, NT>(vt + buf * TT * D, v + (size_t)t0 * D, ntok);
-        tile_async<D, NT>(qt + buf * TT * D, q + (size_t)t0 * D, ntok);
+        if (BULK) {
+            if (tid == 0) {
+                const unsigned bar = smem_addr_u32(&tile_bar[buf]);
+                const unsigned bytes = (unsigned)ntok * D * 4;
+                bulk_bar_expect(bar, 3 * bytes);
+                bulk_copy_g2s(smem_addr_u32(kt + buf * TT * D), k + (size_t)t0 * D, bytes, bar);
+                bulk_copy_g2s(smem_addr_u32(vt + buf * TT * D), v + (size_t)t0 * D, bytes, bar);
+                bulk_copy_g2s(smem_addr_u32(qt + buf * TT * D), q + (size_t)t0 * D, bytes, bar);
+            }
+        } else {
+            tile_async<D, NT>(kt + buf * TT * D, k + (size_t)t0 * D, ntok);
+            tile_async<D, NT>(vt + buf * TT * D, v + (size_t)t0 * D, ntok);
+            tile_async<D, NT>(qt + buf * TT * D, q + (size_t)t0 * D, ntok);
+        }
         if (tid < ntok) {
             cp_async4(gt + (buf * 3 + 0) * TT + tid, alpha + t0 + tid);
             if (RULE != RULE_HEBBIAN) cp_async4(gt + (buf * 3 + 1) * TT + tid, theta + t0 + tid);
@@ -315,6 +374,8 @@ __global__ void __launch_bounds__(FastGeom<D, SPLIT>::NT, (D == 64 && !FROZEN) ?
         const int buf = tile & 1;
         if (tile + 1 < ntiles) { prefetch(tile + 1); cp_async_wait<1>(); }
         else cp_async_wait<0>();
+        // BULK: buffer `buf` is used by tiles buf, buf + 2, ...: phase (tile >> 1) of its mbarrier
+        if (BULK && !bulk_dead) bulk_dead = !bulk_bar_wait(smem_addr_u32(&tile_bar[buf]), (unsigned)(tile >> 1) & 1u);
         __syncthreads();
         const float* kb = kt + buf * TT * D;
         const float* vb = vt + buf * TT * D;
@@ -357,6 +418,7 @@ __global__ void __launch_bounds__(FastGeom<D, SPLIT>::NT, (D == 64 && !FROZEN) ?
             }
         }
     }
+    if (BULK && bulk_dead && tid == 0) atomicExch(&g_bulk_timeout, 1);
     if (mode == STORE_CHUNK) {
         const size_t off = (size_t)((a.seq_len + a.interval - 1) / a.interval) * dd;
         store_state8<D>(M, m_out + off, r, cg);
@@ -721,6 +783,18 @@ static bool fast_fwd_launch(const FwdArgs& a, cudaStream_t st)
             fast_fwd_kernel<D, RULE, false, 2><<<a.batch * 2, FastGeom<D, 2>::NT, smem, st>>>(a);
             return true;
         }
+    }
+    // bulk staging of the stream tiles: every tile starts on a 16-byte boundary (bases checked by
+    // the caller; token rows are D * 4 = 128 or 256 bytes)
+    if (option_value(NLH_OPT_BULK_STAGING)) {
+        if (a.frozen) {
+            if (smem > 48 * 1024) cudaFuncSetAttribute(fast_fwd_kernel<D, RULE, true, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            fast_fwd_kernel<D, RULE, true, 1, true><<<a.batch, FastGeom<D>::NT, smem, st>>>(a);
+        } else {
+            if (smem > 48 * 1024) cudaFuncSetAttribute(fast_fwd_kernel<D, RULE, false, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            fast_fwd_kernel<D, RULE, false, 1, true><<<a.batch, FastGeom<D>::NT, smem, st>>>(a);
+        }
+        return true;
     }
     if (a.frozen) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(fast_fwd_kernel<D, RULE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -659,4 +659,11 @@ int32_t nlh_rule_backward(int32_t rule, const float* k_mem, const float* v_mem,
         frozen, interval, 0, error_clip, m_norm_max), "nlh_rule_backward");
 }
 
+int32_t nlh_bulk_timeout_flag(void)
+{
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_bulk_timeout, sizeof(int)) != cudaSuccess) return -1;
+    return v;
+}
+
 }  // extern "C"

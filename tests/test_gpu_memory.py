@@ -560,6 +560,45 @@ def test_row_split_exact_pair_matches_one_cta_per_problem(D, orc, n, s):
         _check_bwd(g, w, ["d_k", "d_v", "d_q", "d_alpha", "d_theta", "d_eta", "d_m_initial", "d_s_initial"])
 
 
+@pytest.mark.parametrize("d,s,n", [(64, 5, 2), (64, 16, 3), (64, 37, 3), (32, 130, 2), (64, 130, 150)])
+def test_bulk_staged_forward_equals_cp_async_staging(D, orc, d, s, n):
+    """NLH_OPT_BULK_STAGING: the register-resident forward kernels stage the k, v, q tiles with one
+    bulk asynchronous copy per stream and tile, completion counted on an mbarrier (default on). The
+    staging does not touch the arithmetic: every rule's outputs are bit-identical to the cp.async
+    staging, on whole, ragged and single tiles, exact and frozen, and no bounded wait ran out."""
+    import torch
+    p = make_problem(orc, n, s, d, 7100 + d + s + n, "rand")
+    t = to_dev(p)
+    outs = {}
+    D.call("nlh_set_option", option=3, value=0)      # one CTA per problem at every n
+    D.call("nlh_set_option", option=2, value=0)      # frozen rules on the per-token kernels
+    try:
+        for on in (1, 0):
+            D.call("nlh_set_option", option=5, value=on)
+            o = []
+            o += D.titans_forward_dd(t["k"], t["v"], t["q"], t["alpha"], t["theta"], t["eta"], t["m0"], t["s0"])
+            o += D.titans_forward_dd(t["k"], t["v"], t["q"], t["alpha"], t["theta"], t["eta"], t["m0"], t["s0"],
+                                     store_s=False)[::2]
+            o += D.delta_forward_dd(t["k"], t["v"], t["q"], t["alpha"], t["theta"], t["m0"])
+            o += D.hebbian_forward_dd(t["k"], t["v"], t["q"], t["alpha"], t["m0"])
+            o += D.titans_chunkwise_forward_dd(t["k"], t["v"], t["q"], t["alpha"], t["theta"], t["eta"], t["m0"],
+                                               t["s0"], 8)
+            o += D.delta_chunkwise_forward_dd(t["k"], t["v"], t["q"], t["alpha"], t["theta"], t["m0"], 8)
+            o += D.titans_frozen_stream_forward(t["k"], t["v"], t["q"], t["alpha"], t["theta"], t["eta"], t["m0"],
+                                                t["s0"], 8)
+            outs[on] = o
+    finally:
+        for opt in (2, 3, 5):
+            D.call("nlh_set_option", option=opt, value=1)
+    assert len(outs[1]) == len(outs[0])
+    for a, b in zip(outs[1], outs[0]):
+        assert a.shape == b.shape and torch.equal(a, b)
+    assert D.ffi.lib().nlh_bulk_timeout_flag() == 0
+    if n <= 3:
+        w = oracle_exact(orc, "titans", p)
+        assert rel_err(_np(outs[1][0]), w["m_states"]) <= REL and rel_err(_np(outs[1][2]), w["y"]) <= REL
+
+
 def test_null_momentum_trajectory_rejected_off_the_fast_path(D, orc):
     p = make_problem(orc, 1, 6, 16, 2990, "rand")   # d = 16 runs the generic kernels
     t = to_dev(p)
