@@ -534,3 +534,122 @@ def test_stacked_oracle_traced_mode_equals_resident_mode_with_one_head(orc):
     for n, a in out["traced"][1].items():
         b = out["resident"][1][n]
         assert np.abs(a - b).max() <= 1e-5 * max(np.abs(a).max(), 1e-9), n
+
+
+# ── MLP memory (two-layer deep memory) oracle ───────────────────────────────
+def _mlp_loss(mlp, p, dh, kind):
+    _, _, y = mlp.forward(p["k"], p["v"], p["q"], p["alpha"], p["theta"], p["eta"], p["m0"], p["s0"], dh, kind)
+    return float(np.sum(y * p["dy"]))
+
+
+def _mlp_fd(mlp, p, key, idx, dh, kind, eps=1e-6):
+    a = p[key]
+    old = a[idx]
+    a[idx] = old + eps
+    lp = _mlp_loss(mlp, p, dh, kind)
+    a[idx] = old - eps
+    lm = _mlp_loss(mlp, p, dh, kind)
+    a[idx] = old
+    return (lp - lm) / (2 * eps)
+
+
+def test_mlp_memory_oracle_first_token_closed_form():
+    """One token, zero initial momentum: S_1 = -theta * grad and M_1 = (1 - alpha) M_0 + S_1 with the
+    hand-written gradient of 0.5 |MLP(k) - v|^2 (core/src/titans_lmm.rs:771-810), y = MLP(M_1, q)."""
+    from oracle import mlp_memory as mlp
+    d, dh = 4, 8
+    p = mlp.make_problem(1, 1, d, dh, 11, np.float64)
+    ms, sts, y = mlp.forward(p["k"], p["v"], p["q"], p["alpha"], p["theta"], p["eta"], p["m0"], p["s0"], dh,
+                             mlp.ACT_SILU)
+    w1, b1, w2, b2 = mlp.unpack(p["m0"][0], d, dh)
+    k, v = p["k"][0, 0], p["v"][0, 0]
+    pre = w1 @ k + b1
+    sig = 1 / (1 + np.exp(-pre))
+    h = pre * sig
+    e = w2 @ h + b2 - v
+    gp = (w2.T @ e) * (sig + pre * sig * (1 - sig))
+    grad = np.concatenate([np.outer(gp, k).ravel(), gp, np.outer(e, h).ravel(), e])
+    assert np.allclose(sts[0, 1], -p["theta"][0, 0] * grad, rtol=1e-12, atol=1e-14)
+    assert np.allclose(ms[0, 1], (1 - p["alpha"][0, 0]) * p["m0"][0] + sts[0, 1], rtol=1e-12, atol=1e-14)
+    w1n, b1n, w2n, b2n = mlp.unpack(ms[0, 1], d, dh)
+    pq = w1n @ p["q"][0, 0] + b1n
+    assert np.allclose(y[0, 0], w2n @ (pq / (1 + np.exp(-pq))) + b2n, rtol=1e-12, atol=1e-14)
+
+
+def test_mlp_memory_oracle_backward_matches_float64_finite_differences_with_relu():
+    """With ReLU the reference's backward (which drops the activation's second derivative) is the
+    exact gradient: every output of the reverse loop against central differences of
+    L = <y, d_y> in float64, momentum carried in (s0 != 0)."""
+    from oracle import mlp_memory as mlp
+    n, s, d, dh = 2, 5, 4, 8
+    p = mlp.make_problem(n, s, d, dh, 5, np.float64, state_scale=0.5)
+    p["s0"] = np.random.default_rng(6).standard_normal(p["s0"].shape) * 0.05
+    kind = mlp.ACT_RELU
+    ms, sts, _ = mlp.forward(p["k"], p["v"], p["q"], p["alpha"], p["theta"], p["eta"], p["m0"], p["s0"], dh, kind)
+    g = mlp.backward(p["k"], p["v"], p["q"], p["alpha"], p["theta"], p["eta"], ms, sts, p["dy"], dh, kind)
+    rng = np.random.default_rng(7)
+    pairs = [("k", "d_k"), ("v", "d_v"), ("q", "d_q"), ("alpha", "d_alpha"), ("theta", "d_theta"),
+             ("eta", "d_eta"), ("m0", "d_m_initial"), ("s0", "d_s_initial")]
+    worst = 0.0
+    for key, gkey in pairs:
+        flat = p[key].size
+        for j in rng.choice(flat, size=min(12, flat), replace=False):
+            idx = np.unravel_index(j, p[key].shape)
+            fd = _mlp_fd(mlp, p, key, idx, dh, kind)
+            an = g[gkey][idx]
+            err = abs(fd - an) / max(abs(fd), abs(an), 1e-6)
+            worst = max(worst, err)
+            assert err < 1e-5, (key, idx, fd, an)
+    assert worst < 1e-5
+
+
+@pytest.mark.parametrize("kind", [0, 1])
+def test_mlp_memory_oracle_smooth_activations_exact_where_no_second_derivative_enters(kind):
+    """GELU / SiLU: d_q (readout only), d_theta (first order in theta) and — with theta = 0, when the
+    memory is not written — d_alpha, d_eta and the initial-state gradients do not involve act'' and
+    must equal float64 central differences. (With theta > 0 the other outputs are the reference's
+    approximation, not the true gradient: they are pinned by the ReLU case only.)"""
+    from oracle import mlp_memory as mlp
+    n, s, d, dh = 1, 4, 4, 8
+    p = mlp.make_problem(n, s, d, dh, 21 + kind, np.float64, state_scale=0.5)
+    p["s0"] = np.random.default_rng(8).standard_normal(p["s0"].shape) * 0.05
+    rng = np.random.default_rng(9)
+
+    def run():
+        ms, sts, _ = mlp.forward(p["k"], p["v"], p["q"], p["alpha"], p["theta"], p["eta"], p["m0"], p["s0"], dh, kind)
+        return mlp.backward(p["k"], p["v"], p["q"], p["alpha"], p["theta"], p["eta"], ms, sts, p["dy"], dh, kind)
+
+    def check(pairs, tol, g):
+        for key, gkey in pairs:
+            for j in rng.choice(p[key].size, size=min(8, p[key].size), replace=False):
+                idx = np.unravel_index(j, p[key].shape)
+                fd = _mlp_fd(mlp, p, key, idx, dh, kind)
+                an = g[gkey][idx]
+                assert abs(fd - an) / max(abs(fd), abs(an), 1e-6) < tol, (key, idx, fd, an)
+
+    g = run()
+    last = (0, s - 1)
+    for c in range(d):                      # the last token's d_q is pure readout
+        fd = _mlp_fd(mlp, p, "q", last + (c,), dh, kind)
+        assert abs(fd - g["d_q"][last + (c,)]) / max(abs(fd), 1e-6) < 1e-6
+    fd = _mlp_fd(mlp, p, "theta", last, dh, kind)
+    assert abs(fd - g["d_theta"][last]) / max(abs(fd), 1e-6) < 1e-6
+    p["theta"][:] = 0.0
+    g = run()
+    check([("q", "d_q"), ("alpha", "d_alpha"), ("eta", "d_eta"), ("theta", "d_theta"), ("m0", "d_m_initial"),
+           ("s0", "d_s_initial")], 1e-6, g)
+    assert np.abs(g["d_k"]).max() == 0.0 and np.abs(g["d_v"]).max() == 0.0
+
+
+def test_mlp_memory_oracle_norm_projection():
+    """m_norm_max: every stored state has Frobenius norm <= the bound over the WHOLE packed state
+    (core/src/titans_lmm.rs:812-821); disabled at 0 and at >= 1e30 (core/kernels/m_norm_project.cuh)."""
+    from oracle import mlp_memory as mlp
+    d, dh = 4, 8
+    p = mlp.make_problem(2, 6, d, dh, 31, np.float32, state_scale=0.5)
+    args = (p["k"], p["v"], p["q"], p["alpha"], p["theta"], p["eta"], p["m0"], p["s0"], dh, mlp.ACT_GELU)
+    ms, _, _ = mlp.forward(*args, m_norm_max=1.5)
+    assert np.linalg.norm(ms[:, 1:], axis=-1).max() <= 1.5 * (1 + 1e-5)
+    free, _, _ = mlp.forward(*args, m_norm_max=0.0)
+    assert np.linalg.norm(free[:, 1:], axis=-1).max() > 1.5
+    assert np.array_equal(free, mlp.forward(*args, m_norm_max=1e30)[0])
