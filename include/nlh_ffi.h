@@ -203,6 +203,29 @@ uint32_t reduce_partials_clip_cuda(const float* partial_sums, int32_t total_part
     float max_grad_norm, float* out_norm, float* out_scale);
 uint32_t grad_scale_conditional_cuda(float* g, const float* scale_ptr, int32_t n);
 
+/* cuda_ffi.rs:854 / :887 — Titans LMM with a two-layer MLP memory. The state of one problem is the
+ * packed buffer W1[d_hidden,d], b1[d_hidden], W2[d,d_hidden], b2[d] (state_size floats); S has the
+ * same shape. k/v/q/y [batch, seq_len, d] with input_stride = seq_len * d floats between problems;
+ * gates [batch, seq_len]; m_initial / s_initial [batch, state_size]; m_states / s_states
+ * [batch, (seq_len + 1) * state_size] with m_stride floats between problems (slot 0 = initial).
+ * activation: 0 GELU (tanh form), 1 SiLU, 2 ReLU. m_norm_max: Frobenius bound on the whole packed
+ * state after every token (<= 0 or >= 1e30: off); the backward passes gradients straight through
+ * it. The backward ADDS d_m_initial / d_s_initial [state_size] over the batch (caller zeroes them)
+ * and writes every other output. One CTA per problem with the state on the SM: supported for
+ * d, d_hidden <= 512 and state_size <= 33280 floats (d = 64, d_hidden = 256); larger shapes record
+ * NLH_ERR_UNSUPPORTED and launch nothing. */
+void titans_mlp_forward_f32_cuda(const float* k_mem, const float* v_mem, const float* q_mem,
+    const float* alpha, const float* theta, const float* eta, const float* m_initial,
+    const float* s_initial, float* m_states, float* s_states, float* y, int32_t seq_len, int32_t d,
+    int32_t d_hidden, int32_t batch_size, int32_t input_stride, int32_t m_stride,
+    int32_t activation, float m_norm_max);
+void titans_mlp_backward_f32_cuda(const float* k_mem, const float* v_mem, const float* q_mem,
+    const float* alpha, const float* theta, const float* eta, const float* m_states,
+    const float* s_states, const float* d_y, float* d_k_mem, float* d_v_mem, float* d_q_mem,
+    float* d_alpha, float* d_theta, float* d_eta, float* d_m_initial, float* d_s_initial,
+    int32_t seq_len, int32_t d, int32_t d_hidden, int32_t batch_size, int32_t input_stride,
+    int32_t m_stride, int32_t activation, float m_norm_max);
+
 /* cuda_ffi.rs:973 / :1000 — fused forwards: L2-normalise k,q in place, compute
  * the gates, then run the recurrence. */
 void dgd_fused_forward_f32_cuda(float* k_mem, const float* v_mem, float* q_mem,

@@ -21,7 +21,7 @@ LIB = os.path.join(HERE, "libnlh_b200.so")
 
 SOURCES = ["runtime.cu", "memory_ffi.cu", "swa.cu", "swa_f32.cu", "adamw.cu",
            "static_scratch.cu", "wrapper.cu", "glue.cu", "opaque.cu", "opaque_rules.cu",
-           "host_dispatch.cu"]
+           "host_dispatch.cu", "mlp_memory.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC"]
 

@@ -147,6 +147,41 @@ def titans_backward_dd(k, v, q, alpha, theta, eta, ms, ss, d_y, error_clip=0.0, 
                 d_s_initial=ds0)
 
 
+def mlp_state_size(d, d_hidden):
+    """Floats in one packed MLP memory state: W1[d_hidden,d], b1[d_hidden], W2[d,d_hidden], b2[d]."""
+    return d_hidden * d + d_hidden + d * d_hidden + d
+
+
+def titans_mlp_forward_dd(k, v, q, alpha, theta, eta, m0, s0, d_hidden, activation=0, m_norm_max=0.0):
+    """Titans LMM with a two-layer MLP memory (titans_mlp_forward_f32_cuda): m0, s0 [N, state];
+    returns m_states, s_states [N, S+1, state] and y [N, S, d]."""
+    n, s, d = k.shape
+    ssz = mlp_state_size(d, d_hidden)
+    ms = torch.empty(n, s + 1, ssz, dtype=torch.float32, device=k.device)
+    ss = torch.empty(n, s + 1, ssz, dtype=torch.float32, device=k.device)
+    y = torch.empty(n, s, d, dtype=torch.float32, device=k.device)
+    call("titans_mlp_forward_f32_cuda", k_mem=k, v_mem=v, q_mem=q, alpha=alpha, theta=theta, eta=eta,
+         m_initial=m0, s_initial=s0, m_states=ms, s_states=ss, y=y, seq_len=s, d=d, d_hidden=d_hidden,
+         batch_size=n, input_stride=s * d, m_stride=(s + 1) * ssz, activation=activation,
+         m_norm_max=m_norm_max)
+    return ms, ss, y
+
+
+def titans_mlp_backward_dd(k, v, q, alpha, theta, eta, ms, ss, d_y, d_hidden, activation=0):
+    """Backward twin; d_m_initial / d_s_initial [state] are summed over the N problems."""
+    n, s, d = k.shape
+    ssz = mlp_state_size(d, d_hidden)
+    dk, dv, dq = (torch.empty_like(k) for _ in range(3))
+    da, dt, de = (torch.empty_like(alpha) for _ in range(3))
+    dm0 = torch.zeros(ssz, dtype=torch.float32, device=k.device)
+    ds0 = torch.zeros(ssz, dtype=torch.float32, device=k.device)
+    call("titans_mlp_backward_f32_cuda", k_mem=k, v_mem=v, q_mem=q, alpha=alpha, theta=theta, eta=eta,
+         m_states=ms, s_states=ss, d_y=d_y, d_k_mem=dk, d_v_mem=dv, d_q_mem=dq, d_alpha=da, d_theta=dt,
+         d_eta=de, d_m_initial=dm0, d_s_initial=ds0, seq_len=s, d=d, d_hidden=d_hidden, batch_size=n,
+         input_stride=s * d, m_stride=(s + 1) * ssz, activation=activation, m_norm_max=0.0)
+    return dict(d_k=dk, d_v=dv, d_q=dq, d_alpha=da, d_theta=dt, d_eta=de, d_m_initial=dm0, d_s_initial=ds0)
+
+
 def delta_forward_dd(k, v, q, alpha, theta, m0, error_clip=0.0, m_norm_max=0.0, dgd=False):
     n, s, d = k.shape
     ms = _f32(n, s + 1, d * d, device=k.device)
