@@ -620,11 +620,101 @@ class TitansLevel1(TitansLevel0):
             self.chunk = 0
 
 
+class TitansMlpPair(TitansPair):
+    """Titans LMM with a two-layer MLP memory (deep neural memory), kernel pair alone: the packed
+    state W1[256,64] b1 W2[64,256] b2 per head, GELU, both trajectories stored as the ABI asks."""
+    B, H, S, D, DH = 16, 8, 512, 64, 256
+
+    def __init__(self):
+        super().__init__(0)
+        self.name = "titans_mlp"
+        self.SS = self.DH * self.D * 2 + self.DH + self.D
+
+    def describe(self):
+        return {"workload": f"Titans LMM MLP-memory kernel pair (2 layers, d_hidden {self.DH}, GELU, full M and S "
+                            f"trajectories): batch {self.B} x heads {self.H}, head_dim {self.D}, seq {self.S}, fp32",
+                "problems_per_gpu": self.N, "tokens_per_step_per_gpu": self.tokens_per_step,
+                "l2_policy": "trajectories written and read per step (2 x 132 KB per head-token) >> L2"}
+
+    def host_inputs(self, n=None, seed=1234):
+        n = self.N if n is None else n
+        g = np.random.Generator(np.random.Philox(seed))
+        nrm = lambda x: (x / np.linalg.norm(x, axis=-1, keepdims=True)).astype(np.float32)
+        sig = lambda x: (1.0 / (1.0 + np.exp(-x))).astype(np.float32)
+        sh = (n, self.S, self.D)
+        return dict(k=nrm(g.standard_normal(sh)), v=(0.5 * g.standard_normal(sh)).astype(np.float32),
+                    q=nrm(g.standard_normal(sh)), alpha=sig(g.standard_normal(sh[:2]) - 3.0),
+                    theta=np.log1p(np.exp(g.standard_normal(sh[:2]) - 3.0)).astype(np.float32),
+                    eta=sig(g.standard_normal(sh[:2]) + 1.5), dy=g.standard_normal(sh).astype(np.float32),
+                    m0=(0.1 * g.standard_normal((n, self.SS))).astype(np.float32),
+                    s0=np.zeros((n, self.SS), np.float32))
+
+    def setup(self, torch, dispatch):
+        self.torch, self.dd = torch, dispatch
+        self.host = {k: torch.from_numpy(v).pin_memory() for k, v in self.host_inputs().items()}
+        self.dev = {k: v.cuda() for k, v in self.host.items()}
+        n, s, d = self.N, self.S, self.D
+        f32 = lambda *sh: torch.empty(*sh, dtype=torch.float32, device="cuda")
+        self.mstate, self.sstate, self.y = f32(n, s + 1, self.SS), f32(n, s + 1, self.SS), f32(n, s, d)
+        self.out = {k: f32(n, s, d) for k in ("d_k", "d_v", "d_q")}
+        self.out.update({k: f32(n, s) for k in ("d_alpha", "d_theta", "d_eta")})
+        self.out.update({k: f32(self.SS) for k in ("d_m0", "d_s0")})
+        self.host_out = {k: torch.empty(v.shape, dtype=v.dtype).pin_memory()
+                         for k, v in list(self.out.items()) + [("y", self.y)]}
+        self.launches_per_step = 2
+        self.h2d = sum(v.numel() * 4 for k, v in self.host.items())
+        self.d2h = sum(v.numel() * 4 for v in self.host_out.values())
+
+    def fwd(self, t):
+        self.dd.call("titans_mlp_forward_f32_cuda", k_mem=t["k"], v_mem=t["v"], q_mem=t["q"], alpha=t["alpha"],
+                     theta=t["theta"], eta=t["eta"], m_initial=t["m0"], s_initial=t["s0"], m_states=self.mstate,
+                     s_states=self.sstate, y=self.y, seq_len=self.S, d=self.D, d_hidden=self.DH, batch_size=self.N,
+                     input_stride=self.S * self.D, m_stride=(self.S + 1) * self.SS, activation=0, m_norm_max=0.0)
+
+    def bwd(self, t):
+        o = self.out
+        o["d_m0"].zero_(); o["d_s0"].zero_()
+        self.dd.call("titans_mlp_backward_f32_cuda", k_mem=t["k"], v_mem=t["v"], q_mem=t["q"], alpha=t["alpha"],
+                     theta=t["theta"], eta=t["eta"], m_states=self.mstate, s_states=self.sstate, d_y=t["dy"],
+                     d_k_mem=o["d_k"], d_v_mem=o["d_v"], d_q_mem=o["d_q"], d_alpha=o["d_alpha"],
+                     d_theta=o["d_theta"], d_eta=o["d_eta"], d_m_initial=o["d_m0"], d_s_initial=o["d_s0"],
+                     seq_len=self.S, d=self.D, d_hidden=self.DH, batch_size=self.N, input_stride=self.S * self.D,
+                     m_stride=(self.S + 1) * self.SS, activation=0, m_norm_max=0.0)
+
+    def dominant(self):
+        """Backward: reads k, v, q, d_y, gates and every stored M and S state once; writes d_k, d_v,
+        d_q and the gate gradients."""
+        n, s, d = self.N, self.S, self.D
+        streams = 7 * n * s * d * 4 + 6 * n * s * 4
+        return ("mlpm::mlp_bwd_kernel<GELU> (MLP-memory backward, M and S trajectories)",
+                lambda: self.bwd(self.dev), streams + 2 * n * (s + 1) * self.SS * 4, "hbm")
+
+    def cpu_sample(self, oracle, threads, budget_s=12.0):
+        """The numpy restatement of the Rust path (oracle/mlp_memory.py), one problem per host
+        process, shortened sequences of the same head size."""
+        from concurrent.futures import ProcessPoolExecutor
+        from oracle import mlp_memory
+        s = 64
+        jobs = [(1000 + i, s, self.D, self.DH, 0) for i in range(threads)]
+        with ProcessPoolExecutor(max_workers=threads) as ex:
+            list(ex.map(mlp_memory.timed_fwd_bwd, jobs))               # start the workers, import numpy
+            t0 = time.perf_counter()
+            list(ex.map(mlp_memory.timed_fwd_bwd, jobs))
+            t1 = time.perf_counter() - t0
+            reps = max(1, min(512, int(budget_s / max(t1, 1e-3))))
+            jobs = [(2000 + i, s, self.D, self.DH, 0) for i in range(threads * reps)]
+            t0 = time.perf_counter()
+            done = sum(ex.map(mlp_memory.timed_fwd_bwd, jobs, chunksize=reps))
+            dt = time.perf_counter() - t0
+        return done / self.H / dt, (f"{threads * reps} (batch x head) problems of {s} tokens (of {self.N} x {self.S}), "
+                                    f"{reps} per host process, numpy statement of the reference's Rust loop: {dt:.1f} s")
+
+
 def make_workload(name, world=1, small=False, local_batch=0):
     """small: reduced problem counts of the same kernels, sized for profiler captures (inputs still
     larger than L2, a few hundred MB on the device)."""
     if small:
-        TitansPair.B, SwaPair.B, TitansLevel0.B, TitansLevel1.B = 4, 1, 37, 64
+        TitansPair.B, SwaPair.B, TitansLevel0.B, TitansLevel1.B, TitansMlpPair.B = 4, 1, 37, 64, 2
     if name == "titans_chunkwise":
         return TitansPair(64)
     if name == "titans_exact":
@@ -633,6 +723,8 @@ def make_workload(name, world=1, small=False, local_batch=0):
         return TitansLevel0()
     if name == "titans_level1":
         return TitansLevel1()
+    if name == "titans_mlp":
+        return TitansMlpPair()
     if name == "swa":
         return SwaPair()
     if name == "adamw":

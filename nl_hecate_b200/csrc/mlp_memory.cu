@@ -33,6 +33,7 @@ enum { ACT_GELU = 0, ACT_SILU = 1, ACT_RELU = 2 };
 struct Dims {
     int d, dh;
     int o1, o2, o3, ss;      // offsets of b1, W2, b2 in the packed state; its size
+    int tps_d, tps_h;        // log2 of the threads that share a row of d / dh columns (32 each)
     FastDiv div_d, div_h;
 };
 
@@ -42,6 +43,8 @@ static Dims make_dims(int d, int dh)
     D.d = d; D.dh = dh;
     D.o1 = dh * d; D.o2 = D.o1 + dh; D.o3 = D.o2 + d * dh; D.ss = D.o3 + d;
     D.div_d = make_fastdiv(d); D.div_h = make_fastdiv(dh);
+    D.tps_d = 0; while ((32 << D.tps_d) < d) D.tps_d++;
+    D.tps_h = 0; while ((32 << D.tps_h) < dh) D.tps_h++;
     return D;
 }
 
@@ -75,48 +78,65 @@ __device__ __forceinline__ float warp_sum(float v)
     return v;
 }
 
-// out(r) = sum_j W[r, j] x[j] for r < R, W row-major [R, C] (shared or global), x in shared
-// memory. One warp per row, lanes over columns (coalesced / conflict-free), RB rows in flight per
-// warp so that global reads overlap. epi(r, sum) runs on lane 0.
-template <int RB, class Epi>
-__device__ __forceinline__ void rowdot(const float* __restrict__ W, int R, int C, const float* x, Epi epi)
+// Shared-memory layout: one pad float after every 32, for matrices (the whole packed state keeps
+// its flat order) and vectors alike. A thread that walks 32 consecutive columns of its own row then
+// hits 32 different banks whatever the row length, threads on consecutive elements still do, and
+// a vector read at 32 p + j by threads with different p does too.
+__device__ __forceinline__ int P(int i) { return i + (i >> 5); }
+__host__ __device__ inline int padded(int n) { return n + (n >> 5) + 1; }
+
+// out(r) = sum_c W[r, c] x[c], r < R: W row-major [R, C] at flat offset off of the padded buffer
+// Wp, x a padded vector. 2^tps threads per row, each a 32-column segment, combined by shuffles;
+// every (row, segment) pair of the matrix is in flight at once (R * 2^tps <= NT for the sizes of the
+// reference's configs), so a product is one pass of 32 FMAs instead of a chain of row iterations.
+// epi(r, sum) runs on one thread per row.
+template <class Epi>
+__device__ __forceinline__ void rowdot(const float* Wp, int off, int R, int C, int tps, const float* xp, Epi epi)
 {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int r0 = warp * RB; r0 < R; r0 += NW * RB) {
-        float acc[RB];
+    const int TP = 1 << tps, T = (C + 31) >> 5;
+    for (int u0 = 0; u0 < (R << tps); u0 += NT) {
+        const int u = u0 + threadIdx.x, r = u >> tps, p = u & (TP - 1);
+        float acc = 0.0f;
+        if (r < R && p < T) {
+            const int c0 = p << 5, n = min(32, C - c0), f0 = off + r * C + c0;
+            const float* xs = xp + c0 + p;
+            if ((f0 & 31) == 0 && n == 32) {
+                const float* w = Wp + f0 + (f0 >> 5);
+                float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
 #pragma unroll
-        for (int u = 0; u < RB; u++) acc[u] = 0.0f;
-        for (int j = lane; j < C; j += 32) {
-            const float xv = x[j];
-#pragma unroll
-            for (int u = 0; u < RB; u++)
-                if (r0 + u < R) acc[u] = fmaf(W[(size_t)(r0 + u) * C + j], xv, acc[u]);
+                for (int j = 0; j < 32; j += 4) {
+                    a0 = fmaf(w[j], xs[j], a0); a1 = fmaf(w[j + 1], xs[j + 1], a1);
+                    a2 = fmaf(w[j + 2], xs[j + 2], a2); a3 = fmaf(w[j + 3], xs[j + 3], a3);
+                }
+                acc = (a0 + a1) + (a2 + a3);
+            } else {
+                for (int j = 0; j < n; j++) acc = fmaf(Wp[P(f0 + j)], xs[j], acc);
+            }
         }
-#pragma unroll
-        for (int u = 0; u < RB; u++) {
-            const float s = warp_sum(acc[u]);
-            if (lane == 0 && r0 + u < R) epi(r0 + u, s);
-        }
+        for (int o = TP >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (r < R && p == 0) epi(r, acc);
     }
 }
 
-// out(j) = sum_i W[i, j] x[i] for j < C (C <= NT). Thread (g, j) adds rows g, g + G, ... and the G
-// partial sums meet in scr[NT]; epi(j, sum) runs on threads j < C. Contains two block barriers;
-// every thread of the CTA must call it.
-template <class Epi>
-__device__ __forceinline__ void colsum(const float* __restrict__ W, int R, int C, const float* x, float* scr,
+// out(j) = sum_i W[i, j] x[i] for j < C (C <= NT), W at flat offset off of a padded shared buffer
+// (PAD) or of global memory. Thread (g, j) adds rows g, g + G, ...; the G partial sums meet in
+// scr[NT]; epi(j, sum) runs on threads j < C. Two block barriers inside: every thread must call it.
+template <bool PAD, class Epi>
+__device__ __forceinline__ void colsum(const float* __restrict__ W, int off, int R, int C, const float* xp, float* scr,
                                        int g, int j, int G, Epi epi)
 {
     float acc = 0.0f;
     if (g < G) {
+        float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
         int i = g;
         for (; i + 3 * G < R; i += 4 * G) {
-            const float w0 = W[(size_t)i * C + j], w1 = W[(size_t)(i + G) * C + j];
-            const float w2 = W[(size_t)(i + 2 * G) * C + j], w3 = W[(size_t)(i + 3 * G) * C + j];
-            acc = fmaf(w0, x[i], acc); acc = fmaf(w1, x[i + G], acc);
-            acc = fmaf(w2, x[i + 2 * G], acc); acc = fmaf(w3, x[i + 3 * G], acc);
+            const int f0 = off + i * C + j, f1 = f0 + G * C, f2 = f1 + G * C, f3 = f2 + G * C;
+            const float w0 = W[PAD ? P(f0) : f0], w1 = W[PAD ? P(f1) : f1], w2 = W[PAD ? P(f2) : f2], w3 = W[PAD ? P(f3) : f3];
+            a0 = fmaf(w0, xp[P(i)], a0); a1 = fmaf(w1, xp[P(i + G)], a1);
+            a2 = fmaf(w2, xp[P(i + 2 * G)], a2); a3 = fmaf(w3, xp[P(i + 3 * G)], a3);
         }
-        for (; i < R; i += G) acc = fmaf(W[(size_t)i * C + j], x[i], acc);
+        for (; i < R; i += G) { const int f = off + i * C + j; a0 = fmaf(W[PAD ? P(f) : f], xp[P(i)], a0); }
+        acc = (a0 + a1) + (a2 + a3);
         scr[g * C + j] = acc;
     }
     __syncthreads();
@@ -149,15 +169,43 @@ __device__ __forceinline__ void block_sum(float (&v)[K], float* red)
     __syncthreads();
 }
 
-// Element idx of the packed state -> gradient-like outer-product term built from four vectors:
+// Element idx of the packed state -> outer-product term built from four padded vectors:
 //   W1[r,c] -> a1[r] * x1[c],  b1[r] -> a1[r],  W2[r,c] -> a2[r] * x2[c],  b2[r] -> a2[r]
-__device__ __forceinline__ float outer_term(const Dims& D, int idx, const float* a1, const float* x1,
-                                            const float* a2, const float* x2)
+// SD, SDH != 0: the sizes are compile-time constants that divide NT, so for the elements
+// idx = tid + i * NT of one thread the column of W1 is always tid % SD and the column of W2 always
+// tid % SDH; x1c = x1[tid % SD] and x2c = x2[tid % SDH] are then loaded once per pass by the caller,
+// and the region tests and row numbers fold to constants and shifts in the unrolled loops.
+template <int SD, int SDH>
+__device__ __forceinline__ float outer_term(const Dims& D, int idx, const float* a1, const float* x1, float x1c,
+                                            const float* a2, const float* x2, float x2c)
 {
-    if (idx < D.o1) { const int r = fd_div(idx, D.div_d); return a1[r] * x1[idx - r * D.d]; }
-    if (idx < D.o2) return a1[idx - D.o1];
-    if (idx < D.o3) { const int e = idx - D.o2; const int r = fd_div(e, D.div_h); return a2[r] * x2[e - r * D.dh]; }
-    return a2[idx - D.o3];
+    if (SD != 0) {
+        constexpr int o1 = SDH * SD, o2 = o1 + SDH, o3 = o2 + SD * SDH;
+        if (idx < o1) return a1[P(idx / (SD ? SD : 1))] * x1c;
+        if (idx < o2) return a1[P(idx - o1)];
+        if (idx < o3) return a2[P((idx - o2) / (SDH ? SDH : 1))] * x2c;
+        return a2[P(idx - o3)];
+    }
+    if (idx < D.o1) { const int r = fd_div(idx, D.div_d); return a1[P(r)] * x1[P(idx - r * D.d)]; }
+    if (idx < D.o2) return a1[P(idx - D.o1)];
+    if (idx < D.o3) { const int e = idx - D.o2; const int r = fd_div(e, D.div_h); return a2[P(r)] * x2[P(e - r * D.dh)]; }
+    return a2[P(idx - D.o3)];
+}
+constexpr int PNT = NT + NT / 32;      // padded distance of two elements NT apart
+constexpr int UB = 8;                  // elements whose loads are issued before their stores
+
+// n consecutive floats of global memory into a padded shared buffer (coalesced, 8 loads in flight)
+__device__ __forceinline__ void stage(float* dstp, const float* __restrict__ src, int n)
+{
+    int f = threadIdx.x;
+    for (; f + 7 * NT < n; f += 8 * NT) {
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) v[u] = src[f + u * NT];
+#pragma unroll
+        for (int u = 0; u < 8; u++) dstp[P(f + u * NT)] = v[u];
+    }
+    for (; f < n; f += NT) dstp[P(f)] = src[f];
 }
 
 struct FwdArgs {
@@ -169,25 +217,27 @@ struct FwdArgs {
     Dims D;
 };
 
-inline size_t fwd_smem_floats(const Dims& D) { return (size_t)((D.ss + 3) & ~3) + 3 * D.d + 3 * D.dh + D.d + NT + 4 * NW; }
+inline size_t fwd_smem_floats(const Dims& D) { return (size_t)padded(D.ss) + 4 * padded(D.d) + 3 * padded(D.dh) + NT + 4 * NW; }
 
-template <int ACT, int EPT>
+template <int ACT, int EPT, int SD, int SDH>
 __global__ void __launch_bounds__(NT, 1) mlp_fwd_kernel(FwdArgs a)
 {
     extern __shared__ __align__(16) float sm[];
     const Dims& D = a.D;
-    const int d = D.d, dh = D.dh, ss = D.ss, tid = threadIdx.x, b = blockIdx.x;
-    float* Msm = sm;
-    float* kb = Msm + ((ss + 3) & ~3);
-    float* vb = kb + d;
-    float* qb = vb + d;
-    float* pre = qb + d;
-    float* h = pre + dh;
-    float* gp = h + dh;
-    float* e = gp + dh;
-    float* scr = e + d;
+    const int d = SD ? SD : D.d, dh = SD ? SDH : D.dh, ss = SD ? 2 * SD * SDH + SD + SDH : D.ss;
+    const int tid = threadIdx.x, b = blockIdx.x, ptid = P(tid);
+    __builtin_assume(tid >= 0 && tid < NT);
+    const int pd = padded(d), ph = padded(dh);
+    float* Msm = sm;                       // the packed state, padded
+    float* kb = Msm + padded(ss);
+    float* vb = kb + pd;
+    float* qb = vb + pd;
+    float* e = qb + pd;
+    float* pre = e + pd;
+    float* h = pre + ph;
+    float* gp = h + ph;
+    float* scr = gp + ph;
     float* red = scr + NT;
-    const float *W1 = Msm, *b1 = Msm + D.o1, *W2 = Msm + D.o2, *b2 = Msm + D.o3;
 
     const float* k = a.k + (size_t)b * a.in_stride;
     const float* v = a.v + (size_t)b * a.in_stride;
@@ -209,37 +259,49 @@ __global__ void __launch_bounds__(NT, 1) mlp_fwd_kernel(FwdArgs a)
         if (idx < ss) {
             const float m = a.m_init[(size_t)b * ss + idx];
             S[i] = a.s_init[(size_t)b * ss + idx];
-            Msm[idx] = m; mt[idx] = m; st[idx] = S[i];
+            Msm[ptid + i * PNT] = m; mt[idx] = m; st[idx] = S[i];
         }
     }
     for (int t = 0; t < a.seq_len; t++) {
         for (int i = tid; i < 3 * d; i += NT) {
             const int w = fd_div(i, D.div_d), c = i - w * d;
-            kb[i] = (w == 0 ? k : w == 1 ? v : q)[(size_t)t * d + c];     // kb | vb | qb are adjacent
+            (w == 0 ? kb : w == 1 ? vb : qb)[P(c)] = (w == 0 ? k : w == 1 ? v : q)[(size_t)t * d + c];
         }
         const float al = alpha[t], th = theta[t], et = eta[t];
         __syncthreads();
-        rowdot<2>(W1, dh, d, kb, [&](int r, float s) { const float p = s + b1[r]; pre[r] = p; h[r] = act_fn<ACT>(p); });
+        rowdot(Msm, 0, dh, d, D.tps_d, kb, [&](int r, float s) { const float p = s + Msm[P(D.o1 + r)]; pre[P(r)] = p; h[P(r)] = act_fn<ACT>(p); });
         __syncthreads();
-        rowdot<2>(W2, d, dh, h, [&](int r, float s) { e[r] = s + b2[r] - vb[r]; });
+        rowdot(Msm, D.o2, d, dh, D.tps_h, h, [&](int r, float s) { e[P(r)] = s + Msm[P(D.o3 + r)] - vb[P(r)]; });
         __syncthreads();
-        colsum(W2, d, dh, e, scr, gh_, jh, Gh, [&](int j, float s) { gp[j] = s * act_prime<ACT>(pre[j]); });
+        colsum<true>(Msm, D.o2, d, dh, e, scr, gh_, jh, Gh, [&](int j, float s) { gp[P(j)] = s * act_prime<ACT>(pre[P(j)]); });
         // S' = eta S - theta grad, M' = (1 - alpha) M + S'
         float* mn = mt + (size_t)(t + 1) * ss;
         float* sn = st + (size_t)(t + 1) * ss;
         float sq[1] = {0.0f};
         const float keep = 1.0f - al;
+        const float x1c = SD ? kb[P(tid % (SD ? SD : 1))] : 0.0f, x2c = SD ? h[P(tid % (SDH ? SDH : 1))] : 0.0f;
 #pragma unroll
-        for (int i = 0; i < EPT; i++) {
-            const int idx = tid + i * NT;
-            if (idx < ss) {
-                const float g = outer_term(D, idx, gp, kb, e, h);
-                const float s_new = et * S[i] - th * g;
-                const float m_new = fmaf(keep, Msm[idx], s_new);
-                S[i] = s_new; Msm[idx] = m_new;
-                sn[idx] = s_new;
-                if (!clamp) mn[idx] = m_new;
-                sq[0] = fmaf(m_new, m_new, sq[0]);
+        for (int i0 = 0; i0 < EPT; i0 += UB) {
+            float g[UB], mo[UB];
+#pragma unroll
+            for (int u = 0; u < UB; u++) {
+                const int i = i0 + u, idx = tid + i * NT;
+                if (i < EPT && idx < ss) {
+                    g[u] = outer_term<SD, SDH>(D, idx, gp, kb, x1c, e, h, x2c);
+                    mo[u] = Msm[ptid + i * PNT];
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < UB; u++) {
+                const int i = i0 + u, idx = tid + i * NT;
+                if (i < EPT && idx < ss) {
+                    const float s_new = et * S[i] - th * g[u];
+                    const float m_new = fmaf(keep, mo[u], s_new);
+                    S[i] = s_new; Msm[ptid + i * PNT] = m_new;
+                    sn[idx] = s_new;
+                    if (!clamp) mn[idx] = m_new;
+                    sq[0] = fmaf(m_new, m_new, sq[0]);
+                }
             }
         }
         if (clamp) {      // Frobenius projection over the whole packed state (titans_lmm.rs:812-821)
@@ -249,14 +311,14 @@ __global__ void __launch_bounds__(NT, 1) mlp_fwd_kernel(FwdArgs a)
 #pragma unroll
             for (int i = 0; i < EPT; i++) {
                 const int idx = tid + i * NT;
-                if (idx < ss) { const float m = Msm[idx] * scale; Msm[idx] = m; mn[idx] = m; }
+                if (idx < ss) { const float m = Msm[ptid + i * PNT] * scale; Msm[ptid + i * PNT] = m; mn[idx] = m; }
             }
         }
         __syncthreads();
         // y_t = MLP(M_{t+1}, q_t)
-        rowdot<2>(W1, dh, d, qb, [&](int r, float s) { pre[r] = act_fn<ACT>(s + b1[r]); });
+        rowdot(Msm, 0, dh, d, D.tps_d, qb, [&](int r, float s) { pre[P(r)] = act_fn<ACT>(s + Msm[P(D.o1 + r)]); });
         __syncthreads();
-        rowdot<2>(W2, d, dh, pre, [&](int r, float s) { y[(size_t)t * d + r] = s + b2[r]; });
+        rowdot(Msm, D.o2, d, dh, D.tps_h, pre, [&](int r, float s) { y[(size_t)t * d + r] = s + Msm[P(D.o3 + r)]; });
         // no barrier here: the next token stages kb | vb | qb, which nothing above still reads,
         // and its first barrier comes before pre or M are written again
     }
@@ -270,7 +332,11 @@ struct BwdArgs {
     Dims D;
 };
 
-inline size_t bwd_smem_floats(const Dims& D) { return (size_t)((D.ss + 3) & ~3) + 4 * D.d + 8 * D.dh + 3 * D.d + NT + 4 * NW; }
+inline int stage_floats(const Dims& D) { return D.o2 > D.ss - D.o2 ? D.o2 : D.ss - D.o2; }
+inline size_t bwd_smem_floats(const Dims& D)
+{
+    return (size_t)padded(D.ss) + padded(stage_floats(D)) + 7 * padded(D.d) + 8 * padded(D.dh) + NT + 4 * NW;
+}
 
 // Reverse loop (titans_lmm.rs:896-1131). Per token, with dM, dS the gradients of M_{t+1}, S_{t+1}:
 //   1 readout      pq = W1' q + b1', hq = act(pq); dpq = (W2'^T dy) act'(pq); d_q = W1'^T dpq
@@ -281,29 +347,35 @@ inline size_t bwd_smem_floats(const Dims& D) { return (size_t)((D.ss + 3) & ~3) 
 //   6              d_v = -d_err;  d_pre = (W2^T d_err + inj1) act'(pre);  d_k = W1^T d_pre + inj0
 //                  dM <- (1-alpha) dM + {d_pre k^T, d_pre, d_err h^T + e adj^T, d_err};  dS <- eta dS
 // The activation's second derivative does not appear, as in the reference.
-template <int ACT, int EPT>
+// Row products need their matrix in (padded) shared memory: {W1', b1'}, {W1, b1} and {W2, b2} pass
+// through one staging buffer in turn; column sums read global memory directly (coalesced).
+template <int ACT, int EPT, int SD, int SDH>
 __global__ void __launch_bounds__(NT, 1) mlp_bwd_kernel(BwdArgs a)
 {
     extern __shared__ __align__(16) float sm[];
     const Dims& D = a.D;
-    const int d = D.d, dh = D.dh, ss = D.ss, tid = threadIdx.x, b = blockIdx.x;
-    float* dS = sm;
-    float* kb = dS + ((ss + 3) & ~3);     // kb | vb | qb | dyb adjacent
-    float* vb = kb + d;
-    float* qb = vb + d;
-    float* dyb = qb + d;
-    float* pre = dyb + d;                 // act'(pre) after the recompute
-    float* h = pre + dh;
-    float* gp = h + dh;
-    float* hq = gp + dh;
-    float* dpq = hq + dh;                 // act'(pq), then dpq
-    float* adj = dpq + dh;
-    float* inj1 = adj + dh;
-    float* dpre = inj1 + dh;
-    float* e = dpre + dh;
-    float* derr = e + d;
-    float* inj0 = derr + d;
-    float* scr = inj0 + d;
+    const int d = SD ? SD : D.d, dh = SD ? SDH : D.dh, ss = SD ? 2 * SD * SDH + SD + SDH : D.ss;
+    const int tid = threadIdx.x, b = blockIdx.x, ptid = P(tid);
+    __builtin_assume(tid >= 0 && tid < NT);
+    const int pd = padded(d), ph = padded(dh);
+    float* dS = sm;                                   // padded packed state
+    float* stg = dS + padded(ss);                     // staging: {W1, b1} or {W2, b2} of one state
+    float* kb = stg + padded(D.o2 > ss - D.o2 ? D.o2 : ss - D.o2);
+    float* vb = kb + pd;
+    float* qb = vb + pd;
+    float* dyb = qb + pd;
+    float* e = dyb + pd;
+    float* derr = e + pd;
+    float* inj0 = derr + pd;
+    float* pre = inj0 + pd;               // act'(pre)
+    float* h = pre + ph;
+    float* gp = h + ph;
+    float* hq = gp + ph;
+    float* dpq = hq + ph;                 // act'(pq), then dpq
+    float* adj = dpq + ph;
+    float* inj1 = adj + ph;
+    float* dpre = inj1 + ph;
+    float* scr = dpre + ph;
     float* red = scr + NT;
 
     const float* k = a.k + (size_t)b * a.in_stride;
@@ -318,73 +390,120 @@ __global__ void __launch_bounds__(NT, 1) mlp_bwd_kernel(BwdArgs a)
     const float* st = a.s_states + (size_t)b * a.m_stride;
     const int gh_ = fd_div(tid, D.div_h), jh = tid - gh_ * dh, Gh = NT / dh;   // column split, C = dh
     const int gd_ = fd_div(tid, D.div_d), jd = tid - gd_ * d, Gd = NT / d;     // column split, C = d
+    const int w2sz = d * dh;
 
     float dM[EPT];
 #pragma unroll
     for (int i = 0; i < EPT; i++) {
         dM[i] = 0.0f;
         const int idx = tid + i * NT;
-        if (idx < ss) dS[idx] = 0.0f;
+        if (idx < ss) dS[ptid + i * PNT] = 0.0f;
     }
     for (int t = a.seq_len - 1; t >= 0; t--) {
         const float* Mt = mt + (size_t)t * ss;
         const float* Mn = Mt + ss;
         const float* St = st + (size_t)t * ss;
+        if (t > 0) {      // the states token t - 1 reads first (M_{t-1}, S_{t-1}) on their way into L2
+            for (int f = tid * 32; f < ss; f += NT * 32) {
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(Mt - ss + f));
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(St - ss + f));
+            }
+        }
         for (int i = tid; i < 4 * d; i += NT) {
             const int w = fd_div(i, D.div_d), c = i - w * d;
-            kb[i] = (w == 0 ? k : w == 1 ? v : w == 2 ? q : dy)[(size_t)t * d + c];
+            (w == 0 ? kb : w == 1 ? vb : w == 2 ? qb : dyb)[P(c)] = (w == 0 ? k : w == 1 ? v : w == 2 ? q : dy)[(size_t)t * d + c];
         }
         const float al = a.alpha[g0 + t], th = a.theta[g0 + t], et = a.eta[g0 + t];
+        // 1: readout through M_{t+1}
+        stage(stg, Mn, D.o2);
         __syncthreads();
-        // 1: readout through M_{t+1}; 3: the inner gradient's vectors through M_t
-        rowdot<8>(Mn, dh, d, qb, [&](int r, float s) { const float p = s + Mn[D.o1 + r]; hq[r] = act_fn<ACT>(p); dpq[r] = act_prime<ACT>(p); });
-        rowdot<8>(Mt, dh, d, kb, [&](int r, float s) { const float p = s + Mt[D.o1 + r]; h[r] = act_fn<ACT>(p); pre[r] = act_prime<ACT>(p); });
+        rowdot(stg, 0, dh, d, D.tps_d, qb, [&](int r, float s) { const float p = s + stg[P(D.o1 + r)]; hq[P(r)] = act_fn<ACT>(p); dpq[P(r)] = act_prime<ACT>(p); });
+        colsum<false>(Mn, D.o2, d, dh, dyb, scr, gh_, jh, Gh, [&](int j, float s) { dpq[P(j)] *= s; });
+        colsum<true>(stg, 0, dh, d, dpq, scr, gd_, jd, Gd, [&](int j, float s) { d_q[(size_t)t * d + j] = s; });
+        // 3: the inner gradient's vectors through M_t
+        stage(stg, Mt, D.o2);
         __syncthreads();
-        rowdot<4>(Mt + D.o2, d, dh, h, [&](int r, float s) { e[r] = s + Mt[D.o3 + r] - vb[r]; });
-        colsum(Mn + D.o2, d, dh, dyb, scr, gh_, jh, Gh, [&](int j, float s) { dpq[j] *= s; });
-        colsum(Mt + D.o2, d, dh, e, scr, gh_, jh, Gh, [&](int j, float s) { gp[j] = s * pre[j]; });
-        colsum(Mn, dh, d, dpq, scr, gd_, jd, Gd, [&](int j, float s) { d_q[(size_t)t * d + j] = s; });
+        rowdot(stg, 0, dh, d, D.tps_d, kb, [&](int r, float s) { const float p = s + stg[P(D.o1 + r)]; h[P(r)] = act_fn<ACT>(p); pre[P(r)] = act_prime<ACT>(p); });
+        __syncthreads();
+        stage(stg, Mt + D.o2, ss - D.o2);
+        __syncthreads();
+        rowdot(stg, 0, d, dh, D.tps_h, h, [&](int r, float s) { e[P(r)] = s + stg[P(w2sz + r)] - vb[P(r)]; });
+        __syncthreads();
+        colsum<true>(stg, 0, d, dh, e, scr, gh_, jh, Gh, [&](int j, float s) { gp[P(j)] = s * pre[P(j)]; });
         // dM += readout terms; dS += dM; the three gate gradients
         float acc[3] = {0.0f, 0.0f, 0.0f};
+        const int c1 = tid % (SD ? SD : 1), c2 = tid % (SDH ? SDH : 1);
+        {
+            const float q1c = SD ? qb[P(c1)] : 0.0f, hq2c = SD ? hq[P(c2)] : 0.0f;
+            const float k1c = SD ? kb[P(c1)] : 0.0f, h2c = SD ? h[P(c2)] : 0.0f;
 #pragma unroll
-        for (int i = 0; i < EPT; i++) {
-            const int idx = tid + i * NT;
-            if (idx < ss) {
-                const float dm = dM[i] + outer_term(D, idx, dpq, qb, dyb, hq);
-                const float ds = dS[idx] + dm;
-                dM[i] = dm; dS[idx] = ds;
-                acc[0] = fmaf(Mt[idx], dm, acc[0]);
-                acc[1] = fmaf(St[idx], ds, acc[1]);
-                acc[2] = fmaf(outer_term(D, idx, gp, kb, e, h), ds, acc[2]);
+            for (int i0 = 0; i0 < EPT; i0 += UB) {
+                float mv[UB], sv[UB], ro[UB], gr[UB], ds0[UB];
+#pragma unroll
+                for (int u = 0; u < UB; u++) {
+                    const int i = i0 + u, idx = tid + i * NT;
+                    if (i < EPT && idx < ss) {
+                        mv[u] = Mt[idx]; sv[u] = St[idx];
+                        ro[u] = outer_term<SD, SDH>(D, idx, dpq, qb, q1c, dyb, hq, hq2c);
+                        gr[u] = outer_term<SD, SDH>(D, idx, gp, kb, k1c, e, h, h2c);
+                        ds0[u] = dS[ptid + i * PNT];
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < UB; u++) {
+                    const int i = i0 + u, idx = tid + i * NT;
+                    if (i < EPT && idx < ss) {
+                        const float dm = dM[i] + ro[u];
+                        const float ds = ds0[u] + dm;
+                        dM[i] = dm; dS[ptid + i * PNT] = ds;
+                        acc[0] = fmaf(mv[u], dm, acc[0]);
+                        acc[1] = fmaf(sv[u], ds, acc[1]);
+                        acc[2] = fmaf(gr[u], ds, acc[2]);
+                    }
+                }
             }
         }
         block_sum<3>(acc, red);          // its barriers also publish dS
         if (tid == 0) { a.d_alpha[g0 + t] = -acc[0]; a.d_eta[g0 + t] = acc[1]; a.d_theta[g0 + t] = -acc[2]; }
         // 5: products with G = -theta dS
-        const float* dS_W1 = dS; const float* dS_b1 = dS + D.o1; const float* dS_W2 = dS + D.o2; const float* dS_b2 = dS + D.o3;
-        rowdot<2>(dS_W1, dh, d, kb, [&](int r, float s) { adj[r] = -th * (s + dS_b1[r]) * pre[r]; });
-        rowdot<2>(dS_W2, d, dh, h, [&](int r, float s) { derr[r] = -th * (s + dS_b2[r]); });
-        colsum(dS_W2, d, dh, e, scr, gh_, jh, Gh, [&](int j, float s) { inj1[j] = -th * s; });
+        rowdot(dS, 0, dh, d, D.tps_d, kb, [&](int r, float s) { adj[P(r)] = -th * (s + dS[P(D.o1 + r)]) * pre[P(r)]; });
+        rowdot(dS, D.o2, d, dh, D.tps_h, h, [&](int r, float s) { derr[P(r)] = -th * (s + dS[P(D.o3 + r)]); });
+        colsum<true>(dS, D.o2, d, dh, e, scr, gh_, jh, Gh, [&](int j, float s) { inj1[P(j)] = -th * s; });
         // (the barriers of colsum published adj and derr)
-        rowdot<4>(Mt + D.o2, d, dh, adj, [&](int r, float s) { derr[r] += s; });
+        rowdot(stg, 0, d, dh, D.tps_h, adj, [&](int r, float s) { derr[P(r)] += s; });
         __syncthreads();
-        if (tid < d) d_v[(size_t)t * d + tid] = -derr[tid];
-        colsum(Mt + D.o2, d, dh, derr, scr, gh_, jh, Gh, [&](int j, float s) { dpre[j] = (s + inj1[j]) * pre[j]; });
-        colsum(dS_W1, dh, d, gp, scr, gd_, jd, Gd, [&](int j, float s) { inj0[j] = -th * s; });
-        colsum(Mt, dh, d, dpre, scr, gd_, jd, Gd, [&](int j, float s) { d_k[(size_t)t * d + j] = s + inj0[j]; });
+        if (tid < d) d_v[(size_t)t * d + tid] = -derr[P(tid)];
+        colsum<true>(stg, 0, d, dh, derr, scr, gh_, jh, Gh, [&](int j, float s) { dpre[P(j)] = (s + inj1[P(j)]) * pre[P(j)]; });
+        colsum<true>(dS, 0, dh, d, gp, scr, gd_, jd, Gd, [&](int j, float s) { inj0[P(j)] = -th * s; });
+        colsum<false>(Mt, 0, dh, d, dpre, scr, gd_, jd, Gd, [&](int j, float s) { d_k[(size_t)t * d + j] = s + inj0[P(j)]; });
         // 6: carry to token t - 1
         const float keep = 1.0f - al;
+        {
+            const float k1c = SD ? kb[P(c1)] : 0.0f, h2c = SD ? h[P(c2)] : 0.0f, adj2c = SD ? adj[P(c2)] : 0.0f;
+            const int o2 = SD ? SDH * SD + SDH : D.o2, o3 = o2 + d * dh;
 #pragma unroll
-        for (int i = 0; i < EPT; i++) {
-            const int idx = tid + i * NT;
-            if (idx < ss) {
-                float add = outer_term(D, idx, dpre, kb, derr, h);
-                if (idx >= D.o2 && idx < D.o3) {          // cross term e adj^T of W2
-                    const int el = idx - D.o2, r = fd_div(el, D.div_h);
-                    add = fmaf(e[r], adj[el - r * dh], add);
+            for (int i0 = 0; i0 < EPT; i0 += UB) {
+                float add[UB], ds0[UB];
+#pragma unroll
+                for (int u = 0; u < UB; u++) {
+                    const int i = i0 + u, idx = tid + i * NT;
+                    if (i < EPT && idx < ss) {
+                        add[u] = outer_term<SD, SDH>(D, idx, dpre, kb, k1c, derr, h, h2c);
+                        if (idx >= o2 && idx < o3) {          // cross term e adj^T of W2
+                            const int el = idx - o2, r = SD ? el / (SDH ? SDH : 1) : fd_div(el, D.div_h);
+                            add[u] = fmaf(e[P(r)], SD ? adj2c : adj[P(el - r * dh)], add[u]);
+                        }
+                        ds0[u] = dS[ptid + i * PNT];
+                    }
                 }
-                dM[i] = fmaf(keep, dM[i], add);
-                dS[idx] *= et;
+#pragma unroll
+                for (int u = 0; u < UB; u++) {
+                    const int i = i0 + u, idx = tid + i * NT;
+                    if (i < EPT && idx < ss) {
+                        dM[i] = fmaf(keep, dM[i], add[u]);
+                        dS[ptid + i * PNT] = ds0[u] * et;
+                    }
+                }
             }
         }
         __syncthreads();
@@ -395,7 +514,7 @@ __global__ void __launch_bounds__(NT, 1) mlp_bwd_kernel(BwdArgs a)
         const int idx = tid + i * NT;
         if (idx < ss) {
             atomicAdd(a.d_m_init + idx, dM[i]);
-            atomicAdd(a.d_s_init + idx, dS[idx]);
+            atomicAdd(a.d_s_init + idx, dS[ptid + i * PNT]);
         }
     }
 }
@@ -406,7 +525,8 @@ static const char* unsupported(int d, int dh)
 {
     if (d <= 0 || dh <= 0) return "d and d_hidden must be > 0";
     if (d > NT || dh > NT) return "d and d_hidden above 512 are not supported by the on-chip kernels";
-    if ((long long)dh * d * 2 + dh + d > (long long)EPT_LARGE * NT)
+    if ((long long)dh * d * 2 + dh + d > (long long)EPT_LARGE * NT ||
+        bwd_smem_floats(make_dims(d, dh)) * sizeof(float) > 227 * 1024)
         return "packed MLP state above 33280 floats (d = 64, d_hidden = 256) does not fit on one SM";
     return nullptr;
 }
@@ -415,12 +535,15 @@ template <int ACT>
 static bool launch_fwd(const FwdArgs& a, int batch, cudaStream_t st)
 {
     const size_t smem = fwd_smem_floats(a.D) * sizeof(float);
-    if (a.D.ss <= EPT_SMALL * NT) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(mlp_fwd_kernel<ACT, EPT_SMALL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        mlp_fwd_kernel<ACT, EPT_SMALL><<<batch, NT, smem, st>>>(a);
+    if (a.D.d == 64 && a.D.dh == 256) {      // the reference's head size and expansion: static sizes
+        cudaFuncSetAttribute(mlp_fwd_kernel<ACT, EPT_LARGE, 64, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        mlp_fwd_kernel<ACT, EPT_LARGE, 64, 256><<<batch, NT, smem, st>>>(a);
+    } else if (a.D.ss <= EPT_SMALL * NT) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(mlp_fwd_kernel<ACT, EPT_SMALL, 0, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        mlp_fwd_kernel<ACT, EPT_SMALL, 0, 0><<<batch, NT, smem, st>>>(a);
     } else {
-        cudaFuncSetAttribute(mlp_fwd_kernel<ACT, EPT_LARGE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        mlp_fwd_kernel<ACT, EPT_LARGE><<<batch, NT, smem, st>>>(a);
+        cudaFuncSetAttribute(mlp_fwd_kernel<ACT, EPT_LARGE, 0, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        mlp_fwd_kernel<ACT, EPT_LARGE, 0, 0><<<batch, NT, smem, st>>>(a);
     }
     return check_launch("mlp_fwd_kernel");
 }
@@ -429,12 +552,15 @@ template <int ACT>
 static bool launch_bwd(const BwdArgs& a, int batch, cudaStream_t st)
 {
     const size_t smem = bwd_smem_floats(a.D) * sizeof(float);
-    if (a.D.ss <= EPT_SMALL * NT) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(mlp_bwd_kernel<ACT, EPT_SMALL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        mlp_bwd_kernel<ACT, EPT_SMALL><<<batch, NT, smem, st>>>(a);
+    if (a.D.d == 64 && a.D.dh == 256) {
+        cudaFuncSetAttribute(mlp_bwd_kernel<ACT, EPT_LARGE, 64, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        mlp_bwd_kernel<ACT, EPT_LARGE, 64, 256><<<batch, NT, smem, st>>>(a);
+    } else if (a.D.ss <= EPT_SMALL * NT) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(mlp_bwd_kernel<ACT, EPT_SMALL, 0, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        mlp_bwd_kernel<ACT, EPT_SMALL, 0, 0><<<batch, NT, smem, st>>>(a);
     } else {
-        cudaFuncSetAttribute(mlp_bwd_kernel<ACT, EPT_LARGE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        mlp_bwd_kernel<ACT, EPT_LARGE><<<batch, NT, smem, st>>>(a);
+        cudaFuncSetAttribute(mlp_bwd_kernel<ACT, EPT_LARGE, 0, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        mlp_bwd_kernel<ACT, EPT_LARGE, 0, 0><<<batch, NT, smem, st>>>(a);
     }
     return check_launch("mlp_bwd_kernel");
 }

@@ -172,3 +172,13 @@ def make_problem(n, s, d, d_hidden, seed, dtype=np.float32, state_scale=0.1):
              m0=rng.standard_normal((n, state_size(d, d_hidden))) * state_scale,
              s0=np.zeros((n, state_size(d, d_hidden))))
     return {key: np.ascontiguousarray(val, dtype=dtype) for key, val in p.items()}
+
+
+def timed_fwd_bwd(args):
+    """One seeded problem forward + backward (worker of bench.py's CPU arm); returns its tokens."""
+    seed, s, d, d_hidden, activation = args
+    p = make_problem(1, s, d, d_hidden, seed)
+    ms, sts, _ = forward(p["k"], p["v"], p["q"], p["alpha"], p["theta"], p["eta"], p["m0"], p["s0"], d_hidden,
+                         activation)
+    backward(p["k"], p["v"], p["q"], p["alpha"], p["theta"], p["eta"], ms, sts, p["dy"], d_hidden, activation)
+    return s
