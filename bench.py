@@ -714,7 +714,7 @@ def make_workload(name, world=1, small=False, local_batch=0):
     """small: reduced problem counts of the same kernels, sized for profiler captures (inputs still
     larger than L2, a few hundred MB on the device)."""
     if small:
-        TitansPair.B, SwaPair.B, TitansLevel0.B, TitansLevel1.B, TitansMlpPair.B = 4, 1, 37, 64, 2
+        TitansPair.B, SwaPair.B, TitansLevel0.B, TitansLevel1.B, TitansMlpPair.B = 4, 1, 37, 64, 1
     if name == "titans_chunkwise":
         return TitansPair(64)
     if name == "titans_exact":

@@ -519,6 +519,401 @@ __global__ void __launch_bounds__(NT, 1) mlp_bwd_kernel(BwdArgs a)
     }
 }
 
+// ───────────────────── static head size: d = 64, d_hidden = 256 ─────────────────────
+// The reference's head size with its default expansion factor 4. Everything is float4: the packed
+// state is 8272 float4 (17 per thread), region borders fall on float4 borders, and for the float4
+// q = tid + 512 i of one thread the columns are fixed (W1: 4 (tid % 16), W2: 4 (tid % 64)), so the
+// vector operand of every outer product sits in four registers for a whole pass and only the row
+// scalar is read per element. Shared memory is unpadded; row products read 16-byte chunks in an
+// order rotated by the lane, which spreads a quarter-warp over all eight 16-byte bank groups.
+namespace s64 {
+constexpr int D = 64, DH = 256, O1 = DH * D, O2 = O1 + DH, O3 = O2 + D * DH, SS = O3 + D;
+constexpr int NV = SS / 4, V = (NV + NT - 1) / NT;                 // 8272 float4, 17 per thread
+constexpr int SCR = 2048;
+#ifndef NLH_MLP_PB
+#define NLH_MLP_PB 2
+#endif
+constexpr int PB = NLH_MLP_PB;      // float4 per thread whose loads are issued together in the backward's first pass
+
+__device__ __forceinline__ float4 f4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 mul4(float s, float4 a) { return make_float4(s * a.x, s * a.y, s * a.z, s * a.w); }
+__device__ __forceinline__ float4 fma4(float s, float4 a, float4 b) { return make_float4(fmaf(s, a.x, b.x), fmaf(s, a.y, b.y), fmaf(s, a.z, b.z), fmaf(s, a.w, b.w)); }
+__device__ __forceinline__ float4 add4(float4 a, float4 b) { return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); }
+__device__ __forceinline__ float dot4(float4 a, float4 b, float acc) { return fmaf(a.x, b.x, fmaf(a.y, b.y, fmaf(a.z, b.z, fmaf(a.w, b.w, acc)))); }
+__device__ __forceinline__ bool live(int i, int tid) { return i < V - 1 || tid < NV - (V - 1) * NT; }
+
+// Outer-product term of float4 number tid + NT * i of the packed state (i is a compile-time
+// constant after unrolling): W1 -> a1[row] x1v, b1 -> a1, W2 -> a2[row] x2v, b2 -> a2.
+__device__ __forceinline__ float4 term4(int i, int tid, const float* a1, float4 x1v, const float* a2, float4 x2v)
+{
+    if (i < 8) return mul4(a1[(tid >> 4) + 32 * i], x1v);
+    if (i == 8 && tid < 64) return f4(a1 + 4 * tid);
+    if (i == V - 1 && tid >= 64) return f4(a2 + 4 * (tid - 64));
+    return mul4(a2[((tid - 64) >> 6) + 8 * (i - 8)], x2v);
+}
+__device__ __forceinline__ bool in_w2(int i, int tid) { return (i == 8 && tid >= 64) || (i > 8 && i < V - 1) || (i == V - 1 && tid < 64); }
+
+// out(r) = sum_c W[r, c] x[c]; W [R, C] in shared memory, 2^tps threads per row (C = 32 << tps,
+// R << tps = NT). epi(r, sum) on the first thread of each row.
+template <class Epi>
+__device__ __forceinline__ void rowdot(const float* W, int C, int tps, const float* x, Epi epi)
+{
+    const int tid = threadIdx.x, r = tid >> tps, p = tid & ((1 << tps) - 1), lane = tid & 31;
+    const float* w = W + r * C + 32 * p;
+    const float* xs = x + 32 * p;
+    float a0 = 0.0f, a1 = 0.0f;
+#pragma unroll
+    for (int jj = 0; jj < 8; jj += 2) {
+        const int c0 = 4 * ((jj + lane) & 7), c1 = 4 * ((jj + 1 + lane) & 7);
+        a0 = dot4(f4(w + c0), f4(xs + c0), a0);
+        a1 = dot4(f4(w + c1), f4(xs + c1), a1);
+    }
+    float acc = a0 + a1;
+    for (int o = (1 << tps) >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (p == 0) epi(r, acc);
+}
+
+// Two products with the same matrix in one pass over it: s0 = W x0, s1 = W x1.
+template <class Epi>
+__device__ __forceinline__ void rowdot2(const float* W, int C, int tps, const float* x0, const float* x1, Epi epi)
+{
+    const int tid = threadIdx.x, r = tid >> tps, p = tid & ((1 << tps) - 1), lane = tid & 31;
+    const float* w = W + r * C + 32 * p;
+    const float* xa = x0 + 32 * p;
+    const float* xb = x1 + 32 * p;
+    float a0 = 0.0f, a1 = 0.0f, b0 = 0.0f, b1 = 0.0f;
+#pragma unroll
+    for (int jj = 0; jj < 8; jj += 2) {
+        const int c0 = 4 * ((jj + lane) & 7), c1 = 4 * ((jj + 1 + lane) & 7);
+        const float4 w0 = f4(w + c0), w1 = f4(w + c1);
+        a0 = dot4(w0, f4(xa + c0), a0); b0 = dot4(w0, f4(xb + c0), b0);
+        a1 = dot4(w1, f4(xa + c1), a1); b1 = dot4(w1, f4(xb + c1), b1);
+    }
+    float sa = a0 + a1, sb = b0 + b1;
+    for (int o = (1 << tps) >> 1; o > 0; o >>= 1) {
+        sa += __shfl_xor_sync(0xffffffffu, sa, o);
+        sb += __shfl_xor_sync(0xffffffffu, sb, o);
+    }
+    if (p == 0) epi(r, sa, sb);
+}
+
+// out(j) = sum_i W[i, j] x[i]; W [R, C] in shared or global memory (16-byte aligned rows), x in
+// shared memory. Thread (g, cg): 8 consecutive rows, 4 consecutive columns; the NT / (C / 4) partial
+// float4 sums meet in scr[SCR]; epi(j, sum) on threads j < C. Two block barriers inside.
+template <class Epi>
+__device__ __forceinline__ void colsum(const float* __restrict__ W, int C, int lgcg, const float* x, float* scr, Epi epi)
+{
+    const int tid = threadIdx.x, cg = tid & ((1 << lgcg) - 1), g = tid >> lgcg;
+    const float* w = W + (size_t)(8 * g) * C + 4 * cg;
+    const float4 xa = f4(x + 8 * g), xb = f4(x + 8 * g + 4);
+    float4 wv[4];
+#pragma unroll
+    for (int u = 0; u < 4; u++) wv[u] = f4(w + (size_t)u * C);
+    float4 acc = mul4(xa.x, wv[0]);
+    acc = fma4(xa.y, wv[1], acc); acc = fma4(xa.z, wv[2], acc); acc = fma4(xa.w, wv[3], acc);
+#pragma unroll
+    for (int u = 0; u < 4; u++) wv[u] = f4(w + (size_t)(u + 4) * C);
+    acc = fma4(xb.x, wv[0], acc); acc = fma4(xb.y, wv[1], acc); acc = fma4(xb.z, wv[2], acc); acc = fma4(xb.w, wv[3], acc);
+    *reinterpret_cast<float4*>(scr + g * C + 4 * cg) = acc;
+    __syncthreads();
+    if (tid < C) {
+        const int G = NT >> lgcg;
+        float s0 = 0.0f, s1 = 0.0f;
+        for (int gg = 0; gg < G; gg += 2) { s0 += scr[gg * C + tid]; s1 += scr[(gg + 1) * C + tid]; }
+        epi(tid, s0 + s1);
+    }
+    __syncthreads();
+}
+
+// nv float4 of global memory into shared memory
+__device__ __forceinline__ void stage(float* dst, const float* __restrict__ src, int nv)
+{
+    const int tid = threadIdx.x;
+#pragma unroll
+    for (int u0 = 0; u0 < 9; u0 += 3) {
+        float4 v[3];
+#pragma unroll
+        for (int u = 0; u < 3; u++) if (tid + (u0 + u) * NT < nv) v[u] = f4(src + 4 * (tid + (u0 + u) * NT));
+#pragma unroll
+        for (int u = 0; u < 3; u++) if (tid + (u0 + u) * NT < nv) *reinterpret_cast<float4*>(dst + 4 * (tid + (u0 + u) * NT)) = v[u];
+    }
+}
+
+inline size_t fwd_smem_floats() { return (size_t)SS + 7 * D + 4 * DH + SCR + 4 * NW; }
+inline size_t bwd_smem_floats() { return (size_t)SS + O2 + 7 * D + 8 * DH + SCR + 4 * NW; }
+
+// Token loop, rotated: M_{t+1} serves the readout of token t AND the prediction of token t + 1, so
+// both row products with W1' (on q_t and k_{t+1}) share one pass over the matrix, and both with W2'
+// (on act(W1' q_t + b1') and h_{t+1}) the next. A token is then four phases: column sum, update,
+// two double row products. k, v, q of token t + 1 are fetched at the top of token t.
+template <int ACT>
+__global__ void __launch_bounds__(NT, 1) mlp_fwd64_kernel(FwdArgs a)
+{
+    extern __shared__ __align__(16) float sm[];
+    const int tid = threadIdx.x, b = blockIdx.x;
+    float* Msm = sm;
+    float* kvq = Msm + SS;                // two buffers of k | v | q (token parity)
+    float* e = kvq + 6 * D;
+    float* pre = e + D;
+    float* h = pre + DH;
+    float* gp = h + DH;
+    float* hq = gp + DH;
+    float* scr = hq + DH;
+    float* red = scr + SCR;
+    const float* k = a.k + (size_t)b * a.in_stride;
+    const float* v = a.v + (size_t)b * a.in_stride;
+    const float* q = a.q + (size_t)b * a.in_stride;
+    float* y = a.y + (size_t)b * a.in_stride;
+    const float* alpha = a.alpha + (size_t)b * a.seq_len;
+    const float* theta = a.theta + (size_t)b * a.seq_len;
+    const float* eta = a.eta + (size_t)b * a.seq_len;
+    float* mt = a.m_states + (size_t)b * a.m_stride;
+    float* st = a.s_states + (size_t)b * a.m_stride;
+    const bool clamp = m_norm_enabled(a.m_norm_max);
+    float4* M4 = reinterpret_cast<float4*>(Msm);
+    const float* src = tid < D ? k : tid < 2 * D ? v : q;     // stream this thread stages (tid < 3 D)
+
+    float4 S4[V];
+#pragma unroll
+    for (int i = 0; i < V; i++) {
+        S4[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (live(i, tid)) {
+            const int qi = tid + i * NT;
+            const float4 m = f4(a.m_init + (size_t)b * SS + 4 * qi);
+            S4[i] = f4(a.s_init + (size_t)b * SS + 4 * qi);
+            M4[qi] = m;
+            reinterpret_cast<float4*>(mt)[qi] = m;
+            reinterpret_cast<float4*>(st)[qi] = S4[i];
+        }
+    }
+    if (a.seq_len == 0) return;
+    if (tid < 3 * D) kvq[tid] = src[tid & (D - 1)];
+    __syncthreads();
+    rowdot(Msm, D, 1, kvq, [&](int r, float s) { const float p = s + Msm[O1 + r]; pre[r] = p; h[r] = act_fn<ACT>(p); });
+    __syncthreads();
+    rowdot(Msm + O2, DH, 3, h, [&](int r, float s) { e[r] = s + Msm[O3 + r] - kvq[D + r]; });
+    __syncthreads();
+    for (int t = 0; t < a.seq_len; t++) {
+        float* cur = kvq + (t & 1) * 3 * D;
+        float* nxt = kvq + ((t + 1) & 1) * 3 * D;
+        const bool has_next = t + 1 < a.seq_len;
+        float staged = 0.0f;
+        if (has_next && tid < 3 * D) staged = src[(size_t)(t + 1) * D + (tid & (D - 1))];
+        const float al = alpha[t], th = theta[t], et = eta[t];
+        colsum(Msm + O2, DH, 6, e, scr, [&](int j, float s) { gp[j] = s * act_prime<ACT>(pre[j]); });
+        float4* mn = reinterpret_cast<float4*>(mt + (size_t)(t + 1) * SS);
+        float4* sn = reinterpret_cast<float4*>(st + (size_t)(t + 1) * SS);
+        float sq[1] = {0.0f};
+        const float keep = 1.0f - al;
+        const float4 x1v = f4(cur + 4 * (tid & 15)), x2v = f4(h + 4 * (tid & 63));
+#pragma unroll
+        for (int i0 = 0; i0 < V; i0 += 4) {
+            float4 g[4], mo[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int i = i0 + u;
+                if (i < V && live(i, tid)) { g[u] = term4(i, tid, gp, x1v, e, x2v); mo[u] = M4[tid + i * NT]; }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int i = i0 + u;
+                if (i < V && live(i, tid)) {
+                    const float4 s_new = fma4(-th, g[u], mul4(et, S4[i]));
+                    const float4 m_new = fma4(keep, mo[u], s_new);
+                    S4[i] = s_new; M4[tid + i * NT] = m_new;
+                    sn[tid + i * NT] = s_new;
+                    if (!clamp) mn[tid + i * NT] = m_new;
+                    sq[0] = dot4(m_new, m_new, sq[0]);
+                }
+            }
+        }
+        if (clamp) {      // Frobenius projection over the whole packed state (titans_lmm.rs:812-821)
+            block_sum<1>(sq, red);
+            const float norm = sqrtf(sq[0]);
+            const float scale = norm > a.m_norm_max ? a.m_norm_max / norm : 1.0f;
+#pragma unroll
+            for (int i = 0; i < V; i++)
+                if (live(i, tid)) { const float4 m = mul4(scale, M4[tid + i * NT]); M4[tid + i * NT] = m; mn[tid + i * NT] = m; }
+        }
+        if (tid < 3 * D) nxt[tid] = staged;
+        __syncthreads();
+        // W1': readout hidden of q_t, prediction hidden of k_{t+1}
+        rowdot2(Msm, D, 1, cur + 2 * D, nxt, [&](int r, float sq_, float sk) {
+            const float b1 = Msm[O1 + r];
+            hq[r] = act_fn<ACT>(sq_ + b1);
+            if (has_next) { const float p = sk + b1; pre[r] = p; h[r] = act_fn<ACT>(p); }
+        });
+        __syncthreads();
+        // W2': y_t and the error of token t + 1
+        rowdot2(Msm + O2, DH, 3, hq, h, [&](int r, float sy, float se) {
+            const float b2 = Msm[O3 + r];
+            y[(size_t)t * D + r] = sy + b2;
+            if (has_next) e[r] = se + b2 - nxt[D + r];
+        });
+        __syncthreads();
+    }
+}
+
+template <int ACT>
+__global__ void __launch_bounds__(NT, 1) mlp_bwd64_kernel(BwdArgs a)
+{
+    extern __shared__ __align__(16) float sm[];
+    const int tid = threadIdx.x, b = blockIdx.x;
+    float* dS = sm;
+    float* stg = dS + SS;                 // {W1, b1} (O2 floats) or {W2, b2} of one state
+    float* kb = stg + O2;                 // kb | vb | qb | dyb adjacent
+    float* vb = kb + D;
+    float* qb = vb + D;
+    float* dyb = qb + D;
+    float* e = dyb + D;
+    float* derr = e + D;
+    float* inj0 = derr + D;
+    float* pre = inj0 + D;                // act'(pre)
+    float* h = pre + DH;
+    float* gp = h + DH;
+    float* hq = gp + DH;
+    float* dpq = hq + DH;
+    float* adj = dpq + DH;
+    float* inj1 = adj + DH;
+    float* dpre = inj1 + DH;
+    float* scr = dpre + DH;
+    float* red = scr + SCR;
+    const float* k = a.k + (size_t)b * a.in_stride;
+    const float* v = a.v + (size_t)b * a.in_stride;
+    const float* q = a.q + (size_t)b * a.in_stride;
+    const float* dy = a.d_y + (size_t)b * a.in_stride;
+    float* d_k = a.d_k + (size_t)b * a.in_stride;
+    float* d_v = a.d_v + (size_t)b * a.in_stride;
+    float* d_q = a.d_q + (size_t)b * a.in_stride;
+    const size_t g0 = (size_t)b * a.seq_len;
+    const float* mt = a.m_states + (size_t)b * a.m_stride;
+    const float* st = a.s_states + (size_t)b * a.m_stride;
+    float4* dS4 = reinterpret_cast<float4*>(dS);
+
+    float4 dM4[V];
+#pragma unroll
+    for (int i = 0; i < V; i++) {
+        dM4[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (live(i, tid)) dS4[tid + i * NT] = dM4[i];
+    }
+    for (int t = a.seq_len - 1; t >= 0; t--) {
+        const float* Mt = mt + (size_t)t * SS;
+        const float* Mn = Mt + SS;
+        const float* St = st + (size_t)t * SS;
+        if (t > 0) {      // the states token t - 1 reads first (M_{t-1}, S_{t-1}) on their way into L2
+            for (int f = tid * 32; f < SS; f += NT * 32) {
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(Mt - SS + f));
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(St - SS + f));
+            }
+        }
+        if (tid < 4 * D) kb[tid] = (tid < D ? k : tid < 2 * D ? v : tid < 3 * D ? q : dy)[(size_t)t * D + (tid & (D - 1))];
+        const float al = a.alpha[g0 + t], th = a.theta[g0 + t], et = a.eta[g0 + t];
+        // 1: readout through M_{t+1}
+        stage(stg, Mn, O2 / 4);
+        __syncthreads();
+        rowdot(stg, D, 1, qb, [&](int r, float s) { const float p = s + stg[O1 + r]; hq[r] = act_fn<ACT>(p); dpq[r] = act_prime<ACT>(p); });
+        colsum(Mn + O2, DH, 6, dyb, scr, [&](int j, float s) { dpq[j] *= s; });
+        colsum(stg, D, 4, dpq, scr, [&](int j, float s) { d_q[(size_t)t * D + j] = s; });
+        // 3: the inner gradient's vectors through M_t
+        stage(stg, Mt, O2 / 4);
+        __syncthreads();
+        rowdot(stg, D, 1, kb, [&](int r, float s) { const float p = s + stg[O1 + r]; h[r] = act_fn<ACT>(p); pre[r] = act_prime<ACT>(p); });
+        __syncthreads();
+        stage(stg, Mt + O2, (SS - O2) / 4);
+        __syncthreads();
+        rowdot(stg, DH, 3, h, [&](int r, float s) { e[r] = s + stg[D * DH + r] - vb[r]; });
+        __syncthreads();
+        colsum(stg, DH, 6, e, scr, [&](int j, float s) { gp[j] = s * pre[j]; });
+        // dM += readout terms; dS += dM; the three gate gradients
+        float acc[3] = {0.0f, 0.0f, 0.0f};
+        {
+            const float4 q1v = f4(qb + 4 * (tid & 15)), hq2v = f4(hq + 4 * (tid & 63));
+            const float4 k1v = f4(kb + 4 * (tid & 15)), h2v = f4(h + 4 * (tid & 63));
+            const float4* Mt4 = reinterpret_cast<const float4*>(Mt);
+            const float4* St4 = reinterpret_cast<const float4*>(St);
+#pragma unroll
+            for (int i0 = 0; i0 < V; i0 += PB) {
+                float4 mv[PB], sv[PB], ro[PB], gr[PB], ds0[PB];
+#pragma unroll
+                for (int u = 0; u < PB; u++) {
+                    const int i = i0 + u;
+                    if (i < V && live(i, tid)) {
+                        mv[u] = Mt4[tid + i * NT]; sv[u] = St4[tid + i * NT];
+                        ro[u] = term4(i, tid, dpq, q1v, dyb, hq2v);
+                        gr[u] = term4(i, tid, gp, k1v, e, h2v);
+                        ds0[u] = dS4[tid + i * NT];
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < PB; u++) {
+                    const int i = i0 + u;
+                    if (i < V && live(i, tid)) {
+                        const float4 dm = add4(dM4[i], ro[u]);
+                        const float4 ds = add4(ds0[u], dm);
+                        dM4[i] = dm; dS4[tid + i * NT] = ds;
+                        acc[0] = dot4(mv[u], dm, acc[0]);
+                        acc[1] = dot4(sv[u], ds, acc[1]);
+                        acc[2] = dot4(gr[u], ds, acc[2]);
+                    }
+                }
+            }
+        }
+        block_sum<3>(acc, red);          // its barriers also publish dS
+        if (tid == 0) { a.d_alpha[g0 + t] = -acc[0]; a.d_eta[g0 + t] = acc[1]; a.d_theta[g0 + t] = -acc[2]; }
+        // 5: products with G = -theta dS
+        rowdot(dS, D, 1, kb, [&](int r, float s) { adj[r] = -th * (s + dS[O1 + r]) * pre[r]; });
+        rowdot(dS + O2, DH, 3, h, [&](int r, float s) { derr[r] = -th * (s + dS[O3 + r]); });
+        colsum(dS + O2, DH, 6, e, scr, [&](int j, float s) { inj1[j] = -th * s; });
+        rowdot(stg, DH, 3, adj, [&](int r, float s) { derr[r] += s; });
+        __syncthreads();
+        if (tid < D) d_v[(size_t)t * D + tid] = -derr[tid];
+        colsum(stg, DH, 6, derr, scr, [&](int j, float s) { dpre[j] = (s + inj1[j]) * pre[j]; });
+        colsum(dS, D, 4, gp, scr, [&](int j, float s) { inj0[j] = -th * s; });
+        colsum(Mt, D, 4, dpre, scr, [&](int j, float s) { d_k[(size_t)t * D + j] = s + inj0[j]; });
+        // 6: carry to token t - 1
+        const float keep = 1.0f - al;
+        {
+            const float4 k1v = f4(kb + 4 * (tid & 15)), h2v = f4(h + 4 * (tid & 63)), adjv = f4(adj + 4 * (tid & 63));
+#pragma unroll
+            for (int i0 = 0; i0 < V; i0 += 4) {
+                float4 add[4], ds0[4];
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const int i = i0 + u;
+                    if (i < V && live(i, tid)) {
+                        add[u] = term4(i, tid, dpre, k1v, derr, h2v);
+                        if (in_w2(i, tid)) add[u] = fma4(e[((tid - 64) >> 6) + 8 * (i - 8)], adjv, add[u]);   // cross term e adj^T
+                        ds0[u] = dS4[tid + i * NT];
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const int i = i0 + u;
+                    if (i < V && live(i, tid)) {
+                        dM4[i] = fma4(keep, dM4[i], add[u]);
+                        dS4[tid + i * NT] = mul4(et, ds0[u]);
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < V; i++) {
+        if (live(i, tid)) {
+            const int f = 4 * (tid + i * NT);
+            const float4 ds = dS4[tid + i * NT];
+            atomicAdd(a.d_m_init + f, dM4[i].x); atomicAdd(a.d_m_init + f + 1, dM4[i].y);
+            atomicAdd(a.d_m_init + f + 2, dM4[i].z); atomicAdd(a.d_m_init + f + 3, dM4[i].w);
+            atomicAdd(a.d_s_init + f, ds.x); atomicAdd(a.d_s_init + f + 1, ds.y);
+            atomicAdd(a.d_s_init + f + 2, ds.z); atomicAdd(a.d_s_init + f + 3, ds.w);
+        }
+    }
+}
+}  // namespace s64
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
 constexpr int EPT_SMALL = 17, EPT_LARGE = 65;     // packed-state elements per thread
 
 static const char* unsupported(int d, int dh)
@@ -535,9 +930,12 @@ template <int ACT>
 static bool launch_fwd(const FwdArgs& a, int batch, cudaStream_t st)
 {
     const size_t smem = fwd_smem_floats(a.D) * sizeof(float);
-    if (a.D.d == 64 && a.D.dh == 256) {      // the reference's head size and expansion: static sizes
-        cudaFuncSetAttribute(mlp_fwd_kernel<ACT, EPT_LARGE, 64, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        mlp_fwd_kernel<ACT, EPT_LARGE, 64, 256><<<batch, NT, smem, st>>>(a);
+    if (a.D.d == 64 && a.D.dh == 256 && a.in_stride % 4 == 0 && a.m_stride % 4 == 0 && aligned16(a.m_init) &&
+        aligned16(a.s_init) && aligned16(a.m_states) && aligned16(a.s_states)) {
+        // the reference's head size and expansion: the float4 kernels
+        const size_t sm64 = s64::fwd_smem_floats() * sizeof(float);
+        cudaFuncSetAttribute(s64::mlp_fwd64_kernel<ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm64);
+        s64::mlp_fwd64_kernel<ACT><<<batch, NT, sm64, st>>>(a);
     } else if (a.D.ss <= EPT_SMALL * NT) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(mlp_fwd_kernel<ACT, EPT_SMALL, 0, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         mlp_fwd_kernel<ACT, EPT_SMALL, 0, 0><<<batch, NT, smem, st>>>(a);
@@ -552,9 +950,11 @@ template <int ACT>
 static bool launch_bwd(const BwdArgs& a, int batch, cudaStream_t st)
 {
     const size_t smem = bwd_smem_floats(a.D) * sizeof(float);
-    if (a.D.d == 64 && a.D.dh == 256) {
-        cudaFuncSetAttribute(mlp_bwd_kernel<ACT, EPT_LARGE, 64, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        mlp_bwd_kernel<ACT, EPT_LARGE, 64, 256><<<batch, NT, smem, st>>>(a);
+    if (a.D.d == 64 && a.D.dh == 256 && a.in_stride % 4 == 0 && a.m_stride % 4 == 0 && aligned16(a.m_states) &&
+        aligned16(a.s_states)) {
+        const size_t sm64 = s64::bwd_smem_floats() * sizeof(float);
+        cudaFuncSetAttribute(s64::mlp_bwd64_kernel<ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm64);
+        s64::mlp_bwd64_kernel<ACT><<<batch, NT, sm64, st>>>(a);
     } else if (a.D.ss <= EPT_SMALL * NT) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(mlp_bwd_kernel<ACT, EPT_SMALL, 0, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         mlp_bwd_kernel<ACT, EPT_SMALL, 0, 0><<<batch, NT, smem, st>>>(a);
