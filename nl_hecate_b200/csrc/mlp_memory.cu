@@ -639,8 +639,54 @@ __device__ __forceinline__ void stage(float* dst, const float* __restrict__ src,
     }
 }
 
+// Two column sums with the same matrix in one pass: s0 = W^T x0, s1 = W^T x1. scr: 2 * SCR floats.
+template <class Epi>
+__device__ __forceinline__ void colsum2(const float* __restrict__ W, int C, int lgcg, const float* x0, const float* x1,
+                                        float* scr, Epi epi)
+{
+    const int tid = threadIdx.x, cg = tid & ((1 << lgcg) - 1), g = tid >> lgcg;
+    const float* w = W + (size_t)(8 * g) * C + 4 * cg;
+    float4 acc0 = make_float4(0.f, 0.f, 0.f, 0.f), acc1 = acc0;
+#pragma unroll
+    for (int half = 0; half < 2; half++) {
+        float4 wv[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) wv[u] = f4(w + (size_t)(4 * half + u) * C);
+        const float4 xa = f4(x0 + 8 * g + 4 * half), xb = f4(x1 + 8 * g + 4 * half);
+        acc0 = fma4(xa.x, wv[0], acc0); acc0 = fma4(xa.y, wv[1], acc0); acc0 = fma4(xa.z, wv[2], acc0); acc0 = fma4(xa.w, wv[3], acc0);
+        acc1 = fma4(xb.x, wv[0], acc1); acc1 = fma4(xb.y, wv[1], acc1); acc1 = fma4(xb.z, wv[2], acc1); acc1 = fma4(xb.w, wv[3], acc1);
+    }
+    *reinterpret_cast<float4*>(scr + g * C + 4 * cg) = acc0;
+    *reinterpret_cast<float4*>(scr + SCR + g * C + 4 * cg) = acc1;
+    __syncthreads();
+    if (tid < C) {
+        const int G = NT >> lgcg;
+        float s0 = 0.0f, s1 = 0.0f;
+        for (int gg = 0; gg < G; gg++) { s0 += scr[gg * C + tid]; s1 += scr[SCR + gg * C + tid]; }
+        epi(tid, s0, s1);
+    }
+    __syncthreads();
+}
+
+// nv float4 of global memory into shared memory with 16-byte asynchronous copies, all in flight at
+// once; the caller's barrier after it makes them visible.
+__device__ __forceinline__ void stage_async(float* dst, const float* __restrict__ src, int nv)
+{
+    const int tid = threadIdx.x;
+#pragma unroll
+    for (int u = 0; u < 9; u++) {
+        const int qi = tid + u * NT;
+        if (qi < nv) {
+            const unsigned d32 = (unsigned)__cvta_generic_to_shared(dst + 4 * qi);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(d32), "l"(src + 4 * qi) : "memory");
+        }
+    }
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+}
+
 inline size_t fwd_smem_floats() { return (size_t)SS + 7 * D + 4 * DH + SCR + 4 * NW; }
-inline size_t bwd_smem_floats() { return (size_t)SS + O2 + 7 * D + 8 * DH + SCR + 4 * NW; }
+inline size_t bwd_smem_floats() { return (size_t)SS + O2 + 11 * D + 10 * DH + 2 * SCR + 4 * NW; }
 
 // Token loop, rotated: M_{t+1} serves the readout of token t AND the prediction of token t + 1, so
 // both row products with W1' (on q_t and k_{t+1}) share one pass over the matrix, and both with W2'
@@ -754,6 +800,10 @@ __global__ void __launch_bounds__(NT, 1) mlp_fwd64_kernel(FwdArgs a)
     }
 }
 
+// Reverse loop, rotated like the forward: M_t serves the inner gradient of token t AND the readout
+// of token t - 1 (whose M_{t+1} it is). Iteration t stages {W1_t, b1_t} once for the row products on
+// k_t and q_{t-1}, then {W2_t, b2_t} for e_t, the column sums on e_t and dy_{t-1}, and phase 5; the
+// readout vectors of token t - 1 wait in the other half of a double buffer for iteration t - 1.
 template <int ACT>
 __global__ void __launch_bounds__(NT, 1) mlp_bwd64_kernel(BwdArgs a)
 {
@@ -761,23 +811,20 @@ __global__ void __launch_bounds__(NT, 1) mlp_bwd64_kernel(BwdArgs a)
     const int tid = threadIdx.x, b = blockIdx.x;
     float* dS = sm;
     float* stg = dS + SS;                 // {W1, b1} (O2 floats) or {W2, b2} of one state
-    float* kb = stg + O2;                 // kb | vb | qb | dyb adjacent
-    float* vb = kb + D;
-    float* qb = vb + D;
-    float* dyb = qb + D;
-    float* e = dyb + D;
+    float* vec = stg + O2;                // two buffers of k | v | q | dy (token parity)
+    float* e = vec + 8 * D;
     float* derr = e + D;
     float* inj0 = derr + D;
     float* pre = inj0 + D;                // act'(pre)
     float* h = pre + DH;
     float* gp = h + DH;
-    float* hq = gp + DH;
-    float* dpq = hq + DH;
-    float* adj = dpq + DH;
+    float* hqb = gp + DH;                 // two buffers (token parity)
+    float* dpqb = hqb + 2 * DH;           // two buffers: act'(pq), then dpq
+    float* adj = dpqb + 2 * DH;
     float* inj1 = adj + DH;
     float* dpre = inj1 + DH;
-    float* scr = dpre + DH;
-    float* red = scr + SCR;
+    float* scr = dpre + DH;               // 2 * SCR
+    float* red = scr + 2 * SCR;
     const float* k = a.k + (size_t)b * a.in_stride;
     const float* v = a.v + (size_t)b * a.in_stride;
     const float* q = a.q + (size_t)b * a.in_stride;
@@ -789,6 +836,8 @@ __global__ void __launch_bounds__(NT, 1) mlp_bwd64_kernel(BwdArgs a)
     const float* mt = a.m_states + (size_t)b * a.m_stride;
     const float* st = a.s_states + (size_t)b * a.m_stride;
     float4* dS4 = reinterpret_cast<float4*>(dS);
+    const float* src = tid < D ? k : tid < 2 * D ? v : tid < 3 * D ? q : dy;    // stream staged by this thread (tid < 4 D)
+    const int S = a.seq_len;
 
     float4 dM4[V];
 #pragma unroll
@@ -796,39 +845,63 @@ __global__ void __launch_bounds__(NT, 1) mlp_bwd64_kernel(BwdArgs a)
         dM4[i] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (live(i, tid)) dS4[tid + i * NT] = dM4[i];
     }
-    for (int t = a.seq_len - 1; t >= 0; t--) {
+    if (S > 0) {      // readout of the last token through the final state M_S
+        const int cur = (S - 1) & 1;
+        const float* Mn = mt + (size_t)S * SS;
+        float* vc = vec + cur * 4 * D;
+        if (tid < 4 * D) vc[tid] = src[(size_t)(S - 1) * D + (tid & (D - 1))];
+        stage_async(stg, Mn, O2 / 4);
+        __syncthreads();
+        float* hq = hqb + cur * DH;
+        float* dpq = dpqb + cur * DH;
+        rowdot(stg, D, 1, vc + 2 * D, [&](int r, float s) { const float p = s + stg[O1 + r]; hq[r] = act_fn<ACT>(p); dpq[r] = act_prime<ACT>(p); });
+        colsum(Mn + O2, DH, 6, vc + 3 * D, scr, [&](int j, float s) { dpq[j] *= s; });
+        colsum(stg, D, 4, dpq, scr, [&](int j, float s) { d_q[(size_t)(S - 1) * D + j] = s; });
+    }
+    for (int t = S - 1; t >= 0; t--) {
         const float* Mt = mt + (size_t)t * SS;
-        const float* Mn = Mt + SS;
         const float* St = st + (size_t)t * SS;
-        if (t > 0) {      // the states token t - 1 reads first (M_{t-1}, S_{t-1}) on their way into L2
+        const int cur = t & 1, prv = cur ^ 1;
+        const bool has_prev = t > 0;
+        float* vc = vec + cur * 4 * D;        // k_t | v_t | q_t | dy_t
+        float* vp = vec + prv * 4 * D;        // the same of token t - 1
+        float* hq = hqb + cur * DH;
+        float* dpq = dpqb + cur * DH;
+        float* hq_p = hqb + prv * DH;
+        float* dpq_p = dpqb + prv * DH;
+        if (has_prev) {
+            // the states token t - 1 reads first (M_{t-1}, S_{t-1}) on their way into L2
             for (int f = tid * 32; f < SS; f += NT * 32) {
                 asm volatile("prefetch.global.L2 [%0];" ::"l"(Mt - SS + f));
                 asm volatile("prefetch.global.L2 [%0];" ::"l"(St - SS + f));
             }
+            if (tid < 4 * D) vp[tid] = src[(size_t)(t - 1) * D + (tid & (D - 1))];
         }
-        if (tid < 4 * D) kb[tid] = (tid < D ? k : tid < 2 * D ? v : tid < 3 * D ? q : dy)[(size_t)t * D + (tid & (D - 1))];
         const float al = a.alpha[g0 + t], th = a.theta[g0 + t], et = a.eta[g0 + t];
-        // 1: readout through M_{t+1}
-        stage(stg, Mn, O2 / 4);
+        stage_async(stg, Mt, O2 / 4);
         __syncthreads();
-        rowdot(stg, D, 1, qb, [&](int r, float s) { const float p = s + stg[O1 + r]; hq[r] = act_fn<ACT>(p); dpq[r] = act_prime<ACT>(p); });
-        colsum(Mn + O2, DH, 6, dyb, scr, [&](int j, float s) { dpq[j] *= s; });
-        colsum(stg, D, 4, dpq, scr, [&](int j, float s) { d_q[(size_t)t * D + j] = s; });
-        // 3: the inner gradient's vectors through M_t
-        stage(stg, Mt, O2 / 4);
+        // W1_t: hidden of k_t (inner gradient of token t) and of q_{t-1} (readout of token t - 1)
+        rowdot2(stg, D, 1, vc, vp + 2 * D, [&](int r, float sk, float sq_) {
+            const float b1 = stg[O1 + r];
+            const float p = sk + b1;
+            h[r] = act_fn<ACT>(p); pre[r] = act_prime<ACT>(p);
+            if (has_prev) { const float pq = sq_ + b1; hq_p[r] = act_fn<ACT>(pq); dpq_p[r] = act_prime<ACT>(pq); }
+        });
         __syncthreads();
-        rowdot(stg, D, 1, kb, [&](int r, float s) { const float p = s + stg[O1 + r]; h[r] = act_fn<ACT>(p); pre[r] = act_prime<ACT>(p); });
+        stage_async(stg, Mt + O2, (SS - O2) / 4);
         __syncthreads();
-        stage(stg, Mt + O2, (SS - O2) / 4);
+        rowdot(stg, DH, 3, h, [&](int r, float s) { e[r] = s + stg[D * DH + r] - vc[D + r]; });
         __syncthreads();
-        rowdot(stg, DH, 3, h, [&](int r, float s) { e[r] = s + stg[D * DH + r] - vb[r]; });
-        __syncthreads();
-        colsum(stg, DH, 6, e, scr, [&](int j, float s) { gp[j] = s * pre[j]; });
-        // dM += readout terms; dS += dM; the three gate gradients
+        // W2_t^T on e_t (-> gp) and on dy_{t-1} (-> dpq of token t - 1)
+        colsum2(stg, DH, 6, e, vp + 3 * D, scr, [&](int j, float s0, float s1) {
+            gp[j] = s0 * pre[j];
+            if (has_prev) dpq_p[j] *= s1;
+        });
+        // dM += readout terms of token t; dS += dM; the three gate gradients
         float acc[3] = {0.0f, 0.0f, 0.0f};
         {
-            const float4 q1v = f4(qb + 4 * (tid & 15)), hq2v = f4(hq + 4 * (tid & 63));
-            const float4 k1v = f4(kb + 4 * (tid & 15)), h2v = f4(h + 4 * (tid & 63));
+            const float4 q1v = f4(vc + 2 * D + 4 * (tid & 15)), hq2v = f4(hq + 4 * (tid & 63));
+            const float4 k1v = f4(vc + 4 * (tid & 15)), h2v = f4(h + 4 * (tid & 63));
             const float4* Mt4 = reinterpret_cast<const float4*>(Mt);
             const float4* St4 = reinterpret_cast<const float4*>(St);
 #pragma unroll
@@ -839,7 +912,7 @@ __global__ void __launch_bounds__(NT, 1) mlp_bwd64_kernel(BwdArgs a)
                     const int i = i0 + u;
                     if (i < V && live(i, tid)) {
                         mv[u] = Mt4[tid + i * NT]; sv[u] = St4[tid + i * NT];
-                        ro[u] = term4(i, tid, dpq, q1v, dyb, hq2v);
+                        ro[u] = term4(i, tid, dpq, q1v, vc + 3 * D, hq2v);
                         gr[u] = term4(i, tid, gp, k1v, e, h2v);
                         ds0[u] = dS4[tid + i * NT];
                     }
@@ -861,7 +934,7 @@ __global__ void __launch_bounds__(NT, 1) mlp_bwd64_kernel(BwdArgs a)
         block_sum<3>(acc, red);          // its barriers also publish dS
         if (tid == 0) { a.d_alpha[g0 + t] = -acc[0]; a.d_eta[g0 + t] = acc[1]; a.d_theta[g0 + t] = -acc[2]; }
         // 5: products with G = -theta dS
-        rowdot(dS, D, 1, kb, [&](int r, float s) { adj[r] = -th * (s + dS[O1 + r]) * pre[r]; });
+        rowdot(dS, D, 1, vc, [&](int r, float s) { adj[r] = -th * (s + dS[O1 + r]) * pre[r]; });
         rowdot(dS + O2, DH, 3, h, [&](int r, float s) { derr[r] = -th * (s + dS[O3 + r]); });
         colsum(dS + O2, DH, 6, e, scr, [&](int j, float s) { inj1[j] = -th * s; });
         rowdot(stg, DH, 3, adj, [&](int r, float s) { derr[r] += s; });
@@ -869,11 +942,15 @@ __global__ void __launch_bounds__(NT, 1) mlp_bwd64_kernel(BwdArgs a)
         if (tid < D) d_v[(size_t)t * D + tid] = -derr[tid];
         colsum(stg, DH, 6, derr, scr, [&](int j, float s) { dpre[j] = (s + inj1[j]) * pre[j]; });
         colsum(dS, D, 4, gp, scr, [&](int j, float s) { inj0[j] = -th * s; });
-        colsum(Mt, D, 4, dpre, scr, [&](int j, float s) { d_k[(size_t)t * D + j] = s + inj0[j]; });
+        // W1_t^T on d_pre (-> d_k of token t) and on dpq of token t - 1 (-> its d_q)
+        colsum2(Mt, D, 4, dpre, dpq_p, scr, [&](int j, float s0, float s1) {
+            d_k[(size_t)t * D + j] = s0 + inj0[j];
+            if (has_prev) d_q[(size_t)(t - 1) * D + j] = s1;
+        });
         // 6: carry to token t - 1
         const float keep = 1.0f - al;
         {
-            const float4 k1v = f4(kb + 4 * (tid & 15)), h2v = f4(h + 4 * (tid & 63)), adjv = f4(adj + 4 * (tid & 63));
+            const float4 k1v = f4(vc + 4 * (tid & 15)), h2v = f4(h + 4 * (tid & 63)), adjv = f4(adj + 4 * (tid & 63));
 #pragma unroll
             for (int i0 = 0; i0 < V; i0 += 4) {
                 float4 add[4], ds0[4];
