@@ -686,7 +686,13 @@ class TitansMlpPair(TitansPair):
         d_q and the gate gradients."""
         n, s, d = self.N, self.S, self.D
         streams = 7 * n * s * d * 4 + 6 * n * s * 4
-        return ("mlpm::mlp_bwd_kernel<GELU> (MLP-memory backward, M and S trajectories)",
+        # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this kernel at 8 problems x 512
+        # tokens (profiles/titans_mlp_memory_kernels.md); every stored state is read once: proportional to problems
+        self.dominant_traffic = (1_089_973_760 + 3_410_176) / 8 * n
+        self.dominant_traffic_source = ("literal: dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this "
+                                        "kernel at 8 problems x 512 tokens (bench.py --workload titans_mlp --small; "
+                                        "profiles/titans_mlp_memory_kernels.md), scaled by problems; not re-measured by this run")
+        return ("mlpm::s64::mlp_bwd64_kernel<GELU> (MLP-memory backward, M and S trajectories)",
                 lambda: self.bwd(self.dev), streams + 2 * n * (s + 1) * self.SS * 4, "hbm")
 
     def cpu_sample(self, oracle, threads, budget_s=12.0):

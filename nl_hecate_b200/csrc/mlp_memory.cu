@@ -682,8 +682,8 @@ __device__ __forceinline__ void stage_async(float* dst, const float* __restrict_
         }
     }
     asm volatile("cp.async.commit_group;\n" ::: "memory");
-    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
 }
+__device__ __forceinline__ void stage_wait() { asm volatile("cp.async.wait_group 0;\n" ::: "memory"); }
 
 inline size_t fwd_smem_floats() { return (size_t)SS + 7 * D + 4 * DH + SCR + 4 * NW; }
 inline size_t bwd_smem_floats() { return (size_t)SS + O2 + 11 * D + 10 * DH + 2 * SCR + 4 * NW; }
@@ -851,6 +851,7 @@ __global__ void __launch_bounds__(NT, 1) mlp_bwd64_kernel(BwdArgs a)
         float* vc = vec + cur * 4 * D;
         if (tid < 4 * D) vc[tid] = src[(size_t)(S - 1) * D + (tid & (D - 1))];
         stage_async(stg, Mn, O2 / 4);
+        stage_wait();
         __syncthreads();
         float* hq = hqb + cur * DH;
         float* dpq = dpqb + cur * DH;
@@ -869,16 +870,20 @@ __global__ void __launch_bounds__(NT, 1) mlp_bwd64_kernel(BwdArgs a)
         float* dpq = dpqb + cur * DH;
         float* hq_p = hqb + prv * DH;
         float* dpq_p = dpqb + prv * DH;
+        float staged = 0.0f;
+        if (has_prev && tid < 4 * D) staged = src[(size_t)(t - 1) * D + (tid & (D - 1))];
+        const float al = a.alpha[g0 + t], th = a.theta[g0 + t], et = a.eta[g0 + t];
+        stage_async(stg, Mt, O2 / 4);
         if (has_prev) {
-            // the states token t - 1 reads first (M_{t-1}, S_{t-1}) on their way into L2
+            // what token t - 1 reads first (M_{t-1}, S_{t-1}; the streams of token t - 2) on its way into L2
             for (int f = tid * 32; f < SS; f += NT * 32) {
                 asm volatile("prefetch.global.L2 [%0];" ::"l"(Mt - SS + f));
                 asm volatile("prefetch.global.L2 [%0];" ::"l"(St - SS + f));
             }
-            if (tid < 4 * D) vp[tid] = src[(size_t)(t - 1) * D + (tid & (D - 1))];
+            if (t > 1 && tid < 4 * D && (tid & 31) == 0) asm volatile("prefetch.global.L2 [%0];" ::"l"(src + (size_t)(t - 2) * D + (tid & (D - 1))));
+            if (tid < 4 * D) vp[tid] = staged;
         }
-        const float al = a.alpha[g0 + t], th = a.theta[g0 + t], et = a.eta[g0 + t];
-        stage_async(stg, Mt, O2 / 4);
+        stage_wait();
         __syncthreads();
         // W1_t: hidden of k_t (inner gradient of token t) and of q_{t-1} (readout of token t - 1)
         rowdot2(stg, D, 1, vc, vp + 2 * D, [&](int r, float sk, float sq_) {
@@ -889,6 +894,7 @@ __global__ void __launch_bounds__(NT, 1) mlp_bwd64_kernel(BwdArgs a)
         });
         __syncthreads();
         stage_async(stg, Mt + O2, (SS - O2) / 4);
+        stage_wait();
         __syncthreads();
         rowdot(stg, DH, 3, h, [&](int r, float s) { e[r] = s + stg[D * DH + r] - vc[D + r]; });
         __syncthreads();
