@@ -845,6 +845,9 @@ __global__ void __launch_bounds__(NT, 1) mlp_bwd64_kernel(BwdArgs a)
         dM4[i] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (live(i, tid)) dS4[tid + i * NT] = dM4[i];
     }
+    // dS of the next token is eta_t x (dS of this one): the factor is applied when the next token
+    // reads dS in its element pass, so the carry step never touches the shared copy
+    float ds_scale = 1.0f;
     if (S > 0) {      // readout of the last token through the final state M_S
         const int cur = (S - 1) & 1;
         const float* Mn = mt + (size_t)S * SS;
@@ -928,7 +931,7 @@ __global__ void __launch_bounds__(NT, 1) mlp_bwd64_kernel(BwdArgs a)
                     const int i = i0 + u;
                     if (i < V && live(i, tid)) {
                         const float4 dm = add4(dM4[i], ro[u]);
-                        const float4 ds = add4(ds0[u], dm);
+                        const float4 ds = fma4(ds_scale, ds0[u], dm);
                         dM4[i] = dm; dS4[tid + i * NT] = ds;
                         acc[0] = dot4(mv[u], dm, acc[0]);
                         acc[1] = dot4(sv[u], ds, acc[1]);
@@ -958,34 +961,22 @@ __global__ void __launch_bounds__(NT, 1) mlp_bwd64_kernel(BwdArgs a)
         {
             const float4 k1v = f4(vc + 4 * (tid & 15)), h2v = f4(h + 4 * (tid & 63)), adjv = f4(adj + 4 * (tid & 63));
 #pragma unroll
-            for (int i0 = 0; i0 < V; i0 += 4) {
-                float4 add[4], ds0[4];
-#pragma unroll
-                for (int u = 0; u < 4; u++) {
-                    const int i = i0 + u;
-                    if (i < V && live(i, tid)) {
-                        add[u] = term4(i, tid, dpre, k1v, derr, h2v);
-                        if (in_w2(i, tid)) add[u] = fma4(e[((tid - 64) >> 6) + 8 * (i - 8)], adjv, add[u]);   // cross term e adj^T
-                        ds0[u] = dS4[tid + i * NT];
-                    }
-                }
-#pragma unroll
-                for (int u = 0; u < 4; u++) {
-                    const int i = i0 + u;
-                    if (i < V && live(i, tid)) {
-                        dM4[i] = fma4(keep, dM4[i], add[u]);
-                        dS4[tid + i * NT] = mul4(et, ds0[u]);
-                    }
+            for (int i = 0; i < V; i++) {
+                if (live(i, tid)) {
+                    float4 add = term4(i, tid, dpre, k1v, derr, h2v);
+                    if (in_w2(i, tid)) add = fma4(e[((tid - 64) >> 6) + 8 * (i - 8)], adjv, add);   // cross term e adj^T
+                    dM4[i] = fma4(keep, dM4[i], add);
                 }
             }
         }
+        ds_scale = et;
         __syncthreads();
     }
 #pragma unroll
     for (int i = 0; i < V; i++) {
         if (live(i, tid)) {
             const int f = 4 * (tid + i * NT);
-            const float4 ds = dS4[tid + i * NT];
+            const float4 ds = mul4(ds_scale, dS4[tid + i * NT]);
             atomicAdd(a.d_m_init + f, dM4[i].x); atomicAdd(a.d_m_init + f + 1, dM4[i].y);
             atomicAdd(a.d_m_init + f + 2, dM4[i].z); atomicAdd(a.d_m_init + f + 3, dM4[i].w);
             atomicAdd(a.d_s_init + f, ds.x); atomicAdd(a.d_s_init + f + 1, ds.y);
