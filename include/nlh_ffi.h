@@ -546,6 +546,20 @@ int32_t nlh_dgd_backward_dispatch(const float* k_mem, const float* v_mem, const 
     float* d_v_mem, float* d_q_mem, float* d_alpha, float* d_theta, float* d_m_initial, int64_t seq_len,
     int64_t d, float error_clip);
 
+/* core/src/dispatch.rs:897 / :979 — titans_mlp_forward_cuda / titans_mlp_backward_cuda: the MLP-memory
+ * pair on HOST slices, with a batch (k/v/q/y [batch, seq, d], gates [batch, seq], m_initial /
+ * s_initial [batch, state], trajectories [batch, (seq+1)*state]); d_m_initial / d_s_initial [state]
+ * are the sums over the batch and are overwritten. */
+int32_t nlh_titans_mlp_forward_dispatch(const float* k_mem, const float* v_mem, const float* q_mem,
+    const float* alpha, const float* theta, const float* eta, const float* m_initial, const float* s_initial,
+    float* m_states, float* s_states, float* y, int64_t seq_len, int64_t d, int64_t d_hidden, int64_t batch_size,
+    int32_t activation, float m_norm_max);
+int32_t nlh_titans_mlp_backward_dispatch(const float* k_mem, const float* v_mem, const float* q_mem,
+    const float* alpha, const float* theta, const float* eta, const float* m_states, const float* s_states,
+    const float* d_y, float* d_k_mem, float* d_v_mem, float* d_q_mem, float* d_alpha, float* d_theta, float* d_eta,
+    float* d_m_initial, float* d_s_initial, int64_t seq_len, int64_t d, int64_t d_hidden, int64_t batch_size,
+    int32_t activation, float m_norm_max);
+
 /* ── Opaque-VJP registry over the C ABI (boundary of core/src/tape.rs:98-182) ────────────────
  * Keys number the variants of the reference's OpaqueKey enum in declaration order
  * (core/src/tape.rs:100-134). nlh_opaque_backward is the C form of OpaqueBackwardFn

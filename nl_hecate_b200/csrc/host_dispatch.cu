@@ -193,6 +193,71 @@ int32_t nlh_dgd_backward_dispatch(const float* k_mem, const float* v_mem, const 
                          seq_len, d, error_clip);
 }
 
+// Titans LMM with a two-layer MLP memory, host slices in and out: titans_mlp_forward_cuda /
+// titans_mlp_backward_cuda (core/src/dispatch.rs:897-1070), which, unlike the other host-slice
+// functions, take a batch. d_m_initial / d_s_initial [state_size] are the sums over the batch.
+int32_t nlh_titans_mlp_forward_dispatch(const float* k_mem, const float* v_mem, const float* q_mem,
+    const float* alpha, const float* theta, const float* eta, const float* m_initial, const float* s_initial,
+    float* m_states, float* s_states, float* y, int64_t seq_len, int64_t d, int64_t d_hidden, int64_t batch_size,
+    int32_t activation, float m_norm_max)
+{
+    const char* where = "nlh_titans_mlp_forward_dispatch";
+    if (seq_len <= 0 || d <= 0 || d_hidden <= 0 || batch_size <= 0 || !k_mem || !v_mem || !q_mem || !alpha || !theta ||
+        !eta || !m_initial || !s_initial || !m_states || !s_states || !y)
+        return hd_fail(where, NLH_ERR_INVALID_ARG, "bad dimensions or NULL pointer");
+    const long long ss = 2 * d * d_hidden + d_hidden + d, sd = batch_size * seq_len * d, sg_ = batch_size * seq_len;
+    const long long tr = batch_size * (seq_len + 1) * ss;
+    if ((seq_len + 1) * ss > 0x7fffffffLL) return hd_fail(where, NLH_ERR_INVALID_ARG, "m_stride does not fit the int32 argument of the entry");
+    cudaStream_t st = current_stream();
+    Staging sg;
+    float *dk = sg.upload(k_mem, sd, st), *dv = sg.upload(v_mem, sd, st), *dq = sg.upload(q_mem, sd, st);
+    float *dal = sg.upload(alpha, sg_, st), *dth = sg.upload(theta, sg_, st), *det = sg.upload(eta, sg_, st);
+    float *dm0 = sg.upload(m_initial, batch_size * ss, st), *ds0 = sg.upload(s_initial, batch_size * ss, st);
+    float *dms = sg.empty(tr), *dss = sg.empty(tr), *dy = sg.empty(sd);
+    if (!sg.ok) return hd_fail(where, NLH_ERR_CUDA, "device staging failed");
+    nlh_clear_status();
+    titans_mlp_forward_f32_cuda(dk, dv, dq, dal, dth, det, dm0, ds0, dms, dss, dy, (int)seq_len, (int)d, (int)d_hidden,
+                                (int)batch_size, (int)(seq_len * d), (int)((seq_len + 1) * ss), activation, m_norm_max);
+    if (nlh_last_status() != NLH_OK) return nlh_last_status();
+    if (!download(m_states, dms, tr, st) || !download(s_states, dss, tr, st) || !download(y, dy, sd, st))
+        return hd_fail(where, NLH_ERR_CUDA, "download failed");
+    return hd_finish(where, st);
+}
+int32_t nlh_titans_mlp_backward_dispatch(const float* k_mem, const float* v_mem, const float* q_mem,
+    const float* alpha, const float* theta, const float* eta, const float* m_states, const float* s_states,
+    const float* d_y, float* d_k_mem, float* d_v_mem, float* d_q_mem, float* d_alpha, float* d_theta, float* d_eta,
+    float* d_m_initial, float* d_s_initial, int64_t seq_len, int64_t d, int64_t d_hidden, int64_t batch_size,
+    int32_t activation, float m_norm_max)
+{
+    const char* where = "nlh_titans_mlp_backward_dispatch";
+    if (seq_len <= 0 || d <= 0 || d_hidden <= 0 || batch_size <= 0 || !k_mem || !v_mem || !q_mem || !alpha || !theta ||
+        !eta || !m_states || !s_states || !d_y || !d_k_mem || !d_v_mem || !d_q_mem || !d_alpha || !d_theta || !d_eta ||
+        !d_m_initial || !d_s_initial)
+        return hd_fail(where, NLH_ERR_INVALID_ARG, "bad dimensions or NULL pointer");
+    const long long ss = 2 * d * d_hidden + d_hidden + d, sd = batch_size * seq_len * d, sg_ = batch_size * seq_len;
+    const long long tr = batch_size * (seq_len + 1) * ss;
+    if ((seq_len + 1) * ss > 0x7fffffffLL) return hd_fail(where, NLH_ERR_INVALID_ARG, "m_stride does not fit the int32 argument of the entry");
+    cudaStream_t st = current_stream();
+    Staging sg;
+    float *dk = sg.upload(k_mem, sd, st), *dv = sg.upload(v_mem, sd, st), *dq = sg.upload(q_mem, sd, st);
+    float *dal = sg.upload(alpha, sg_, st), *dth = sg.upload(theta, sg_, st), *det = sg.upload(eta, sg_, st);
+    float *dms = sg.upload(m_states, tr, st), *dss = sg.upload(s_states, tr, st), *ddy = sg.upload(d_y, sd, st);
+    float *gk = sg.empty(sd), *gv = sg.empty(sd), *gq = sg.empty(sd);
+    float *ga = sg.empty(sg_), *gt = sg.empty(sg_), *ge = sg.empty(sg_);
+    float *gm = sg.zeros(ss, st), *gs = sg.zeros(ss, st);
+    if (!sg.ok) return hd_fail(where, NLH_ERR_CUDA, "device staging failed");
+    nlh_clear_status();
+    titans_mlp_backward_f32_cuda(dk, dv, dq, dal, dth, det, dms, dss, ddy, gk, gv, gq, ga, gt, ge, gm, gs, (int)seq_len,
+                                 (int)d, (int)d_hidden, (int)batch_size, (int)(seq_len * d), (int)((seq_len + 1) * ss),
+                                 activation, m_norm_max);
+    if (nlh_last_status() != NLH_OK) return nlh_last_status();
+    const bool ok = download(d_k_mem, gk, sd, st) && download(d_v_mem, gv, sd, st) && download(d_q_mem, gq, sd, st) &&
+                    download(d_alpha, ga, sg_, st) && download(d_theta, gt, sg_, st) && download(d_eta, ge, sg_, st) &&
+                    download(d_m_initial, gm, ss, st) && download(d_s_initial, gs, ss, st);
+    if (!ok) return hd_fail(where, NLH_ERR_CUDA, "download failed");
+    return hd_finish(where, st);
+}
+
 int32_t nlh_swa_forward_dispatch(const float* q, const float* k, const float* v, float* out,
     float* attn_weights, int64_t seq_len, int64_t num_heads, int64_t head_dim, int64_t window_size)
 {

@@ -541,6 +541,30 @@ def host_rule_backward(rule, k, v, q, alpha, m_states, d_y, theta=None, eta=None
     return g
 
 
+def host_titans_mlp_pair(k, v, q, alpha, theta, eta, m0, s0, d_y, d_hidden, activation=0, m_norm_max=0.0):
+    """Host arrays in, host arrays out through nlh_titans_mlp_{forward,backward}_dispatch
+    (k, v, q, d_y [n, s, d]; gates [n, s]; m0, s0 [n, state]). Returns (forward dict, gradient dict)."""
+    k, v, q, alpha, theta, eta, m0, s0, d_y = map(_h, (k, v, q, alpha, theta, eta, m0, s0, d_y))
+    n, s, d = k.shape
+    ssz = mlp_state_size(d, d_hidden)
+    f = {"m_states": np.empty((n, s + 1, ssz), np.float32), "s_states": np.empty((n, s + 1, ssz), np.float32),
+         "y": np.empty((n, s, d), np.float32)}
+    call("nlh_titans_mlp_forward_dispatch", k_mem=_hp(k), v_mem=_hp(v), q_mem=_hp(q), alpha=_hp(alpha),
+         theta=_hp(theta), eta=_hp(eta), m_initial=_hp(m0), s_initial=_hp(s0), m_states=_hp(f["m_states"]),
+         s_states=_hp(f["s_states"]), y=_hp(f["y"]), seq_len=s, d=d, d_hidden=d_hidden, batch_size=n,
+         activation=activation, m_norm_max=m_norm_max)
+    e = lambda *sh: np.empty(sh, np.float32)
+    g = {"d_k": e(n, s, d), "d_v": e(n, s, d), "d_q": e(n, s, d), "d_alpha": e(n, s), "d_theta": e(n, s),
+         "d_eta": e(n, s), "d_m_initial": e(ssz), "d_s_initial": e(ssz)}
+    call("nlh_titans_mlp_backward_dispatch", k_mem=_hp(k), v_mem=_hp(v), q_mem=_hp(q), alpha=_hp(alpha),
+         theta=_hp(theta), eta=_hp(eta), m_states=_hp(f["m_states"]), s_states=_hp(f["s_states"]), d_y=_hp(d_y),
+         d_k_mem=_hp(g["d_k"]), d_v_mem=_hp(g["d_v"]), d_q_mem=_hp(g["d_q"]), d_alpha=_hp(g["d_alpha"]),
+         d_theta=_hp(g["d_theta"]), d_eta=_hp(g["d_eta"]), d_m_initial=_hp(g["d_m_initial"]),
+         d_s_initial=_hp(g["d_s_initial"]), seq_len=s, d=d, d_hidden=d_hidden, batch_size=n,
+         activation=activation, m_norm_max=m_norm_max)
+    return f, g
+
+
 def host_swa_forward(q, k, v, num_heads, head_dim, window):
     q, k, v = map(_h, (q, k, v))
     s = q.shape[0]

@@ -109,3 +109,24 @@ def test_unsupported_and_invalid_shapes_launch_nothing(D):
     with pytest.raises(RuntimeError, match="activation"):
         D.call("titans_mlp_forward_f32_cuda", d=4, d_hidden=8, activation=3, **kw)
     D.call("titans_mlp_forward_f32_cuda", d=4, d_hidden=8, activation=0, **{**kw, "batch_size": 0})
+
+
+def test_host_slice_entries_match_the_oracle(D):
+    """nlh_titans_mlp_{forward,backward}_dispatch: the compiled counterpart of the reference's
+    titans_mlp_forward_cuda / titans_mlp_backward_cuda (core/src/dispatch.rs:897-1070) — host arrays
+    in and out, a batch of problems."""
+    from oracle import mlp_memory as mlp
+    n, s, d, dh = 3, 7, 64, 256
+    p = mlp.make_problem(n, s, d, dh, 990)
+    wm, ws, wy = mlp.forward(p["k"], p["v"], p["q"], p["alpha"], p["theta"], p["eta"], p["m0"], p["s0"], dh, 1)
+    wg = mlp.backward(p["k"], p["v"], p["q"], p["alpha"], p["theta"], p["eta"], wm, ws, p["dy"], dh, 1)
+    f, g = D.host_titans_mlp_pair(p["k"], p["v"], p["q"], p["alpha"], p["theta"], p["eta"], p["m0"], p["s0"], p["dy"],
+                                  dh, activation=1)
+    assert rel_err(f["y"], wy) <= REL_FWD and rel_err(f["m_states"], wm) <= REL_FWD and rel_err(f["s_states"], ws) <= REL_FWD
+    for key in ("d_k", "d_v", "d_q", "d_alpha", "d_theta", "d_eta"):
+        assert rel_err(g[key], wg[key]) <= REL_BWD, key
+    for key in ("d_m_initial", "d_s_initial"):
+        assert rel_err(g[key], wg[key].sum(axis=0)) <= REL_BWD, key
+    with pytest.raises(RuntimeError):
+        D.host_titans_mlp_pair(p["k"], p["v"], p["q"], p["alpha"], p["theta"], p["eta"], p["m0"], p["s0"], p["dy"],
+                               dh, activation=7)
