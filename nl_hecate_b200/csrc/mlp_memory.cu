@@ -913,6 +913,7 @@ __global__ void __launch_bounds__(NT, 1) mlp_bwd64_kernel(BwdArgs a)
             const float4 k1v = f4(vc + 4 * (tid & 15)), h2v = f4(h + 4 * (tid & 63));
             const float4* Mt4 = reinterpret_cast<const float4*>(Mt);
             const float4* St4 = reinterpret_cast<const float4*>(St);
+            const float4* stg4 = reinterpret_cast<const float4*>(stg);
 #pragma unroll
             for (int i0 = 0; i0 < V; i0 += PB) {
                 float4 mv[PB], sv[PB], ro[PB], gr[PB], ds0[PB];
@@ -920,7 +921,10 @@ __global__ void __launch_bounds__(NT, 1) mlp_bwd64_kernel(BwdArgs a)
                 for (int u = 0; u < PB; u++) {
                     const int i = i0 + u;
                     if (i < V && live(i, tid)) {
-                        mv[u] = Mt4[tid + i * NT]; sv[u] = St4[tid + i * NT];
+                        // the {W2, b2} half of M_t is in the staging buffer at this point
+                        const bool staged_half = i > 8 || (i == 8 && tid >= 64);
+                        mv[u] = staged_half ? stg4[tid + i * NT - O2 / 4] : Mt4[tid + i * NT];
+                        sv[u] = St4[tid + i * NT];
                         ro[u] = term4(i, tid, dpq, q1v, vc + 3 * D, hq2v);
                         gr[u] = term4(i, tid, gp, k1v, e, h2v);
                         ds0[u] = dS4[tid + i * NT];
