@@ -688,7 +688,7 @@ class TitansMlpPair(TitansPair):
         streams = 7 * n * s * d * 4 + 6 * n * s * 4
         # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this kernel at 8 problems x 512
         # tokens (profiles/titans_mlp_memory_kernels.md); every stored state is read once: proportional to problems
-        self.dominant_traffic = (1_090_088_192 + 3_696_640) / 8 * n
+        self.dominant_traffic = (1_091_155_968 + 3_302_144) / 8 * n
         self.dominant_traffic_source = ("literal: dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this "
                                         "kernel at 8 problems x 512 tokens (bench.py --workload titans_mlp --small; "
                                         "profiles/titans_mlp_memory_kernels.md), scaled by problems; not re-measured by this run")
