@@ -130,3 +130,32 @@ def test_host_slice_entries_match_the_oracle(D):
     with pytest.raises(RuntimeError):
         D.host_titans_mlp_pair(p["k"], p["v"], p["q"], p["alpha"], p["theta"], p["eta"], p["m0"], p["s0"], p["dy"],
                                dh, activation=7)
+
+
+def test_unaligned_state_buffers_take_the_generic_kernels(D):
+    """The float4 kernels of head 64 / hidden 256 need 16-byte aligned state buffers; with a
+    trajectory that starts 4 bytes off the library runs the generic kernels instead — same results."""
+    import torch
+    from oracle import mlp_memory as mlp
+    n, s, d, dh = 2, 5, 64, 256
+    t, ms, ss, y, g = _pair(D, mlp, n, s, d, dh, 0, 970)
+    ssz = D.mlp_state_size(d, dh)
+    raw_m = torch.empty(n * (s + 1) * ssz + 1, device="cuda")
+    raw_s = torch.empty(n * (s + 1) * ssz + 1, device="cuda")
+    ms2, ss2 = raw_m[1:], raw_s[1:]
+    assert ms2.data_ptr() % 16 == 4
+    y2 = torch.empty_like(y)
+    D.call("titans_mlp_forward_f32_cuda", k_mem=t["k"], v_mem=t["v"], q_mem=t["q"], alpha=t["alpha"], theta=t["theta"],
+           eta=t["eta"], m_initial=t["m0"], s_initial=t["s0"], m_states=ms2.data_ptr(), s_states=ss2.data_ptr(), y=y2,
+           seq_len=s, d=d, d_hidden=dh, batch_size=n, input_stride=s * d, m_stride=(s + 1) * ssz, activation=0,
+           m_norm_max=0.0)
+    assert rel_err(_np(y2), _np(y)) <= 1e-6 and rel_err(_np(ms2), _np(ms).ravel()) <= 1e-6
+    out = {k_: torch.empty_like(t["k"]) for k_ in ("d_k_mem", "d_v_mem", "d_q_mem")}
+    out.update({k_: torch.empty_like(t["alpha"]) for k_ in ("d_alpha", "d_theta", "d_eta")})
+    out.update(d_m_initial=torch.zeros(ssz, device="cuda"), d_s_initial=torch.zeros(ssz, device="cuda"))
+    D.call("titans_mlp_backward_f32_cuda", k_mem=t["k"], v_mem=t["v"], q_mem=t["q"], alpha=t["alpha"], theta=t["theta"],
+           eta=t["eta"], m_states=ms2.data_ptr(), s_states=ss2.data_ptr(), d_y=t["dy"], seq_len=s, d=d, d_hidden=dh,
+           batch_size=n, input_stride=s * d, m_stride=(s + 1) * ssz, activation=0, m_norm_max=0.0, **out)
+    for a_, b_ in (("d_k_mem", "d_k"), ("d_v_mem", "d_v"), ("d_q_mem", "d_q"), ("d_alpha", "d_alpha"),
+                   ("d_theta", "d_theta"), ("d_eta", "d_eta"), ("d_m_initial", "d_m_initial")):
+        assert rel_err(_np(out[a_]), _np(g[b_])) <= 1e-5, a_
