@@ -19,6 +19,8 @@ and passes gradients straight through the Frobenius-norm projection; both are fo
 ReLU the statement is the exact gradient, which is how tests/test_oracle.py pins it (float64
 central differences); GELU and SiLU are pinned on the terms that do not involve act''.
 The drop-in entry sums d_m_initial / d_s_initial over the batch (titans_mlp_backward.cu:557-561).
+PARITY UNPINNED: the reference holds no golden vectors for this path and its Rust code cannot be
+run where this was written; the pins are the finite-difference and closed-form checks named above.
 """
 from __future__ import annotations
 
